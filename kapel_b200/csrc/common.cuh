@@ -1,0 +1,78 @@
+// Shared by every kernel file: error reporting, element types, warp and block reductions.
+//
+// Every launcher is `extern "C" int kb_<name>(..., void* stream)`: 0 on success, non-zero
+// after storing a message that `kb_last_error()` returns. A launcher checks every size it was
+// given and refuses what its kernel cannot take; it never launches a kernel on sizes it has
+// not checked.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <cstdarg>
+#include <cstdint>
+#include <cstdio>
+
+#define KB_DT_F32 0
+#define KB_DT_BF16 1
+
+namespace kb {
+
+int fail(const char* fmt, ...);          // stores the message, returns 1
+int check_launch(const char* what);      // cudaGetLastError -> fail(...)
+
+#define KB_REQUIRE(cond, ...)                 \
+    do {                                      \
+        if (!(cond)) return kb::fail(__VA_ARGS__); \
+    } while (0)
+
+template <typename T> struct Elem;
+template <> struct Elem<float> {
+    static __device__ __forceinline__ float load(const float* p) { return *p; }
+    static __device__ __forceinline__ void store(float* p, float v) { *p = v; }
+};
+template <> struct Elem<__nv_bfloat16> {
+    static __device__ __forceinline__ float load(const __nv_bfloat16* p) { return __bfloat162float(*p); }
+    static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
+};
+
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);
+    return v;
+}
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, o));
+    return v;
+}
+
+// Sum over a block of up to 1024 threads; `scratch` holds 32 floats. Every thread gets the
+// total. The order of the additions depends on the block size only.
+__device__ __forceinline__ float block_sum(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_sum(v);
+    __syncthreads();                       // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float t = (lane < nwarps) ? scratch[lane] : 0.f;
+    return warp_sum(t);
+}
+__device__ __forceinline__ float block_max(float v, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+    v = warp_max(v);
+    __syncthreads();
+    if (lane == 0) scratch[warp] = v;
+    __syncthreads();
+    const int nwarps = (blockDim.x + 31) >> 5;
+    float t = (lane < nwarps) ? scratch[lane] : -INFINITY;
+    return warp_max(t);
+}
+
+__device__ __forceinline__ float gelu_tanh(float x) {
+    // x/2 * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3)))
+    const float c = 0.7978845608028654f;
+    return 0.5f * x * (1.f + tanhf(c * (x + 0.044715f * x * x * x)));
+}
+__device__ __forceinline__ float silu(float x) { return x / (1.f + __expf(-x)); }
+
+}  // namespace kb

@@ -1,0 +1,215 @@
+// Embedding rows, rotary tables, rotation fused with the cache append, gated activations, casts.
+//
+// Counterparts in Kapel's thread kernels (kernels/src/lib.rs): gather_rows :1145 and affine_any
+// :1328 (here one kernel), rope_table :1092, rope_any :1545 and write_rows_any :1579 (here one
+// kernel), glu_any :2489, widen_16/narrow_16 :375,386.
+#include "common.cuh"
+
+namespace kb {
+
+// ---------------------------------------------------------------------------------------
+// x[r, :] = table[ids[r], :] * scale, in 32-bit. An id outside the table gives a row of NaN.
+template <typename T>
+__global__ void embed_kernel(float* __restrict__ out, const T* __restrict__ table, const int* __restrict__ ids,
+                             int rows, int width, int vocab, float scale) {
+    const int r = blockIdx.x;
+    if (r >= rows) return;
+    const int id = ids[r];
+    float* o = out + (size_t)r * width;
+    if (id < 0 || id >= vocab) {
+        for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = __int_as_float(0x7fc00000);
+        return;
+    }
+    const T* t = table + (size_t)id * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) o[i] = Elem<T>::load(t + i) * scale;
+}
+
+// ---------------------------------------------------------------------------------------
+// cos_sin[r, j] = (cos, sin)(positions[r] * theta^(-2j / rotary)), angle in 64-bit.
+__global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __restrict__ positions, int rows,
+                                  int half, int rotary, double theta) {
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= rows * half) return;
+    const int r = i / half, j = i % half;
+    const double w = pow(theta, -(2.0 * (double)j) / (double)rotary);
+    const double a = (double)positions[r] * w;
+    double s, c;
+    sincos(a, &s, &c);
+    cos_sin[i] = make_float2((float)c, (float)s);
+}
+
+// ---------------------------------------------------------------------------------------
+// One thread a pair of components of one head vector of one row of the stacked q|k|v product.
+// Heads [0, Hq) are queries (rotated, written to q_out), [Hq, Hq+Hkv) keys (rotated, written to
+// the key table at the row's line), [Hq+Hkv, Hq+2Hkv) values (copied to the value table).
+// Pairing "half": (j, j + rotary/2) for j < rotary/2; components from `rotary` on pass through.
+// A row whose line is negative writes no key and no value (a padding row).
+template <typename T>
+__global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __restrict__ cos_sin,
+                                   const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
+                                   T* __restrict__ v_table, int rows, int hq, int hkv, int d, int rotary,
+                                   int write_kv, long long table_lines) {
+    const int half_d = d >> 1, half_r = rotary >> 1;
+    const int heads = hq + 2 * hkv;
+    const long long total = (long long)rows * heads * half_d;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int i = (int)(idx % half_d);
+    const int h = (int)((idx / half_d) % heads);
+    const int r = (int)(idx / ((long long)half_d * heads));
+    const T* src = qkv + ((size_t)r * heads + h) * d;
+    int ia, ib;
+    bool rotate;
+    if (i < half_r) {
+        ia = i; ib = i + half_r; rotate = true;
+    } else {
+        ia = rotary + 2 * (i - half_r); ib = ia + 1; rotate = false;
+    }
+    float a = Elem<T>::load(src + ia), b = Elem<T>::load(src + ib);
+    T* dst;
+    if (h < hq) {
+        dst = q_out + ((size_t)r * hq + h) * d;
+    } else {
+        if (!write_kv) return;
+        const int line = lines[r];
+        if (line < 0 || line >= table_lines) return;
+        const bool is_key = h < hq + hkv;
+        const int kvh = is_key ? h - hq : h - hq - hkv;
+        dst = (is_key ? k_table : v_table) + ((size_t)line * hkv + kvh) * d;
+        if (!is_key) rotate = false;
+    }
+    if (rotate) {
+        const float2 cs = cos_sin[(size_t)r * half_r + i];
+        const float ra = a * cs.x - b * cs.y;
+        const float rb = b * cs.x + a * cs.y;
+        a = ra; b = rb;
+    }
+    Elem<T>::store(dst + ia, a);
+    Elem<T>::store(dst + ib, b);
+}
+
+// ---------------------------------------------------------------------------------------
+// out[r, i] = act(x[r, i]) * x[r, n + i]: the gated unit after a stacked gate|up product.
+template <typename T>
+__global__ void glu_kernel(T* __restrict__ out, const T* __restrict__ x, long long rows, int n, int act) {
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= rows * n) return;
+    const long long r = idx / n;
+    const int i = (int)(idx % n);
+    const float g = Elem<T>::load(x + r * 2 * n + i), u = Elem<T>::load(x + r * 2 * n + n + i);
+    const float a = act == 0 ? gelu_tanh(g) : silu(g);
+    Elem<T>::store(out + idx, a * u);
+}
+
+template <typename TO, typename TI>
+__global__ void cast_kernel(TO* __restrict__ out, const TI* __restrict__ in, long long n) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) Elem<TO>::store(out + i, Elem<TI>::load(in + i));
+}
+
+// rows wanted: out[i, :] = x[rows[i], :]
+__global__ void gather_rows_f32_kernel(float* __restrict__ out, const float* __restrict__ x,
+                                       const int* __restrict__ rows, int n, int width, int src_rows) {
+    const int i = blockIdx.x;
+    if (i >= n) return;
+    const int r = rows[i];
+    for (int c = threadIdx.x; c < width; c += blockDim.x)
+        out[(size_t)i * width + c] = (r >= 0 && r < src_rows) ? x[(size_t)r * width + c] : __int_as_float(0x7fc00000);
+}
+
+}  // namespace kb
+
+using namespace kb;
+typedef __nv_bfloat16 bf16;
+
+extern "C" int kb_embed(float* out, const void* table, int table_dt, const int* ids, int rows, int width,
+                        int vocab, float scale, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0 && vocab > 0, "embed: rows %d, width %d, vocab %d", rows, width, vocab);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (table_dt == KB_DT_F32)
+        embed_kernel<float><<<rows, threads, 0, s>>>(out, (const float*)table, ids, rows, width, vocab, scale);
+    else if (table_dt == KB_DT_BF16)
+        embed_kernel<bf16><<<rows, threads, 0, s>>>(out, (const bf16*)table, ids, rows, width, vocab, scale);
+    else
+        return fail("embed: table dtype code %d is not known", table_dt);
+    return check_launch("embed");
+}
+
+extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int rotary, double theta,
+                             void* stream) {
+    KB_REQUIRE(rows >= 0 && rotary > 0 && rotary % 2 == 0, "rope_table: rows %d, rotary %d (must be even)", rows, rotary);
+    KB_REQUIRE(theta > 0, "rope_table: theta %g must be positive", theta);
+    if (rows == 0) return 0;
+    const int half = rotary / 2;
+    const long long n = (long long)rows * half;
+    KB_REQUIRE(n < (1ll << 31), "rope_table: %lld entries is too many", n);
+    rope_table_kernel<<<(unsigned)((n + 255) / 256), 256, 0, (cudaStream_t)stream>>>((float2*)cos_sin, positions, rows,
+                                                                                  half, rotary, theta);
+    return check_launch("rope_table");
+}
+
+extern "C" int kb_rope_append(const void* qkv, int dt, const float* cos_sin, const int* lines, void* q_out,
+                              void* k_table, void* v_table, int rows, int hq, int hkv, int d, int rotary,
+                              int write_kv, long long table_lines, void* stream) {
+    KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && d > 0 && d % 2 == 0, "rope_append: rows %d, heads %d/%d, head_dim %d", rows, hq, hkv, d);
+    KB_REQUIRE(rotary >= 0 && rotary <= d && rotary % 2 == 0, "rope_append: rotary %d must be even and at most head_dim %d", rotary, d);
+    if (rows == 0) return 0;
+    const long long total = (long long)rows * (hq + 2 * hkv) * (d / 2);
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == KB_DT_F32)
+        rope_append_kernel<float><<<blocks, 256, 0, s>>>((const float*)qkv, (const float2*)cos_sin, lines, (float*)q_out,
+                                                        (float*)k_table, (float*)v_table, rows, hq, hkv, d, rotary,
+                                                        write_kv, table_lines);
+    else if (dt == KB_DT_BF16)
+        rope_append_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out,
+                                                       (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d, rotary,
+                                                       write_kv, table_lines);
+    else
+        return fail("rope_append: dtype code %d is not known", dt);
+    return check_launch("rope_append");
+}
+
+extern "C" int kb_glu(void* out, const void* x, int dt, long long rows, int n, int act, void* stream) {
+    KB_REQUIRE(rows >= 0 && n > 0, "glu: rows %lld, width %d", rows, n);
+    KB_REQUIRE(act == 0 || act == 1, "glu: activation code %d is not known (0 gelu_tanh, 1 silu)", act);
+    if (rows == 0) return 0;
+    const long long total = rows * n;
+    const unsigned blocks = (unsigned)((total + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (dt == KB_DT_F32)
+        glu_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)x, rows, n, act);
+    else if (dt == KB_DT_BF16)
+        glu_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)x, rows, n, act);
+    else
+        return fail("glu: dtype code %d is not known", dt);
+    return check_launch("glu");
+}
+
+extern "C" int kb_cast(void* out, int out_dt, const void* in, int in_dt, long long n, void* stream) {
+    KB_REQUIRE(n >= 0, "cast: %lld elements", n);
+    if (n == 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    cudaStream_t s = (cudaStream_t)stream;
+    if (out_dt == KB_DT_F32 && in_dt == KB_DT_BF16)
+        cast_kernel<float, bf16><<<blocks, 256, 0, s>>>((float*)out, (const bf16*)in, n);
+    else if (out_dt == KB_DT_BF16 && in_dt == KB_DT_F32)
+        cast_kernel<bf16, float><<<blocks, 256, 0, s>>>((bf16*)out, (const float*)in, n);
+    else if (out_dt == KB_DT_F32 && in_dt == KB_DT_F32)
+        cast_kernel<float, float><<<blocks, 256, 0, s>>>((float*)out, (const float*)in, n);
+    else if (out_dt == KB_DT_BF16 && in_dt == KB_DT_BF16)
+        cast_kernel<bf16, bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)in, n);
+    else
+        return fail("cast: dtype codes %d -> %d are not known", in_dt, out_dt);
+    return check_launch("cast");
+}
+
+extern "C" int kb_gather_rows_f32(float* out, const float* x, const int* rows, int n, int width, int src_rows,
+                                  void* stream) {
+    KB_REQUIRE(n >= 0 && width > 0, "gather_rows: n %d, width %d", n, width);
+    if (n == 0) return 0;
+    gather_rows_f32_kernel<<<n, 256, 0, (cudaStream_t)stream>>>(out, x, rows, n, width, src_rows);
+    return check_launch("gather_rows");
+}

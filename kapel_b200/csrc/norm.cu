@@ -1,0 +1,121 @@
+// RMS norms with an offset on the weight, alone and fused with the residual sum.
+//
+// y = x / sqrt(mean(x^2) + eps) * (offset + w), sums and products in 32-bit
+// (Kapel: kernels/src/lib.rs norm_16 :2467, norm_block_any :1522; crates/kapel-ops/src/norm.rs:123-135).
+// One block a row, any width. Each thread walks the same components in every pass, so a pass may
+// read what the pass before wrote without a barrier beyond the reductions' own. The order of the
+// additions depends on the width and the block size only, never on the number of rows.
+#include "common.cuh"
+
+namespace kb {
+
+template <typename TX, typename TW, typename TY>
+__global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ w, int width,
+                               float eps, float offset) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float ss = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = Elem<TX>::load(x + base + i);
+        ss += v * v;
+    }
+    ss = block_sum(ss, scratch);
+    const float inv = 1.f / sqrtf(ss / (float)width + eps);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = Elem<TX>::load(x + base + i);
+        Elem<TY>::store(y + base + i, v * inv * (offset + Elem<TW>::load(w + i)));
+    }
+}
+
+// residual += norm_post(branch); then, if w_next, h = norm_next(residual).
+// With w_post null the branch is added as it is (a block without a norm after its branches).
+template <typename TB, typename TW, typename TH>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TB* __restrict__ branch,
+                                   const TW* __restrict__ w_post, float eps_post, float off_post,
+                                   const TW* __restrict__ w_next, float eps_next, float off_next,
+                                   TH* __restrict__ h, int width) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float inv = 1.f;
+    if (w_post != nullptr) {
+        float ss = 0.f;
+        for (int i = threadIdx.x; i < width; i += blockDim.x) {
+            const float v = Elem<TB>::load(branch + base + i);
+            ss += v * v;
+        }
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float ss2 = 0.f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float b = Elem<TB>::load(branch + base + i);
+        if (w_post != nullptr) b = b * inv * (off_post + Elem<TW>::load(w_post + i));
+        const float r = residual[base + i] + b;
+        residual[base + i] = r;
+        ss2 += r * r;
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float r = residual[base + i];       // written by this thread above
+        Elem<TH>::store(h + base + i, r * inv2 * (off_next + Elem<TW>::load(w_next + i)));
+    }
+}
+
+static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
+
+}  // namespace kb
+
+using namespace kb;
+typedef __nv_bfloat16 bf16;
+
+// x: f32 or bf16; w: f32 or bf16; y: f32 or bf16.
+extern "C" int kb_rmsnorm(void* y, int y_dt, const void* x, int x_dt, const void* w, int w_dt, int rows, int width,
+                          float eps, float offset, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0, "rmsnorm: rows %d, width %d", rows, width);
+    KB_REQUIRE(eps >= 0.f, "rmsnorm: eps %g is negative", eps);
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int t = threads_for(width);
+#define KB_NORM(TX, TW, TY) \
+    rmsnorm_kernel<TX, TW, TY><<<rows, t, 0, s>>>((TY*)y, (const TX*)x, (const TW*)w, width, eps, offset)
+    const int code = x_dt * 4 + w_dt * 2 + y_dt;
+    switch (code) {
+        case 0: KB_NORM(float, float, float); break;
+        case 1: KB_NORM(float, float, bf16); break;
+        case 2: KB_NORM(float, bf16, float); break;
+        case 3: KB_NORM(float, bf16, bf16); break;
+        case 4: KB_NORM(bf16, float, float); break;
+        case 5: KB_NORM(bf16, float, bf16); break;
+        case 6: KB_NORM(bf16, bf16, float); break;
+        case 7: KB_NORM(bf16, bf16, bf16); break;
+        default: return fail("rmsnorm: dtype codes x %d, w %d, y %d are not known", x_dt, w_dt, y_dt);
+    }
+#undef KB_NORM
+    return check_launch("rmsnorm");
+}
+
+// residual: f32 in and out. branch and h share the activation dtype `act_dt`; both weights share `w_dt`.
+extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int act_dt, const void* w_post, float eps_post,
+                              float off_post, const void* w_next, float eps_next, float off_next, void* h, int w_dt,
+                              int rows, int width, void* stream) {
+    KB_REQUIRE(rows >= 0 && width > 0, "add_rmsnorm: rows %d, width %d", rows, width);
+    KB_REQUIRE(w_next == nullptr || h != nullptr, "add_rmsnorm: a following norm needs an output");
+    if (rows == 0) return 0;
+    cudaStream_t s = (cudaStream_t)stream;
+    const int t = threads_for(width);
+#define KB_ADDNORM(TB, TW)                                                                                   \
+    add_rmsnorm_kernel<TB, TW, TB><<<rows, t, 0, s>>>(residual, (const TB*)branch, (const TW*)w_post, eps_post, \
+                                                      off_post, (const TW*)w_next, eps_next, off_next, (TB*)h, width)
+    const int code = act_dt * 2 + w_dt;
+    switch (code) {
+        case 0: KB_ADDNORM(float, float); break;
+        case 1: KB_ADDNORM(float, bf16); break;
+        case 2: KB_ADDNORM(bf16, float); break;
+        case 3: KB_ADDNORM(bf16, bf16); break;
+        default: return fail("add_rmsnorm: dtype codes act %d, w %d are not known", act_dt, w_dt);
+    }
+#undef KB_ADDNORM
+    return check_launch("add_rmsnorm");
+}

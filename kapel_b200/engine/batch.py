@@ -1,0 +1,86 @@
+"""One step's rows on the device: what the cache manager planned, copied over in one piece.
+
+Kapel uploads `ids, positions, lines, pages, rows, slots` as separate small tensors
+(crates/kapel-models/src/cache.rs:822-842). Here they are slices of one int32 buffer that
+crosses from pinned host memory in a single copy.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Sequence
+
+import numpy as np
+import torch
+
+from ..cache import Plan
+
+
+class GroupBatch:
+    __slots__ = ("lines", "block_table")
+
+    def __init__(self, lines, block_table):
+        self.lines = lines                # [rows] int32 on the device
+        self.block_table = block_table    # [entries, width] int32 on the device
+
+
+def _chunks_touched(row_count: np.ndarray, window: Optional[int], chunk: int) -> int:
+    """The most key chunks (cut at absolute multiples of `chunk`) any row of the step reads."""
+    c = row_count[row_count > 0].astype(np.int64)
+    if c.size == 0:
+        return 1
+    first = np.maximum(0, c - window) if window else np.zeros_like(c)
+    return int(((c - 1) // chunk - first // chunk + 1).max())
+
+
+class StepBatch:
+    """Device views of a step. `memo` holds what parts share within the step (rotary tables)."""
+
+    def __init__(self, plan: Plan, ids: Sequence[int], want_rows: Sequence[int], device, chunk: int,
+                 fixed_slots: Optional[int] = None):
+        self.plan = plan
+        self.rows = plan.rows
+        self.entries = len(plan.entries)
+        self.chunk = chunk
+        self.fixed_slots = fixed_slots
+        self.memo: Dict[object, object] = {}
+        self._slots_memo: Dict[Optional[int], int] = {}
+        parts: List[np.ndarray] = [
+            np.asarray(ids, np.int32), plan.positions, plan.row_entry, plan.row_count,
+            np.asarray(want_rows, np.int32), plan.slots,
+        ]
+        for g in plan.groups:
+            parts.append(g.lines)
+            parts.append(g.block_table.reshape(-1))
+        sizes = [p.size for p in parts]
+        total = sum(sizes)
+        host = torch.empty((max(total, 1),), dtype=torch.int32, pin_memory=(device.type == "cuda"))
+        flat = host.numpy()
+        at = 0
+        for p in parts:
+            flat[at : at + p.size] = p
+            at += p.size
+        self.h2d_bytes = total * 4
+        dev = host.to(device, non_blocking=True)
+        self._host = host                 # keeps the pinned buffer alive until the copy is done
+        self._assign(dev, sizes, [g.block_table.shape for g in plan.groups])
+
+    def _assign(self, dev, sizes, table_shapes):
+        views, at = [], 0
+        for n in sizes:
+            views.append(dev[at : at + n])
+            at += n
+        self.ids, self.positions, self.row_entry, self.row_count, self.want_rows, self.slots = views[:6]
+        self.groups = []
+        for i, shape in enumerate(table_shapes):
+            self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
+
+    def attention_slots(self, window: Optional[int]) -> int:
+        """Chunk slots the row-wise attention kernel needs for a layer with this window."""
+        if window not in self._slots_memo:
+            if self.fixed_slots is not None:
+                n = self.fixed_slots
+                if window:
+                    n = min(n, (window - 1) // self.chunk + 2)
+            else:
+                n = _chunks_touched(self.plan.row_count, window, self.chunk)
+            self._slots_memo[window] = max(1, n)
+        return self._slots_memo[window]

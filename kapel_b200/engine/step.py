@@ -1,0 +1,189 @@
+"""The step function: a batch of (request, its next tokens) in, logits at the wanted places out.
+
+It runs only the tokens it is given, as one batch, from the cache that earlier steps left:
+portions of prompts beside single decoded tokens, cut anywhere. Kapel's counterpart is
+`Model::run_batch_with` (crates/kapel-models/src/model.rs:986-1033) over `KvCache::begin`
+(crates/kapel-models/src/cache.rs:822-842). Lengths move only once the step's kernels are
+enqueued; if anything fails before, the pages the plan took go back.
+"""
+from __future__ import annotations
+
+import json
+from dataclasses import dataclass, field
+from pathlib import Path
+from typing import Hashable, List, Optional, Sequence, Tuple
+
+import torch
+
+from .. import kernels as K
+from ..cache import CacheFull, CacheManager
+from ..config import config_from_dir, config_from_json
+from ..parts import BuildContext
+from ..weights import check_names, load_tensors, random_tensors
+from .batch import StepBatch
+from .model import ModelParts
+
+PAGE_SIZE = 16           # positions a page; Kapel's PAGE (crates/kapel-models/src/cache.rs:49)
+
+_DTYPES = {
+    "bfloat16": torch.bfloat16, "bf16": torch.bfloat16,
+    "float32": torch.float32, "f32": torch.float32, "fp32": torch.float32,
+}
+
+
+def parse_dtype(name) -> torch.dtype:
+    if isinstance(name, torch.dtype):
+        if name not in (torch.bfloat16, torch.float32):
+            raise ValueError(f"dtype {name} is not bfloat16 or float32")
+        return name
+    try:
+        return _DTYPES[str(name).lower()]
+    except KeyError:
+        raise ValueError(f"dtype {name!r} is not one of {sorted(_DTYPES)}") from None
+
+
+@dataclass
+class StepEntry:
+    """A request's next tokens and the places among them whose logits are wanted."""
+
+    id: Hashable
+    tokens: Sequence[int]
+    want: Sequence[int] = field(default_factory=list)
+
+
+def require_device() -> torch.device:
+    if not torch.cuda.is_available():
+        raise RuntimeError("kapel_b200 runs on a CUDA device (sm_100a); none is available and there is no CPU path")
+    K.library()
+    return torch.device("cuda", torch.cuda.current_device())
+
+
+class Engine:
+    """A loaded model, its cache and its step function.
+
+    `max_tokens` sizes every group's page pool (ceil(max_tokens / page) pages); `max_sequences`
+    the slots. `dtype` "bfloat16" runs the serving kernels, "float32" everything in true 32-bit.
+    """
+
+    def __init__(self, config, tensors, dtype="bfloat16", max_tokens: int = 8192, max_sequences: int = 64,
+                 device: Optional[torch.device] = None, pages: Optional[int] = None, raw_config: Optional[dict] = None):
+        self.device = device or require_device()
+        self.dtype = parse_dtype(dtype)
+        self.config = config
+        self.raw_config = raw_config
+        self.spec = config.to_spec()
+        ctx = BuildContext(dtype=self.dtype, device=self.device, page_size=PAGE_SIZE)
+        self.ctx = ctx
+        self.model = ModelParts(self.spec, ctx)
+        check_names(self.model.expected_tensors(), {n: tuple(t.shape) for n, t in tensors.items()}, "the given tensors")
+        self.model.load(tensors)
+        n_pages = pages if pages is not None else -(-max_tokens // PAGE_SIZE)
+        self.cache = CacheManager(
+            self.model.cache_needs(), PAGE_SIZE, n_pages, max_sequences,
+            allocate=self._allocate, dtype=self.dtype,
+        )
+        self.chunk = K.attention_chunk()
+        self.steps = 0
+        self.last_h2d_bytes = 0
+
+    # ------------------------------------------------------------------ construction
+    @classmethod
+    def from_dir(cls, folder, dtype="bfloat16", **kw) -> "Engine":
+        config, raw = config_from_dir(folder)
+        device = kw.pop("device", None) or require_device()
+        from ..parts import expected_tensors
+
+        tensors = load_tensors(folder, expected_tensors(config.to_spec()), device)
+        return cls(config, tensors, dtype=dtype, device=device, raw_config=raw, **kw)
+
+    @classmethod
+    def random(cls, config, seed: int = 0, dtype="bfloat16", **kw) -> "Engine":
+        """A model of `config` (a typed configuration or config.json's dict) with random weights
+        made on the device; for timing, where only the shapes matter."""
+        if isinstance(config, dict):
+            config = config_from_json(config)
+        device = kw.pop("device", None) or require_device()
+        tensors = random_tensors(config, seed, device=device)
+        return cls(config, tensors, dtype=dtype, device=device, **kw)
+
+    def _allocate(self, shape, dtype):
+        if isinstance(dtype, str):
+            dtype = getattr(torch, dtype)
+        return torch.zeros(shape, dtype=dtype, device=self.device)
+
+    # ------------------------------------------------------------------ the step
+    @property
+    def vocab_size(self) -> int:
+        return self.spec.vocab_size
+
+    def _validate(self, entries: Sequence[StepEntry]):
+        ids: List[int] = []
+        want_rows: List[int] = []
+        counts: List[Tuple[Hashable, int]] = []
+        vocab = self.spec.vocab_size
+        for e in entries:
+            n = len(e.tokens)
+            if n == 0:
+                raise ValueError(f"request {e.id!r} brings no token")
+            for t in e.tokens:
+                if not 0 <= int(t) < vocab:
+                    raise ValueError(f"request {e.id!r}: token {t} is outside the vocabulary (0..{vocab - 1})")
+            for w in e.want:
+                if not 0 <= int(w) < n:
+                    raise ValueError(f"request {e.id!r}: wanted place {w} is outside its {n} tokens")
+                want_rows.append(len(ids) + int(w))
+            ids.extend(int(t) for t in e.tokens)
+            counts.append((e.id, n))
+        return ids, want_rows, counts
+
+    def plan(self, entries: Sequence[StepEntry]):
+        """Checks the entries, admits new requests into the cache and takes the step's pages."""
+        ids, want_rows, counts = self._validate(entries)
+        limit = self.spec.max_positions
+        added = []
+        try:
+            for seq_id, n in counts:
+                if seq_id not in self.cache:
+                    self.cache.add_sequence(seq_id)
+                    added.append(seq_id)
+                if limit is not None and self.cache.length(seq_id) + n > limit:
+                    raise ValueError(
+                        f"request {seq_id!r} would reach {self.cache.length(seq_id) + n} positions; the model allows {limit}"
+                    )
+            plan = self.cache.plan(counts)
+        except Exception:
+            for seq_id in added:
+                self.cache.remove_sequence(seq_id)
+            raise
+        return plan, ids, want_rows
+
+    def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
+        """Runs one batch; returns float32 logits [number of wanted places, vocab] on the device,
+        in the order of the entries and of each entry's `want`."""
+        entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
+        if not entries:
+            return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
+        plan, ids, want_rows = self.plan(entries)
+        try:
+            batch = StepBatch(plan, ids, want_rows, self.device, self.chunk)
+            self.last_h2d_bytes = batch.h2d_bytes
+            self._clear_fresh_state(plan)
+            logits = self.model.forward(batch, self.cache)
+        except Exception:
+            self.cache.abort(plan)
+            raise
+        self.cache.commit(plan)
+        self.steps += 1
+        return logits
+
+    def _clear_fresh_state(self, plan) -> None:
+        if not self.cache.states or not plan.fresh.any():
+            return
+        slots = torch.as_tensor(plan.slots[plan.fresh], dtype=torch.long, device=self.device)
+        for table in self.cache.states.values():
+            table.index_fill_(0, slots, 0)
+
+    def end(self, seq_id) -> None:
+        """The request is finished: everything it holds goes back."""
+        if seq_id in self.cache:
+            self.cache.remove_sequence(seq_id)

@@ -1,0 +1,275 @@
+"""Tensor-level entry points of the CUDA library (`kapel_b200/csrc`).
+
+Every function here checks devices, dtypes, shapes and contiguity, then calls one C launcher
+on torch's current stream. There is no other implementation behind them: without the built
+library, or without a CUDA device, they raise. Tensors are torch tensors only as owners of
+device memory; no torch operator computes anything on this path.
+"""
+from __future__ import annotations
+
+import ctypes
+import threading
+from typing import Optional
+
+import torch
+
+_lib = None
+_lock = threading.Lock()
+
+F32, BF16 = 0, 1
+_CODES = {torch.float32: F32, torch.bfloat16: BF16}
+
+ACT_CODES = {"gelu_tanh": 0, "silu": 1}
+
+
+class KernelError(RuntimeError):
+    """A launcher refused its arguments or a launch failed; the message is the library's."""
+
+
+def library():
+    """The loaded library; builds it at the first call if it is missing or stale."""
+    global _lib
+    if _lib is None:
+        with _lock:
+            if _lib is None:
+                from ..csrc.build import ensure_built
+
+                path = ensure_built()
+                lib = ctypes.CDLL(str(path))
+                lib.kb_last_error.restype = ctypes.c_char_p
+                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats"):
+                    getattr(lib, name).restype = ctypes.c_longlong
+                _lib = lib
+    return _lib
+
+
+def library_path() -> str:
+    library()
+    from ..csrc.build import ensure_built
+
+    return str(ensure_built(verbose=False))
+
+
+def _check(code: int) -> None:
+    if code != 0:
+        raise KernelError(library().kb_last_error().decode("utf-8", "replace"))
+
+
+def _stream() -> ctypes.c_void_p:
+    return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
+
+
+def _ptr(t: Optional[torch.Tensor]) -> ctypes.c_void_p:
+    return ctypes.c_void_p(0 if t is None else t.data_ptr())
+
+
+def _dt(t: torch.Tensor, what: str) -> int:
+    if t.dtype not in _CODES:
+        raise KernelError(f"{what}: dtype {t.dtype} is not float32 or bfloat16")
+    return _CODES[t.dtype]
+
+
+def _need(t: torch.Tensor, what: str, dtype=None, shape=None) -> torch.Tensor:
+    if not t.is_cuda:
+        raise KernelError(f"{what}: tensor is on {t.device}; the kernels run on a CUDA device only")
+    if not t.is_contiguous():
+        raise KernelError(f"{what}: tensor is not contiguous")
+    if dtype is not None and t.dtype != dtype:
+        raise KernelError(f"{what}: dtype {t.dtype}, expected {dtype}")
+    if shape is not None:
+        if len(shape) != t.dim() or any(s is not None and s != a for s, a in zip(shape, t.shape)):
+            raise KernelError(f"{what}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+    return t
+
+
+def _f(x: float) -> ctypes.c_float:
+    return ctypes.c_float(float(x))
+
+
+# ------------------------------------------------------------------------------------------
+def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """out[r] = table[ids[r]] * scale in float32."""
+    _need(table, "embed table")
+    _need(ids, "embed ids", torch.int32)
+    vocab, width = table.shape
+    rows = ids.numel()
+    if out is None:
+        out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+    _need(out, "embed out", torch.float32, (rows, width))
+    _check(library().kb_embed(_ptr(out), _ptr(table), _dt(table, "embed table"), _ptr(ids), rows, width, vocab, _f(scale), _stream()))
+    return out
+
+
+def rope_table(positions: torch.Tensor, rotary: int, theta: float) -> torch.Tensor:
+    """[rows, rotary/2, 2] float32 of (cos, sin); angles in float64 on the device."""
+    _need(positions, "rope positions", torch.int32)
+    rows = positions.numel()
+    out = torch.empty((rows, rotary // 2, 2), dtype=torch.float32, device=positions.device)
+    _check(library().kb_rope_table(_ptr(out), _ptr(positions), rows, int(rotary), ctypes.c_double(float(theta)), _stream()))
+    return out
+
+
+def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int, rotary: int, write_kv: bool = True):
+    """Rotates the q and k heads of the stacked product `qkv` [rows, (hq + 2 hkv) d], returns q
+    [rows, hq, d], and writes k and v at each row's line of the tables [lines, hkv, d]."""
+    rows = qkv.shape[0]
+    _need(qkv, "rope_append qkv", shape=(rows, (hq + 2 * hkv) * d))
+    dt = _dt(qkv, "rope_append qkv")
+    if rotary:
+        _need(cos_sin, "rope_append cos_sin", torch.float32, (rows, rotary // 2, 2))
+    q = torch.empty((rows, hq, d), dtype=qkv.dtype, device=qkv.device)
+    table_lines = 0
+    if write_kv:
+        _need(lines, "rope_append lines", torch.int32, (rows,))
+        _need(k_table, "rope_append k table", qkv.dtype)
+        _need(v_table, "rope_append v table", qkv.dtype)
+        if k_table.shape[-2:] != (hkv, d) or v_table.shape != k_table.shape:
+            raise KernelError(f"rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} do not end in ({hkv}, {d})")
+        table_lines = k_table.numel() // (hkv * d)
+    _check(
+        library().kb_rope_append(
+            _ptr(qkv), dt, _ptr(cos_sin if rotary else None), _ptr(lines if write_kv else None), _ptr(q),
+            _ptr(k_table if write_kv else None), _ptr(v_table if write_kv else None),
+            rows, hq, hkv, d, int(rotary), int(bool(write_kv)), ctypes.c_longlong(table_lines), _stream(),
+        )
+    )
+    return q
+
+
+def glu(x: torch.Tensor, activation: str) -> torch.Tensor:
+    """act(x[:, :n]) * x[:, n:] for a stacked gate|up product."""
+    _need(x, "glu input")
+    if activation not in ACT_CODES:
+        raise KernelError(f"glu: activation {activation!r} is not known")
+    rows, two_n = x.shape
+    n = two_n // 2
+    out = torch.empty((rows, n), dtype=x.dtype, device=x.device)
+    _check(library().kb_glu(_ptr(out), _ptr(x), _dt(x, "glu input"), ctypes.c_longlong(rows), n, ACT_CODES[activation], _stream()))
+    return out
+
+
+def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
+    _need(x, "cast input")
+    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    _check(library().kb_cast(_ptr(out), _dt(out, "cast output"), _ptr(x), _dt(x, "cast input"), ctypes.c_longlong(x.numel()), _stream()))
+    return out
+
+
+def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
+    _need(x, "gather_rows input", torch.float32)
+    _need(rows, "gather_rows rows", torch.int32)
+    n, width = rows.numel(), x.shape[1]
+    out = torch.empty((n, width), dtype=torch.float32, device=x.device)
+    _check(library().kb_gather_rows_f32(_ptr(out), _ptr(x), _ptr(rows), n, width, x.shape[0], _stream()))
+    return out
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, out_dtype: torch.dtype) -> torch.Tensor:
+    _need(x, "rmsnorm input")
+    rows, width = x.shape
+    _need(weight, "rmsnorm weight", shape=(width,))
+    y = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    _check(
+        library().kb_rmsnorm(_ptr(y), _dt(y, "rmsnorm output"), _ptr(x), _dt(x, "rmsnorm input"), _ptr(weight),
+                             _dt(weight, "rmsnorm weight"), rows, width, _f(eps), _f(offset), _stream())
+    )
+    return y
+
+
+def add_rmsnorm(residual, branch, post, nxt, out_dtype):
+    """residual += norm_post(branch) (post = (weight, eps, offset) or None: plain add); returns
+    norm_next(residual) when nxt = (weight, eps, offset) is given, else None. In place on residual."""
+    rows, width = residual.shape
+    _need(residual, "add_rmsnorm residual", torch.float32)
+    _need(branch, "add_rmsnorm branch", out_dtype, (rows, width))
+    w_post, eps_post, off_post = post if post is not None else (None, 0.0, 0.0)
+    w_next, eps_next, off_next = nxt if nxt is not None else (None, 0.0, 0.0)
+    ws = [w for w in (w_post, w_next) if w is not None]
+    for w in ws:
+        _need(w, "add_rmsnorm weight", shape=(width,))
+    if len({w.dtype for w in ws}) > 1:
+        raise KernelError("add_rmsnorm: the two norms' weights differ in dtype; call the norms one by one")
+    w_dt = _dt(ws[0], "add_rmsnorm weight") if ws else F32
+    h = torch.empty((rows, width), dtype=out_dtype, device=residual.device) if w_next is not None else None
+    _check(
+        library().kb_add_rmsnorm(_ptr(residual), _ptr(branch), _dt(branch, "add_rmsnorm branch"), _ptr(w_post), _f(eps_post),
+                                 _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), w_dt, rows, width, _stream())
+    )
+    return h
+
+
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, softcap: Optional[float] = None) -> torch.Tensor:
+    """a [m, k] . w [n, k]^T -> [m, n]; float32 x float32 in true 32-bit, bfloat16 x bfloat16 on
+    tensor cores with 32-bit sums. `softcap` c applies c * tanh(x / c) to the result."""
+    _need(a, "gemm input")
+    _need(w, "gemm weight")
+    m, k = a.shape
+    n, k2 = w.shape
+    if k != k2:
+        raise KernelError(f"gemm: input [{m}, {k}] against weight [{n}, {k2}]")
+    if a.dtype != w.dtype:
+        raise KernelError(f"gemm: input {a.dtype} against weight {w.dtype}")
+    epi, cap = (1, softcap) if softcap is not None else (0, 0.0)
+    lib = library()
+    if a.dtype == torch.float32:
+        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+        _check(lib.kb_gemm_f32(_ptr(out), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
+        if out_dtype is not None and out_dtype != torch.float32:
+            out = cast(out, out_dtype)
+        return out
+    out_dtype = out_dtype or torch.bfloat16
+    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
+    scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
+    _check(lib.kb_gemm_bf16(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _ptr(scratch), _stream()))
+    return out
+
+
+_ATT_CHUNK = None
+
+
+def attention_chunk() -> int:
+    global _ATT_CHUNK
+    if _ATT_CHUNK is None:
+        _ATT_CHUNK = int(library().kb_attention_chunk())
+    return _ATT_CHUNK
+
+
+def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count, page_size: int, window: Optional[int],
+                         scale: float, softcap: Optional[float], slots: int) -> torch.Tensor:
+    """Attention of each query row over its sequence's pages; `slots` is the largest number of
+    key chunks (of `attention_chunk()` positions, cut at absolute multiples) any row touches."""
+    rows, hq, d = q.shape
+    _need(q, "attention q")
+    _need(k_table, "attention k table", q.dtype)
+    _need(v_table, "attention v table", q.dtype)
+    hkv = k_table.shape[-2]
+    if k_table.shape[-1] != d or v_table.shape != k_table.shape:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} against head_dim {d}")
+    n_pages = k_table.numel() // (page_size * hkv * d)
+    _need(block_table, "attention block table", torch.int32)
+    _need(row_entry, "attention row_entry", torch.int32, (rows,))
+    _need(row_count, "attention row_count", torch.int32, (rows,))
+    out = torch.empty_like(q)
+    lib = library()
+    need = lib.kb_paged_attention_scratch_floats(rows, hq, d, int(slots))
+    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    _check(
+        lib.kb_paged_attention_rows(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
+                                    _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(page_size), int(block_table.shape[1]),
+                                    int(n_pages), int(window or 0), int(slots), _f(scale), _f(softcap or 0.0), _ptr(scratch), _stream())
+    )
+    return out
+
+
+def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uniform: Optional[torch.Tensor] = None) -> torch.Tensor:
+    """One token a row: the first largest logit where temperature <= 0 (or none is given), else
+    a draw with the row's uniform number."""
+    _need(logits, "sample logits", torch.float32)
+    rows, vocab = logits.shape
+    if temperature is not None:
+        _need(temperature, "sample temperature", torch.float32, (rows,))
+        _need(uniform, "sample uniform", torch.float32, (rows,))
+    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    _check(library().kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _stream()))
+    return out

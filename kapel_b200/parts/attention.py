@@ -1,0 +1,65 @@
+"""Grouped-query attention over the paged cache.
+
+q, k, v come from one stacked product (Kapel stacks them at load: crates/kapel-models/src/model.rs:415-480,
+1506-1517); one kernel rotates q and k and appends k and v to the cache at the rows' lines
+(Kapel: rope_any twice and write_rows_any twice, model.rs:1561-1579); attention reads the pages
+through the block table with scale, soft cap and window as arguments (model.rs:1580-1590);
+then the output product (model.rs:1633-1637).
+"""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from ..cache import CacheNeeds, PagedKV
+from .base import Part, linear, matrix_for
+from .registry import build_part
+
+
+class Attention(Part):
+    @staticmethod
+    def expected_tensors(spec):
+        qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim
+        w = spec.weights
+        return {w["q"]: (qd, spec.hidden), w["k"]: (kvd, spec.hidden), w["v"]: (kvd, spec.hidden), w["o"]: (spec.hidden, qd)}
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        if spec.num_heads % spec.num_kv_heads:
+            raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
+        if spec.head_dim % 16:
+            raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
+        self.position = build_part("position", spec.position, ctx)
+
+    def load(self, tensors):
+        w = self.spec.weights
+        parts = [tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]]
+        if len({p.dtype for p in parts}) != 1:
+            raise ValueError("attention: q, k and v weights differ in dtype and cannot be stacked")
+        rows = sum(p.shape[0] for p in parts)
+        stacked = torch.empty((rows, self.spec.hidden), dtype=parts[0].dtype, device=parts[0].device)
+        at = 0
+        for p in parts:
+            stacked[at : at + p.shape[0]].copy_(p)
+            at += p.shape[0]
+        self.w_qkv = matrix_for(self.ctx, stacked)
+        self.w_o = matrix_for(self.ctx, tensors[w["o"]])
+
+    def cache_needs(self) -> CacheNeeds:
+        s = self.spec
+        return CacheNeeds(paged=PagedKV(s.num_kv_heads, s.head_dim, s.window))
+
+    def forward(self, h, batch, cache):
+        s = self.spec
+        qkv = linear(self.ctx, h, self.w_qkv)
+        k_table, v_table = cache.tables()
+        group = batch.groups[cache.group]
+        q = K.rope_append(
+            qkv, self.position.tables(batch), group.lines, k_table, v_table,
+            s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim, write_kv=cache.owns,
+        )
+        y = K.paged_attention_rows(
+            q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count,
+            self.ctx.page_size, s.window, s.scale, s.softcap, batch.attention_slots(s.window),
+        )
+        return linear(self.ctx, y.view(y.shape[0], s.num_heads * s.head_dim), self.w_o)

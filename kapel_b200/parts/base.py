@@ -1,0 +1,104 @@
+"""The interfaces of parts, and what a part is given when it is built and when it runs.
+
+Every part class has:
+
+    expected_tensors(spec) -> {tensor name: shape}      (a static method; no device needed)
+    __init__(spec, ctx)                                 (ctx: BuildContext)
+    load(tensors)                                       (tensors: {name: device tensor})
+
+and, by category:
+
+    norm          forward(x, out_dtype=None) -> y       x float32 or activation dtype, [rows, width]
+                  fuse_key() -> a (weight, eps, offset) triple if the fused kernel may apply it, else None
+    position      apply(q_and_k ...) is not called by the engine: a mixer owns its position
+                  encoding and asks it for what it needs; kind "rope" gives `tables(batch)`.
+    mixer         cache_needs() -> CacheNeeds
+                  forward(h, batch, cache) -> [rows, hidden] in the activation dtype
+                      h: [rows, hidden]; batch: engine.batch.StepBatch; cache: LayerCache
+    feed_forward  forward(h) -> [rows, hidden]
+    block         forward(x, h, batch, cache, next_norm) -> (x, h_next)
+                      x: the float32 residual [rows, hidden] (updated in place);
+                      h: this block's first norm already applied to x, or None;
+                      next_norm: the norm that the next consumer applies to x first, or None;
+                      h_next: next_norm(x) if the block computed it on the way, else None.
+    embedding     forward(ids) -> float32 [rows, hidden]
+    head          forward(x_rows) -> float32 logits [n, vocab]
+
+No part knows which model it is in: sizes and constants come from its spec, tensors by the
+names its spec gives.
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass
+from typing import Dict, Optional
+
+import torch
+
+
+@dataclass
+class BuildContext:
+    """`dtype` is the activation dtype of the path: bfloat16 (serving) or float32 (everything
+    in true 32-bit). `page_size` is the cache's."""
+
+    dtype: torch.dtype
+    device: torch.device
+    page_size: int = 16
+
+    @property
+    def is_f32(self) -> bool:
+        return self.dtype == torch.float32
+
+
+class LayerCache:
+    """What one layer run sees of the cache: the tables of the layer whose cache it uses, and
+    whether it may write them (`owns` is False for a layer that reads another layer's cache)."""
+
+    def __init__(self, manager, cache_layer: int, owns: bool):
+        self.manager = manager
+        self.layer = cache_layer
+        self.owns = owns
+
+    @property
+    def group(self) -> int:
+        return self.manager.group_of_layer[self.layer]
+
+    def tables(self):
+        return self.manager.tables(self.layer)
+
+    def state(self):
+        return self.manager.states[self.layer]
+
+
+class Part:
+    @staticmethod
+    def expected_tensors(spec) -> Dict[str, tuple]:
+        return {}
+
+    def __init__(self, spec, ctx: BuildContext):
+        self.spec = spec
+        self.ctx = ctx
+
+    def load(self, tensors) -> None:
+        pass
+
+
+def matrix_for(ctx: BuildContext, t: torch.Tensor) -> torch.Tensor:
+    """A weight as the products take it: kept as stored (bfloat16, or float32 if the file has
+    it in 32-bit); widened to float32 on the 32-bit path."""
+    if ctx.is_f32 and t.dtype != torch.float32:
+        return t.to(torch.float32)
+    return t.contiguous()
+
+
+def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
+           softcap: Optional[float] = None) -> torch.Tensor:
+    """x . w^T through the library's kernels. A weight kept in 32-bit on the bfloat16 path is
+    multiplied in true 32-bit: the input is widened first and the result narrowed after."""
+    from .. import kernels as K
+
+    out_dtype = out_dtype or ctx.dtype
+    if w.dtype == torch.float32 and x.dtype != torch.float32:
+        x = K.cast(x, torch.float32)
+    elif w.dtype == torch.bfloat16 and x.dtype != torch.bfloat16:
+        x = K.cast(x, torch.bfloat16)
+    return K.gemm(x, w, out_dtype=out_dtype, softcap=softcap)

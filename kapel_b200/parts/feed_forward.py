@@ -1,0 +1,40 @@
+"""The gated feed-forward: down(act(gate(h)) * up(h)), gate and up as one stacked product
+(crates/kapel-models/src/model.rs:1429-1456; the gated unit kernels/src/lib.rs glu_any :2489)."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels as K
+from .base import Part, linear, matrix_for
+
+
+class GatedMLP(Part):
+    @staticmethod
+    def expected_tensors(spec):
+        w = spec.weights
+        return {
+            w["gate"]: (spec.intermediate, spec.hidden),
+            w["up"]: (spec.intermediate, spec.hidden),
+            w["down"]: (spec.hidden, spec.intermediate),
+        }
+
+    def __init__(self, spec, ctx):
+        super().__init__(spec, ctx)
+        if spec.activation not in K.ACT_CODES:
+            raise ValueError(f"gated_mlp: activation {spec.activation!r} is not built")
+
+    def load(self, tensors):
+        w = self.spec.weights
+        gate, up = tensors[w["gate"]], tensors[w["up"]]
+        if gate.dtype != up.dtype:
+            raise ValueError("gated_mlp: gate and up weights differ in dtype and cannot be stacked")
+        stacked = torch.empty((2 * self.spec.intermediate, self.spec.hidden), dtype=gate.dtype, device=gate.device)
+        stacked[: self.spec.intermediate].copy_(gate)
+        stacked[self.spec.intermediate :].copy_(up)
+        self.w_gate_up = matrix_for(self.ctx, stacked)
+        self.w_down = matrix_for(self.ctx, tensors[w["down"]])
+
+    def forward(self, h):
+        gu = linear(self.ctx, h, self.w_gate_up)
+        inner = K.glu(gu, self.spec.activation)
+        return linear(self.ctx, inner, self.w_down)

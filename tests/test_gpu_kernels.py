@@ -1,0 +1,309 @@
+"""Each kernel alone against its plain reference, at sizes other than the engine's."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gemma2 as P
+from helpers import rel_err
+
+pytestmark = pytest.mark.gpu
+
+DT = {"float32": torch.float32, "bfloat16": torch.bfloat16}
+
+
+def K():
+    from kapel_b200 import kernels
+
+    return kernels
+
+
+def dev(t):
+    return t.cuda().contiguous()
+
+
+def rnd(*shape, seed=0, dtype=torch.float32, scale=1.0):
+    g = torch.Generator().manual_seed(seed)
+    return (torch.randn(*shape, generator=g) * scale).to(dtype)
+
+
+# ------------------------------------------------------------------------------------------
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_embed(dtype):
+    table = rnd(300, 100, seed=1, dtype=DT[dtype])
+    ids = torch.tensor([0, 299, 17, 17, 5], dtype=torch.int32)
+    out = K().embed(dev(table), dev(ids), 9.8125).cpu()
+    want = P.embed(table.double(), ids.long(), 9.8125)
+    assert rel_err(out.numpy(), want.numpy()) < 1e-6
+    bad = K().embed(dev(table), dev(torch.tensor([300, -1], dtype=torch.int32)), 1.0).cpu()
+    assert torch.isnan(bad).all(), "an id outside the table must not give a silent row"
+
+
+def test_rope_table():
+    pos = torch.tensor([0, 1, 7, 100, 8191, 131071], dtype=torch.int32)
+    for theta, rotary in [(10000.0, 16), (500000.0, 48), (1e6, 256)]:
+        got = K().rope_table(dev(pos), rotary, theta).cpu().double()
+        w = P.rope_frequencies(theta, rotary)
+        angle = pos.double()[:, None] * w[None, :]
+        assert (got[..., 0] - torch.cos(angle)).abs().max() < 1e-6
+        assert (got[..., 1] - torch.sin(angle)).abs().max() < 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,d,rotary", [(4, 2, 16, 16), (6, 1, 32, 32), (3, 3, 48, 48), (2, 1, 64, 32)])
+def test_rope_append(dtype, hq, hkv, d, rotary):
+    rows, lines_total = 9, 40
+    qkv = rnd(rows, (hq + 2 * hkv) * d, seed=2, dtype=DT[dtype])
+    pos = torch.tensor([0, 1, 2, 3, 50, 51, 7, 1000, 0], dtype=torch.int32)
+    lines = torch.tensor([5, 6, 7, 39, 0, 1, 17, -1, 20], dtype=torch.int32)
+    kt = torch.full((lines_total, hkv, d), 7.0, dtype=DT[dtype])
+    vt = torch.full((lines_total, hkv, d), 7.0, dtype=DT[dtype])
+    kd, vd = dev(kt), dev(vt)
+    cs = K().rope_table(dev(pos), rotary, 10000.0)
+    q = K().rope_append(dev(qkv), cs, dev(lines), kd, vd, hq, hkv, d, rotary).cpu()
+    x = qkv.double().reshape(rows, hq + 2 * hkv, d)
+
+    def rot(t):
+        r = P.rope(t[..., :rotary], pos, 10000.0)
+        return torch.cat([r, t[..., rotary:]], dim=-1)
+
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    assert rel_err(q.double().numpy(), rot(x[:, :hq]).numpy()) < tol
+    k_want, v_want = rot(x[:, hq : hq + hkv]), x[:, hq + hkv :]
+    kc, vc = kd.cpu().double(), vd.cpu().double()
+    written = set()
+    for r in range(rows):
+        l = int(lines[r])
+        if l < 0:
+            continue
+        written.add(l)
+        assert rel_err(kc[l].numpy(), k_want[r].numpy()) < tol
+        assert rel_err(vc[l].numpy(), v_want[r].numpy()) < tol
+    for l in range(lines_total):
+        if l not in written:
+            assert (kc[l] == 7.0).all() and (vc[l] == 7.0).all(), f"line {l} was written by no row"
+
+
+@pytest.mark.parametrize("xdt,wdt,ydt", [("float32", "float32", "float32"), ("float32", "bfloat16", "bfloat16"),
+                                          ("bfloat16", "bfloat16", "bfloat16"), ("bfloat16", "float32", "float32")])
+@pytest.mark.parametrize("width", [24, 100, 2304, 5000])
+def test_rmsnorm(xdt, wdt, ydt, width):
+    x = rnd(7, width, seed=3, dtype=DT[xdt], scale=3.0)
+    w = rnd(width, seed=4, dtype=DT[wdt], scale=0.1)
+    for eps, offset in [(1e-6, 1.0), (1e-5, 0.0)]:
+        got = K().rmsnorm(dev(x), dev(w), eps, offset, DT[ydt]).cpu().double()
+        want = P.rms_norm(x.double(), w.double(), eps, offset)
+        assert rel_err(got.numpy(), want.numpy()) < (1e-6 if ydt == "float32" else 1e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("width", [40, 2304])
+def test_add_rmsnorm(dtype, width):
+    res = rnd(5, width, seed=5, scale=2.0)
+    br = rnd(5, width, seed=6, dtype=DT[dtype])
+    w1 = rnd(width, seed=7, dtype=DT[dtype], scale=0.1)
+    w2 = rnd(width, seed=8, dtype=DT[dtype], scale=0.1)
+    tol = 1e-6 if dtype == "float32" else 1e-2
+    for post, nxt in [(True, True), (True, False), (False, True), (False, False)]:
+        r = dev(res.clone())
+        h = K().add_rmsnorm(r, dev(br), (dev(w1), 1e-6, 1.0) if post else None, (dev(w2), 1e-5, 1.0) if nxt else None, DT[dtype])
+        b = P.rms_norm(br.double(), w1.double(), 1e-6) if post else br.double()
+        want_r = res.double() + b
+        assert rel_err(r.cpu().double().numpy(), want_r.numpy()) < 1e-6
+        if nxt:
+            assert rel_err(h.cpu().double().numpy(), P.rms_norm(want_r, w2.double(), 1e-5).numpy()) < tol
+        else:
+            assert h is None
+
+
+@pytest.mark.parametrize("m", [1, 3, 64, 65, 130])
+@pytest.mark.parametrize("n,k", [(8, 8), (100, 96), (1000, 520), (72, 17)])
+def test_gemm_f32(m, n, k):
+    a, w = rnd(m, k, seed=9), rnd(n, k, seed=10)
+    got = K().gemm(dev(a), dev(w)).cpu().double()
+    want = a.double() @ w.double().T
+    assert rel_err(got.numpy(), want.numpy()) < 2e-6
+    got = K().gemm(dev(a), dev(w), softcap=3.0).cpu().double()
+    assert rel_err(got.numpy(), (3.0 * torch.tanh(want / 3.0)).numpy()) < 2e-6
+
+
+def test_gemm_f32_does_not_depend_on_the_batch():
+    a, w = rnd(70, 200, seed=11), rnd(90, 200, seed=12)
+    whole = K().gemm(dev(a), dev(w)).cpu()
+    alone = K().gemm(dev(a[33:34]), dev(w)).cpu()
+    assert torch.equal(whole[33:34], alone)
+
+
+@pytest.mark.parametrize("m", [1, 5, 16, 17, 33, 64, 65, 200, 300])
+@pytest.mark.parametrize("n,k", [(8, 8), (72, 32), (1000, 96), (2304, 520), (520, 2304), (136, 4104)])
+def test_gemm_bf16(m, n, k):
+    a, w = rnd(m, k, seed=13, dtype=torch.bfloat16), rnd(n, k, seed=14, dtype=torch.bfloat16)
+    want = a.double() @ w.double().T
+    got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+    assert rel_err(got.numpy(), want.numpy()) < 2e-5, "float32 output of bfloat16 inputs"
+    got = K().gemm(dev(a), dev(w)).cpu().double()
+    assert rel_err(got.numpy(), want.numpy()) < 1e-2
+    got = K().gemm(dev(a), dev(w), out_dtype=torch.float32, softcap=30.0).cpu().double()
+    assert rel_err(got.numpy(), (30.0 * torch.tanh(want / 30.0)).numpy()) < 2e-5
+
+
+def test_gemm_bf16_refuses_what_it_cannot_take():
+    a, w = rnd(4, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
+    with pytest.raises(K().KernelError, match="multiple of 8"):
+        K().gemm(dev(a), dev(w))
+
+
+def test_gemm_bf16_small_rows_do_not_depend_on_the_batch():
+    a, w = rnd(40, 2304, seed=15, dtype=torch.bfloat16), rnd(520, 2304, seed=16, dtype=torch.bfloat16)
+    whole = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu()
+    for r in (0, 17, 39):
+        alone = K().gemm(dev(a[r : r + 1]), dev(w), out_dtype=torch.float32).cpu()
+        assert torch.equal(whole[r : r + 1], alone)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+def test_glu(dtype, act):
+    x = rnd(6, 2 * 50, seed=17, dtype=DT[dtype], scale=2.0)
+    got = K().glu(dev(x), act).cpu().double()
+    g, u = x.double()[:, :50], x.double()[:, 50:]
+    want = (P.gelu_tanh(g) if act == "gelu_tanh" else g * torch.sigmoid(g)) * u
+    assert rel_err(got.numpy(), want.numpy()) < (1e-6 if dtype == "float32" else 1e-2)
+
+
+# ------------------------------------------------------------------------------------------
+def paged_reference(q, k_table, v_table, block_table, row_entry, row_count, page, window, scale, cap):
+    """Row by row in 64-bit, as crates/kapel-ref/src/paged.rs:28-92."""
+    rows, hq, d = q.shape
+    hkv = k_table.shape[-2]
+    group = hq // hkv
+    kt, vt = k_table.double().reshape(-1, hkv, d), v_table.double().reshape(-1, hkv, d)
+    out = torch.zeros(rows, hq, d, dtype=torch.float64)
+    for r in range(rows):
+        e, c = int(row_entry[r]), int(row_count[r])
+        first = max(0, c - window) if window else 0
+        if c <= first:
+            continue
+        lines = [int(block_table[e, j // page]) * page + j % page for j in range(first, c)]
+        for h in range(hq):
+            keys, vals = kt[lines, h // group], vt[lines, h // group]
+            s = scale * (keys @ q[r, h].double())
+            if cap:
+                s = cap * torch.tanh(s / cap)
+            p = torch.exp(s - s.max())
+            out[r, h] = (p / p.sum()) @ vals
+    return out
+
+
+def make_paged_case(dtype, hq, hkv, d, lengths, q_lens, page=16, seed=0, n_pages=None):
+    """Sequences of `lengths` already in a scrambled paged cache; the last q_lens[i] positions of
+    sequence i are this step's query rows."""
+    g = torch.Generator().manual_seed(seed)
+    need = sum(-(-n // page) for n in lengths)
+    n_pages = n_pages or need + 3
+    perm = torch.randperm(n_pages, generator=g).tolist()
+    width = max(-(-n // page) for n in lengths)
+    bt = torch.full((len(lengths), width), -1, dtype=torch.int32)
+    k_table = torch.randn(n_pages, page, hkv, d, generator=g).to(DT[dtype])
+    v_table = torch.randn(n_pages, page, hkv, d, generator=g).to(DT[dtype])
+    for i, n in enumerate(lengths):
+        for p in range(-(-n // page)):
+            bt[i, p] = perm.pop()
+    row_entry, row_count = [], []
+    for i, (n, ql) in enumerate(zip(lengths, q_lens)):
+        for c in range(n - ql + 1, n + 1):
+            row_entry.append(i)
+            row_count.append(c)
+    q = torch.randn(len(row_entry), hq, d, generator=g).to(DT[dtype])
+    return q, k_table, v_table, bt, torch.tensor(row_entry, dtype=torch.int32), torch.tensor(row_count, dtype=torch.int32)
+
+
+def run_rows(q, kt, vt, bt, re, rc, page, window, scale, cap):
+    from kapel_b200.engine.batch import _chunks_touched
+
+    slots = _chunks_touched(rc.numpy(), window, K().attention_chunk())
+    return K().paged_attention_rows(dev(q), dev(kt), dev(vt), dev(bt), dev(re), dev(rc), page, window, scale, cap, slots).cpu()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (12, 1, 64), (8, 4, 128), (2, 1, 256), (9, 1, 80)])
+@pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0)])
+def test_paged_attention_rows(dtype, hq, hkv, d, window, cap):
+    lengths, q_lens = [1, 37, 300, 700], [1, 5, 1, 33]
+    q, kt, vt, bt, re, rc = make_paged_case(dtype, hq, hkv, d, lengths, q_lens, seed=hq * 100 + d)
+    scale = 1.0 / math.sqrt(d * 1.5)
+    got = run_rows(q, kt, vt, bt, re, rc, 16, window, scale, cap).double()
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
+    assert rel_err(got.numpy(), want.numpy()) < (1e-5 if dtype == "float32" else 1.5e-2)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_paged_attention_far_key_and_window_edge(dtype):
+    """One key among hundreds is made to stand out, first far away, then exactly at the window's
+    edge, then one position beyond it: the output must follow that key's value, then not."""
+    hq, hkv, d, n, page, window = 2, 1, 32, 600, 16, 128
+    q, kt, vt, bt, re, rc = make_paged_case(dtype, hq, hkv, d, [n], [1], seed=3)
+    q = q * 0.05
+    scale = 1.0
+
+    def plant(pos):
+        kt2, vt2 = kt.clone(), vt.clone()
+        line = int(bt[0, pos // page]) * page + pos % page
+        kt2.reshape(-1, hkv, d)[line, 0] = (q[0, 0].float() * 400).to(kt.dtype)      # a score far above the rest
+        vt2.reshape(-1, hkv, d)[line, 0] = 5.0
+        return kt2, vt2
+
+    tol = 1e-5 if dtype == "float32" else 1.5e-2
+    for pos, win, seen in [(3, None, True), (n - window, window, True), (n - window - 1, window, False)]:
+        kt2, vt2 = plant(pos)
+        got = run_rows(q, kt2, vt2, bt, re, rc, page, win, scale, None).double()
+        want = paged_reference(q, kt2, vt2, bt, re, rc, page, win, scale, None)
+        assert rel_err(got.numpy(), want.numpy()) < tol
+        assert (abs(float(got[0, 0].mean()) - 5.0) < 0.1) == seen
+
+
+def test_paged_attention_row_that_sees_nothing_gives_zeros():
+    q, kt, vt, bt, re, rc = make_paged_case("float32", 4, 2, 16, [20], [2], seed=4)
+    rc[0] = 0
+    got = run_rows(q, kt, vt, bt, re, rc, 16, None, 0.25, None)
+    assert (got[0] == 0).all() and torch.isfinite(got).all()
+
+
+# ------------------------------------------------------------------------------------------
+def test_sample_greedy_rules():
+    nan = float("nan")
+    logits = torch.tensor([[1.0, 5.0, 5.0, 2.0], [nan, -3.0, nan, -3.0], [nan, nan, nan, nan], [-1e30, -2e30, -1e30, -3e30]])
+    got = K().sample(dev(logits)).cpu().tolist()
+    assert got == [P.plain_argmax(row) for row in logits.tolist()] == [1, 1, 0, 0]
+    big = rnd(3, 256000, seed=20)
+    big[1, 123456] = 100.0
+    big[2, 255999] = 100.0
+    got = K().sample(dev(big)).cpu().tolist()
+    assert got == big.argmax(dim=1).tolist()
+
+
+def test_sample_temperature_follows_plain_rule_and_probabilities():
+    vocab = 1000
+    logits = rnd(1, vocab, seed=21, scale=2.0)
+    temps = torch.tensor([0.8])
+    rng = P.PlainRng(7)
+    agree = 0
+    n = 300
+    rows = logits.repeat(n, 1)
+    us = torch.tensor([rng.uniform() for _ in range(n)], dtype=torch.float32)
+    got = K().sample(dev(rows), dev(temps.repeat(n)), dev(us)).cpu().tolist()
+    want = [P.plain_choose(logits[0].double().tolist(), 0.8, float(u)) for u in us]
+    agree = sum(int(a == b) for a, b in zip(got, want))
+    assert agree >= n - 3, f"{n - agree} of {n} draws differ from the plain rule (32-bit against 64-bit sums)"
+    # draws follow the probabilities
+    small = torch.tensor([[0.0, math.log(2.0), math.log(4.0), -1e9]])
+    m = 20000
+    g = torch.Generator().manual_seed(5)
+    us = torch.rand(m, generator=g)
+    got = K().sample(dev(small.repeat(m, 1)), dev(torch.ones(m)), dev(us)).cpu()
+    freq = torch.bincount(got.long(), minlength=4).double() / m
+    assert (freq - torch.tensor([1 / 7, 2 / 7, 4 / 7, 0.0], dtype=torch.float64)).abs().max() < 0.015
+    # temperature 0 in a row of a sampled batch is greedy
+    got = K().sample(dev(small.repeat(2, 1)), dev(torch.tensor([0.0, 1.0])), dev(torch.tensor([0.99, 0.0]))).cpu().tolist()
+    assert got == [2, 0]
