@@ -13,7 +13,10 @@ int fail(const char* fmt, ...) {
     return 1;
 }
 
+static unsigned long long g_launches = 0;
+
 int check_launch(const char* what) {
+    ++g_launches;                         // every kernel launch of this library passes here once
     const cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return fail("%s: launch failed: %s", what, cudaGetErrorString(e));
     return 0;
@@ -22,6 +25,9 @@ int check_launch(const char* what) {
 }  // namespace kb
 
 extern "C" const char* kb_last_error() { return kb::g_error; }
+
+// Kernels this library has launched (or recorded into a graph under capture) so far.
+extern "C" unsigned long long kb_launch_count() { return kb::g_launches; }
 
 // The compute capability this library was built for, as major * 10 + minor.
 extern "C" int kb_built_for() { return 100; }

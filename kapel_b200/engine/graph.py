@@ -1,0 +1,134 @@
+"""Decode steps recorded once as CUDA graphs and replayed.
+
+A pass in which every request brings one token has the same kernels at the same sizes as any
+other such pass of as many rows, so it is captured once per (rows, block-table width) bucket
+and replayed with new inputs copied into the same buffers: one host-to-device copy and one
+graph launch instead of a few hundred kernel launches. Kapel does the same with its
+`record_step` / `replay_step` (crates/kapel-models/src/model.rs:1055-1255) and the row buckets of
+its engine (crates/kapel-infer/src/engine.rs:166-177). Padding rows have seen nothing and write
+nowhere (count 0, line -1), so they need no scratch pages. The cache tables never move, so a
+recording stays valid for the engine's life.
+"""
+from __future__ import annotations
+
+from typing import Dict, List, Optional, Tuple
+
+import numpy as np
+import torch
+
+from .batch import GroupBatch
+
+ROW_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
+WIDTH_STEP = 64          # block-table widths are rounded up to a multiple of this many pages
+
+
+class StaticBatch:
+    """A batch of fixed size whose inputs live in one device buffer that replays rewrite."""
+
+    def __init__(self, rows: int, width: int, n_groups: int, device, chunk: int, page_size: int):
+        self.rows = self.entries = rows
+        self.width = width
+        self.chunk = chunk
+        self.memo: Dict[object, object] = {}
+        sizes = [rows] * 6 + [rows, rows * width] * n_groups
+        self.total = sum(sizes)
+        self.host = torch.empty((self.total,), dtype=torch.int32, pin_memory=True)
+        self.dev = torch.empty((self.total,), dtype=torch.int32, device=device)
+        views, at = [], 0
+        for n in sizes:
+            views.append(self.dev[at : at + n])
+            at += n
+        self.ids, self.positions, self.row_entry, self.row_count, self.want_rows, self.slots = views[:6]
+        self.groups = [GroupBatch(views[6 + 2 * g], views[7 + 2 * g].view(rows, width)) for g in range(n_groups)]
+        self._sizes = sizes
+        self.fixed_slots = max(1, -(-(width * page_size) // chunk))
+        self.h2d_bytes = self.total * 4
+
+    def attention_slots(self, window: Optional[int]) -> int:
+        n = self.fixed_slots
+        if window:
+            n = min(n, (window - 1) // self.chunk + 2)
+        return max(1, n)
+
+    def fill(self, plan, ids) -> None:
+        """Writes a plan of at most `rows` single-token entries into the buffers; the rest are
+        padding rows."""
+        n = plan.rows
+        rows, width = self.rows, self.width
+        flat = self.host.numpy()
+        at = 0
+
+        def put(values, pad):
+            nonlocal at
+            flat[at : at + n] = values
+            flat[at + n : at + rows] = pad
+            at += rows
+
+        put(np.asarray(ids, np.int32), 0)
+        put(plan.positions, 0)
+        put(plan.row_entry, 0)
+        flat[at - rows + n : at] = np.arange(n, rows, dtype=np.int32)     # a padding row is its own entry
+        put(plan.row_count, 0)
+        put(np.arange(n, dtype=np.int32), 0)
+        flat[at - rows + n : at] = np.arange(n, rows, dtype=np.int32)     # every row is wanted
+        put(plan.slots, 0)
+        for g in plan.groups:
+            put(g.lines, -1)
+            table = flat[at : at + rows * width].reshape(rows, width)
+            table[:] = -1
+            w = g.block_table.shape[1]
+            table[:n, :w] = g.block_table
+            at += rows * width
+        self.dev.copy_(self.host, non_blocking=True)
+
+
+class DecodeGraphs:
+    def __init__(self, engine, max_rows: int):
+        self.engine = engine
+        self.max_rows = max_rows
+        self.graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, StaticBatch, torch.Tensor]] = {}
+        self.replays = 0
+        self.replayed_kernels = 0      # kernels that ran inside replays (the library counts only launches it makes itself)
+        self.pool = None
+
+    def bucket(self, rows: int, width: int) -> Optional[Tuple[int, int]]:
+        for b in ROW_BUCKETS:
+            if b >= rows:
+                return b, -(-width // WIDTH_STEP) * WIDTH_STEP
+        return None
+
+    def run(self, plan, ids) -> Optional[torch.Tensor]:
+        """Logits [rows, vocab] of a decode-only plan through a recording, or None if no bucket
+        takes it. The result is a view of the recording's output: use it before the next replay."""
+        width = max(g.block_table.shape[1] for g in plan.groups) if plan.groups else 1
+        key = self.bucket(plan.rows, width)
+        if key is None:
+            return None
+        eng = self.engine
+        if key not in self.graphs:
+            static = StaticBatch(key[0], key[1], len(plan.groups), eng.device, eng.chunk, eng.cache.page_size)
+            static.fill(plan, ids)
+            # Once eagerly on a side stream (kernels set their attributes, the allocator warms up), then the capture.
+            side = torch.cuda.Stream()
+            side.wait_stream(torch.cuda.current_stream())
+            with torch.cuda.stream(side):
+                eng.model.forward(static, eng.cache)
+            torch.cuda.current_stream().wait_stream(side)
+            graph = torch.cuda.CUDAGraph()
+            static.memo.clear()
+            from .. import kernels as K
+
+            before = K.launch_count()
+            with torch.cuda.graph(graph, pool=self.pool):
+                out = eng.model.forward(static, eng.cache)
+            static.kernels = K.launch_count() - before
+            if self.pool is None:
+                self.pool = graph.pool()
+            self.graphs[key] = (graph, static, out)
+        graph, static, out = self.graphs[key]
+        static.fill(plan, ids)
+        graph.replay()
+        self.replays += 1
+        self.replayed_kernels += static.kernels
+        eng.last_h2d_bytes = static.h2d_bytes
+        return out[: plan.rows]

@@ -37,6 +37,10 @@ class ModelParts:
         self.final_norm.load(tensors)
         self.head.load(tensors)
 
+    def graph_safe(self) -> bool:
+        """Whether every part only enqueues kernels, so that a decode step can be recorded."""
+        return all(p.graph_safe for p in (self.embedding, self.final_norm, self.head, *self.blocks))
+
     def cache_needs(self) -> Dict[int, CacheNeeds]:
         """What each cache-owning layer keeps: layers named as `cache_of` in the schedule."""
         owners = sorted({e.cache_of for e in self.spec.schedule})

@@ -1,0 +1,298 @@
+"""The scheduler above the step function: admit, cut prompts into portions, decode, finish, free.
+
+The policy is Kapel's `Engine` (crates/kapel-infer/src/engine.rs):
+  * admission is first come, first served, while the pages that running prompts will still take,
+    plus the newcomer's, plus a reserve, fit what is free; alone, a request takes what there is
+    (:355-388);
+  * a pass holds one token of every decoding request first, then portions of prompts in
+    admission order until `max_pass_tokens` is spent (:402-421);
+  * a request whose pending tokens all ran in the pass produces a token (:575-580);
+  * it ends at an end-of-sequence token (unless `ignore_eos`), at a stop sequence, at
+    `max_tokens`, or on an error (:642-660);
+  * when pages run out the request admitted last is suspended: its pages go back, it waits at
+    the front of the queue, and its prompt and generated tokens are computed again later; a
+    request that is alone and still does not fit ends with `CacheFull` (:431-457,392-399);
+  * if a pass fails every running request ends (:463-476).
+Pages are counted per layer group: a pass fits when every group has the pages it needs.
+
+The scheduler needs of its engine only `cache` (a CacheManager), `step(entries)`, `end(id)` and
+`vocab_size`, so its decisions are tested on the CPU with a stand-in.
+"""
+from __future__ import annotations
+
+import itertools
+from collections import deque
+from dataclasses import dataclass, field
+from typing import Deque, Dict, List, Optional, Sequence
+
+import numpy as np
+
+from ..cache import CacheFull
+from ..sampling import Sampler, Sampling
+from .step import StepEntry
+
+
+@dataclass
+class EngineOptions:
+    """Kapel's `EngineOptions` (engine.rs:36-64) without the growing cache and prefix sharing."""
+
+    max_pass_tokens: int = 2048
+    max_sequences: int = 256
+    reserve: float = 0.0
+
+
+@dataclass
+class Request:
+    """Kapel's `Request` (crates/kapel-infer/src/generate.rs:72-123), for token ids."""
+
+    prompt: Sequence[int]
+    sampling: Sampling = field(default_factory=Sampling)
+    max_tokens: int = 256
+    eos_ids: Sequence[int] = ()
+    ignore_eos: bool = False
+    stop: Sequence[Sequence[int]] = ()          # token sequences that end the answer
+
+
+@dataclass
+class Event:
+    id: int
+    token: Optional[int]
+    finish: Optional[str] = None                # "eos", "stop", "length", "error"
+    error: Optional[str] = None
+
+
+@dataclass
+class EngineStats:
+    """Kapel's `EngineStats` (engine.rs:104-121), pages per layer group."""
+
+    waiting: int = 0
+    running: int = 0
+    pages: List[int] = field(default_factory=list)
+    free_pages: List[int] = field(default_factory=list)
+    preemptions: int = 0
+    passes: int = 0
+    recorded_passes: int = 0
+    released_pages: int = 0
+
+
+class _Entry:
+    __slots__ = ("request", "sequence", "prompt_len", "sampler", "running", "generated")
+
+    def __init__(self, request: Request):
+        self.request = request
+        self.sequence: List[int] = [int(t) for t in request.prompt]
+        self.prompt_len = len(self.sequence)
+        self.sampler = Sampler(request.sampling)
+        self.running = False
+        self.generated = 0
+
+
+class Scheduler:
+    def __init__(self, engine, options: Optional[EngineOptions] = None):
+        self.engine = engine
+        self.cache = engine.cache
+        self.options = options or EngineOptions()
+        self.entries: Dict[int, _Entry] = {}
+        self.waiting: Deque[int] = deque()
+        self.running: List[int] = []
+        self._ids = itertools.count()
+        self.preemptions = 0
+        self.passes = 0
+
+    # ------------------------------------------------------------------ requests
+    def add(self, request: Request) -> int:
+        if len(request.prompt) == 0:
+            raise ValueError("a request needs at least one prompt token")
+        vocab = self.engine.vocab_size
+        for t in request.prompt:
+            if not 0 <= int(t) < vocab:
+                raise ValueError(f"prompt token {t} is outside the vocabulary (0..{vocab - 1})")
+        rid = next(self._ids)
+        self.entries[rid] = _Entry(request)
+        self.waiting.append(rid)
+        return rid
+
+    def cancel(self, rid: int) -> None:
+        """Ends a request wherever it is; its pages go back (engine.rs:308-318)."""
+        entry = self.entries.pop(rid, None)
+        if entry is None:
+            return
+        if entry.running:
+            self.running.remove(rid)
+            self.engine.end(rid)
+        else:
+            try:
+                self.waiting.remove(rid)
+            except ValueError:
+                pass
+
+    def has_work(self) -> bool:
+        return bool(self.waiting or self.running)
+
+    def stats(self) -> EngineStats:
+        return EngineStats(
+            waiting=len(self.waiting), running=len(self.running), pages=self.cache.total_pages(),
+            free_pages=self.cache.free_pages(), preemptions=self.preemptions, passes=self.passes,
+            recorded_passes=getattr(self.engine, "recorded_passes", 0), released_pages=self.cache.released_pages,
+        )
+
+    # ------------------------------------------------------------------ arithmetic
+    def _cached(self, rid: int) -> int:
+        return self.cache.length(rid) if rid in self.cache else 0
+
+    def _pending(self, rid: int) -> int:
+        return len(self.entries[rid].sequence) - self._cached(rid)
+
+    def _peak_need(self, rid: int, tokens: int) -> List[int]:
+        """Pages each group must still give for `tokens` more positions of `rid`. A windowed
+        group never holds more than its window plus one pass at a time, whatever the length."""
+        need = self.cache.pages_needed(rid, tokens)
+        page = self.cache.page_size
+        for g, group in enumerate(self.cache.groups):
+            if group.window is not None:
+                cap = -(-(group.window + self.options.max_pass_tokens) // page) + 1
+                need[g] = min(need[g], cap)
+        return need
+
+    # ------------------------------------------------------------------ admission
+    def _admit(self) -> List[Event]:
+        events: List[Event] = []
+        n_groups = len(self.cache.groups)
+        promised = [0] * n_groups
+        for rid in self.running:
+            for g, n in enumerate(self._peak_need(rid, self._pending(rid) + 1)):
+                promised[g] += n
+        total = self.cache.total_pages()
+        margin = [int(np.ceil(self.options.reserve * t)) for t in total]
+        while self.waiting and len(self.running) < self.options.max_sequences and self.cache.free_slots() > 0:
+            rid = self.waiting[0]
+            entry = self.entries[rid]
+            needed = self._peak_need(rid, len(entry.sequence) + 1)
+            free = self.cache.free_pages()
+            fits = all(promised[g] + needed[g] + margin[g] <= free[g] for g in range(n_groups))
+            alone = not self.running and all(needed[g] <= free[g] for g in range(n_groups))
+            if not (fits or alone):
+                if not self.running and any(needed[g] > total[g] for g in range(n_groups)):
+                    # It could never run, even alone in an empty cache: end it instead of waiting forever.
+                    self.waiting.popleft()
+                    del self.entries[rid]
+                    g = next(g for g in range(n_groups) if needed[g] > total[g])
+                    events.append(Event(rid, None, "error", str(CacheFull(needed[g], total[g], self.cache.groups[g].name))))
+                    continue
+                break
+            for g in range(n_groups):
+                promised[g] += needed[g]
+            self.waiting.popleft()
+            self.cache.add_sequence(rid)
+            entry.running = True
+            self.running.append(rid)
+        return events
+
+    def _suspend_last(self) -> None:
+        rid = self.running.pop()
+        self.entries[rid].running = False
+        self.engine.end(rid)
+        self.waiting.appendleft(rid)
+        self.preemptions += 1
+
+    def _plan(self) -> List[tuple]:
+        budget = max(1, self.options.max_pass_tokens)
+        out = []
+        for rid in self.running:
+            if self._pending(rid) == 1:
+                out.append((rid, 1))
+                budget = max(0, budget - 1)
+        for rid in self.running:
+            pending = self._pending(rid)
+            if pending > 1 and budget > 0:
+                count = min(pending, budget)
+                out.append((rid, count))
+                budget -= count
+        return out
+
+    # ------------------------------------------------------------------ one pass
+    def step(self) -> List[Event]:
+        """One pass of the model: a token of every decoding request and portions of prompts.
+        Returns the tokens it gave and the requests that ended; nothing when there is no work."""
+        events = self._admit()
+        while True:
+            pass_ = self._plan()
+            need = [0] * len(self.cache.groups)
+            for rid, count in pass_:
+                for g, n in enumerate(self.cache.pages_needed(rid, count)):
+                    need[g] += n
+            free = self.cache.free_pages()
+            short = [g for g in range(len(need)) if need[g] > free[g]]
+            if not short:
+                break
+            if len(self.running) == 1:
+                rid = self.running[0]
+                g = short[0]
+                error = CacheFull(need[g], free[g], self.cache.groups[g].name)
+                self.cancel(rid)
+                events.append(Event(rid, None, "error", str(error)))
+                return events
+            self._suspend_last()
+        if not pass_:
+            return events
+        producing = [rid for rid, count in pass_ if count == self._pending(rid)]
+        entries = []
+        for rid, count in pass_:
+            entry = self.entries[rid]
+            at = self._cached(rid)
+            tokens = entry.sequence[at : at + count]
+            entries.append(StepEntry(rid, tokens, [count - 1] if count == self._pending(rid) else []))
+        try:
+            logits = self.engine.step(entries)
+            self.passes += 1
+            tokens = self._choose(logits, producing)
+        except Exception as e:                      # the pass failed: every running request ends
+            for rid in list(self.running):
+                self.cancel(rid)
+                events.append(Event(rid, None, "error", f"{type(e).__name__}: {e}"))
+            return events
+        for rid, token in zip(producing, tokens):
+            entry = self.entries[rid]
+            entry.sequence.append(int(token))
+            entry.generated += 1
+            finish = self._finish_reason(entry, int(token))
+            events.append(Event(rid, int(token), finish))
+            if finish is not None:
+                self.cancel(rid)
+        return events
+
+    def _finish_reason(self, entry: _Entry, token: int) -> Optional[str]:
+        req = entry.request
+        if not req.ignore_eos and token in req.eos_ids:
+            return "eos"
+        generated = entry.sequence[entry.prompt_len:]
+        for stop in req.stop:
+            n = len(stop)
+            if n and len(generated) >= n and list(generated[-n:]) == [int(t) for t in stop]:
+                return "stop"
+        if entry.generated >= req.max_tokens:
+            return "length"
+        return None
+
+    # ------------------------------------------------------------------ choosing tokens
+    def _choose(self, logits, producing: List[int]) -> List[int]:
+        """One token per producing request: on the device when only the logits decide (greedy
+        without penalties, or a plain temperature; engine.rs:584-597), else on the host in
+        64-bit with the request's own sampler (engine.rs:599-616)."""
+        if not producing:
+            return []
+        entries = [self.entries[rid] for rid in producing]
+        if getattr(logits, "is_cuda", False) and all(e.request.sampling.on_device() for e in entries):
+            import torch
+
+            from .. import kernels as K
+
+            if all(e.request.sampling.is_greedy() for e in entries):
+                return K.sample(logits).cpu().tolist()
+            temps = [max(0.0, e.request.sampling.temperature) for e in entries]
+            us = [e.sampler.uniform() if t > 0 else 0.0 for e, t in zip(entries, temps)]
+            host = torch.tensor([temps, us], dtype=torch.float32).pin_memory()
+            dev = host.to(logits.device, non_blocking=True)
+            return K.sample(logits, dev[0], dev[1]).cpu().tolist()
+        rows = np.asarray(logits.detach().cpu().numpy() if hasattr(logits, "detach") else logits, dtype=np.float64)
+        return [e.sampler.choose(rows[i], e.sequence, e.prompt_len) for i, e in enumerate(entries)]

@@ -66,7 +66,8 @@ class Engine:
     """
 
     def __init__(self, config, tensors, dtype="bfloat16", max_tokens: int = 8192, max_sequences: int = 64,
-                 device: Optional[torch.device] = None, pages: Optional[int] = None, raw_config: Optional[dict] = None):
+                 device: Optional[torch.device] = None, pages: Optional[int] = None, raw_config: Optional[dict] = None,
+                 graphs: bool = True):
         self.device = device or require_device()
         self.dtype = parse_dtype(dtype)
         self.config = config
@@ -85,6 +86,9 @@ class Engine:
         self.chunk = K.attention_chunk()
         self.steps = 0
         self.last_h2d_bytes = 0
+        from .graph import DecodeGraphs
+
+        self.graphs = DecodeGraphs(self, max_sequences) if (graphs and self.model.graph_safe()) else None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -165,10 +169,15 @@ class Engine:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
         plan, ids, want_rows = self.plan(entries)
         try:
-            batch = StepBatch(plan, ids, want_rows, self.device, self.chunk)
-            self.last_h2d_bytes = batch.h2d_bytes
             self._clear_fresh_state(plan)
-            logits = self.model.forward(batch, self.cache)
+            logits = None
+            # A pass of single tokens whose logits are all wanted goes through a recording.
+            if self.graphs is not None and plan.rows == len(entries) and len(want_rows) == plan.rows:
+                logits = self.graphs.run(plan, ids)
+            if logits is None:
+                batch = StepBatch(plan, ids, want_rows, self.device, self.chunk)
+                self.last_h2d_bytes = batch.h2d_bytes
+                logits = self.model.forward(batch, self.cache)
         except Exception:
             self.cache.abort(plan)
             raise
@@ -182,6 +191,10 @@ class Engine:
         slots = torch.as_tensor(plan.slots[plan.fresh], dtype=torch.long, device=self.device)
         for table in self.cache.states.values():
             table.index_fill_(0, slots, 0)
+
+    @property
+    def recorded_passes(self) -> int:
+        return self.graphs.replays if self.graphs is not None else 0
 
     def end(self, seq_id) -> None:
         """The request is finished: everything it holds goes back."""

@@ -39,8 +39,14 @@ def library():
                 lib.kb_last_error.restype = ctypes.c_char_p
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
+                lib.kb_launch_count.restype = ctypes.c_ulonglong
                 _lib = lib
     return _lib
+
+
+def launch_count() -> int:
+    """Kernels launched (or recorded under a graph capture) by this library so far."""
+    return int(library().kb_launch_count())
 
 
 def library_path() -> str:

@@ -17,6 +17,8 @@ from .registry import build_part
 
 
 class Attention(Part):
+    graph_safe = True
+
     @staticmethod
     def expected_tensors(spec):
         qd, kvd = spec.num_heads * spec.head_dim, spec.num_kv_heads * spec.head_dim

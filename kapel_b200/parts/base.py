@@ -16,6 +16,7 @@ and, by category:
                   forward(h, batch, cache) -> [rows, hidden] in the activation dtype
                       h: [rows, hidden]; batch: engine.batch.StepBatch; cache: LayerCache
     feed_forward  forward(h) -> [rows, hidden]
+    every part    graph_safe: bool (see `Part`)
     block         forward(x, h, batch, cache, next_norm) -> (x, h_next)
                       x: the float32 residual [rows, hidden] (updated in place);
                       h: this block's first norm already applied to x, or None;
@@ -70,6 +71,11 @@ class LayerCache:
 
 
 class Part:
+    # True when `forward` only enqueues kernels whose arguments are device tensors of the batch:
+    # such a part can be recorded into a CUDA graph. A part that reads the plan on the host (a
+    # loop over requests, say) leaves it False, and the engine then runs every step eagerly.
+    graph_safe = False
+
     @staticmethod
     def expected_tensors(spec) -> Dict[str, tuple]:
         return {}

@@ -38,6 +38,10 @@ class SandwichBlock(Part):
         self.ffn = build_part("feed_forward", spec.ffn, ctx)
         self.norms = {r: build_part("norm", spec.norms[r], ctx) for r in self.norm_roles}
 
+    @property
+    def graph_safe(self) -> bool:
+        return all(p.graph_safe for p in (self.mixer, self.ffn, *self.norms.values()))
+
     def load(self, tensors):
         self.mixer.load(tensors)
         self.ffn.load(tensors)

@@ -14,6 +14,8 @@ from .base import Part, linear, matrix_for
 
 
 class Embedding(Part):
+    graph_safe = True
+
     @staticmethod
     def expected_tensors(spec):
         return {}          # the table's shape is the model's [vocab, hidden]; ModelParts adds it
@@ -32,6 +34,8 @@ class Embedding(Part):
 
 
 class VocabHead(Part):
+    graph_safe = True
+
     def load(self, tensors):
         self.table = matrix_for(self.ctx, tensors[self.spec.weight])
 

@@ -9,6 +9,8 @@ from .base import Part, linear, matrix_for
 
 
 class GatedMLP(Part):
+    graph_safe = True
+
     @staticmethod
     def expected_tensors(spec):
         w = spec.weights

@@ -7,6 +7,8 @@ from .base import Part
 
 
 class RMSNorm(Part):
+    graph_safe = True
+
     @staticmethod
     def expected_tensors(spec):
         return {spec.weight: (spec.width,)}

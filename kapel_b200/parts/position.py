@@ -11,6 +11,8 @@ from .base import Part
 
 
 class Rope(Part):
+    graph_safe = True
+
     def __init__(self, spec, ctx):
         super().__init__(spec, ctx)
         if spec.pairing != "half":
@@ -32,6 +34,8 @@ class Rope(Part):
 
 
 class NoPosition(Part):
+    graph_safe = True
+
     rotary_dim = 0
 
     def tables(self, batch):

@@ -1,0 +1,178 @@
+"""Generation through the entry points, the replay program, long decoding, first tokens,
+and the scheduler over the real engine with so few pages that requests are suspended."""
+import json
+import os
+import subprocess
+import sys
+
+import numpy as np
+import pytest
+import torch
+
+import plain_gemma2 as P
+from helpers import (ROOT, TINY, TOL, TraceBuilder, compare_trace, embed_scale_for, make_model_dir, plain_logits,
+                     plain_model, random_tokens, run_trace_engine, run_trace_program)
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def folders():
+    return {name: make_model_dir(raw, seed) for name, (raw, seed) in TINY.items()}
+
+
+def plain_greedy(folder, raw, prompt, n, dtype="float32"):
+    cfg, w = plain_model(folder)
+    seq = list(prompt)
+    margins = []
+    for _ in range(n):
+        row = P.forward(cfg, w, seq, embed_scale=embed_scale_for(raw, dtype))[-1].numpy()
+        order = np.argsort(row)
+        margins.append(float(row[order[-1]] - row[order[-2]]))
+        seq.append(int(order[-1]))
+    return seq[len(prompt):], margins
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(folders, name):
+    """Tiny A: prompts of 5, 17, 33, 40 and 24 greedy tokens each; in 32-bit the tokens are the plain ones."""
+    import kapel_b200
+
+    raw, _ = TINY[name]
+    rng = np.random.default_rng(21)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in ([5, 17, 33, 40] if name == "A" else [1, 50, 90])]
+    model = kapel_b200.Model(str(folders[name]), device="cuda", dtype="f32", max_tokens_cached=512, max_sequences=8)
+    want = [plain_greedy(folders[name], raw, p, 24) for p in prompts]
+    for p, (tokens, margins) in zip(prompts, want):
+        got = model.generate(p, max_tokens=24)
+        assert got == tokens, f"prompt of {len(p)}: {got} != {tokens} (smallest margin {min(margins):.2e})"
+        assert list(model.generate(p, max_tokens=24, stream=True)) == tokens
+    assert model.generate_batch(prompts, max_tokens=24) == [t for t, _ in want], "together = each alone"
+    assert model.engine.recorded_passes > 0, "decode steps went through recordings"
+    # bfloat16: the same tokens as long as the plain margin is well above bfloat16's error
+    bf = kapel_b200.Model(str(folders[name]), device="cuda", dtype="bf16", max_tokens_cached=512, max_sequences=8)
+    for p, (tokens, margins) in zip(prompts, want):
+        got = bf.generate(p, max_tokens=24)
+        safe = next((i for i, m in enumerate(margins) if m < 0.05), len(margins))
+        assert got[:safe] == tokens[:safe]
+    assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
+
+
+def test_temperature_same_seed_same_tokens_and_chunked_prefill(folders):
+    """Tiny B's workload: prompts 1, 50, 90 in portions of 32 mixed with decodes, 40 steps at 0.8, seed 7."""
+    import kapel_b200
+
+    raw, _ = TINY["B"]
+    rng = np.random.default_rng(22)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (1, 50, 90)]
+    model = kapel_b200.Model(str(folders["B"]), dtype="f32", max_tokens_cached=512, max_sequences=8)
+    a = model.generate_batch(prompts, max_tokens=40, temperature=0.8, seed=7, max_pass_tokens=32)
+    b = model.generate_batch(prompts, max_tokens=40, temperature=0.8, seed=7, max_pass_tokens=32)
+    c = model.generate_batch(prompts, max_tokens=40, temperature=0.8, seed=8, max_pass_tokens=32)
+    assert a == b and a != c and all(len(x) == 40 for x in a)
+    # request i draws with seed + i: alone with that seed it gets the same tokens
+    assert model.generate(prompts[1], max_tokens=40, temperature=0.8, seed=8) == a[1]
+    # the filters run on the host with the same generator
+    d = model.generate(prompts[2], max_tokens=10, temperature=0.8, top_k=5, top_p=0.9, seed=3)
+    assert d == model.generate(prompts[2], max_tokens=10, temperature=0.8, top_k=5, top_p=0.9, seed=3)
+    assert model.generate(prompts[2], max_tokens=5, temperature=0.8, top_k=1, seed=3) == model.generate(prompts[2], max_tokens=5)
+
+
+def test_scheduler_with_few_pages_suspends_and_still_gives_each_its_tokens(folders):
+    import kapel_b200
+    from kapel_b200.engine.scheduler import Request
+
+    raw, _ = TINY["A"]
+    rng = np.random.default_rng(23)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (40, 33, 17, 5, 28)]
+    n_new = 20
+    alone = kapel_b200.Model(str(folders["A"]), dtype="f32", max_tokens_cached=256, max_sequences=2)
+    want = [alone.generate(p, max_tokens=n_new) for p in prompts]
+    pages = -(-(40 + n_new + 1) // 16) + 3
+    small = kapel_b200.Model(str(folders["A"]), dtype="f32", max_tokens_cached=pages * 16, max_sequences=8)
+    sched = small.scheduler(max_pass_tokens=24)
+    ids = [sched.add(Request(p, max_tokens=n_new)) for p in prompts]
+    out = {r: [] for r in ids}
+    while sched.has_work():
+        for ev in sched.step():
+            assert ev.finish != "error", ev.error
+            if ev.token is not None:
+                out[ev.id].append(ev.token)
+    assert [out[r] for r in ids] == want
+    st = sched.stats()
+    assert st.preemptions > 0 and st.free_pages == st.pages
+    small.engine.cache.check()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding_and_first_tokens(folders, dtype):
+    """A one-token prompt, then every token one by one up to the model's limit: first tokens of a
+    sequence, page edges, the window passing pages, recordings replayed throughout."""
+    from kapel_b200.engine import Engine
+
+    for name in ("A", "B"):
+        raw, _ = TINY[name]
+        n = raw["max_position_embeddings"]
+        toks = random_tokens(np.random.default_rng(24), n, raw["vocab_size"])
+        plain = {"s": plain_logits(folders[name], toks, embed_scale=embed_scale_for(raw, dtype))}
+        engine = Engine.from_dir(folders[name], dtype=dtype, max_tokens=n, max_sequences=2)
+        tb = TraceBuilder()
+        for i, t in enumerate(toks):
+            tb.step([("s", [t], [0])], end=["s"] if i == n - 1 else [])
+        worst = compare_trace(run_trace_engine(engine, tb.steps), tb, plain, TOL[dtype], f"long {name} {dtype}")
+        print(f"long decode {name} {dtype}: {n} tokens, worst {worst:.2e}")
+        assert engine.recorded_passes == n
+        with pytest.raises(ValueError, match="allows"):
+            engine.step([("t", toks + [1], [0])])
+        assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_recorded_step_equals_eager_step_bit_for_bit(folders):
+    from kapel_b200.engine import Engine
+
+    raw, _ = TINY["B"]
+    toks = random_tokens(np.random.default_rng(25), 60, raw["vocab_size"])
+    outs = []
+    for graphs in (True, False):
+        engine = Engine.from_dir(folders["B"], dtype="bfloat16", max_tokens=128, max_sequences=4, graphs=graphs)
+        tb = TraceBuilder()
+        tb.step([("a", toks[:30], [29]), ("b", toks[:7], [6])])
+        for i in range(30, 60):
+            tb.step([("a", [toks[i]], [0]), ("b", [toks[i - 23]], [0])])
+        res = run_trace_engine(engine, tb.steps)
+        outs.append(np.concatenate([res[s] for s in sorted(res)]))
+        assert (engine.recorded_passes > 0) == graphs
+    assert np.array_equal(outs[0], outs[1])
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_replay_program(folders, dtype):
+    """bin/trace_run as a program: whole, then portions beside decoded tokens, pages used again."""
+    raw, _ = TINY["A"]
+    rng = np.random.default_rng(26)
+    reqs = {f"r{i}": random_tokens(rng, n, raw["vocab_size"]) for i, n in enumerate([40, 17, 33, 64, 50])}
+    plain = {r: plain_logits(folders["A"], t, embed_scale=embed_scale_for(raw, dtype)) for r, t in reqs.items()}
+    tb = TraceBuilder()
+    tb.step([("r0", reqs["r0"], range(40))], end=["r0"])
+    tb.step([("r1", reqs["r1"][:9], [8]), ("r2", reqs["r2"][:2], [0, 1])])
+    tb.step([("r1", reqs["r1"][9:10], [0]), ("r2", reqs["r2"][2:20], [17]), ("r3", reqs["r3"][:33], [])])
+    tb.step([("r3", reqs["r3"][33:], [30])])                     # r1 and r2 are left out of this step
+    tb.step([("r1", reqs["r1"][10:], [6]), ("r2", reqs["r2"][20:], [12])], end=["r1", "r2", "r3"])
+    tb.step([("r4", reqs["r4"], [0, 49])], end=["r4"])
+    res = run_trace_program(folders["A"], dtype, tb.steps, max_tokens=192)
+    compare_trace(res, tb, plain, TOL[dtype], f"program {dtype}")
+    assert 3 in res and res[3].shape == (1, raw["vocab_size"])
+
+
+def test_command_line(folders):
+    raw, _ = TINY["A"]
+    prompt = random_tokens(np.random.default_rng(27), 12, raw["vocab_size"])
+    want, _ = plain_greedy(folders["A"], raw, prompt, 8)
+    cmd = [sys.executable, "-m", "kapel_b200", "run", str(folders["A"]), "--tokens", ",".join(map(str, prompt)),
+           "--max-tokens", "8", "--greedy", "--dtype", "f32", "--stats"]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=str(ROOT), timeout=600)
+    assert r.returncode == 0, r.stderr
+    assert [int(t) for t in r.stdout.strip().splitlines()[-1].split(",")] == want
+    assert "tokens/s" in r.stderr
+    r = subprocess.run(cmd[:5] + ["--quantize", "int8", "--tokens", "1"], capture_output=True, text=True, cwd=str(ROOT), timeout=600)
+    assert r.returncode == 1 and "quantized" in r.stderr
