@@ -341,3 +341,55 @@ extern "C" int kb_gemm_bf16(void* c, int c_dt, const void* a, const void* w, int
     tile_kernel<<<grid, 256, smem, s>>>(ap, wp, c, c_dt, m, n, k, epilogue, cap);
     return check_launch("gemm_bf16 tile");
 }
+
+// ---------------------------------------------------------------------------------------
+// The product for callers that cannot allocate (declared and described in no_alloc.h; no
+// counterpart in smallbard/kapel). The split-K partial sums live in this array, which is part
+// of the library's image on every device that loads it.
+#include "no_alloc.h"
+#include <mutex>
+
+static __device__ __align__(256) float g_no_alloc_scratch[KB_NO_ALLOC_SCRATCH_FLOATS];
+
+namespace kb {
+
+constexpr int NO_ALLOC_MAX_DEVICES = 64;
+static float* g_no_alloc_ptr[NO_ALLOC_MAX_DEVICES] = {};
+static std::mutex g_no_alloc_mutex;
+
+// The device address of the scratch array on the current device. In host code the array's
+// name is only a handle for the runtime, not an address a kernel could use; the address comes
+// from cudaGetSymbolAddress, once per device, with that device current.
+static int no_alloc_scratch(float** out) {
+    int dev = -1;
+    cudaError_t e = cudaGetDevice(&dev);
+    if (e != cudaSuccess) return fail("gemm_bf16_no_alloc: no current device: %s", cudaGetErrorString(e));
+    if (dev < 0 || dev >= NO_ALLOC_MAX_DEVICES) return fail("gemm_bf16_no_alloc: device %d is beyond the %d this entry point keeps addresses for", dev, NO_ALLOC_MAX_DEVICES);
+    std::lock_guard<std::mutex> lock(g_no_alloc_mutex);
+    if (g_no_alloc_ptr[dev] == nullptr) {
+        void* p = nullptr;
+        e = cudaGetSymbolAddress(&p, g_no_alloc_scratch);
+        if (e != cudaSuccess || p == nullptr)
+            return fail("gemm_bf16_no_alloc: cannot find the built-in scratch array on device %d: %s", dev, cudaGetErrorString(e));
+        g_no_alloc_ptr[dev] = static_cast<float*>(p);
+    }
+    *out = g_no_alloc_ptr[dev];
+    return 0;
+}
+
+}  // namespace kb
+
+extern "C" int kb_gemm_bf16_no_alloc(void* c, int c_dt, const void* a, const void* w, int m, int n, int k, int epilogue,
+                                     float cap, void* stream) {
+    KB_REQUIRE(m >= 0 && n > 0 && k > 0, "gemm_bf16_no_alloc: m %d, n %d, k %d", m, n, k);
+    KB_REQUIRE(m <= 64, "gemm_bf16_no_alloc: m = %d; this entry point takes at most 64 rows", m);
+    const long long need = kb_gemm_bf16_scratch_floats(m, n, k);
+    KB_REQUIRE(need <= (long long)KB_NO_ALLOC_SCRATCH_FLOATS,
+               "gemm_bf16_no_alloc: [%d, %d] x [%d, %d] needs %lld scratch values; the built-in array holds %d", m, k, n, k,
+               need, KB_NO_ALLOC_SCRATCH_FLOATS);
+    float* scratch = nullptr;
+    if (int e = no_alloc_scratch(&scratch)) return e;
+    // Nothing has to start at zero: each split writes all m x n of its partial sums before the
+    // reduction reads them, and the reduction reads nothing else.
+    return kb_gemm_bf16(c, c_dt, a, w, m, n, k, epilogue, cap, scratch, stream);
+}
