@@ -130,6 +130,40 @@ def prefill_flops(cfg, layers, tokens):
     return gemm + att
 
 
+def breakdown(model, batch, tokens) -> int:
+    """Where a step's time goes: each kernel entry point timed with CUDA events (every call
+    synchronises, so the sums are device times, not a step time)."""
+    import torch
+
+    from kapel_b200 import kernels as K
+    from kapel_b200.engine import StepEntry
+
+    engine = model.engine
+    engine.graphs = None                                  # eager steps only
+    ids = [f"s{i}" for i in range(batch)]
+    for s in ids:                                         # history in portions of 2,048
+        for at in range(0, HISTORY, PREFILL_TOKENS):
+            engine.step([StepEntry(s, tokens(PREFILL_TOKENS), [])])
+    engine.step([StepEntry("p", tokens(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+    engine.end("p")
+    engine.step([StepEntry(s, tokens(1), [0]) for s in ids])
+    torch.cuda.synchronize()
+    K.enable_timing()
+    engine.step([StepEntry("p", tokens(PREFILL_TOKENS), [PREFILL_TOKENS - 1])])
+    engine.end("p")
+    rows = K.timing_report()
+    print(f"prefill of {PREFILL_TOKENS} tokens: {sum(r[3] for r in rows):.3f} ms in kernels")
+    for name, shape, calls, ms in rows:
+        print(f"  {ms:9.3f} ms  {calls:4d} x {name} {shape}")
+    engine.step([StepEntry(s, tokens(1), [0]) for s in ids])
+    rows = K.timing_report()
+    print(f"decode step, batch {batch}, {HISTORY} tokens of history: {sum(r[3] for r in rows):.3f} ms in kernels")
+    for name, shape, calls, ms in rows:
+        print(f"  {ms:9.3f} ms  {calls:4d} x {name} {shape}")
+    K.disable_timing()
+    return 0
+
+
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -139,6 +173,8 @@ def main() -> int:
     ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
+    ap.add_argument("--breakdown", action="store_true",
+                    help="instead of the JSON line: device time by kernel for one prefill step and one eager decode step")
     args = ap.parse_args()
 
     if args.impl == "reference":
@@ -184,6 +220,9 @@ def main() -> int:
         torch.cuda.synchronize()
         clocks.active = False
         return a.elapsed_time(b) / n
+
+    if args.breakdown:
+        return breakdown(model, args.batch, tokens)
 
     # ---------------------------------------------------------------- prefill of 2,048 tokens
     def prefill_once():

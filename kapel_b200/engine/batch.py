@@ -31,6 +31,21 @@ def _chunks_touched(row_count: np.ndarray, window: Optional[int], chunk: int) ->
     return int(((c - 1) // chunk - first // chunk + 1).max())
 
 
+DECODE_SPLIT = 256       # keys a block of the tensor-core attention kernel when every request brings few tokens
+PROMPT_SPLIT = 1024      # the same for prompt portions, when the tiles alone would leave most of the GPU idle
+
+
+def cut_tiles(q_start, q_len, tokens_per_tile: int):
+    """(tile_entry, tile_row0, tile_nq): each request's rows in runs of at most `tokens_per_tile`."""
+    entry, row0, nq = [], [], []
+    for e, (start, n) in enumerate(zip(q_start.tolist(), q_len.tolist())):
+        for at in range(0, n, tokens_per_tile):
+            entry.append(e)
+            row0.append(start + at)
+            nq.append(min(tokens_per_tile, n - at))
+    return np.asarray(entry, np.int32), np.asarray(row0, np.int32), np.asarray(nq, np.int32)
+
+
 class StepBatch:
     """Device views of a step. `memo` holds what parts share within the step (rotary tables)."""
 
@@ -72,6 +87,31 @@ class StepBatch:
         self.groups = []
         for i, shape in enumerate(table_shapes):
             self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
+
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int):
+        """How the tensor-core attention kernel cuts this step: (decode mode, (tile_entry, tile_row0,
+        tile_nq) on the device, split, slots). Decode mode when every request's rows fit 16; the
+        keys are split across blocks when the tiles alone are too few to fill the GPU."""
+        key = ("tiles", heads_per_kv, kv_heads)
+        if key not in self.memo:
+            from .. import kernels as K
+
+            plan = self.plan
+            decode = int(plan.q_len.max()) * heads_per_kv <= K.attention_mma_rows(True)
+            per_tile = max(1, K.attention_mma_rows(decode) // heads_per_kv)
+            arrays = cut_tiles(plan.q_start, plan.q_len, per_tile)
+            n = arrays[0].size
+            host = torch.from_numpy(np.concatenate(arrays)).pin_memory() if self.ids.is_cuda else torch.from_numpy(np.concatenate(arrays))
+            dev = host.to(self.ids.device, non_blocking=True)
+            tiles = (dev[:n], dev[n : 2 * n], dev[2 * n :])
+            longest = int(plan.row_count.max())
+            if decode:
+                split = DECODE_SPLIT
+            else:
+                split = 0 if n * kv_heads >= 96 else PROMPT_SPLIT
+            slots = max(1, -(-longest // split)) if split else 1
+            self.memo[key] = (decode, tiles, split, slots, host)
+        return self.memo[key][:4]
 
     def attention_slots(self, window: Optional[int]) -> int:
         """Chunk slots the row-wise attention kernel needs for a layer with this window."""

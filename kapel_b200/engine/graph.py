@@ -11,12 +11,14 @@ recording stays valid for the engine's life.
 """
 from __future__ import annotations
 
+import gc
+import weakref
 from typing import Dict, List, Optional, Tuple
 
 import numpy as np
 import torch
 
-from .batch import GroupBatch
+from .batch import DECODE_SPLIT, GroupBatch
 
 ROW_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 WIDTH_STEP = 64          # block-table widths are rounded up to a multiple of this many pages
@@ -42,6 +44,10 @@ class StaticBatch:
         self.groups = [GroupBatch(views[6 + 2 * g], views[7 + 2 * g].view(rows, width)) for g in range(n_groups)]
         self._sizes = sizes
         self.fixed_slots = max(1, -(-(width * page_size) // chunk))
+        # the tensor-core attention kernel's tiles: every row a tile of one token
+        every = torch.arange(rows, dtype=torch.int32, device=device)
+        self._tiles = (every, every.clone(), torch.ones(rows, dtype=torch.int32, device=device))
+        self._mma_slots = max(1, -(-(width * page_size) // DECODE_SPLIT))
         self.h2d_bytes = self.total * 4
 
     def attention_slots(self, window: Optional[int]) -> int:
@@ -49,6 +55,9 @@ class StaticBatch:
         if window:
             n = min(n, (window - 1) // self.chunk + 2)
         return max(1, n)
+
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int):
+        return True, self._tiles, DECODE_SPLIT, self._mma_slots
 
     def fill(self, plan, ids) -> None:
         """Writes a plan of at most `rows` single-token entries into the buffers; the rest are
@@ -84,7 +93,10 @@ class StaticBatch:
 
 class DecodeGraphs:
     def __init__(self, engine, max_rows: int):
-        self.engine = engine
+        # A weak reference: an engine and its recordings must not form a cycle, or an engine that
+        # is no longer used would be destroyed by the cyclic collector at a time of its choosing,
+        # and destroying a recording while another engine is capturing one invalidates the capture.
+        self._engine = weakref.ref(engine)
         self.max_rows = max_rows
         self.graphs: Dict[Tuple[int, int], Tuple[torch.cuda.CUDAGraph, StaticBatch, torch.Tensor]] = {}
         self.replays = 0
@@ -104,7 +116,7 @@ class DecodeGraphs:
         key = self.bucket(plan.rows, width)
         if key is None:
             return None
-        eng = self.engine
+        eng = self._engine()
         if key not in self.graphs:
             static = StaticBatch(key[0], key[1], len(plan.groups), eng.device, eng.chunk, eng.cache.page_size)
             static.fill(plan, ids)
@@ -119,8 +131,14 @@ class DecodeGraphs:
             from .. import kernels as K
 
             before = K.launch_count()
-            with torch.cuda.graph(graph, pool=self.pool):
-                out = eng.model.forward(static, eng.cache)
+            collecting = gc.isenabled()
+            gc.disable()                   # nothing may be destroyed while the stream is capturing
+            try:
+                with torch.cuda.graph(graph, pool=self.pool):
+                    out = eng.model.forward(static, eng.cache)
+            finally:
+                if collecting:
+                    gc.enable()
             static.kernels = K.launch_count() - before
             if self.pool is None:
                 self.pool = graph.pool()

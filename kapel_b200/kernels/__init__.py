@@ -37,7 +37,7 @@ def library():
                 path = ensure_built()
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
-                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats"):
+                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 _lib = lib
@@ -268,6 +268,49 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
     return out
 
 
+def attention_mma_rows(decode: bool) -> int:
+    """Rows (token, query head of one kv head's group) a tile of the tensor-core kernel holds."""
+    return int(library().kb_attention_mma_rows(int(bool(decode))))
+
+
+def attention_mma_takes(dtype, d: int, heads_per_kv: int) -> bool:
+    """Whether the tensor-core kernel takes these sizes (else the row-wise kernel does)."""
+    return dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and heads_per_kv <= 16
+
+
+def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
+                        scale: float, softcap: Optional[float], decode: bool, split: int, slots: int) -> torch.Tensor:
+    """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
+    tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
+    one request at consecutive positions. `split` > 0 cuts the keys at absolute multiples of it
+    over `slots` blocks (slots >= ceil(longest count / split))."""
+    rows, hq, d = q.shape
+    _need(q, "attention q", torch.bfloat16)
+    _need(k_table, "attention k table", torch.bfloat16)
+    _need(v_table, "attention v table", torch.bfloat16)
+    hkv = k_table.shape[-2]
+    if k_table.shape[-1] != d or v_table.shape != k_table.shape:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} against head_dim {d}")
+    n_pages = k_table.numel() // (page_size * hkv * d)
+    tile_entry, tile_row0, tile_nq = tiles
+    n_tiles = tile_entry.numel()
+    for t in tiles:
+        _need(t, "attention tiles", torch.int32, (n_tiles,))
+    _need(block_table, "attention block table", torch.int32)
+    _need(row_count, "attention row_count", torch.int32, (rows,))
+    out = torch.empty_like(q)
+    lib = library()
+    need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
+    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    _check(
+        lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
+                             _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
+                             int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
+                             _f(softcap or 0.0), int(bool(decode)), _ptr(scratch), _stream())
+    )
+    return out
+
+
 def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uniform: Optional[torch.Tensor] = None) -> torch.Tensor:
     """One token a row: the first largest logit where temperature <= 0 (or none is given), else
     a draw with the row's uniform number."""
@@ -279,3 +322,57 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
     out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
     _check(library().kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _stream()))
     return out
+
+
+# ------------------------------------------------------------------------------------------
+# Timing by kernel name, in the manner of Kapel's `Timed<B>` wrapper backend
+# (crates/kapel-cli/examples/profile.rs:17-56): every entry point above is bracketed by CUDA
+# events and its device time added up under its name and its largest argument's shape.
+_TIMED = ("embed", "rope_table", "rope_append", "glu", "cast", "gather_rows", "rmsnorm", "add_rmsnorm", "gemm",
+          "paged_attention_rows", "paged_attention_mma", "sample")
+_timing = None
+_originals = {}
+
+
+def enable_timing() -> None:
+    """Wraps the entry points with CUDA-event timers (each call then synchronises: for
+    measuring where a step's time goes, never while timing the step itself, and not with
+    recorded steps)."""
+    global _timing
+    if _timing is not None:
+        return
+    _timing = {}
+    g = globals()
+    for name in _TIMED:
+        fn = g[name]
+        _originals[name] = fn
+
+        def timed(*args, __fn=fn, __name=name, **kw):
+            shape = max((tuple(a.shape) for a in args if isinstance(a, torch.Tensor)), key=lambda s: int(torch.Size(s).numel()), default=())
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            out = __fn(*args, **kw)
+            b.record()
+            b.synchronize()
+            rec = _timing.setdefault((__name, shape), [0, 0.0])
+            rec[0] += 1
+            rec[1] += a.elapsed_time(b)
+            return out
+
+        g[name] = timed
+
+
+def disable_timing() -> None:
+    global _timing
+    for name, fn in _originals.items():
+        globals()[name] = fn
+    _originals.clear()
+    _timing = None
+
+
+def timing_report(reset: bool = True):
+    """[(name, shape, calls, total ms)] sorted by total time."""
+    rows = sorted(((n, s, c, ms) for (n, s), (c, ms) in (_timing or {}).items()), key=lambda r: -r[3])
+    if reset and _timing is not None:
+        _timing.clear()
+    return rows

@@ -60,8 +60,16 @@ class Attention(Part):
             qkv, self.position.tables(batch), group.lines, k_table, v_table,
             s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim, write_kv=cache.owns,
         )
-        y = K.paged_attention_rows(
-            q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count,
-            self.ctx.page_size, s.window, s.scale, s.softcap, batch.attention_slots(s.window),
-        )
+        heads_per_kv = s.num_heads // s.num_kv_heads
+        if K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
+            decode, tiles, split, slots = batch.attention_tiles(heads_per_kv, s.num_kv_heads)
+            y = K.paged_attention_mma(
+                q, k_table, v_table, group.block_table, batch.row_count, tiles,
+                self.ctx.page_size, s.window, s.scale, s.softcap, decode, split, slots,
+            )
+        else:                   # the 32-bit path, and sizes the tensor-core kernel does not take
+            y = K.paged_attention_rows(
+                q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count,
+                self.ctx.page_size, s.window, s.scale, s.softcap, batch.attention_slots(s.window),
+            )
         return linear(self.ctx, y.view(y.shape[0], s.num_heads * s.head_dim), self.w_o)

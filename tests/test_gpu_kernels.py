@@ -308,3 +308,65 @@ def test_sample_temperature_follows_plain_rule_and_probabilities():
     # temperature 0 in a row of a sampled batch is greedy
     got = K().sample(dev(small.repeat(2, 1)), dev(torch.tensor([0.0, 1.0])), dev(torch.tensor([0.99, 0.0]))).cpu().tolist()
     assert got == [2, 0]
+
+
+# ------------------------------------------------------------------------------------------
+def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split):
+    from kapel_b200.engine.batch import cut_tiles
+
+    hq, hkv = q.shape[1], kt.shape[-2]
+    per_tile = max(1, K().attention_mma_rows(decode) // (hq // hkv))
+    q_len = np.asarray(q_lens, np.int32)
+    q_start = np.concatenate(([0], np.cumsum(q_len)[:-1])).astype(np.int32)
+    tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(q_start, q_len, per_tile))
+    slots = max(1, -(-int(rc.max()) // split)) if split else 1
+    return K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, window, scale, cap, decode, split, slots).cpu()
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 1, 64), (8, 4, 128), (8, 4, 256), (5, 1, 80)])
+@pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0)])
+@pytest.mark.parametrize("split", [0, 64, 256])
+def test_paged_attention_mma_prompt_mode(hq, hkv, d, window, cap, split):
+    lengths, q_lens = [1, 37, 300, 700], [1, 37, 130, 33]
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d)
+    scale = 1.0 / math.sqrt(d * 1.5)
+    got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, False, split).double()
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
+    assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (16, 1, 64), (8, 4, 128), (8, 4, 256), (2, 2, 96)])
+@pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0)])
+@pytest.mark.parametrize("split", [64, 256])
+def test_paged_attention_mma_decode_mode(hq, hkv, d, window, cap, split):
+    group = hq // hkv
+    lengths = [1, 37, 300, 700, 64, 65]
+    q_lens = [1, min(2, 16 // group), 1, max(1, 16 // group), 1, 1]
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d + 1)
+    rc[0] = 0                      # a padding row: sees nothing, gives zeros
+    scale = 1.0 / math.sqrt(d * 1.5)
+    got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, True, split).double()
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
+    assert (got[0] == 0).all()
+    assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("decode", [False, True])
+def test_paged_attention_mma_far_key_and_window_edge(decode):
+    hq, hkv, d, n, page, window = 2, 1, 32, 600, 16, 128
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, [n], [1], seed=3)
+    q = q * 0.05
+
+    def plant(pos):
+        kt2, vt2 = kt.clone(), vt.clone()
+        line = int(bt[0, pos // page]) * page + pos % page
+        kt2.reshape(-1, hkv, d)[line, 0] = (q[0, 0].float() * 400).to(kt.dtype)
+        vt2.reshape(-1, hkv, d)[line, 0] = 5.0
+        return kt2, vt2
+
+    for pos, win, seen in [(3, None, True), (n - window, window, True), (n - window - 1, window, False)]:
+        kt2, vt2 = plant(pos)
+        got = run_mma(q, kt2, vt2, bt, rc, [1], page, win, 1.0, None, decode, 256 if decode else 0).double()
+        want = paged_reference(q, kt2, vt2, bt, re, rc, page, win, 1.0, None)
+        assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+        assert (abs(float(got[0, 0].mean()) - 5.0) < 0.1) == seen
