@@ -7,10 +7,15 @@
 //
 //  * a tile is up to MROWS rows of one request and one kv head; a row is (token, query head of
 //    the kv head's group), so the group shares every key and value it loads;
-//  * keys and values arrive in shared memory 64 positions at a time by cp.async, two stages;
-//  * prompt mode (DECODE = false, 64 rows): each of 4 warps owns 16 rows and walks all keys;
-//  * decode mode (DECODE = true, 16 rows): the 4 warps share the 16 rows and each takes a quarter
-//    of every 64 keys with a softmax state of its own, merged through shared memory at the end;
+//  * `attention_mma_kernel` (prompt portions, 64 rows): keys and values arrive 64 positions at a
+//    time by cp.async in two stages; each of 4 warps owns 16 rows and walks all keys;
+//  * `attention_decode_kernel` (16 rows: a few tokens of one request): the 4 warps share the rows;
+//    each warp streams its own tiles of 16 keys through a three-stage pipeline of its own, filled
+//    by the copy engine (cp.async.bulk, one copy a key row, completion on an mbarrier), so the
+//    loop has no block-wide barrier, a tile costs two instructions a lane to fetch, and ~128 KB
+//    are in flight a multiprocessor; each warp keeps a softmax state of its own and the four are
+//    merged through shared memory. Every wait on an mbarrier gives up after about a second,
+//    raises a flag that `kb_attention_error` reports, and the block leaves without writing;
 //  * score = scale * q.k, then cap * tanh(score / cap) (tanh.approx), then the mask: a row that
 //    has seen c positions reads keys [max(0, c - window), c);
 //  * with `split` > 0 the keys are also cut at absolute multiples of `split` across blockIdx.z;
@@ -38,6 +43,7 @@ struct AttMmaParams {
     float* partial;            // [rows, hq, slots, d + 2] when slots > 1
     int rows, hq, hkv, d, page_size, table_width, n_pages;
     int window, split, slots;
+    int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
     float scale, cap;
 };
 
@@ -70,21 +76,177 @@ __device__ __forceinline__ float am_tanh(float x) {
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+__device__ __forceinline__ float am_exp2(float x) {      // 2^x, one instruction; 2^-inf = 0
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
 __device__ __forceinline__ uint32_t am_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
 
-// HD: the largest head_dim this instantiation takes (registers are sized by it).
-template <int HD, bool DECODE>
+// ---- the copy engine: bulk copies global -> shared that complete on an mbarrier
+__device__ int g_attention_error = 0;       // set when a wait on an mbarrier ran out
+
+__device__ __forceinline__ uint32_t am_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void am_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(am_saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void am_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(am_saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void am_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
+    asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                 ::"r"(am_saddr(dst)), "l"(src), "r"(bytes), "r"(am_saddr(bar)) : "memory");
+}
+// Waits for the phase with this parity to complete; false if it did not within ~1 s.
+__device__ __forceinline__ bool am_mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = am_saddr(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - start > 2000000000ll) return false;
+    }
+}
+
+// One warp's work on one tile part: 16 query rows against NKEYS keys that lie in shared memory.
+// S = Q K^T, scale, soft cap, mask, online softmax, O += P V. HD sizes the registers; d <= HD.
+//   q16: the warp's 16 query rows; tK, tV: the first of the NKEYS key and value rows; j0: the
+//   absolute position of the first key; cnt/fst: count and first visible key of rows g and g+8
+//   (a row beyond the tile's own has count INT_MAX: what it computes is never written).
+//   FULL: d == HD, known when the kernel is compiled, so the loops carry no size tests.
+template <int HD, int NKEYS, bool FULL>
+__device__ __forceinline__ void am_tile(const bf16* q16, const bf16* tK, const bf16* tV, int ld, int d, int j0,
+                                        const int (&cnt)[2], const int (&fst)[2], int fst_hi, int cnt_lo, int klo,
+                                        int khi, float sc, float cap, float (&o)[HD / 8][4], float (&m_run)[2],
+                                        float (&l_run)[2], int lane) {
+    constexpr int NT_S = NKEYS / 8;
+    constexpr int NT_O = HD / 8;
+    const int t = lane & 3;
+    const float LOG2E = 1.4426950408889634f;
+    float s[NT_S][4];
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        if (FULL || ks * 16 < d) {
+            uint32_t a[4];
+            am_ldmatrix_x4(a, q16 + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + ks * 16 + (lane >> 4) * 8);
+#pragma unroll
+            for (int nb = 0; nb < NT_S / 2; ++nb) {
+                uint32_t b[4];
+                am_ldmatrix_x4(b, tK + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * ld + ks * 16 + ((lane >> 3) & 1) * 8);
+                am_mma(s[2 * nb], a, b[0], b[1]);
+                am_mma(s[2 * nb + 1], a, b[2], b[3]);
+            }
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+    // Only a tile at an edge (of the causal triangle, of a window, of the block's key range) needs
+    // the mask: fst_hi and cnt_lo are the warp's largest first-visible key and smallest count.
+    const bool inner = j0 >= fst_hi && j0 + NKEYS <= cnt_lo && j0 >= klo && j0 + NKEYS <= khi;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            float v = s[nt][e] * sc;
+            if (cap > 0.f) v = cap * am_tanh(v);
+            if (!inner) {
+                const int j = j0 + nt * 8 + t * 2 + (e & 1);
+                const bool seen = j >= fst[h] && j < cnt[h] && j >= klo && j < khi;
+                v = seen ? v : -INFINITY;
+            }
+            s[nt][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        alpha[h] = (m_new == -INFINITY) ? 1.f : am_exp2((m_run[h] - m_new) * LOG2E);
+        m_run[h] = m_new;
+        l_run[h] *= alpha[h];
+    }
+    // p = exp(s - m); the row sums stay per thread until the end
+    uint32_t pa[NT_S / 2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            pv[e] = (s[nt][e] == -INFINITY) ? 0.f : am_exp2((s[nt][e] - m_run[h]) * LOG2E);
+            l_run[h] += pv[e];
+        }
+        // the C layout of two neighbouring n-tiles is the A layout of one k16 step
+        pa[nt >> 1][(nt & 1) * 2] = am_pack(pv[0], pv[1]);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = am_pack(pv[2], pv[3]);
+    }
+    // The running maximum settles after a few tiles; then there is nothing to rescale.
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+    }
+#pragma unroll
+    for (int kb = 0; kb < NT_S / 2; ++kb) {
+#pragma unroll
+        for (int nd = 0; nd < HD / 16; ++nd) {
+            if (FULL || nd * 16 < d) {
+                uint32_t b[4];
+                am_ldmatrix_x4_trans(b, tV + (kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + nd * 16 + (lane >> 4) * 8);
+                am_mma(o[2 * nd], pa[kb], b[0], b[1]);
+                am_mma(o[2 * nd + 1], pa[kb], b[2], b[3]);
+            }
+        }
+    }
+}
+
+// The line of key position j of a request, or -1 if the block table has no page for it.
+__device__ __forceinline__ long long am_line(const AttMmaParams& p, int entry, int j) {
+    const int lp = j / p.page_size;
+    const int page = lp < p.table_width ? p.block_table[(size_t)entry * p.table_width + lp] : -1;
+    return (page >= 0 && page < p.n_pages) ? (long long)page * p.page_size + j % p.page_size : -1;
+}
+
+// What both kernels know of their tile.
+struct AmTile {
+    int entry, row0, nq, rows_valid, c_first, klo, khi, group;
+};
+
+__device__ __forceinline__ AmTile am_tile_info(const AttMmaParams& p, int tile, int slot) {
+    AmTile x;
+    x.group = p.hq / p.hkv;
+    x.entry = p.tile_entry[tile];
+    x.row0 = p.tile_row0[tile];
+    x.nq = p.tile_nq[tile];
+    x.rows_valid = x.nq * x.group;
+    x.c_first = p.row_count[x.row0];
+    x.klo = (p.window > 0 && x.c_first > p.window) ? x.c_first - p.window : 0;
+    x.khi = x.c_first > 0 ? x.c_first + x.nq - 1 : 0;       // a padding row sees nothing
+    if (p.split > 0) {
+        x.klo = max(x.klo, slot * p.split);
+        x.khi = min(x.khi, (slot + 1) * p.split);
+    }
+    return x;
+}
+
+// Prompt portions: 64 rows a block, each warp 16 of them over all the block's keys.
+template <int HD, bool FULL>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_mma_kernel(const AttMmaParams p) {
-    constexpr int MROWS = DECODE ? 16 : 64;
-    constexpr int WKEYS = DECODE ? AM_KT / 4 : AM_KT;      // keys a warp handles of each tile
-    constexpr int NT_S = WKEYS / 8;                         // score n-tiles a warp
-    constexpr int NT_O = HD / 8;                            // output n-tiles
+    constexpr int MROWS = 64;
+    constexpr int NT_O = HD / 8;
     extern __shared__ __align__(128) unsigned char am_smem[];
-
     const int d = p.d;
     const int ld = d + AM_PAD;
     bf16* sQ = reinterpret_cast<bf16*>(am_smem);
@@ -93,255 +255,278 @@ attention_mma_kernel(const AttMmaParams p) {
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int tile = blockIdx.x, kvh = blockIdx.y, slot = blockIdx.z;
-    const int group = p.hq / p.hkv;
-    const int entry = p.tile_entry[tile];
-    const int row0 = p.tile_row0[tile];
-    const int nq = p.tile_nq[tile];
-    const int rows_valid = nq * group;
-    const int c_first = p.row_count[row0];
-    const int c_last = c_first + nq - 1;
-
-    // The keys this block walks.
-    int klo = (p.window > 0 && c_first > p.window) ? c_first - p.window : 0;
-    int khi = c_last;
-    if (c_first <= 0) khi = 0;                              // a padding row sees nothing
-    if (p.split > 0) {
-        klo = max(klo, slot * p.split);
-        khi = min(khi, (slot + 1) * p.split);
-    }
+    const int kvh = blockIdx.y, slot = blockIdx.z;
+    // Later tiles of a prompt see more keys: they start first.
+    const AmTile x = am_tile_info(p, gridDim.x - 1 - blockIdx.x, slot);
+    const int group = x.group, row0 = x.row0, rows_valid = x.rows_valid, klo = x.klo, khi = x.khi;
     if (klo >= khi) {
-        if (p.slots == 1 && c_first <= 0) {
+        if (p.slots == 1 && x.c_first <= 0)
             for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
                 const int r = i / d, c = i % d;
                 p.out[((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + c] = __float2bfloat16_rn(0.f);
             }
-        }
         return;
     }
     const int k_begin = klo / AM_KT * AM_KT;               // tiles are cut at multiples of KT
     const int n_tiles = (khi - k_begin + AM_KT - 1) / AM_KT;
 
-    // ---- loads
     const int chunks = d / 8;                               // 16-byte chunks a row
-    {
-        for (int i = tid; i < MROWS * chunks; i += AM_THREADS) {
-            const int r = i / chunks, ch = i % chunks;
-            const bool valid = r < rows_valid;
-            const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
-            am_cp_async16(sQ + r * ld + ch * 8, src, valid);
-        }
+    for (int i = tid; i < MROWS * chunks; i += AM_THREADS) {
+        const int r = i / chunks, ch = i % chunks;
+        const bool valid = r < rows_valid;
+        const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
+        am_cp_async16(sQ + r * ld + ch * 8, src, valid);
     }
-    // Two threads a key row: each loads half of the row's chunks, of K and of V.
-    const int lrow = tid >> 1, lhalf = tid & 1;
-    auto load_tile = [&](int stage, int kt) {
-        const int j = k_begin + kt * AM_KT + lrow;
-        bool valid = j >= klo && j < khi;
-        size_t line = 0;
-        if (valid) {
-            const int lp = j / p.page_size;
-            const int page = lp < p.table_width ? p.block_table[(size_t)entry * p.table_width + lp] : -1;
-            valid = page >= 0 && page < p.n_pages;
-            line = valid ? (size_t)page * p.page_size + j % p.page_size : 0;
+    // A tile's 64 lines (page * page_size + offset, or -1) wait in shared memory, written one
+    // iteration ahead by the first 64 threads; then consecutive threads copy consecutive 16-byte
+    // pieces of a key row, so a warp's copy instruction covers whole rows.
+    int* sLine = reinterpret_cast<int*>(sV + 2 * AM_KT * ld);          // [2][KT]
+    auto find_lines = [&](int kt) {
+        if (tid < AM_KT) {
+            const int j = k_begin + kt * AM_KT + tid;
+            sLine[(kt & 1) * AM_KT + tid] = (kt < n_tiles && j >= klo && j < khi) ? (int)am_line(p, x.entry, j) : -1;
         }
-        const bf16* ksrc = p.k_table + (line * p.hkv + kvh) * d;
-        const bf16* vsrc = p.v_table + (line * p.hkv + kvh) * d;
-        bf16* kd = sK + ((size_t)stage * AM_KT + lrow) * ld;
-        bf16* vd = sV + ((size_t)stage * AM_KT + lrow) * ld;
-        const int half = (chunks + 1) / 2;
-        const int c0 = lhalf * half, c1 = min(chunks, c0 + half);
-        for (int ch = c0; ch < c1; ++ch) am_cp_async16(kd + ch * 8, ksrc + ch * 8, valid);
-        for (int ch = c0; ch < c1; ++ch) am_cp_async16(vd + ch * 8, vsrc + ch * 8, valid);
     };
+    auto load_tile = [&](int stage, int kt) {
+        const int* lines = sLine + (kt & 1) * AM_KT;
+        for (int idx = tid; idx < AM_KT * chunks; idx += AM_THREADS) {
+            const int r = idx / chunks, ch = idx - r * chunks;
+            const int line = lines[r];
+            const bool valid = line >= 0;
+            const size_t off = ((size_t)(valid ? line : 0) * p.hkv + kvh) * d + ch * 8;
+            am_cp_async16(sK + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.k_table + off, valid);
+            am_cp_async16(sV + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.v_table + off, valid);
+        }
+    };
+    find_lines(0);
+    find_lines(1);
+    __syncthreads();
     load_tile(0, 0);
     am_commit();
 
-    // ---- state
     float o[NT_O][4];
 #pragma unroll
     for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
     float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-
-    const int wrow = DECODE ? 0 : warp * 16;                // first row of this warp
-    const int wkey = DECODE ? warp * WKEYS : 0;             // first key of this warp within a tile
-    // rows g and g + 8 of the warp's 16: their tokens' counts and first visible keys
+    const int wrow = warp * 16;
     int cnt[2], fst[2];
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         const int r = wrow + g + h * 8;
-        const bool valid = r < rows_valid;
-        cnt[h] = valid ? c_first + r / group : 0;
-        fst[h] = (p.window > 0 && cnt[h] > p.window) ? cnt[h] - p.window : 0;
+        const bool own = r < rows_valid;
+        cnt[h] = own ? x.c_first + r / group : 0x7fffffff;
+        fst[h] = (own && p.window > 0 && cnt[h] > p.window) ? cnt[h] - p.window : 0;
     }
+    const int fst_hi = __reduce_max_sync(0xffffffffu, max(fst[0], fst[1]));
+    const int cnt_lo = __reduce_min_sync(0xffffffffu, min(cnt[0], cnt[1]));
     const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
-    const float LOG2E = 1.4426950408889634f;
 
     for (int kt = 0; kt < n_tiles; ++kt) {
         am_wait<0>();
         __syncthreads();                                    // tile kt landed; the other stage is free
         if (kt + 1 < n_tiles) load_tile((kt + 1) & 1, kt + 1);
         am_commit();
-        const bf16* tK = sK + (size_t)(kt & 1) * AM_KT * ld;
-        const bf16* tV = sV + (size_t)(kt & 1) * AM_KT * ld;
-        const int j0 = k_begin + kt * AM_KT + wkey;         // first key of this warp's part
-
-        // scores S[16 x WKEYS] = Q K^T
-        float s[NT_S][4];
-#pragma unroll
-        for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-        for (int ks = 0; ks < HD / 16; ++ks) {
-            if (ks * 16 < d) {
-                uint32_t a[4];
-                am_ldmatrix_x4(a, sQ + (wrow + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-                for (int nb = 0; nb < NT_S / 2; ++nb) {
-                    uint32_t b[4];
-                    am_ldmatrix_x4(b, tK + (wkey + nb * 16 + (lane & 7) + (lane >> 4) * 8) * ld + ks * 16 + ((lane >> 3) & 1) * 8);
-                    am_mma(s[2 * nb], a, b[0], b[1]);
-                    am_mma(s[2 * nb + 1], a, b[2], b[3]);
-                }
-            }
-        }
-        // scale, soft cap, mask; tile maximum
-        float mx[2] = {-INFINITY, -INFINITY};
-#pragma unroll
-        for (int nt = 0; nt < NT_S; ++nt)
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                const int j = j0 + nt * 8 + t * 2 + (e & 1);
-                float v = s[nt][e] * sc;
-                if (p.cap > 0.f) v = p.cap * am_tanh(v);
-                const bool seen = j >= fst[h] && j < cnt[h] && j >= klo && j < khi;
-                v = seen ? v : -INFINITY;
-                s[nt][e] = v;
-                mx[h] = fmaxf(mx[h], v);
-            }
-        float alpha[2];
-#pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-            const float m_new = fmaxf(m_run[h], mx[h]);
-            alpha[h] = (m_new == -INFINITY) ? 1.f : exp2f((m_run[h] - m_new) * LOG2E);
-            m_run[h] = m_new;
-            l_run[h] *= alpha[h];
-        }
-        // p = exp(s - m); the row sums stay per thread until the end
-        uint32_t pa[NT_S / 2][4];
-#pragma unroll
-        for (int nt = 0; nt < NT_S; ++nt) {
-            float pv[4];
-#pragma unroll
-            for (int e = 0; e < 4; ++e) {
-                const int h = e >> 1;
-                pv[e] = (s[nt][e] == -INFINITY) ? 0.f : exp2f((s[nt][e] - m_run[h]) * LOG2E);
-                l_run[h] += pv[e];
-            }
-            // the C layout of two neighbouring n-tiles is the A layout of one k16 step
-            pa[nt >> 1][(nt & 1) * 2] = am_pack(pv[0], pv[1]);
-            pa[nt >> 1][(nt & 1) * 2 + 1] = am_pack(pv[2], pv[3]);
-        }
-#pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-        }
-        // O += P V
-#pragma unroll
-        for (int kb = 0; kb < NT_S / 2; ++kb) {
-#pragma unroll
-            for (int nd = 0; nd < HD / 16; ++nd) {
-                if (nd * 16 < d) {
-                    uint32_t b[4];
-                    am_ldmatrix_x4_trans(b, tV + (wkey + kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + nd * 16 + (lane >> 4) * 8);
-                    am_mma(o[2 * nd], pa[kb], b[0], b[1]);
-                    am_mma(o[2 * nd + 1], pa[kb], b[2], b[3]);
-                }
-            }
-        }
+        find_lines(kt + 2);                                 // read after the next barrier; last read before this one
+        am_tile<HD, AM_KT, FULL>(sQ + wrow * ld, sK + (size_t)(kt & 1) * AM_KT * ld, sV + (size_t)(kt & 1) * AM_KT * ld, ld, d,
+                           k_begin + kt * AM_KT, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap, o, m_run, l_run, lane);
     }
     am_wait<0>();
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
+        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
+    }
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = wrow + g + h * 8;
+        if (r >= rows_valid) continue;
+        const int row = row0 + r / group, head = kvh * group + r % group;
+        if (p.slots == 1) {
+            const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
+            bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i)
+                if (i * 8 < d)
+                    *reinterpret_cast<uint32_t*>(dst + i * 8 + t * 2) = am_pack(o[i][h * 2] * inv, o[i][h * 2 + 1] * inv);
+        } else {
+            float* dst = p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2);
+#pragma unroll
+            for (int i = 0; i < NT_O; ++i)
+                if (i * 8 < d) { dst[i * 8 + t * 2] = o[i][h * 2]; dst[i * 8 + t * 2 + 1] = o[i][h * 2 + 1]; }
+            if (t == 0) { dst[d] = m_run[h]; dst[d + 1] = l_run[h]; }
+        }
+    }
+}
 
-    // ---- row sums across the 4 lanes of a row
+// A few tokens of one request: 16 rows a block shared by its 4 warps. Warp w walks the tiles of
+// 16 keys numbered w, w + 4, w + 8, ... of the block's keys through a pipeline of its own.
+constexpr int AD_WK = 16;             // keys a warp tile
+constexpr int AD_STAGES = 3;
+
+template <int HD, bool FULL>
+__global__ void __launch_bounds__(AM_THREADS)
+attention_decode_kernel(const AttMmaParams p) {
+    constexpr int NT_O = HD / 8;
+    extern __shared__ __align__(128) unsigned char am_smem[];
+    const int d = p.d;
+    const int ld = d + AM_PAD;
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int g = lane >> 2, t = lane & 3;
+    bf16* sQ = reinterpret_cast<bf16*>(am_smem);            // [16][ld]
+    bf16* sW = sQ + 16 * ld + (size_t)warp * (2 * AD_STAGES * AD_WK * ld);   // this warp's [STAGES][K|V][16][ld]
+    // after the pipelines (or the merge buffers, whichever is larger): one mbarrier a warp and stage
+    uint64_t* bars = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + warp * AD_STAGES;
+
+    const int kvh = blockIdx.y, slot = blockIdx.z;
+    const AmTile x = am_tile_info(p, blockIdx.x, slot);
+    const int group = x.group, row0 = x.row0, rows_valid = x.rows_valid, klo = x.klo, khi = x.khi;
+    if (klo >= khi) {                                       // nothing here: the merge kernel skips this slot
+        if (p.slots == 1 && x.c_first <= 0)                 // a padding row without a merge kernel: zeros
+            for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
+                const int r = i / d, c = i % d;
+                p.out[((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + c] = __float2bfloat16_rn(0.f);
+            }
+        return;
+    }
+    const int k_begin = klo / AD_WK * AD_WK;
+    const int n_tiles = (khi - k_begin + AD_WK - 1) / AD_WK;
+
+    if (lane == 0) {
+#pragma unroll
+        for (int s = 0; s < AD_STAGES; ++s) am_mbar_init(bars + s, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int chunks = d / 8;
+    for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
+        const int r = i / chunks, ch = i % chunks;
+        const bool valid = r < rows_valid;
+        const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
+        am_cp_async16(sQ + r * ld + ch * 8, src, valid);
+    }
+    am_commit();
+    __syncthreads();                                        // every warp's barriers are initialised
+
+    // Lane r (r < 16) owns key row r of a tile: it asks the copy engine for the row's keys and its
+    // values (two copies of d elements), or clears the rows if the position is not the block's.
+    const uint32_t row_bytes = (uint32_t)d * sizeof(bf16);
+    auto load_tile = [&](int stage, int tile) {
+        const int j = k_begin + tile * AD_WK + lane;
+        const long long line = (lane < AD_WK && j >= klo && j < khi) ? am_line(p, x.entry, j) : -1;
+        const unsigned live = __ballot_sync(0xffffffffu, line >= 0);
+        bf16* kd = sW + ((size_t)(2 * stage) * AD_WK + lane) * ld;
+        bf16* vd = sW + ((size_t)(2 * stage + 1) * AD_WK + lane) * ld;
+        if (lane == 0) am_mbar_expect_tx(bars + stage, 2u * row_bytes * (uint32_t)__popc(live));
+        __syncwarp();                                       // the expectation is set before a copy can complete
+        if (line >= 0) {
+            const size_t off = ((size_t)line * p.hkv + kvh) * d;
+            am_bulk_copy(kd, p.k_table + off, row_bytes, bars + stage);
+            am_bulk_copy(vd, p.v_table + off, row_bytes, bars + stage);
+        } else if (lane < AD_WK) {
+            for (int c = 0; c < chunks; ++c) {
+                *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+                *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
+            }
+        }
+    };
+#pragma unroll
+    for (int s = 0; s < AD_STAGES; ++s)
+        if (warp + 4 * s < n_tiles) load_tile(s, warp + 4 * s);
+    am_wait<0>();                                           // this thread's part of Q has landed
+    __syncthreads();                                        // and everyone else's
+
+    float o[NT_O][4];
+#pragma unroll
+    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
+    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
+    int cnt[2], fst[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        const int r = g + h * 8;
+        const bool own = r < rows_valid;
+        cnt[h] = own ? x.c_first + r / group : 0x7fffffff;
+        fst[h] = (own && p.window > 0 && cnt[h] > p.window) ? cnt[h] - p.window : 0;
+    }
+    const int fst_hi = __reduce_max_sync(0xffffffffu, max(fst[0], fst[1]));
+    const int cnt_lo = __reduce_min_sync(0xffffffffu, min(cnt[0], cnt[1]));
+    const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
+
+    bool failed = false;
+    for (int i = 0; warp + 4 * i < n_tiles; ++i) {
+        const int tile = warp + 4 * i, stage = i % AD_STAGES;
+        if (!am_mbar_wait(bars + stage, (uint32_t)(i / AD_STAGES) & 1u)) { failed = true; break; }
+        __syncwarp();                                       // zero rows written by other lanes are visible
+        am_tile<HD, AD_WK, FULL>(sQ, sW + (size_t)(2 * stage) * AD_WK * ld, sW + (size_t)(2 * stage + 1) * AD_WK * ld, ld, d,
+                           k_begin + tile * AD_WK, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap, o, m_run, l_run, lane);
+        __syncwarp();                                       // every lane has read the stage
+        if (tile + 4 * AD_STAGES < n_tiles) load_tile(stage, tile + 4 * AD_STAGES);
+    }
+    if (failed) {
+        // A copy never completed. Give the others in flight the same bounded chance to land (they
+        // write into this block's shared memory), raise the flag, and leave without writing.
+        for (int s = 0; s < AD_STAGES; ++s) am_mbar_wait(bars + s, 0u), am_mbar_wait(bars + s, 1u);
+        if (lane == 0) atomicExch(&g_attention_error, 1);
+    }
+    failed = __syncthreads_or(failed);
+    if (failed) return;
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
     }
 
-    if (DECODE) {
-        // Merge the 4 warps' states: O, m, l per row through shared memory (the stages are free).
-        __syncthreads();
-        float* mO = reinterpret_cast<float*>(sK);           // [4][16][d]
-        float* mM = mO + 4 * 16 * d;                        // [4][16]
-        float* mL = mM + 4 * 16;
+    // Merge the 4 warps' states through shared memory (the pipelines are drained).
+    const float LOG2E = 1.4426950408889634f;
+    __syncthreads();
+    const int md = d + 4;                                   // padded: rows g and g + 1 land in different banks
+    float* mO = reinterpret_cast<float*>(sQ + 16 * ld);     // [4][16][md]
+    float* mM = mO + 4 * 16 * md;                           // [4][16]
+    float* mL = mM + 4 * 16;
 #pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-            if (i * 8 < d) {
+    for (int i = 0; i < NT_O; ++i)
+        if (i * 8 < d) {
 #pragma unroll
-                for (int e = 0; e < 4; ++e)
-                    mO[((size_t)warp * 16 + g + (e >> 1) * 8) * d + i * 8 + t * 2 + (e & 1)] = o[i][e];
-            }
+            for (int e = 0; e < 4; ++e)
+                mO[((size_t)warp * 16 + g + (e >> 1) * 8) * md + i * 8 + t * 2 + (e & 1)] = o[i][e];
         }
-        if (t == 0) {
-#pragma unroll
-            for (int h = 0; h < 2; ++h) {
-                mM[warp * 16 + g + h * 8] = m_run[h];
-                mL[warp * 16 + g + h * 8] = l_run[h];
-            }
-        }
-        __syncthreads();
-        for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
-            const int r = i / d, c = i % d;
-            float mx = -INFINITY;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mM[w * 16 + r]);
-            float acc = 0.f, l = 0.f;
-#pragma unroll
-            for (int w = 0; w < 4; ++w) {
-                const float mw = mM[w * 16 + r];
-                const float f = (mw == -INFINITY) ? 0.f : exp2f((mw - mx) * LOG2E);
-                acc = fmaf(f, mO[((size_t)w * 16 + r) * d + c], acc);
-                l = fmaf(f, mL[w * 16 + r], l);
-            }
-            const int row = row0 + r / group, head = kvh * group + r % group;
-            if (p.slots == 1) {
-                p.out[((size_t)row * p.hq + head) * d + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
-            } else {
-                float* dst = p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2);
-                dst[c] = acc;
-                if (c == 0) { dst[d] = mx; dst[d + 1] = l; }
-            }
-        }
-    } else {
+    if (t == 0) {
 #pragma unroll
         for (int h = 0; h < 2; ++h) {
-            const int r = wrow + g + h * 8;
-            if (r >= rows_valid) continue;
-            const int row = row0 + r / group, head = kvh * group + r % group;
-            if (p.slots == 1) {
-                const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
-                bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
+            mM[warp * 16 + g + h * 8] = m_run[h];
+            mL[warp * 16 + g + h * 8] = l_run[h];
+        }
+    }
+    __syncthreads();
+    for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
+        const int r = i / d, c = i % d;
+        float mx = -INFINITY;
 #pragma unroll
-                for (int i = 0; i < NT_O; ++i)
-                    if (i * 8 < d)
-                        *reinterpret_cast<uint32_t*>(dst + i * 8 + t * 2) = am_pack(o[i][h * 2] * inv, o[i][h * 2 + 1] * inv);
-            } else {
-                float* dst = p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2);
+        for (int w = 0; w < 4; ++w) mx = fmaxf(mx, mM[w * 16 + r]);
+        float acc = 0.f, l = 0.f;
 #pragma unroll
-                for (int i = 0; i < NT_O; ++i)
-                    if (i * 8 < d) { dst[i * 8 + t * 2] = o[i][h * 2]; dst[i * 8 + t * 2 + 1] = o[i][h * 2 + 1]; }
-                if (t == 0) { dst[d] = m_run[h]; dst[d + 1] = l_run[h]; }
-            }
+        for (int w = 0; w < 4; ++w) {
+            const float mw = mM[w * 16 + r];
+            const float f = (mw == -INFINITY) ? 0.f : am_exp2((mw - mx) * LOG2E);
+            acc = fmaf(f, mO[((size_t)w * 16 + r) * md + c], acc);
+            l = fmaf(f, mL[w * 16 + r], l);
+        }
+        const int row = row0 + r / group, head = kvh * group + r % group;
+        if (p.slots == 1) {
+            p.out[((size_t)row * p.hq + head) * d + c] = __float2bfloat16_rn(l > 0.f ? acc / l : 0.f);
+        } else {
+            float* dst = p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2);
+            dst[c] = acc;
+            if (c == 0) { dst[d] = mx; dst[d + 1] = l; }
         }
     }
 }
 
 // out[row, head, :] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the absolute slots the
-// row's own keys fall in; a row that sees nothing gets zeros.
-__global__ void attention_mma_combine_kernel(const AttMmaParams p) {
+// row's own keys fall in; a row that sees nothing gets zeros. One block a (row, head): its first
+// warp turns the slots' maxima and sums into weights, then every thread adds up its components
+// with independent loads.
+__global__ void __launch_bounds__(128)
+attention_mma_combine_kernel(const AttMmaParams p) {
+    extern __shared__ float cw[];                           // [slots] weights
     const int row = blockIdx.x, head = blockIdx.y;
     const int count = p.row_count[row];
     bf16* o = p.out + ((size_t)row * p.hq + head) * p.d;
@@ -351,43 +536,70 @@ __global__ void attention_mma_combine_kernel(const AttMmaParams p) {
     }
     const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
     const int z0 = first / p.split, z1 = min(p.slots - 1, (count - 1) / p.split);
-    const float* base = p.partial + ((size_t)row * p.hq + head) * p.slots * (p.d + 2);
+    const int nz = z1 - z0 + 1;
     const int stride = p.d + 2;
-    float mx = -INFINITY;
-    for (int z = z0; z <= z1; ++z) mx = fmaxf(mx, base[(size_t)z * stride + p.d]);
-    float denom = 0.f;
-    for (int z = z0; z <= z1; ++z) {
-        const float m = base[(size_t)z * stride + p.d];
-        denom += (m == -INFINITY ? 0.f : __expf(m - mx)) * base[(size_t)z * stride + p.d + 1];
+    const float* base = p.partial + (((size_t)row * p.hq + head) * p.slots + z0) * stride;
+    if (threadIdx.x < 32) {
+        const int lane = threadIdx.x;
+        float mx = -INFINITY;
+        for (int z = lane; z < nz; z += 32) mx = fmaxf(mx, base[(size_t)z * stride + p.d]);
+        mx = warp_max(mx);
+        float denom = 0.f;
+        for (int z = lane; z < nz; z += 32) {
+            const float m = base[(size_t)z * stride + p.d];
+            const float w = (m == -INFINITY) ? 0.f : __expf(m - mx);
+            cw[z] = w;
+            denom += w * base[(size_t)z * stride + p.d + 1];
+        }
+        denom = warp_sum(denom);
+        const float inv = denom > 0.f ? 1.f / denom : 0.f;
+        for (int z = lane; z < nz; z += 32) cw[z] *= inv;
     }
-    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    __syncthreads();
     for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
         float acc = 0.f;
-        for (int z = z0; z <= z1; ++z) {
-            const float m = base[(size_t)z * stride + p.d];
-            const float w = m == -INFINITY ? 0.f : __expf(m - mx);
-            acc = fmaf(w, base[(size_t)z * stride + i], acc);
-        }
-        o[i] = __float2bfloat16_rn(acc * inv);
+#pragma unroll 4
+        for (int z = 0; z < nz; ++z) acc = fmaf(cw[z], base[(size_t)z * stride + i], acc);
+        o[i] = __float2bfloat16_rn(acc);
     }
 }
 
-template <int HD, bool DECODE>
-static int launch_mma(const AttMmaParams& p, int tiles, cudaStream_t s) {
-    constexpr int MROWS = DECODE ? 16 : 64;
+template <int HD>
+static int launch_prompt(const AttMmaParams& p, int tiles, cudaStream_t s) {
     const int ld = p.d + AM_PAD;
-    size_t smem = ((size_t)MROWS * ld + 4 * (size_t)AM_KT * ld) * sizeof(bf16);
-    if (DECODE) {
-        const size_t merge = ((size_t)4 * 16 * p.d + 2 * 4 * 16) * sizeof(float);
-        const size_t stages = 4 * (size_t)AM_KT * ld * sizeof(bf16);
-        if (merge > stages) smem += merge - stages;
-    }
+    const size_t smem = ((size_t)64 * ld + 4 * (size_t)AM_KT * ld) * sizeof(bf16) + 2 * AM_KT * sizeof(int);
     if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
-    if (smem > 48 * 1024)
-        cudaFuncSetAttribute(attention_mma_kernel<HD, DECODE>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
     dim3 grid(tiles, p.hkv, p.slots);
-    attention_mma_kernel<HD, DECODE><<<grid, AM_THREADS, smem, s>>>(p);
+    if (p.d == HD) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_mma_kernel<HD, true><<<grid, AM_THREADS, smem, s>>>(p);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_mma_kernel<HD, false><<<grid, AM_THREADS, smem, s>>>(p);
+    }
     return check_launch("attention_mma");
+}
+
+template <int HD>
+static int launch_decode(const AttMmaParams& p, int tiles, cudaStream_t s) {
+    const int ld = p.d + AM_PAD;
+    const size_t pipes = (size_t)4 * 2 * AD_STAGES * AD_WK * ld * sizeof(bf16);
+    const size_t merge = ((size_t)4 * 16 * (p.d + 4) + 2 * 4 * 16) * sizeof(float);
+    size_t bars = (size_t)16 * ld * sizeof(bf16) + (pipes > merge ? pipes : merge);
+    bars = (bars + 15) / 16 * 16;
+    const size_t smem = bars + 4 * AD_STAGES * sizeof(uint64_t);
+    AttMmaParams q = p;
+    q.decode_bar_offset = (int)bars;
+    if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
+    dim3 grid(tiles, p.hkv, p.slots);
+    if (p.d == HD) {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_decode_kernel<HD, true><<<grid, AM_THREADS, smem, s>>>(q);
+    } else {
+        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
+        attention_decode_kernel<HD, false><<<grid, AM_THREADS, smem, s>>>(q);
+    }
+    return check_launch("attention_decode");
 }
 
 }  // namespace kb
@@ -396,6 +608,14 @@ using namespace kb;
 
 // Rows a tile may hold in each mode; the host cuts requests into tiles of rows / group tokens.
 extern "C" int kb_attention_mma_rows(int decode) { return decode ? 16 : 64; }
+
+// 1 if a wait inside an attention kernel ever ran out (and clears the flag); synchronises the device.
+extern "C" int kb_attention_error() {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_attention_error, sizeof(int)) != cudaSuccess) return -1;
+    if (flag) cudaMemcpyToSymbol(g_attention_error, &zero, sizeof(int));
+    return flag;
+}
 
 extern "C" long long kb_attention_mma_scratch_floats(int rows, int hq, int d, int slots) {
     return slots > 1 ? (long long)rows * hq * slots * (d + 2) : 0;
@@ -411,8 +631,9 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     KB_REQUIRE(hq / hkv <= (decode ? 16 : 64), "attention_mma: %d query heads a kv head do not fit a tile of %d rows", hq / hkv, decode ? 16 : 64);
     KB_REQUIRE(page_size > 0 && table_width > 0 && n_pages > 0, "attention_mma: page_size %d, table width %d, pages %d", page_size, table_width, n_pages);
     KB_REQUIRE(window >= 0 && cap >= 0.f, "attention_mma: window %d, cap %g", window, cap);
-    KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AM_KT == 0 && slots >= 1 && slots <= 65535),
-               "attention_mma: split %d (a multiple of %d) with %d slots", split, AM_KT, slots);
+    KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AM_KT == 0 && slots >= 1 && slots <= 8192),
+               "attention_mma: split %d (a multiple of %d) with %d slots (at most 8192)", split, AM_KT, slots);
+    KB_REQUIRE(!(decode && split == 0 && slots != 1), "attention_mma: decode mode without a split has one slot");
     KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_mma: %d slots need scratch memory", slots);
     KB_REQUIRE(hkv <= 65535, "attention_mma: %d kv heads is too many for one launch", hkv);
     if (rows == 0 || tiles == 0) return 0;
@@ -422,15 +643,16 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.tile_nq = tile_nq; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
     p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width;
     p.n_pages = n_pages; p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
+    p.decode_bar_offset = 0;
     cudaStream_t s = (cudaStream_t)stream;
     int e;
-    if (d <= 64) e = decode ? launch_mma<64, true>(p, tiles, s) : launch_mma<64, false>(p, tiles, s);
-    else if (d <= 128) e = decode ? launch_mma<128, true>(p, tiles, s) : launch_mma<128, false>(p, tiles, s);
-    else e = decode ? launch_mma<256, true>(p, tiles, s) : launch_mma<256, false>(p, tiles, s);
+    if (d <= 64) e = decode ? launch_decode<64>(p, tiles, s) : launch_prompt<64>(p, tiles, s);
+    else if (d <= 128) e = decode ? launch_decode<128>(p, tiles, s) : launch_prompt<128>(p, tiles, s);
+    else e = decode ? launch_decode<256>(p, tiles, s) : launch_prompt<256>(p, tiles, s);
     if (e) return e;
     if (slots > 1) {
         dim3 grid(rows, hq);
-        attention_mma_combine_kernel<<<grid, 128, 0, s>>>(p);
+        attention_mma_combine_kernel<<<grid, 128, (size_t)slots * sizeof(float), s>>>(p);
         return check_launch("attention_mma combine");
     }
     return 0;

@@ -31,8 +31,39 @@ def _chunks_touched(row_count: np.ndarray, window: Optional[int], chunk: int) ->
     return int(((c - 1) // chunk - first // chunk + 1).max())
 
 
-DECODE_SPLIT = 256       # keys a block of the tensor-core attention kernel when every request brings few tokens
-PROMPT_SPLIT = 1024      # the same for prompt portions, when the tiles alone would leave most of the GPU idle
+PROMPT_SPLIT = 1024      # keys a block of the prompt attention kernel when the tiles alone would leave most of the GPU idle
+SPLIT_STEP = 64          # splits are multiples of the kernels' key tile
+
+
+def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = None):
+    """(split, slots) of the decode attention kernel, which runs one block a multiprocessor.
+    Keys are cut at absolute multiples of `split`; `slots` covers the longest request
+    (`longest` positions). A row reads at most `window` keys, so only about window / split of the
+    slots do work. The split is chosen so that the working blocks (`pairs` (tile, kv head)
+    pairs times working slots) take as little time as possible: waves of blocks times the keys a
+    block walks plus what a block costs to start and to merge (about 192 keys' worth)."""
+    pairs = max(1, pairs)
+    span = min(longest, window) if window else longest
+    best = None
+    most = max(1, -(-span // SPLIT_STEP))
+    for want in range(1, min(most, 4 * sms) + 1):
+        split = max(SPLIT_STEP, -(-(-(-span // want)) // SPLIT_STEP) * SPLIT_STEP)
+        working = -(-span // split) + (1 if (window and longest > window) else 0)
+        cost = -(-(pairs * working) // sms) * (split + 192)
+        if best is None or cost < best[0]:
+            best = (cost, split)
+    split = best[1]
+    return split, max(1, -(-longest // split))
+
+
+_SMS = {}
+
+
+def sm_count(device) -> int:
+    key = str(device)
+    if key not in _SMS:
+        _SMS[key] = torch.cuda.get_device_properties(device).multi_processor_count if torch.device(device).type == "cuda" else 148
+    return _SMS[key]
 
 
 def cut_tiles(q_start, q_len, tokens_per_tile: int):
@@ -88,11 +119,11 @@ class StepBatch:
         for i, shape in enumerate(table_shapes):
             self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
 
-    def attention_tiles(self, heads_per_kv: int, kv_heads: int):
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None):
         """How the tensor-core attention kernel cuts this step: (decode mode, (tile_entry, tile_row0,
         tile_nq) on the device, split, slots). Decode mode when every request's rows fit 16; the
         keys are split across blocks when the tiles alone are too few to fill the GPU."""
-        key = ("tiles", heads_per_kv, kv_heads)
+        key = ("tiles", heads_per_kv, kv_heads, window)
         if key not in self.memo:
             from .. import kernels as K
 
@@ -106,10 +137,10 @@ class StepBatch:
             tiles = (dev[:n], dev[n : 2 * n], dev[2 * n :])
             longest = int(plan.row_count.max())
             if decode:
-                split = DECODE_SPLIT
+                split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window)
             else:
                 split = 0 if n * kv_heads >= 96 else PROMPT_SPLIT
-            slots = max(1, -(-longest // split)) if split else 1
+                slots = max(1, -(-longest // split)) if split else 1
             self.memo[key] = (decode, tiles, split, slots, host)
         return self.memo[key][:4]
 

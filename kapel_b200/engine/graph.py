@@ -18,7 +18,7 @@ from typing import Dict, List, Optional, Tuple
 import numpy as np
 import torch
 
-from .batch import DECODE_SPLIT, GroupBatch
+from .batch import GroupBatch, decode_split, sm_count
 
 ROW_BUCKETS = (1, 2, 4, 8, 16, 24, 32, 48, 64, 96, 128, 192, 256)
 WIDTH_STEP = 64          # block-table widths are rounded up to a multiple of this many pages
@@ -47,7 +47,9 @@ class StaticBatch:
         # the tensor-core attention kernel's tiles: every row a tile of one token
         every = torch.arange(rows, dtype=torch.int32, device=device)
         self._tiles = (every, every.clone(), torch.ones(rows, dtype=torch.int32, device=device))
-        self._mma_slots = max(1, -(-(width * page_size) // DECODE_SPLIT))
+        self._longest = width * page_size
+        self._device = device
+        self._mma = {}
         self.h2d_bytes = self.total * 4
 
     def attention_slots(self, window: Optional[int]) -> int:
@@ -56,8 +58,11 @@ class StaticBatch:
             n = min(n, (window - 1) // self.chunk + 2)
         return max(1, n)
 
-    def attention_tiles(self, heads_per_kv: int, kv_heads: int):
-        return True, self._tiles, DECODE_SPLIT, self._mma_slots
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None):
+        if (kv_heads, window) not in self._mma:
+            self._mma[(kv_heads, window)] = decode_split(self.rows * kv_heads, self._longest, sm_count(self._device), window)
+        split, slots = self._mma[(kv_heads, window)]
+        return True, self._tiles, split, slots
 
     def fill(self, plan, ids) -> None:
         """Writes a plan of at most `rows` single-token entries into the buffers; the rest are

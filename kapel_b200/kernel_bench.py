@@ -1,0 +1,180 @@
+"""Times each kernel of a decode step (and of a prompt step) alone, at given layer sizes.
+
+    python -m kapel_b200.kernel_bench [--batch 8] [--history 6144] [--prompt 2048] [--iters 20]
+
+For every kernel: device time by CUDA events (mean of `iters` launches after 3 warm-ups), the
+bytes it has to move, and the bandwidth that makes. Operands rotate through enough copies to
+exceed L2, so a launch never finds its weights or its cache pages in L2 from the launch before.
+Sizes default to Gemma 2 2B's; they are arguments, not constants of the package.
+"""
+from __future__ import annotations
+
+import argparse
+import json
+import math
+import os
+import sys
+
+import numpy as np
+import torch
+
+
+def _time(fn, iters, warm=3):
+    """Microseconds a call: `iters` calls recorded into one CUDA graph (so the host's launch cost
+    is not in the figure), the graph replayed three times, the best replay taken."""
+    import gc
+
+    for i in range(warm):
+        fn(i)
+    torch.cuda.synchronize()
+    graph = torch.cuda.CUDAGraph()
+    gc.disable()
+    try:
+        with torch.cuda.graph(graph):
+            for i in range(iters):
+                fn(warm + i)
+    finally:
+        gc.enable()
+    best = float("inf")
+    for _ in range(3):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        graph.replay()
+        b.record()
+        torch.cuda.synchronize()
+        best = min(best, a.elapsed_time(b))
+    return best / iters * 1e3
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
+    ap.add_argument("--batch", type=int, default=8)
+    ap.add_argument("--history", type=int, default=6144)
+    ap.add_argument("--prompt", type=int, default=2048)
+    ap.add_argument("--iters", type=int, default=20)
+    ap.add_argument("--hidden", type=int, default=2304)
+    ap.add_argument("--heads", type=int, default=8)
+    ap.add_argument("--kv-heads", type=int, default=4)
+    ap.add_argument("--head-dim", type=int, default=256)
+    ap.add_argument("--intermediate", type=int, default=9216)
+    ap.add_argument("--vocab", type=int, default=256000)
+    ap.add_argument("--window", type=int, default=4096)
+    ap.add_argument("--only", default="", help="comma-separated substrings of kernel names to run")
+    args = ap.parse_args(argv)
+
+    from . import kernels as K
+    from .engine.batch import PROMPT_SPLIT, cut_tiles, decode_split, sm_count
+
+    dev = torch.device("cuda", torch.cuda.current_device())
+    K.library()
+    B, H, Hq, Hkv, D, I, V = args.batch, args.hidden, args.heads, args.kv_heads, args.head_dim, args.intermediate, args.vocab
+    bf = torch.bfloat16
+    rows = []
+
+    def want(name):
+        return not args.only or any(s in name for s in args.only.split(","))
+
+    def report(name, us, nbytes, flops=0.0):
+        rows.append((name, us, nbytes, flops))
+        gbs = nbytes / us / 1e3
+        tf = flops / us / 1e6
+        print(f"{name:44s} {us:9.2f} us  {nbytes / 1e6:9.2f} MB  {gbs:8.1f} GB/s" + (f"  {tf:8.1f} TFLOP/s" if flops else ""), flush=True)
+
+    def copies(nbytes):
+        return max(2, int(math.ceil(300e6 / max(nbytes, 1))))       # enough to exceed L2 (126 MB) twice over
+
+    # ------------------------------------------------------------------ products
+    def gemm_case(name, m, n, k, out_dtype=bf, softcap=None):
+        if not want(name):
+            return
+        nbytes = n * k * 2
+        c = min(copies(nbytes), 8)
+        ws = [torch.randn(n, k, device=dev, dtype=torch.float32).mul_(0.02).to(bf) for _ in range(c)]
+        a = torch.randn(m, k, device=dev).to(bf)
+        us = _time(lambda i: K.gemm(a, ws[i % c], out_dtype=out_dtype, softcap=softcap), args.iters)
+        report(f"{name} [{m}x{k}]x[{n}x{k}]", us, nbytes + m * k * 2 + m * n * 2, 2.0 * m * n * k)
+
+    for m, tag in ((B, "decode"), (args.prompt, "prompt")):
+        gemm_case(f"gemm qkv {tag}", m, (Hq + 2 * Hkv) * D, H)
+        gemm_case(f"gemm o {tag}", m, H, Hq * D)
+        gemm_case(f"gemm gate_up {tag}", m, 2 * I, H)
+        gemm_case(f"gemm down {tag}", m, H, I)
+    gemm_case("gemm head decode", B, V, H, out_dtype=torch.float32, softcap=30.0)
+
+    # ------------------------------------------------------------------ small kernels
+    for m, tag in ((B, "decode"), (args.prompt, "prompt")):
+        if want(f"add_rmsnorm {tag}"):
+            res = torch.randn(m, H, device=dev)
+            br = torch.randn(m, H, device=dev).to(bf)
+            w1, w2 = torch.randn(H, device=dev).to(bf), torch.randn(H, device=dev).to(bf)
+            us = _time(lambda i: K.add_rmsnorm(res, br, (w1, 1e-6, 1.0), (w2, 1e-6, 1.0), bf), args.iters)
+            report(f"add_rmsnorm {tag} [{m}x{H}]", us, m * H * (4 + 4 + 2 + 2))
+        if want(f"glu {tag}"):
+            x = torch.randn(m, 2 * I, device=dev).to(bf)
+            us = _time(lambda i: K.glu(x, "gelu_tanh"), args.iters)
+            report(f"glu {tag} [{m}x{2 * I}]", us, m * I * 6)
+
+    # ------------------------------------------------------------------ attention over a paged cache
+    page = 16
+    ctx = args.history
+    pages_per_seq = -(-(ctx + 1) // page)
+    n_layers_rot = 2
+    n_pages = B * pages_per_seq
+    tables = [(torch.randn(n_pages, page, Hkv, D, device=dev).to(bf), torch.randn(n_pages, page, Hkv, D, device=dev).to(bf))
+              for _ in range(n_layers_rot)]
+    perm = torch.randperm(n_pages).to(torch.int32).reshape(B, pages_per_seq)
+    bt = perm.to(dev)
+    scale, cap = 1.0 / math.sqrt(D), 50.0
+
+    def decode_case(window):
+        name = f"attention decode window={window}"
+        if not want(name):
+            return
+        q = torch.randn(B, Hq, D, device=dev).to(bf)
+        rc = torch.full((B,), ctx + 1, dtype=torch.int32, device=dev)
+        q_start, q_len = np.arange(B, dtype=np.int32), np.ones(B, np.int32)
+        per_tile = max(1, K.attention_mma_rows(True) // (Hq // Hkv))
+        tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(q_start, q_len, per_tile))
+        split, slots = decode_split(B * Hkv, ctx + 1, sm_count(dev), window)
+        seen = min(ctx + 1, window) if window else ctx + 1
+        us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
+                                                   True, split, slots), args.iters)
+        report(f"{name} split={split}x{slots}", us, B * seen * Hkv * D * 2 * 2)
+
+    decode_case(None)
+    decode_case(args.window)
+
+    def prompt_case(window):
+        name = f"attention prompt window={window}"
+        if not want(name):
+            return
+        t = args.prompt
+        q = torch.randn(t, Hq, D, device=dev).to(bf)
+        rc = torch.arange(1, t + 1, dtype=torch.int32, device=dev)
+        per_tile = max(1, K.attention_mma_rows(False) // (Hq // Hkv))
+        tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
+        n = tiles[0].numel()
+        split = 0 if n * Hkv >= 96 else PROMPT_SPLIT
+        slots = max(1, -(-t // split)) if split else 1
+        pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
+        us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
+                                                   False, split, slots), max(3, args.iters // 4))
+        report(f"{name} [{t} tokens]", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
+
+    if args.prompt <= ctx:
+        prompt_case(None)
+        prompt_case(args.window)
+
+    if want("rope_append"):
+        for m, tag in ((B, "decode"), (args.prompt, "prompt")):
+            qkv = torch.randn(m, (Hq + 2 * Hkv) * D, device=dev).to(bf)
+            pos = torch.arange(m, dtype=torch.int32, device=dev)
+            cs = K.rope_table(pos, D, 10000.0)
+            lines = torch.arange(m, dtype=torch.int32, device=dev)
+            us = _time(lambda i: K.rope_append(qkv, cs, lines, tables[0][0], tables[0][1], Hq, Hkv, D, D), args.iters)
+            report(f"rope_append {tag} [{m}]", us, m * (Hq + 2 * Hkv) * D * 4)
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -62,7 +62,7 @@ class Attention(Part):
         )
         heads_per_kv = s.num_heads // s.num_kv_heads
         if K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
-            decode, tiles, split, slots = batch.attention_tiles(heads_per_kv, s.num_kv_heads)
+            decode, tiles, split, slots = batch.attention_tiles(heads_per_kv, s.num_kv_heads, s.window)
             y = K.paged_attention_mma(
                 q, k_table, v_table, group.block_table, batch.row_count, tiles,
                 self.ctx.page_size, s.window, s.scale, s.softcap, decode, split, slots,
