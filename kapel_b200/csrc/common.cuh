@@ -34,6 +34,19 @@ template <> struct Elem<__nv_bfloat16> {
     static __device__ __forceinline__ void store(__nv_bfloat16* p, float v) { *p = __float2bfloat16_rn(v); }
 };
 
+// An input that may still be a stack of split-K partial sums: element i is the sum over `splits`
+// slices `stride` elements apart, added in slice order. With one slice it is the element itself.
+template <typename T> struct Src {
+    const T* p;
+    int splits;
+    size_t stride;
+    __device__ __forceinline__ float at(size_t i) const {
+        float v = Elem<T>::load(p + i);
+        for (int s = 1; s < splits; ++s) v += Elem<T>::load(p + (size_t)s * stride + i);
+        return v;
+    }
+};
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -44,8 +44,8 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
 // the key table at the row's line), [Hq+Hkv, Hq+2Hkv) values (copied to the value table).
 // Pairing "half": (j, j + rotary/2) for j < rotary/2; components from `rotary` on pass through.
 // A row whose line is negative writes no key and no value (a padding row).
-template <typename T>
-__global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __restrict__ cos_sin,
+template <typename TI, typename T>
+__global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__ cos_sin,
                                    const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
                                    T* __restrict__ v_table, int rows, int hq, int hkv, int d, int rotary,
                                    int write_kv, long long table_lines) {
@@ -57,7 +57,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __re
     const int i = (int)(idx % half_d);
     const int h = (int)((idx / half_d) % heads);
     const int r = (int)(idx / ((long long)half_d * heads));
-    const T* src = qkv + ((size_t)r * heads + h) * d;
+    const size_t src = ((size_t)r * heads + h) * d;
     int ia, ib;
     bool rotate;
     if (i < half_r) {
@@ -65,7 +65,6 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __re
     } else {
         ia = rotary + 2 * (i - half_r); ib = ia + 1; rotate = false;
     }
-    float a = Elem<T>::load(src + ia), b = Elem<T>::load(src + ib);
     T* dst;
     if (h < hq) {
         dst = q_out + ((size_t)r * hq + h) * d;
@@ -78,6 +77,7 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __re
         dst = (is_key ? k_table : v_table) + ((size_t)line * hkv + kvh) * d;
         if (!is_key) rotate = false;
     }
+    float a = qkv.at(src + ia), b = qkv.at(src + ib);      // read only by the threads that write
     if (rotate) {
         const float2 cs = cos_sin[(size_t)r * half_r + i];
         const float ra = a * cs.x - b * cs.y;
@@ -90,13 +90,13 @@ __global__ void rope_append_kernel(const T* __restrict__ qkv, const float2* __re
 
 // ---------------------------------------------------------------------------------------
 // out[r, i] = act(x[r, i]) * x[r, n + i]: the gated unit after a stacked gate|up product.
-template <typename T>
-__global__ void glu_kernel(T* __restrict__ out, const T* __restrict__ x, long long rows, int n, int act) {
+template <typename TI, typename T>
+__global__ void glu_kernel(T* __restrict__ out, const Src<TI> x, long long rows, int n, int act) {
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
     if (idx >= rows * n) return;
     const long long r = idx / n;
     const int i = (int)(idx % n);
-    const float g = Elem<T>::load(x + r * 2 * n + i), u = Elem<T>::load(x + r * 2 * n + n + i);
+    const float g = x.at(r * 2 * n + i), u = x.at(r * 2 * n + n + i);
     const float a = act == 0 ? gelu_tanh(g) : silu(g);
     Elem<T>::store(out + idx, a * u);
 }
@@ -150,41 +150,46 @@ extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int
     return check_launch("rope_table");
 }
 
-extern "C" int kb_rope_append(const void* qkv, int dt, const float* cos_sin, const int* lines, void* q_out,
-                              void* k_table, void* v_table, int rows, int hq, int hkv, int d, int rotary,
-                              int write_kv, long long table_lines, void* stream) {
+// qkv: `in_dt` (float32 or bfloat16), as `splits` slices `split_stride` elements apart that are
+// added up on the way in; q_out and the tables: `out_dt`.
+extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long split_stride, const float* cos_sin,
+                              const int* lines, void* q_out, void* k_table, void* v_table, int out_dt, int rows,
+                              int hq, int hkv, int d, int rotary, int write_kv, long long table_lines, void* stream) {
     KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && d > 0 && d % 2 == 0, "rope_append: rows %d, heads %d/%d, head_dim %d", rows, hq, hkv, d);
     KB_REQUIRE(rotary >= 0 && rotary <= d && rotary % 2 == 0, "rope_append: rotary %d must be even and at most head_dim %d", rotary, d);
+    KB_REQUIRE(splits >= 1, "rope_append: %d slices", splits);
     if (rows == 0) return 0;
     const long long total = (long long)rows * (hq + 2 * hkv) * (d / 2);
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dt == KB_DT_F32)
-        rope_append_kernel<float><<<blocks, 256, 0, s>>>((const float*)qkv, (const float2*)cos_sin, lines, (float*)q_out,
-                                                        (float*)k_table, (float*)v_table, rows, hq, hkv, d, rotary,
-                                                        write_kv, table_lines);
-    else if (dt == KB_DT_BF16)
-        rope_append_kernel<bf16><<<blocks, 256, 0, s>>>((const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out,
-                                                       (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d, rotary,
-                                                       write_kv, table_lines);
-    else
-        return fail("rope_append: dtype code %d is not known", dt);
+#define KB_ROPE(TI, T)                                                                                              \
+    rope_append_kernel<TI, T><<<blocks, 256, 0, s>>>(Src<TI>{(const TI*)qkv, splits, (size_t)split_stride},          \
+                                                     (const float2*)cos_sin, lines, (T*)q_out, (T*)k_table,         \
+                                                     (T*)v_table, rows, hq, hkv, d, rotary, write_kv, table_lines)
+    if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ROPE(float, float);
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_ROPE(float, bf16);
+    else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_ROPE(bf16, bf16);
+    else return fail("rope_append: dtype codes %d -> %d are not known", in_dt, out_dt);
+#undef KB_ROPE
     return check_launch("rope_append");
 }
 
-extern "C" int kb_glu(void* out, const void* x, int dt, long long rows, int n, int act, void* stream) {
+extern "C" int kb_glu(void* out, int out_dt, const void* x, int in_dt, int splits, long long split_stride,
+                      long long rows, int n, int act, void* stream) {
     KB_REQUIRE(rows >= 0 && n > 0, "glu: rows %lld, width %d", rows, n);
     KB_REQUIRE(act == 0 || act == 1, "glu: activation code %d is not known (0 gelu_tanh, 1 silu)", act);
+    KB_REQUIRE(splits >= 1, "glu: %d slices", splits);
     if (rows == 0) return 0;
     const long long total = rows * n;
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
-    if (dt == KB_DT_F32)
-        glu_kernel<float><<<blocks, 256, 0, s>>>((float*)out, (const float*)x, rows, n, act);
-    else if (dt == KB_DT_BF16)
-        glu_kernel<bf16><<<blocks, 256, 0, s>>>((bf16*)out, (const bf16*)x, rows, n, act);
-    else
-        return fail("glu: dtype code %d is not known", dt);
+#define KB_GLU(TI, T) \
+    glu_kernel<TI, T><<<blocks, 256, 0, s>>>((T*)out, Src<TI>{(const TI*)x, splits, (size_t)split_stride}, rows, n, act)
+    if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_GLU(float, float);
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_GLU(float, bf16);
+    else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_GLU(bf16, bf16);
+    else return fail("glu: dtype codes %d -> %d are not known", in_dt, out_dt);
+#undef KB_GLU
     return check_launch("glu");
 }
 

@@ -1,6 +1,8 @@
 // C[M,N] = A[M,K] . W[N,K]^T for bfloat16 inputs with 32-bit accumulation, on the warp-level
-// tensor-core path (mma.sync m16n8k16). Two kernels:
+// tensor-core path (mma.sync m16n8k16). Three kernels:
 //
+//  * `row16_kernel` for M <= 16 (decoding a few sequences): weights straight from global memory
+//    into B fragments, activations through L1, no shared memory, split over K;
 //  * `stream_kernel` for M <= 64 (decode and short portions): the weight matrix is read once,
 //    straight from global memory into B fragments, 16 bytes a thread; the few activation rows
 //    wait in shared memory. Work is split over K when N alone gives too few blocks; partial
@@ -152,6 +154,88 @@ __global__ void splitk_reduce_kernel(const float* __restrict__ partial, void* __
 }
 
 // ---------------------------------------------------------------------------------------
+// M <= 16 (decoding a few sequences): nothing waits in shared memory and nothing synchronises.
+// A warp owns 8 * NT columns and walks its share of K in groups of 32 with the same k permutation
+// as above; the weights come straight from global memory past L1, the few activation rows come
+// through L1, where every warp of the multiprocessor finds them again. Four groups of loads are
+// in flight a thread before the first MMA of an iteration. HI: rows 8..15 exist (M > 8).
+__device__ __forceinline__ uint4 ld_stream16(const bf16* p) {
+    uint4 v;
+    asm volatile("ld.global.nc.L1::no_allocate.v4.u32 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p));
+    return v;
+}
+
+constexpr int R16_U = 4;                          // k32 groups a loop iteration
+
+template <int NT, bool HI>
+__global__ void __launch_bounds__(128)
+row16_kernel(const bf16* __restrict__ a, const bf16* __restrict__ w, float* __restrict__ partial,
+             void* __restrict__ c, int c_dt, int m, int n, int k, int k_per_split, int epi, float cap) {
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int g = lane >> 2, t = lane & 3;
+    const int n_warp = blockIdx.x * (32 * NT) + warp * (8 * NT);
+    const int split = blockIdx.y;
+    const int k_begin = split * k_per_split;
+    const int k_end = min(k, k_begin + k_per_split);
+
+    float acc[NT][4];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) acc[j][0] = acc[j][1] = acc[j][2] = acc[j][3] = 0.f;
+    const bf16* wrow[NT];
+    bool wvalid[NT];
+#pragma unroll
+    for (int j = 0; j < NT; ++j) {
+        const int col = n_warp + j * 8 + g;
+        wvalid[j] = col < n;
+        wrow[j] = w + (size_t)(wvalid[j] ? col : 0) * k;
+    }
+    const bool lo_valid = g < m, hi_valid = HI && (g + 8) < m;
+    const bf16* alo = a + (size_t)(lo_valid ? g : 0) * k;
+    const bf16* ahi = a + (size_t)(hi_valid ? g + 8 : 0) * k;
+    const uint4 zero = make_uint4(0u, 0u, 0u, 0u);
+
+    for (int k0 = k_begin; k0 < k_end; k0 += 32 * R16_U) {
+        uint4 bw[R16_U][NT], al[R16_U], ah[R16_U];
+#pragma unroll
+        for (int u = 0; u < R16_U; ++u) {
+            const int kq = k0 + u * 32 + t * 8;
+            const bool ok = kq < k_end;                     // k_end is a multiple of 8: the 16 bytes are whole
+#pragma unroll
+            for (int j = 0; j < NT; ++j) bw[u][j] = (ok && wvalid[j]) ? ld_stream16(wrow[j] + kq) : zero;
+            al[u] = (ok && lo_valid) ? __ldg(reinterpret_cast<const uint4*>(alo + kq)) : zero;
+            ah[u] = (HI && ok && hi_valid) ? __ldg(reinterpret_cast<const uint4*>(ahi + kq)) : zero;
+        }
+#pragma unroll
+        for (int u = 0; u < R16_U; ++u) {
+            const uint32_t a1[4] = {al[u].x, ah[u].x, al[u].y, ah[u].y};
+            const uint32_t a2[4] = {al[u].z, ah[u].z, al[u].w, ah[u].w};
+#pragma unroll
+            for (int j = 0; j < NT; ++j) {
+                mma_bf16(acc[j], a1, bw[u][j].x, bw[u][j].y);
+                mma_bf16(acc[j], a2, bw[u][j].z, bw[u][j].w);
+            }
+        }
+    }
+#pragma unroll
+    for (int j = 0; j < NT; ++j)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int row = g + (e >> 1) * 8;
+            const int col = n_warp + j * 8 + t * 2 + (e & 1);
+            if (row >= m || col >= n) continue;
+            const float v = acc[j][e];
+            if (partial != nullptr) {
+                partial[((size_t)split * m + row) * n + col] = v;
+            } else {
+                const float o = epilogue_apply(v, epi, cap);
+                if (c_dt == KB_DT_F32) static_cast<float*>(c)[(size_t)row * n + col] = o;
+                else static_cast<bf16*>(c)[(size_t)row * n + col] = __float2bfloat16_rn(o);
+            }
+        }
+}
+
+// ---------------------------------------------------------------------------------------
 // Larger M: 128 x 128 x 64 tiles, 8 warps as 2 x 4, each warp 64 x 32.
 constexpr int TL_BM = 128, TL_BN = 128, TL_BK = 64, TL_STAGES = 3;
 constexpr int TL_STAGE_ELEMS = (TL_BM + TL_BN) * TL_BK;
@@ -265,6 +349,21 @@ static int stream_splits(int n, int k, int bn, int sms) {
     return splits;
 }
 
+// The same for the M <= 16 kernel (64 columns a block of 4 warps): about four blocks a
+// multiprocessor, each split at least 256 long. It depends on n and k only.
+constexpr int R16_NT = 2;
+static void row16_plan(int n, int k, int sms, int* splits, int* k_per_split) {
+    const int col_blocks = (n + 32 * R16_NT - 1) / (32 * R16_NT);
+    int s = (4 * sms + col_blocks / 2) / col_blocks;
+    const int max_splits = (k + 255) / 256;
+    if (s > max_splits) s = max_splits;
+    if (s < 1) s = 1;
+    int per = (k + s - 1) / s;
+    per = (per + 31) / 32 * 32;
+    *k_per_split = per;
+    *splits = (k + per - 1) / per;
+}
+
 static int g_sms = 0;
 static int sm_count() {
     if (g_sms == 0) {
@@ -283,9 +382,29 @@ using namespace kb;
 // Scratch floats the streaming kernel needs for a product of these sizes (0 when it does not split).
 extern "C" long long kb_gemm_bf16_scratch_floats(int m, int n, int k) {
     if (m <= 0 || m > 64) return 0;
-    const int nt = 2;                                   // every instantiation below uses NT = 2
-    const int splits = stream_splits(n, k, 64 * nt, sm_count());
+    int splits, per;
+    if (m <= 16) row16_plan(n, k, sm_count(), &splits, &per);
+    else splits = stream_splits(n, k, 64 * 2, sm_count());      // every instantiation below uses NT = 2
     return splits > 1 ? (long long)splits * m * n : 0;
+}
+
+// How many partial sums the M <= 16 kernel leaves for a weight [n, k] (1: none, it writes the result).
+extern "C" int kb_gemm_bf16_row16_splits(int n, int k) {
+    int splits, per;
+    row16_plan(n, k, sm_count(), &splits, &per);
+    return splits;
+}
+
+static int launch_row16(const bf16* a, const bf16* w, float* partial, void* c, int c_dt, int m, int n, int k, int epi,
+                        float cap, cudaStream_t s) {
+    int splits, per;
+    row16_plan(n, k, sm_count(), &splits, &per);
+    dim3 grid((n + 32 * R16_NT - 1) / (32 * R16_NT), splits);
+    if (splits > 1 && partial == nullptr) return fail("gemm_bf16: %d splits over K need scratch memory", splits);
+    float* out = splits > 1 ? partial : nullptr;
+    if (m > 8) row16_kernel<R16_NT, true><<<grid, 128, 0, s>>>(a, w, out, c, c_dt, m, n, k, per, epi, cap);
+    else row16_kernel<R16_NT, false><<<grid, 128, 0, s>>>(a, w, out, c, c_dt, m, n, k, per, epi, cap);
+    return check_launch("gemm_bf16 row16");
 }
 
 template <int MT, int NT>
@@ -327,7 +446,16 @@ extern "C" int kb_gemm_bf16(void* c, int c_dt, const void* a, const void* w, int
     cudaStream_t s = (cudaStream_t)stream;
     const bf16* ap = (const bf16*)a;
     const bf16* wp = (const bf16*)w;
-    if (m <= 16) return launch_stream<1, 2>(ap, wp, scratch, c, c_dt, m, n, k, epilogue, cap, s);
+    if (m <= 16) {
+        if (int e = launch_row16(ap, wp, scratch, c, c_dt, m, n, k, epilogue, cap, s)) return e;
+        const int splits = kb_gemm_bf16_row16_splits(n, k);
+        if (splits > 1) {
+            const long long mn = (long long)m * n;
+            splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, s>>>(scratch, c, c_dt, mn, splits, epilogue, cap);
+            return check_launch("gemm_bf16 split-K reduce");
+        }
+        return 0;
+    }
     if (m <= 32) return launch_stream<2, 2>(ap, wp, scratch, c, c_dt, m, n, k, epilogue, cap, s);
     if (m <= 64) return launch_stream<4, 2>(ap, wp, scratch, c, c_dt, m, n, k, epilogue, cap, s);
     const size_t smem = (size_t)TL_STAGES * TL_STAGE_ELEMS * sizeof(bf16);
@@ -340,6 +468,27 @@ extern "C" int kb_gemm_bf16(void* c, int c_dt, const void* a, const void* w, int
     KB_REQUIRE(grid.y <= 65535, "gemm_bf16: %d rows is too many for one launch", m);
     tile_kernel<<<grid, 256, smem, s>>>(ap, wp, c, c_dt, m, n, k, epilogue, cap);
     return check_launch("gemm_bf16 tile");
+}
+
+// The M <= 16 product without its reduction: partial[s, m, n] for s < kb_gemm_bf16_row16_splits(n, k),
+// to be added up by whoever reads them (a norm, a gated unit, the rotation). With one split the
+// "partial" sums are the result.
+extern "C" int kb_gemm_bf16_partial(float* partial, const void* a, const void* w, int m, int n, int k, void* stream) {
+    KB_REQUIRE(m > 0 && m <= 16 && n > 0 && k > 0, "gemm_bf16_partial: m %d (1..16), n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_bf16_partial: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_bf16_partial: operands must be 16-byte aligned");
+    KB_REQUIRE(partial != nullptr, "gemm_bf16_partial: no output");
+    // One split writes its sums through the "direct" path as float32, which is the same memory.
+    return launch_row16((const bf16*)a, (const bf16*)w, partial, partial, KB_DT_F32, m, n, k, 0, 0.f, (cudaStream_t)stream);
+}
+
+// out[i] = sum over `splits` slices of partial[s * mn + i], in slice order.
+extern "C" int kb_splitk_reduce(void* out, int out_dt, const float* partial, long long mn, int splits, void* stream) {
+    KB_REQUIRE(mn >= 0 && splits >= 1, "splitk_reduce: %lld elements, %d slices", mn, splits);
+    KB_REQUIRE(out_dt == KB_DT_F32 || out_dt == KB_DT_BF16, "splitk_reduce: output dtype code %d is not known", out_dt);
+    if (mn == 0) return 0;
+    splitk_reduce_kernel<<<(unsigned)((mn + 255) / 256), 256, 0, (cudaStream_t)stream>>>(partial, out, out_dt, mn, splits, 0, 0.f);
+    return check_launch("splitk_reduce");
 }
 
 // ---------------------------------------------------------------------------------------

@@ -30,7 +30,7 @@ __global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, con
 // residual += norm_post(branch); then, if w_next, h = norm_next(residual).
 // With w_post null the branch is added as it is (a block without a norm after its branches).
 template <typename TB, typename TW, typename TH>
-__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TB* __restrict__ branch,
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const Src<TB> branch,
                                    const TW* __restrict__ w_post, float eps_post, float off_post,
                                    const TW* __restrict__ w_next, float eps_next, float off_next,
                                    TH* __restrict__ h, int width) {
@@ -40,7 +40,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TB* __res
     if (w_post != nullptr) {
         float ss = 0.f;
         for (int i = threadIdx.x; i < width; i += blockDim.x) {
-            const float v = Elem<TB>::load(branch + base + i);
+            const float v = branch.at(base + i);
             ss += v * v;
         }
         ss = block_sum(ss, scratch);
@@ -48,7 +48,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const TB* __res
     }
     float ss2 = 0.f;
     for (int i = threadIdx.x; i < width; i += blockDim.x) {
-        float b = Elem<TB>::load(branch + base + i);
+        float b = branch.at(base + i);
         if (w_post != nullptr) b = b * inv * (off_post + Elem<TW>::load(w_post + i));
         const float r = residual[base + i] + b;
         residual[base + i] = r;
@@ -96,25 +96,32 @@ extern "C" int kb_rmsnorm(void* y, int y_dt, const void* x, int x_dt, const void
     return check_launch("rmsnorm");
 }
 
-// residual: f32 in and out. branch and h share the activation dtype `act_dt`; both weights share `w_dt`.
-extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int act_dt, const void* w_post, float eps_post,
-                              float off_post, const void* w_next, float eps_next, float off_next, void* h, int w_dt,
-                              int rows, int width, void* stream) {
+// residual: f32 in and out. branch: `branch_dt`, as `splits` slices `split_stride` elements apart
+// that are added up on the way in (1 slice: the branch itself). h: `h_dt`. Both weights: `w_dt`.
+extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt, int splits, long long split_stride,
+                              const void* w_post, float eps_post, float off_post, const void* w_next, float eps_next,
+                              float off_next, void* h, int h_dt, int w_dt, int rows, int width, void* stream) {
     KB_REQUIRE(rows >= 0 && width > 0, "add_rmsnorm: rows %d, width %d", rows, width);
     KB_REQUIRE(w_next == nullptr || h != nullptr, "add_rmsnorm: a following norm needs an output");
+    KB_REQUIRE(splits >= 1 && (splits == 1 || split_stride >= (long long)rows * width), "add_rmsnorm: %d slices %lld apart", splits, split_stride);
     if (rows == 0) return 0;
     cudaStream_t s = (cudaStream_t)stream;
     const int t = threads_for(width);
-#define KB_ADDNORM(TB, TW)                                                                                   \
-    add_rmsnorm_kernel<TB, TW, TB><<<rows, t, 0, s>>>(residual, (const TB*)branch, (const TW*)w_post, eps_post, \
-                                                      off_post, (const TW*)w_next, eps_next, off_next, (TB*)h, width)
-    const int code = act_dt * 2 + w_dt;
+#define KB_ADDNORM(TB, TW, TH)                                                                                   \
+    add_rmsnorm_kernel<TB, TW, TH><<<rows, t, 0, s>>>(residual, Src<TB>{(const TB*)branch, splits, (size_t)split_stride}, \
+                                                      (const TW*)w_post, eps_post, off_post, (const TW*)w_next,    \
+                                                      eps_next, off_next, (TH*)h, width)
+    const int code = branch_dt * 4 + w_dt * 2 + h_dt;
     switch (code) {
-        case 0: KB_ADDNORM(float, float); break;
-        case 1: KB_ADDNORM(float, bf16); break;
-        case 2: KB_ADDNORM(bf16, float); break;
-        case 3: KB_ADDNORM(bf16, bf16); break;
-        default: return fail("add_rmsnorm: dtype codes act %d, w %d are not known", act_dt, w_dt);
+        case 0: KB_ADDNORM(float, float, float); break;
+        case 1: KB_ADDNORM(float, float, bf16); break;
+        case 2: KB_ADDNORM(float, bf16, float); break;
+        case 3: KB_ADDNORM(float, bf16, bf16); break;
+        case 4: KB_ADDNORM(bf16, float, float); break;
+        case 5: KB_ADDNORM(bf16, float, bf16); break;
+        case 6: KB_ADDNORM(bf16, bf16, float); break;
+        case 7: KB_ADDNORM(bf16, bf16, bf16); break;
+        default: return fail("add_rmsnorm: dtype codes branch %d, w %d, h %d are not known", branch_dt, w_dt, h_dt);
     }
 #undef KB_ADDNORM
     return check_launch("add_rmsnorm");

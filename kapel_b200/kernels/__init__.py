@@ -92,6 +92,51 @@ def _f(x: float) -> ctypes.c_float:
     return ctypes.c_float(float(x))
 
 
+class SplitSum:
+    """A product that is still a stack of split-K partial sums: `partials` is float32
+    [splits, rows, cols] and the value is their sum over the first dimension. The kernels that
+    read a product next (the norm with the residual sum, the gated unit, the rotation) add the
+    slices up on the way in, so the sum is never written out and read back; `finish` does it
+    for anything else."""
+
+    __slots__ = ("partials",)
+
+    def __init__(self, partials: torch.Tensor):
+        self.partials = partials
+
+    @property
+    def shape(self):
+        return tuple(self.partials.shape[1:])
+
+    @property
+    def splits(self) -> int:
+        return int(self.partials.shape[0])
+
+    @property
+    def device(self):
+        return self.partials.device
+
+
+def _src(x, what: str):
+    """(tensor to read, dtype code, slices, elements between slices) of a tensor or a SplitSum."""
+    if isinstance(x, SplitSum):
+        t = _need(x.partials, what, torch.float32)
+        return t, F32, x.splits, t.shape[1] * t.shape[2]
+    _need(x, what)
+    return x, _dt(x, what), 1, 0
+
+
+def finish(x, dtype: torch.dtype) -> torch.Tensor:
+    """A SplitSum added up into a tensor of `dtype`; a tensor as it is (cast if need be)."""
+    if isinstance(x, SplitSum):
+        _need(x.partials, "finish partials", torch.float32)
+        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        _check(library().kb_splitk_reduce(_ptr(out), _dt(out, "finish output"), _ptr(x.partials),
+                                          ctypes.c_longlong(out.numel()), x.splits, _stream()))
+        return out
+    return x if x.dtype == dtype else cast(x, dtype)
+
+
 # ------------------------------------------------------------------------------------------
 def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[torch.Tensor] = None) -> torch.Tensor:
     """out[r] = table[ids[r]] * scale in float32."""
@@ -115,42 +160,48 @@ def rope_table(positions: torch.Tensor, rotary: int, theta: float) -> torch.Tens
     return out
 
 
-def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int, rotary: int, write_kv: bool = True):
-    """Rotates the q and k heads of the stacked product `qkv` [rows, (hq + 2 hkv) d], returns q
-    [rows, hq, d], and writes k and v at each row's line of the tables [lines, hkv, d]."""
+def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int, rotary: int, write_kv: bool = True,
+                out_dtype: Optional[torch.dtype] = None):
+    """Rotates the q and k heads of the stacked product `qkv` [rows, (hq + 2 hkv) d] (a tensor or a
+    SplitSum), returns q [rows, hq, d], and writes k and v at each row's line of the tables
+    [lines, hkv, d]."""
+    src, in_dt, splits, stride = _src(qkv, "rope_append qkv")
     rows = qkv.shape[0]
-    _need(qkv, "rope_append qkv", shape=(rows, (hq + 2 * hkv) * d))
-    dt = _dt(qkv, "rope_append qkv")
+    if tuple(qkv.shape) != (rows, (hq + 2 * hkv) * d):
+        raise KernelError(f"rope_append: qkv {tuple(qkv.shape)}, expected {(rows, (hq + 2 * hkv) * d)}")
+    out_dtype = out_dtype or (src.dtype if not isinstance(qkv, SplitSum) else k_table.dtype)
     if rotary:
         _need(cos_sin, "rope_append cos_sin", torch.float32, (rows, rotary // 2, 2))
-    q = torch.empty((rows, hq, d), dtype=qkv.dtype, device=qkv.device)
+    q = torch.empty((rows, hq, d), dtype=out_dtype, device=src.device)
     table_lines = 0
     if write_kv:
         _need(lines, "rope_append lines", torch.int32, (rows,))
-        _need(k_table, "rope_append k table", qkv.dtype)
-        _need(v_table, "rope_append v table", qkv.dtype)
+        _need(k_table, "rope_append k table", out_dtype)
+        _need(v_table, "rope_append v table", out_dtype)
         if k_table.shape[-2:] != (hkv, d) or v_table.shape != k_table.shape:
             raise KernelError(f"rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} do not end in ({hkv}, {d})")
         table_lines = k_table.numel() // (hkv * d)
     _check(
         library().kb_rope_append(
-            _ptr(qkv), dt, _ptr(cos_sin if rotary else None), _ptr(lines if write_kv else None), _ptr(q),
-            _ptr(k_table if write_kv else None), _ptr(v_table if write_kv else None),
-            rows, hq, hkv, d, int(rotary), int(bool(write_kv)), ctypes.c_longlong(table_lines), _stream(),
+            _ptr(src), in_dt, splits, ctypes.c_longlong(stride), _ptr(cos_sin if rotary else None),
+            _ptr(lines if write_kv else None), _ptr(q), _ptr(k_table if write_kv else None), _ptr(v_table if write_kv else None),
+            _dt(q, "rope_append output"), rows, hq, hkv, d, int(rotary), int(bool(write_kv)), ctypes.c_longlong(table_lines), _stream(),
         )
     )
     return q
 
 
-def glu(x: torch.Tensor, activation: str) -> torch.Tensor:
-    """act(x[:, :n]) * x[:, n:] for a stacked gate|up product."""
-    _need(x, "glu input")
+def glu(x, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Tensor:
+    """act(x[:, :n]) * x[:, n:] for a stacked gate|up product (a tensor or a SplitSum)."""
+    src, in_dt, splits, stride = _src(x, "glu input")
     if activation not in ACT_CODES:
         raise KernelError(f"glu: activation {activation!r} is not known")
     rows, two_n = x.shape
     n = two_n // 2
-    out = torch.empty((rows, n), dtype=x.dtype, device=x.device)
-    _check(library().kb_glu(_ptr(out), _ptr(x), _dt(x, "glu input"), ctypes.c_longlong(rows), n, ACT_CODES[activation], _stream()))
+    out_dtype = out_dtype or (src.dtype if not isinstance(x, SplitSum) else torch.bfloat16)
+    out = torch.empty((rows, n), dtype=out_dtype, device=src.device)
+    _check(library().kb_glu(_ptr(out), _dt(out, "glu output"), _ptr(src), in_dt, splits, ctypes.c_longlong(stride),
+                            ctypes.c_longlong(rows), n, ACT_CODES[activation], _stream()))
     return out
 
 
@@ -184,10 +235,13 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
 
 def add_rmsnorm(residual, branch, post, nxt, out_dtype):
     """residual += norm_post(branch) (post = (weight, eps, offset) or None: plain add); returns
-    norm_next(residual) when nxt = (weight, eps, offset) is given, else None. In place on residual."""
+    norm_next(residual) when nxt = (weight, eps, offset) is given, else None. In place on
+    residual. `branch` is a tensor or a SplitSum."""
     rows, width = residual.shape
     _need(residual, "add_rmsnorm residual", torch.float32)
-    _need(branch, "add_rmsnorm branch", out_dtype, (rows, width))
+    src, b_dt, splits, stride = _src(branch, "add_rmsnorm branch")
+    if tuple(branch.shape) != (rows, width):
+        raise KernelError(f"add_rmsnorm: branch {tuple(branch.shape)} against residual {(rows, width)}")
     w_post, eps_post, off_post = post if post is not None else (None, 0.0, 0.0)
     w_next, eps_next, off_next = nxt if nxt is not None else (None, 0.0, 0.0)
     ws = [w for w in (w_post, w_next) if w is not None]
@@ -198,15 +252,19 @@ def add_rmsnorm(residual, branch, post, nxt, out_dtype):
     w_dt = _dt(ws[0], "add_rmsnorm weight") if ws else F32
     h = torch.empty((rows, width), dtype=out_dtype, device=residual.device) if w_next is not None else None
     _check(
-        library().kb_add_rmsnorm(_ptr(residual), _ptr(branch), _dt(branch, "add_rmsnorm branch"), _ptr(w_post), _f(eps_post),
-                                 _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), w_dt, rows, width, _stream())
+        library().kb_add_rmsnorm(_ptr(residual), _ptr(src), b_dt, splits, ctypes.c_longlong(stride), _ptr(w_post), _f(eps_post),
+                                 _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), _CODES[out_dtype], w_dt,
+                                 rows, width, _stream())
     )
     return h
 
 
-def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, softcap: Optional[float] = None) -> torch.Tensor:
+def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, softcap: Optional[float] = None,
+         keep_split: bool = False):
     """a [m, k] . w [n, k]^T -> [m, n]; float32 x float32 in true 32-bit, bfloat16 x bfloat16 on
-    tensor cores with 32-bit sums. `softcap` c applies c * tanh(x / c) to the result."""
+    tensor cores with 32-bit sums. `softcap` c applies c * tanh(x / c) to the result. With
+    `keep_split`, a product that the kernel splits over K comes back as a SplitSum (its partial
+    sums, not yet added up) for a kernel that adds them on the way in."""
     _need(a, "gemm input")
     _need(w, "gemm weight")
     m, k = a.shape
@@ -224,6 +282,12 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             out = cast(out, out_dtype)
         return out
     out_dtype = out_dtype or torch.bfloat16
+    if keep_split and softcap is None and 0 < m <= 16:
+        splits = int(lib.kb_gemm_bf16_row16_splits(n, k))
+        if splits > 1:
+            partials = torch.empty((splits, m, n), dtype=torch.float32, device=a.device)
+            _check(lib.kb_gemm_bf16_partial(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
+            return SplitSum(partials)
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
     need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
     scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None

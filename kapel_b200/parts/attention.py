@@ -53,12 +53,13 @@ class Attention(Part):
 
     def forward(self, h, batch, cache):
         s = self.spec
-        qkv = linear(self.ctx, h, self.w_qkv)
+        qkv = linear(self.ctx, h, self.w_qkv, keep_split=True)
         k_table, v_table = cache.tables()
         group = batch.groups[cache.group]
         q = K.rope_append(
             qkv, self.position.tables(batch), group.lines, k_table, v_table,
             s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim, write_kv=cache.owns,
+            out_dtype=self.ctx.dtype,
         )
         heads_per_kv = s.num_heads // s.num_kv_heads
         if K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
@@ -72,4 +73,4 @@ class Attention(Part):
                 q, k_table, v_table, group.block_table, batch.row_entry, batch.row_count,
                 self.ctx.page_size, s.window, s.scale, s.softcap, batch.attention_slots(s.window),
             )
-        return linear(self.ctx, y.view(y.shape[0], s.num_heads * s.head_dim), self.w_o)
+        return linear(self.ctx, y.view(y.shape[0], s.num_heads * s.head_dim), self.w_o, keep_split=True)

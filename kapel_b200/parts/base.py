@@ -13,9 +13,10 @@ and, by category:
     position      apply(q_and_k ...) is not called by the engine: a mixer owns its position
                   encoding and asks it for what it needs; kind "rope" gives `tables(batch)`.
     mixer         cache_needs() -> CacheNeeds
-                  forward(h, batch, cache) -> [rows, hidden] in the activation dtype
+                  forward(h, batch, cache) -> [rows, hidden] in the activation dtype (or a
+                      kernels.SplitSum of that shape, which the block's residual sum adds up)
                       h: [rows, hidden]; batch: engine.batch.StepBatch; cache: LayerCache
-    feed_forward  forward(h) -> [rows, hidden]
+    feed_forward  forward(h) -> [rows, hidden] (a tensor or a kernels.SplitSum)
     every part    graph_safe: bool (see `Part`)
     block         forward(x, h, batch, cache, next_norm) -> (x, h_next)
                       x: the float32 residual [rows, hidden] (updated in place);
@@ -97,9 +98,11 @@ def matrix_for(ctx: BuildContext, t: torch.Tensor) -> torch.Tensor:
 
 
 def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,
-           softcap: Optional[float] = None) -> torch.Tensor:
+           softcap: Optional[float] = None, keep_split: bool = False):
     """x . w^T through the library's kernels. A weight kept in 32-bit on the bfloat16 path is
-    multiplied in true 32-bit: the input is widened first and the result narrowed after."""
+    multiplied in true 32-bit: the input is widened first and the result narrowed after. With
+    `keep_split` the result may be a `kernels.SplitSum` (partial sums of a product split over K)
+    for a consumer that adds them up itself: `add_branch`, `kernels.glu`, `kernels.rope_append`."""
     from .. import kernels as K
 
     out_dtype = out_dtype or ctx.dtype
@@ -107,4 +110,4 @@ def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optio
         x = K.cast(x, torch.float32)
     elif w.dtype == torch.bfloat16 and x.dtype != torch.bfloat16:
         x = K.cast(x, torch.bfloat16)
-    return K.gemm(x, w, out_dtype=out_dtype, softcap=softcap)
+    return K.gemm(x, w, out_dtype=out_dtype, softcap=softcap, keep_split=keep_split)

@@ -37,6 +37,6 @@ class GatedMLP(Part):
         self.w_down = matrix_for(self.ctx, tensors[w["down"]])
 
     def forward(self, h):
-        gu = linear(self.ctx, h, self.w_gate_up)
-        inner = K.glu(gu, self.spec.activation)
-        return linear(self.ctx, inner, self.w_down)
+        gu = linear(self.ctx, h, self.w_gate_up, keep_split=True)
+        inner = K.glu(gu, self.spec.activation, out_dtype=self.ctx.dtype)
+        return linear(self.ctx, inner, self.w_down, keep_split=True)

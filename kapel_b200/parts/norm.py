@@ -32,7 +32,7 @@ def add_branch(ctx, residual, branch, post_norm, next_norm):
     post_key = post_norm.fuse_key() if hasattr(post_norm, "fuse_key") else None
     next_key = next_norm.fuse_key() if hasattr(next_norm, "fuse_key") else None
     if post_norm is not None and post_key is None:
-        branch = post_norm.forward(branch)
+        branch = post_norm.forward(K.finish(branch, ctx.dtype))
     if next_key is not None and (post_key is None or post_key[0].dtype == next_key[0].dtype):
         return K.add_rmsnorm(residual, branch, post_key, next_key, ctx.dtype)
     K.add_rmsnorm(residual, branch, post_key, None, ctx.dtype)

@@ -156,11 +156,18 @@ def test_gemm_bf16_refuses_what_it_cannot_take():
 
 
 def test_gemm_bf16_small_rows_do_not_depend_on_the_batch():
+    """Within a kernel (17..64 rows here; up to 16 rows in a test of its own below) a row's sums
+    are added in the same order whatever else is in the batch: bit for bit. Across kernels the
+    order differs, and the results agree to rounding."""
     a, w = rnd(40, 2304, seed=15, dtype=torch.bfloat16), rnd(520, 2304, seed=16, dtype=torch.bfloat16)
     whole = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu()
+    part = K().gemm(dev(a[7:40]), dev(w), out_dtype=torch.float32).cpu()
+    assert torch.equal(whole[7:40], part)
+    part = K().gemm(dev(a[20:38]), dev(w), out_dtype=torch.float32).cpu()
+    assert torch.equal(whole[20:38], part)
     for r in (0, 17, 39):
         alone = K().gemm(dev(a[r : r + 1]), dev(w), out_dtype=torch.float32).cpu()
-        assert torch.equal(whole[r : r + 1], alone)
+        assert rel_err(alone.numpy(), whole[r : r + 1].numpy()) < 2e-6
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -370,3 +377,62 @@ def test_paged_attention_mma_far_key_and_window_edge(decode):
         want = paged_reference(q, kt2, vt2, bt, re, rc, page, win, 1.0, None)
         assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
         assert (abs(float(got[0, 0].mean()) - 5.0) < 0.1) == seen
+
+
+# ------------------------------------------------------------------------------------------
+def test_split_sums_are_added_up_by_their_readers():
+    """A decode-size product split over K stays a stack of partial sums; the norm, the gated unit
+    and the rotation add the slices up themselves and give what they give for the finished sum."""
+    m, k = 5, 2304
+    a = rnd(m, k, seed=30, dtype=torch.bfloat16)
+    for n in (2304, 4096):
+        w = rnd(n, k, seed=31, dtype=torch.bfloat16, scale=0.05)
+        split = K().gemm(dev(a), dev(w), keep_split=True)
+        assert isinstance(split, K().SplitSum) and split.splits > 1 and split.shape == (m, n)
+        whole = K().gemm(dev(a), dev(w), out_dtype=torch.float32)
+        done = K().finish(split, torch.float32)
+        assert torch.equal(done, whole), "the same kernel and the same order of additions"
+        assert rel_err(done.cpu().numpy(), (a.double() @ w.double().T).numpy()) < 2e-5
+    # the residual sum with both norms
+    n = 2304
+    w = rnd(n, k, seed=32, dtype=torch.bfloat16, scale=0.05)
+    split = K().gemm(dev(a), dev(w), keep_split=True)
+    branch = (a.double() @ w.double().T)
+    res = rnd(m, n, seed=33)
+    w1, w2 = rnd(n, seed=34, dtype=torch.bfloat16, scale=0.1), rnd(n, seed=35, dtype=torch.bfloat16, scale=0.1)
+    r = dev(res.clone())
+    h = K().add_rmsnorm(r, split, (dev(w1), 1e-6, 1.0), (dev(w2), 1e-6, 1.0), torch.bfloat16)
+    want_r = res.double() + P.rms_norm(branch, w1.double(), 1e-6)
+    assert rel_err(r.cpu().double().numpy(), want_r.numpy()) < 1e-5
+    assert rel_err(h.cpu().double().numpy(), P.rms_norm(want_r, w2.double(), 1e-6).numpy()) < 1e-2
+    # the gated unit
+    n = 2 * 1152
+    w = rnd(n, k, seed=36, dtype=torch.bfloat16, scale=0.05)
+    split = K().gemm(dev(a), dev(w), keep_split=True)
+    assert isinstance(split, K().SplitSum)
+    x = a.double() @ w.double().T
+    got = K().glu(split, "gelu_tanh", out_dtype=torch.bfloat16).cpu().double()
+    assert rel_err(got.numpy(), (P.gelu_tanh(x[:, :1152]) * x[:, 1152:]).numpy()) < 1e-2
+    # the rotation and the cache append
+    hq, hkv, d = 8, 4, 64
+    w = rnd((hq + 2 * hkv) * d, k, seed=37, dtype=torch.bfloat16, scale=0.05)
+    split = K().gemm(dev(a), dev(w), keep_split=True)
+    assert isinstance(split, K().SplitSum)
+    pos = torch.tensor([0, 3, 9, 100, 7], dtype=torch.int32)
+    lines = torch.tensor([4, 0, 9, -1, 2], dtype=torch.int32)
+    kt = torch.zeros(10, hkv, d, dtype=torch.bfloat16).cuda()
+    vt = torch.zeros(10, hkv, d, dtype=torch.bfloat16).cuda()
+    cs = K().rope_table(dev(pos), d, 10000.0)
+    q = K().rope_append(split, cs, dev(lines), kt, vt, hq, hkv, d, d, out_dtype=torch.bfloat16).cpu().double()
+    x = (a.double() @ w.double().T).reshape(m, hq + 2 * hkv, d)
+    assert rel_err(q.numpy(), P.rope(x[:, :hq], pos, 10000.0).numpy()) < 1e-2
+    assert rel_err(kt.cpu().double()[4].numpy(), P.rope(x[:, hq : hq + hkv], pos, 10000.0)[0].numpy()) < 1e-2
+    assert rel_err(vt.cpu().double()[9].numpy(), x[2, hq + hkv :].numpy()) < 1e-2
+
+
+@pytest.mark.parametrize("m", [1, 7, 8, 9, 16])
+def test_gemm_bf16_rows_up_to_16_do_not_depend_on_the_batch(m):
+    a, w = rnd(16, 2304, seed=38, dtype=torch.bfloat16), rnd(520, 2304, seed=39, dtype=torch.bfloat16)
+    whole = K().gemm(dev(a[:m]), dev(w), out_dtype=torch.float32).cpu()
+    alone = K().gemm(dev(a[m - 1 : m]), dev(w), out_dtype=torch.float32).cpu()
+    assert torch.equal(whole[m - 1 : m], alone)
