@@ -1,0 +1,279 @@
+// C[M,N] = A[M,K] . W[N,K]^T for bfloat16 inputs on the fifth-generation tensor cores:
+// tcgen05.mma issued by one thread, operands staged in shared memory by TMA (cp.async.bulk.tensor,
+// 128-byte swizzle, no multicast), the 128 x 256 accumulator in tensor memory (TMEM), read back
+// with tcgen05.ld for the epilogue. Used for prompt portions (M > 64); Kapel's counterpart is the
+// cutile `batched_matmul_nt` (crates/kapel-cuda/src/tile.rs:65-87), which has no sm_100 path.
+//
+// One block computes one 128 x 256 tile of C. Six warps:
+//   warp 0    one lane walks K in steps of 64 and asks TMA for the A and W tiles of each step, four
+//             stages deep; a stage is free again when the MMAs that read it have completed
+//             (tcgen05.commit on the stage's "empty" mbarrier)
+//   warp 1    allocates 256 TMEM columns; one lane waits for a stage to fill and issues four
+//             128 x 256 x 16 MMAs on it (the shared-memory descriptors step 32 bytes through the
+//             swizzle atom), then commits; after the last step it commits on the "accumulator full"
+//             mbarrier
+//   warps 2-5 wait for the accumulator, read their quarter of its 128 lanes 32 columns at a time,
+//             apply the epilogue (soft cap) and store
+// Rows and columns beyond M, N and K are zero-filled by TMA on the way in and skipped on the way out.
+//
+// Every wait on an mbarrier gives up after about a second: the waiter raises a flag that
+// `kb_tcgen05_error` reports, skips its remaining work, and the block still meets at its final
+// barrier, frees its TMEM and returns.
+#include <cuda.h>
+#include <mutex>
+#include <unordered_map>
+
+#include "common.cuh"
+
+namespace kb {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_THREADS = 192;
+constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;                  // 16 KB
+constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;                  // 32 KB
+constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
+constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int TC_TMEM_COLS = 256;
+
+__device__ int g_tcgen05_error = 0;
+
+__device__ __forceinline__ uint32_t tc_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+
+__device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(tc_saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_saddr(bar)), "r"(bytes) : "memory");
+}
+// false if the phase with this parity did not complete within ~1 s
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = tc_saddr(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - start > 2000000000ll) return false;
+    }
+}
+__device__ __forceinline__ void tc_tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(tc_saddr(dst)), "l"(map), "r"(tc_saddr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tc_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(tc_saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void tc_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void tc_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+
+// Shared-memory matrix descriptor of a K-major tile with 128-byte rows under the 128-byte swizzle:
+// start address / 16 in bits [0,14); leading byte offset / 16 = 1 in [16,30); stride byte offset
+// / 16 = 64 (eight rows of 128 bytes) in [32,46); version 1 in [46,48); layout type 2 (128-byte
+// swizzle) in [61,64).
+__device__ __forceinline__ uint64_t tc_smem_desc(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D float32 (1 at bit 4), A and B bfloat16 (1 at bits 7 and 10),
+// both K-major (0 at bits 15, 16), N / 8 at bits [17,23), M / 16 at bits [24,29).
+constexpr uint32_t TC_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(TC_BN >> 3) << 17) | ((uint32_t)(TC_BM >> 4) << 24);
+
+__device__ __forceinline__ void tc_mma(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(TC_IDESC), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+}
+
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                    void* __restrict__ c, int c_dt, int m, int n, int k, int epi, float cap) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    // 1024-byte alignment for the 128-byte swizzle
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + TC_STAGES * TC_STAGE_BYTES);
+    uint64_t* empty = full + TC_STAGES;
+    uint64_t* accum = empty + TC_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    const int k_tiles = (k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
+        tc_mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(TC_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % TC_STAGES;
+                if (kt >= TC_STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / TC_STAGES) - 1) & 1u)) { failed = true; break; }
+                unsigned char* a_dst = smem + s * TC_STAGE_BYTES;
+                tc_mbar_expect_tx(full + s, TC_STAGE_BYTES);
+                tc_tma_load_2d(a_dst, &map_a, kt * TC_BK, m0, full + s);
+                tc_tma_load_2d(a_dst + TC_A_BYTES, &map_w, kt * TC_BK, n0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % TC_STAGES;
+                if (!tc_mbar_wait(full + s, (uint32_t)(kt / TC_STAGES) & 1u)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t a_addr = tc_saddr(smem + s * TC_STAGE_BYTES);
+                const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + TC_A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < TC_BK / 16; ++kk)            // 32 bytes further into the swizzle atom each step
+                    tc_mma(tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), (kt | kk) != 0 ? 1u : 0u);
+                tc_commit(empty + s);                               // arrives when these MMAs have read the stage
+            }
+            if (!failed) tc_commit(accum);                          // arrives when the accumulator is complete
+        }
+    } else {
+        const int quarter = warp & 3;                               // the TMEM lanes this warp may read
+        // the same answer in every lane: the TMEM loads below must run with the whole warp together
+        if (!__all_sync(0xffffffffu, tc_mbar_wait(accum, 0u))) {
+            failed = true;
+        } else {
+            tc_fence_after();
+            const int row = m0 + quarter * 32 + lane;
+            const bool vec = (c_dt == KB_DT_BF16) ? (n % 8 == 0) : (n % 4 == 0);
+            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
+                uint32_t r[32];
+                __syncwarp();                                       // lanes that skipped their stores rejoin here
+                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                const int col = n0 + c0;
+                if (row >= m || col >= n) continue;
+                float v[32];
+#pragma unroll
+                for (int j = 0; j < 32; ++j) {
+                    v[j] = __uint_as_float(r[j]);
+                    if (epi == 1) v[j] = cap * tanhf(v[j] / cap);
+                }
+                if (c_dt == KB_DT_BF16) {
+                    bf16* dst = static_cast<bf16*>(c) + (size_t)row * n + col;
+                    if (vec && col + 32 <= n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 8) {
+                            uint4 o;
+                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
+                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
+                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+                            *reinterpret_cast<uint4*>(dst + j) = o;
+                        }
+                    } else {
+                        for (int j = 0; j < 32 && col + j < n; ++j) dst[j] = __float2bfloat16_rn(v[j]);
+                    }
+                } else {
+                    float* dst = static_cast<float*>(c) + (size_t)row * n + col;
+                    if (vec && col + 32 <= n) {
+#pragma unroll
+                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
+                    } else {
+                        for (int j = 0; j < 32 && col + j < n; ++j) dst[j] = v[j];
+                    }
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(&g_tcgen05_error, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// ---- tensor maps
+typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+static EncodeTiledFn g_encode = nullptr;
+
+static int get_encoder() {
+    if (g_encode != nullptr) return 0;
+    void* fn = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res);
+    if (e != cudaSuccess || fn == nullptr || res != cudaDriverEntryPointSuccess)
+        return fail("gemm_tcgen05: the driver does not give cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
+    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
+    return 0;
+}
+
+// A [rows, k] bfloat16 row-major matrix seen in boxes of box_rows x 64 elements, 128-byte swizzle.
+static int make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
+    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
+    const cuuint64_t strides[1] = {(cuuint64_t)k * sizeof(bf16)};
+    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
+    const cuuint32_t elem[2] = {1, 1};
+    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
+                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
+                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+    if (r != CUDA_SUCCESS) return fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d for [%d, %d]", (int)r, rows, k);
+    return 0;
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+// 1 if a wait inside the tcgen05 product ever ran out (and clears the flag); synchronises the device.
+extern "C" int kb_tcgen05_error() {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_tcgen05_error, sizeof(int)) != cudaSuccess) return -1;
+    if (flag) cudaMemcpyToSymbol(g_tcgen05_error, &zero, sizeof(int));
+    return flag;
+}
+
+// a: bf16 [m,k]; w: bf16 [n,k]; c: bf16 or f32 [m,n]. Any m, n; k a multiple of 8.
+extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, int m, int n, int k, int epilogue,
+                               float cap, void* stream) {
+    KB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_tcgen05: m %d, n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_tcgen05: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(c_dt == KB_DT_F32 || c_dt == KB_DT_BF16, "gemm_tcgen05: output dtype code %d is not known", c_dt);
+    KB_REQUIRE(epilogue == 0 || (epilogue == 1 && cap > 0.f), "gemm_tcgen05: epilogue %d with cap %g", epilogue, cap);
+    KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)c & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+    if (int e = get_encoder()) return e;
+    CUtensorMap map_a, map_w;
+    if (int e = make_map(&map_a, a, m, k, TC_BM)) return e;
+    if (int e = make_map(&map_w, w, n, k, TC_BN)) return e;
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", TC_SMEM_BYTES, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    dim3 grid((n + TC_BN - 1) / TC_BN, (m + TC_BM - 1) / TC_BM);
+    KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d rows is too many for one launch", m);
+    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
+    return check_launch("gemm_tcgen05");
+}

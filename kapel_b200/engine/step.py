@@ -200,3 +200,7 @@ class Engine:
         """The request is finished: everything it holds goes back."""
         if seq_id in self.cache:
             self.cache.remove_sequence(seq_id)
+
+    def check(self) -> None:
+        """Synchronises and raises if a kernel's bounded wait ever ran out (`kernels.check_async_errors`)."""
+        K.check_async_errors()

@@ -21,6 +21,12 @@ _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 ACT_CODES = {"gelu_tanh": 0, "silu": 1}
 
+# Which kernel multiplies more than 64 rows of bfloat16: "tcgen05" (TMA, TMEM, tcgen05.mma) or
+# "mma" (the warp-level mma.sync tile kernel, kept as the yardstick the tcgen05 kernel is measured against).
+import os as _os
+
+GEMM_LARGE = _os.environ.get("KAPEL_B200_GEMM_LARGE", "tcgen05")
+
 
 class KernelError(RuntimeError):
     """A launcher refused its arguments or a launch failed; the message is the library's."""
@@ -42,6 +48,19 @@ def library():
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 _lib = lib
     return _lib
+
+
+def check_async_errors() -> None:
+    """Raises if a bounded wait inside a kernel (on an mbarrier: a TMA copy or a tensor-core
+    commit that never arrived) ran out since the last check. Synchronises the device."""
+    lib = library()
+    bad = []
+    if lib.kb_attention_error() != 0:
+        bad.append("paged attention (a bulk copy into shared memory never completed)")
+    if lib.kb_tcgen05_error() != 0:
+        bad.append("tcgen05 product (a TMA load or an MMA commit never arrived)")
+    if bad:
+        raise KernelError("a wait inside a kernel gave up after its time limit: " + "; ".join(bad))
 
 
 def launch_count() -> int:
@@ -289,6 +308,9 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             _check(lib.kb_gemm_bf16_partial(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
             return SplitSum(partials)
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    if m > 64 and GEMM_LARGE == "tcgen05":
+        _check(lib.kb_gemm_tcgen05(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
+        return out
     need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
     scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
     _check(lib.kb_gemm_bf16(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _ptr(scratch), _stream()))

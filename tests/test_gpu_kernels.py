@@ -149,6 +149,27 @@ def test_gemm_bf16(m, n, k):
     assert rel_err(got.numpy(), (30.0 * torch.tanh(want / 30.0)).numpy()) < 2e-5
 
 
+@pytest.mark.parametrize("m,n,k", [(65, 256, 64), (128, 256, 128), (129, 300, 200), (2048, 2304, 2048), (300, 4104, 72), (1000, 18432, 2304)])
+def test_gemm_tcgen05(m, n, k):
+    """The tcgen05 kernel (more than 64 rows) and, as a yardstick, the mma.sync tile kernel."""
+    a, w = rnd(m, k, seed=40, dtype=torch.bfloat16), rnd(n, k, seed=41, dtype=torch.bfloat16, scale=0.1)
+    want = a.double() @ w.double().T
+    got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+    K().check_async_errors()
+    assert rel_err(got.numpy(), want.numpy()) < 2e-5
+    got = K().gemm(dev(a), dev(w)).cpu().double()
+    assert rel_err(got.numpy(), want.numpy()) < 1e-2
+    import kapel_b200.kernels as KK
+
+    old = KK.GEMM_LARGE
+    KK.GEMM_LARGE = "mma"
+    try:
+        got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+    finally:
+        KK.GEMM_LARGE = old
+    assert rel_err(got.numpy(), want.numpy()) < 2e-5
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take():
     a, w = rnd(4, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
     with pytest.raises(K().KernelError, match="multiple of 8"):
