@@ -100,7 +100,7 @@ class CacheGroup:
         self.window = needs.window
         self.pool = PagePool(n_pages)
         self.layers: List[int] = []
-        self.keys: Dict[int, object] = {}      # layer -> table [pages, page_size, kv_heads, head_dim]
+        self.keys: Dict[int, object] = {}      # layer -> table [pages, kv_heads, page_size, head_dim]
         self.values: Dict[int, object] = {}
 
     @property
@@ -153,10 +153,11 @@ class CacheManager:
 
     # ------------------------------------------------------------------ device tables
     def allocate_tables(self, allocate: Callable, dtype) -> None:
-        """Makes K and V tables [pages, page_size, kv_heads, head_dim] per layer, and state
+        """Makes K and V tables [pages, kv_heads, page_size, head_dim] per layer (the keys of one kv
+        head in one page lie together, so a kernel fetches them in one piece), and state
         tables [slots + 1, *shape]; they never move afterwards, so a recorded step stays valid."""
         for g in self.groups:
-            shape = (max(g.pool.n_pages, 1), self.page_size, g.needs.kv_heads, g.needs.head_dim)
+            shape = (max(g.pool.n_pages, 1), g.needs.kv_heads, self.page_size, g.needs.head_dim)
             for layer in g.layers:
                 g.keys[layer] = allocate(shape, dtype)
                 g.values[layer] = allocate(shape, dtype)

@@ -11,16 +11,21 @@
 //    time by cp.async in two stages; each of 4 warps owns 16 rows and walks all keys;
 //  * `attention_decode_kernel` (16 rows: a few tokens of one request): the 4 warps share the rows;
 //    each warp streams its own tiles of 16 keys through a three-stage pipeline of its own, filled
-//    by the copy engine (cp.async.bulk, one copy a key row, completion on an mbarrier), so the
-//    loop has no block-wide barrier, a tile costs two instructions a lane to fetch, and ~128 KB
-//    are in flight a multiprocessor; each warp keeps a softmax state of its own and the four are
-//    merged through shared memory. Every wait on an mbarrier gives up after about a second,
-//    raises a flag that `kb_attention_error` reports, and the block leaves without writing;
+//    by TMA: the cache tables are [pages, kv heads, page size, head_dim], so the 16 keys of a kv
+//    head lie together, and a tile arrives as head_dim / 64 boxes of 16 x 64 elements for the keys
+//    and as many for the values (cp.async.bulk.tensor, 128-byte swizzle, completion on an
+//    mbarrier). The loop has no block-wide barrier, a tile costs one instruction in each of 8 lanes
+//    to fetch, and ~128 KB are in flight a multiprocessor. The products are taken with the
+//    operands swapped (S^T = K Q^T, O^T = V^T P^T: the keys are the MMAs' M). Each warp keeps a
+//    softmax state of its own and the four are merged through shared memory. Every wait on an
+//    mbarrier gives up after about a second, raises a flag that `kb_attention_error` reports, and
+//    the block leaves without writing;
 //  * score = scale * q.k, then cap * tanh(score / cap) (tanh.approx), then the mask: a row that
 //    has seen c positions reads keys [max(0, c - window), c);
 //  * with `split` > 0 the keys are also cut at absolute multiples of `split` across blockIdx.z;
 //    each block writes (sum p.v, max, sum p) to scratch memory and a second kernel merges them.
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 namespace kb {
 
@@ -32,7 +37,7 @@ constexpr int AM_PAD = 8;             // elements of padding a shared-memory row
 
 struct AttMmaParams {
     const bf16* q;             // [rows, hq, d]
-    const bf16* k_table;       // [lines, hkv, d]
+    const bf16* k_table;       // [pages, hkv, page_size, d]
     const bf16* v_table;
     const int* block_table;    // [entries, table_width]
     const int* row_count;      // [rows]
@@ -99,6 +104,18 @@ __device__ __forceinline__ void am_mbar_expect_tx(uint64_t* bar, uint32_t bytes)
 __device__ __forceinline__ void am_bulk_copy(void* dst, const void* src, uint32_t bytes, uint64_t* bar) {
     asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
                  ::"r"(am_saddr(dst)), "l"(src), "r"(bytes), "r"(am_saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void am_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(am_saddr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void am_ldmatrix_x4_at(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
+}
+__device__ __forceinline__ void am_ldmatrix_x4_trans_at(uint32_t (&r)[4], uint32_t saddr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(saddr));
 }
 // Waits for the phase with this parity to complete; false if it did not within ~1 s.
 __device__ __forceinline__ bool am_mbar_wait(uint64_t* bar, uint32_t parity) {
@@ -211,6 +228,115 @@ __device__ __forceinline__ void am_tile(const bf16* q16, const bf16* tK, const b
     }
 }
 
+// The same work with the operands swapped, for the decode kernel, where only a few of the 16
+// rows exist: S^T = K Q^T and O^T = V^T P^T. The 16 keys are the MMAs' M; the rows ("heads" here:
+// (token, query head) pairs) are their N, eight a block, NB blocks. Q waits in registers as B
+// fragments (`bq`), so it costs no load in the loop; O^T is 16 x NB x 4 registers instead of 128;
+// and 16 keys cost 16 + 16 MMAs and ldmatrix instead of 32 + 32 and 48.
+//   Lane (g, t) holds S^T[key g (+8)][head 8 nb + 2t (+1)]; cnt/fst are those heads' counts and
+//   first visible keys; m_run/l_run their softmax states (every g holds a copy; the row sums stay
+//   per lane until the end). `ot[nd][nb]` holds O^T[dim 16 nd + g (+8)][head 8 nb + 2t (+1)].
+//   tK, tV: shared-memory addresses (1024-byte aligned) of the tile's keys and values as TMA left
+//   them: boxes of 16 rows x 64 elements (2 KB), one after the other along head_dim, each under the
+//   128-byte swizzle: the 16-byte piece c of row r lies at piece c ^ (r & 7).
+template <int HD, int NB, bool FULL>
+__device__ __forceinline__ void ad_tile(const uint32_t (&bq)[HD / 16][NB][2], uint32_t tK, uint32_t tV, int d,
+                                        int j0, const int (&cnt)[NB][2], const int (&fst)[NB][2], int fst_hi, int cnt_lo,
+                                        int klo, int khi, float sc, float cap, float (&ot)[HD / 16][NB][4],
+                                        float (&m_run)[NB][2], float (&l_run)[NB][2], int lane) {
+    const int g = lane >> 2, t = lane & 3;
+    const float LOG2E = 1.4426950408889634f;
+    float st[NB][4];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) st[nb][0] = st[nb][1] = st[nb][2] = st[nb][3] = 0.f;
+    const int krow = (lane & 7) + ((lane >> 3) & 1) * 8;       // the key row this lane addresses
+    const uint32_t ka = tK + krow * 128;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        if (FULL || ks * 16 < d) {
+            uint32_t a[4];
+            const int piece = ((ks & 3) << 1) + (lane >> 4);   // 16-byte piece within the box's 128-byte row
+            am_ldmatrix_x4_at(a, ka + (ks >> 2) * 2048 + ((piece ^ (krow & 7)) << 4));
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) am_mma(st[nb], a, bq[ks][nb][0], bq[ks][nb][1]);
+        }
+    }
+    const bool inner = j0 >= fst_hi && j0 + 16 <= cnt_lo && j0 >= klo && j0 + 16 <= khi;
+    float alpha[NB][2];
+    uint32_t pb[NB][2];
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) {
+        float mx[2] = {-INFINITY, -INFINITY};
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e & 1;                             // head 2t + h; key g + 8 (e >> 1)
+            float v = st[nb][e] * sc;
+            if (cap > 0.f) v = cap * am_tanh(v);
+            if (!inner) {
+                const int j = j0 + g + (e >> 1) * 8;
+                const bool seen = j >= fst[nb][h] && j < cnt[nb][h] && j >= klo && j < khi;
+                v = seen ? v : -INFINITY;
+            }
+            st[nb][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                        // over the 16 keys: across g
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 4));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 8));
+            mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 16));
+            const float m_new = fmaxf(m_run[nb][h], mx[h]);
+            alpha[nb][h] = (m_new == -INFINITY) ? 1.f : am_exp2((m_run[nb][h] - m_new) * LOG2E);
+            m_run[nb][h] = m_new;
+            l_run[nb][h] *= alpha[nb][h];
+        }
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e & 1;
+            pv[e] = (st[nb][e] == -INFINITY) ? 0.f : am_exp2((st[nb][e] - m_run[nb][h]) * LOG2E);
+            l_run[nb][h] += pv[e];
+        }
+        // P^T as a B fragment: lane (g, t) needs P[head 8 nb + g][keys 2t, 2t+1, 2t+8, 2t+9]. Key 2t
+        // lives in lane (2t, g / 2), key 2t + 1 in lane (2t + 1, g / 2); the head picks the component.
+        const int src_a = (2 * t) * 4 + (g >> 1), src_b = src_a + 4;
+        float qa[4], qb[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            qa[e] = __shfl_sync(0xffffffffu, pv[e], src_a);
+            qb[e] = __shfl_sync(0xffffffffu, pv[e], src_b);
+        }
+        const int odd = g & 1;
+        pb[nb][0] = am_pack(odd ? qa[1] : qa[0], odd ? qb[1] : qb[0]);
+        pb[nb][1] = am_pack(odd ? qa[3] : qa[2], odd ? qb[3] : qb[2]);
+    }
+    bool rescale = false;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb) rescale = rescale || alpha[nb][0] != 1.f || alpha[nb][1] != 1.f;
+    if (__any_sync(0xffffffffu, rescale)) {                  // the running maximum settles after a few tiles
+#pragma unroll
+        for (int nd = 0; nd < HD / 16; ++nd)
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) {
+                ot[nd][nb][0] *= alpha[nb][0]; ot[nd][nb][1] *= alpha[nb][1];
+                ot[nd][nb][2] *= alpha[nb][0]; ot[nd][nb][3] *= alpha[nb][1];
+            }
+    }
+    // V^T as A fragments by transposing loads: matrix i of a load is keys 8 (i / 2).., dims 8 (i % 2)..
+    const int vrow = (lane & 7) + ((lane >> 4) & 1) * 8;
+    const uint32_t va = tV + vrow * 128;
+#pragma unroll
+    for (int nd = 0; nd < HD / 16; ++nd) {
+        if (FULL || nd * 16 < d) {
+            uint32_t a[4];
+            const int piece = ((nd & 3) << 1) + ((lane >> 3) & 1);
+            am_ldmatrix_x4_trans_at(a, va + (nd >> 2) * 2048 + ((piece ^ (vrow & 7)) << 4));
+#pragma unroll
+            for (int nb = 0; nb < NB; ++nb) am_mma(ot[nd][nb], a, pb[nb][0], pb[nb][1]);
+        }
+    }
+}
+
 // The line of key position j of a request, or -1 if the block table has no page for it.
 __device__ __forceinline__ long long am_line(const AttMmaParams& p, int entry, int j) {
     const int lp = j / p.page_size;
@@ -293,7 +419,7 @@ attention_mma_kernel(const AttMmaParams p) {
             const int r = idx / chunks, ch = idx - r * chunks;
             const int line = lines[r];
             const bool valid = line >= 0;
-            const size_t off = ((size_t)(valid ? line : 0) * p.hkv + kvh) * d + ch * 8;
+            const size_t off = kv_row(valid ? line : 0, kvh, p.hkv, p.page_size) * d + ch * 8;
             am_cp_async16(sK + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.k_table + off, valid);
             am_cp_async16(sV + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.v_table + off, valid);
         }
@@ -363,18 +489,24 @@ attention_mma_kernel(const AttMmaParams p) {
 constexpr int AD_WK = 16;             // keys a warp tile
 constexpr int AD_STAGES = 3;
 
-template <int HD, bool FULL>
+template <int HD, int NB, bool FULL>
 __global__ void __launch_bounds__(AM_THREADS)
-attention_decode_kernel(const AttMmaParams p) {
-    constexpr int NT_O = HD / 8;
+attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap map_k,
+                        const __grid_constant__ CUtensorMap map_v) {
     extern __shared__ __align__(128) unsigned char am_smem[];
     const int d = p.d;
     const int ld = d + AM_PAD;
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
     bf16* sQ = reinterpret_cast<bf16*>(am_smem);            // [16][ld]
-    bf16* sW = sQ + 16 * ld + (size_t)warp * (2 * AD_STAGES * AD_WK * ld);   // this warp's [STAGES][K|V][16][ld]
-    // after the pipelines (or the merge buffers, whichever is larger): one mbarrier a warp and stage
+    // The pipelines start at the next multiple of 1024 bytes (the swizzle's period); a stage is the
+    // tile's keys then its values, each head_dim / 64 boxes of 2 KB.
+    const int nbox = (d + 63) / 64;
+    const uint32_t stage_bytes = 2u * nbox * 2048u;
+    const uint32_t smem0 = am_saddr(am_smem);
+    const uint32_t pipes = ((smem0 + 16 * ld * (uint32_t)sizeof(bf16) + 1023u) & ~1023u);
+    const uint32_t my_pipe = pipes + (uint32_t)warp * AD_STAGES * stage_bytes;
+    unsigned char* pipes_ptr = am_smem + (pipes - smem0);
     uint64_t* bars = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + warp * AD_STAGES;
 
     const int kvh = blockIdx.y, slot = blockIdx.z;
@@ -406,26 +538,29 @@ attention_decode_kernel(const AttMmaParams p) {
     am_commit();
     __syncthreads();                                        // every warp's barriers are initialised
 
-    // Lane r (r < 16) owns key row r of a tile: it asks the copy engine for the row's keys and its
-    // values (two copies of d elements), or clears the rows if the position is not the block's.
-    const uint32_t row_bytes = (uint32_t)d * sizeof(bf16);
+    // A tile is 16 consecutive positions from a multiple of 16: with pages of a multiple of 16
+    // positions it lies in one page, where the kv head's rows are consecutive. Lane i < nbox asks
+    // TMA for box i of the keys, lane nbox + i for box i of the values. A tile whose page the
+    // block table does not hold is cleared instead. Positions of the tile outside the block's
+    // range arrive too (they are masked): what a page holds beyond a sequence's end is what an
+    // earlier sequence left there, finite values that meet a weight of exactly zero.
+    const uint32_t tile_bytes = stage_bytes;
     auto load_tile = [&](int stage, int tile) {
-        const int j = k_begin + tile * AD_WK + lane;
-        const long long line = (lane < AD_WK && j >= klo && j < khi) ? am_line(p, x.entry, j) : -1;
-        const unsigned live = __ballot_sync(0xffffffffu, line >= 0);
-        bf16* kd = sW + ((size_t)(2 * stage) * AD_WK + lane) * ld;
-        bf16* vd = sW + ((size_t)(2 * stage + 1) * AD_WK + lane) * ld;
-        if (lane == 0) am_mbar_expect_tx(bars + stage, 2u * row_bytes * (uint32_t)__popc(live));
-        __syncwarp();                                       // the expectation is set before a copy can complete
+        const int j = k_begin + tile * AD_WK;
+        const long long line = am_line(p, x.entry, max(j, klo));       // the tile's page, by a position the block owns
+        const uint32_t dst = my_pipe + (uint32_t)stage * stage_bytes;
         if (line >= 0) {
-            const size_t off = ((size_t)line * p.hkv + kvh) * d;
-            am_bulk_copy(kd, p.k_table + off, row_bytes, bars + stage);
-            am_bulk_copy(vd, p.v_table + off, row_bytes, bars + stage);
-        } else if (lane < AD_WK) {
-            for (int c = 0; c < chunks; ++c) {
-                *reinterpret_cast<uint4*>(kd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-                *reinterpret_cast<uint4*>(vd + c * 8) = make_uint4(0u, 0u, 0u, 0u);
-            }
+            const long long page = line / p.page_size;
+            const int row = (int)((page * p.hkv + kvh) * p.page_size + j % p.page_size);
+            if (lane == 0) am_mbar_expect_tx(bars + stage, tile_bytes);
+            __syncwarp();                                   // the expectation is set before a copy can complete
+            if (lane < nbox) am_tma_box(dst + lane * 2048u, &map_k, lane * 64, row, bars + stage);
+            else if (lane < 2 * nbox) am_tma_box(dst + lane * 2048u, &map_v, (lane - nbox) * 64, row, bars + stage);
+        } else {
+            uint4* z = reinterpret_cast<uint4*>(pipes_ptr + (size_t)(warp * AD_STAGES + stage) * stage_bytes);
+            for (uint32_t i = lane; i < stage_bytes / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+            __syncwarp();
+            if (lane == 0) am_mbar_expect_tx(bars + stage, 0u);         // nothing to wait for: the phase completes
         }
     };
 #pragma unroll
@@ -434,20 +569,42 @@ attention_decode_kernel(const AttMmaParams p) {
     am_wait<0>();                                           // this thread's part of Q has landed
     __syncthreads();                                        // and everyone else's
 
-    float o[NT_O][4];
+    // Q as B fragments: lane (g, t) holds Q[row 8 nb + g][dims 16 ks + 2t, +1 and + 8 + 2t, +1].
+    uint32_t bq[HD / 16][NB][2];
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i) o[i][0] = o[i][1] = o[i][2] = o[i][3] = 0.f;
-    float m_run[2] = {-INFINITY, -INFINITY}, l_run[2] = {0.f, 0.f};
-    int cnt[2], fst[2];
+    for (int ks = 0; ks < HD / 16; ++ks)
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        const int r = g + h * 8;
-        const bool own = r < rows_valid;
-        cnt[h] = own ? x.c_first + r / group : 0x7fffffff;
-        fst[h] = (own && p.window > 0 && cnt[h] > p.window) ? cnt[h] - p.window : 0;
-    }
-    const int fst_hi = __reduce_max_sync(0xffffffffu, max(fst[0], fst[1]));
-    const int cnt_lo = __reduce_min_sync(0xffffffffu, min(cnt[0], cnt[1]));
+        for (int nb = 0; nb < NB; ++nb) {
+            bq[ks][nb][0] = bq[ks][nb][1] = 0u;
+            if (FULL || ks * 16 < d) {
+                const bf16* qp = sQ + (nb * 8 + g) * ld + ks * 16 + t * 2;
+                bq[ks][nb][0] = *reinterpret_cast<const uint32_t*>(qp);
+                bq[ks][nb][1] = *reinterpret_cast<const uint32_t*>(qp + 8);
+            }
+        }
+    float ot[HD / 16][NB][4];
+#pragma unroll
+    for (int nd = 0; nd < HD / 16; ++nd)
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb) ot[nd][nb][0] = ot[nd][nb][1] = ot[nd][nb][2] = ot[nd][nb][3] = 0.f;
+    float m_run[NB][2], l_run[NB][2];
+    int cnt[NB][2], fst[NB][2];
+    int fst_max = 0, cnt_min = 0x7fffffff;
+#pragma unroll
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {
+            m_run[nb][h] = -INFINITY;
+            l_run[nb][h] = 0.f;
+            const int r = nb * 8 + t * 2 + h;                // this lane's rows ("heads")
+            const bool own = r < rows_valid;
+            cnt[nb][h] = own ? x.c_first + r / group : 0x7fffffff;
+            fst[nb][h] = (own && p.window > 0 && cnt[nb][h] > p.window) ? cnt[nb][h] - p.window : 0;
+            fst_max = max(fst_max, fst[nb][h]);
+            cnt_min = min(cnt_min, cnt[nb][h]);
+        }
+    const int fst_hi = __reduce_max_sync(0xffffffffu, fst_max);
+    const int cnt_lo = __reduce_min_sync(0xffffffffu, cnt_min);
     const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
 
     bool failed = false;
@@ -455,8 +612,9 @@ attention_decode_kernel(const AttMmaParams p) {
         const int tile = warp + 4 * i, stage = i % AD_STAGES;
         if (!am_mbar_wait(bars + stage, (uint32_t)(i / AD_STAGES) & 1u)) { failed = true; break; }
         __syncwarp();                                       // zero rows written by other lanes are visible
-        am_tile<HD, AD_WK, FULL>(sQ, sW + (size_t)(2 * stage) * AD_WK * ld, sW + (size_t)(2 * stage + 1) * AD_WK * ld, ld, d,
-                           k_begin + tile * AD_WK, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap, o, m_run, l_run, lane);
+        const uint32_t tk = my_pipe + (uint32_t)stage * stage_bytes;
+        ad_tile<HD, NB, FULL>(bq, tk, tk + nbox * 2048u, d, k_begin + tile * AD_WK, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap,
+                              ot, m_run, l_run, lane);
         __syncwarp();                                       // every lane has read the stage
         if (tile + 4 * AD_STAGES < n_tiles) load_tile(stage, tile + 4 * AD_STAGES);
     }
@@ -469,31 +627,39 @@ attention_decode_kernel(const AttMmaParams p) {
     failed = __syncthreads_or(failed);
     if (failed) return;
 #pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
-        l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 2);
-    }
+    for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+        for (int h = 0; h < 2; ++h) {                        // the row sums over the 16 key lanes
+            l_run[nb][h] += __shfl_xor_sync(0xffffffffu, l_run[nb][h], 4);
+            l_run[nb][h] += __shfl_xor_sync(0xffffffffu, l_run[nb][h], 8);
+            l_run[nb][h] += __shfl_xor_sync(0xffffffffu, l_run[nb][h], 16);
+        }
 
     // Merge the 4 warps' states through shared memory (the pipelines are drained).
     const float LOG2E = 1.4426950408889634f;
-    __syncthreads();
-    const int md = d + 4;                                   // padded: rows g and g + 1 land in different banks
-    float* mO = reinterpret_cast<float*>(sQ + 16 * ld);     // [4][16][md]
+    const int md = d + 4;
+    float* mO = reinterpret_cast<float*>(pipes_ptr);        // [4][16][md], over the drained pipelines
     float* mM = mO + 4 * 16 * md;                           // [4][16]
     float* mL = mM + 4 * 16;
 #pragma unroll
-    for (int i = 0; i < NT_O; ++i)
-        if (i * 8 < d) {
+    for (int nd = 0; nd < HD / 16; ++nd)
+        if (FULL || nd * 16 < d) {
 #pragma unroll
-            for (int e = 0; e < 4; ++e)
-                mO[((size_t)warp * 16 + g + (e >> 1) * 8) * md + i * 8 + t * 2 + (e & 1)] = o[i][e];
-        }
-    if (t == 0) {
+            for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
-        for (int h = 0; h < 2; ++h) {
-            mM[warp * 16 + g + h * 8] = m_run[h];
-            mL[warp * 16 + g + h * 8] = l_run[h];
+                for (int e = 0; e < 4; ++e) {
+                    const int r = nb * 8 + t * 2 + (e & 1);
+                    if (r < rows_valid) mO[((size_t)warp * 16 + r) * md + nd * 16 + g + (e >> 1) * 8] = ot[nd][nb][e];
+                }
         }
+    if (g == 0) {
+#pragma unroll
+        for (int nb = 0; nb < NB; ++nb)
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+                const int r = nb * 8 + t * 2 + h;
+                if (r < rows_valid) { mM[warp * 16 + r] = m_run[nb][h]; mL[warp * 16 + r] = l_run[nb][h]; }
+            }
     }
     __syncthreads();
     for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
@@ -580,25 +746,38 @@ static int launch_prompt(const AttMmaParams& p, int tiles, cudaStream_t s) {
     return check_launch("attention_mma");
 }
 
+// max_rows: the most rows ((token, query head) pairs) any tile holds: up to 8 take one block of
+// eight "heads" in the MMAs' N, up to 16 two. The tensor maps cover the whole key and value tables
+// as [pages * kv heads * page size, head_dim] matrices.
 template <int HD>
-static int launch_decode(const AttMmaParams& p, int tiles, cudaStream_t s) {
+static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStream_t s) {
+    if (p.page_size % AD_WK != 0) return fail("attention_mma: decode mode needs pages of a multiple of %d positions, got %d", AD_WK, p.page_size);
     const int ld = p.d + AM_PAD;
-    const size_t pipes = (size_t)4 * 2 * AD_STAGES * AD_WK * ld * sizeof(bf16);
+    const int nbox = (p.d + 63) / 64;
+    const size_t stage = (size_t)2 * nbox * 2048;
+    const size_t pipes = (size_t)4 * AD_STAGES * stage;
     const size_t merge = ((size_t)4 * 16 * (p.d + 4) + 2 * 4 * 16) * sizeof(float);
-    size_t bars = (size_t)16 * ld * sizeof(bf16) + (pipes > merge ? pipes : merge);
+    // Q, then up to 1023 bytes to reach the swizzle's period plus whatever the base itself is off by
+    size_t bars = (size_t)16 * ld * sizeof(bf16) + 2048 + (pipes > merge ? pipes : merge);
     bars = (bars + 15) / 16 * 16;
     const size_t smem = bars + 4 * AD_STAGES * sizeof(uint64_t);
+    if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
     AttMmaParams q = p;
     q.decode_bar_offset = (int)bars;
-    if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
+    const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
+    CUtensorMap map_k, map_v;
+    if (int e = encode_map_bf16(&map_k, p.k_table, rows, p.d, p.d, AD_WK)) return e;
+    if (int e = encode_map_bf16(&map_v, p.v_table, rows, p.d, p.d, AD_WK)) return e;
     dim3 grid(tiles, p.hkv, p.slots);
-    if (p.d == HD) {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_decode_kernel<HD, true><<<grid, AM_THREADS, smem, s>>>(q);
-    } else {
-        if (smem > 48 * 1024) cudaFuncSetAttribute(attention_decode_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_decode_kernel<HD, false><<<grid, AM_THREADS, smem, s>>>(q);
-    }
+#define KB_DECODE(NB, FULL)                                                                                                    \
+    do {                                                                                                                       \
+        if (smem > 48 * 1024)                                                                                                  \
+            cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        attention_decode_kernel<HD, NB, FULL><<<grid, AM_THREADS, smem, s>>>(q, map_k, map_v);                                 \
+    } while (0)
+    if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true); else KB_DECODE(1, false); }
+    else               { if (p.d == HD) KB_DECODE(2, true); else KB_DECODE(2, false); }
+#undef KB_DECODE
     return check_launch("attention_decode");
 }
 
@@ -626,9 +805,12 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
                                 int page_size, int table_width, int n_pages, int window, int split, int slots,
                                 float scale, float cap, int decode, float* scratch, void* stream) {
+    // decode: 0 for prompt portions; else the most rows (tokens x query heads of a kv head) any tile
+    // holds, at most 16.
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_mma: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
     KB_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_mma: head_dim %d must be a multiple of 16, at most 256", d);
     KB_REQUIRE(hq / hkv <= (decode ? 16 : 64), "attention_mma: %d query heads a kv head do not fit a tile of %d rows", hq / hkv, decode ? 16 : 64);
+    KB_REQUIRE(decode >= 0 && decode <= 16 && (decode == 0 || decode >= hq / hkv), "attention_mma: decode mode with %d rows a tile (1..16, at least the group of %d)", decode, hq / hkv);
     KB_REQUIRE(page_size > 0 && table_width > 0 && n_pages > 0, "attention_mma: page_size %d, table width %d, pages %d", page_size, table_width, n_pages);
     KB_REQUIRE(window >= 0 && cap >= 0.f, "attention_mma: window %d, cap %g", window, cap);
     KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AM_KT == 0 && slots >= 1 && slots <= 8192),
@@ -646,9 +828,9 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.decode_bar_offset = 0;
     cudaStream_t s = (cudaStream_t)stream;
     int e;
-    if (d <= 64) e = decode ? launch_decode<64>(p, tiles, s) : launch_prompt<64>(p, tiles, s);
-    else if (d <= 128) e = decode ? launch_decode<128>(p, tiles, s) : launch_prompt<128>(p, tiles, s);
-    else e = decode ? launch_decode<256>(p, tiles, s) : launch_prompt<256>(p, tiles, s);
+    if (d <= 64) e = decode ? launch_decode<64>(p, tiles, decode, s) : launch_prompt<64>(p, tiles, s);
+    else if (d <= 128) e = decode ? launch_decode<128>(p, tiles, decode, s) : launch_prompt<128>(p, tiles, s);
+    else e = decode ? launch_decode<256>(p, tiles, decode, s) : launch_prompt<256>(p, tiles, s);
     if (e) return e;
     if (slots > 1) {
         dim3 grid(rows, hq);

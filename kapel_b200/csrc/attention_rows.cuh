@@ -48,7 +48,7 @@ template <> struct Vec<__nv_bfloat16> {
 
 struct AttParams {
     const void* q;            // [rows, hq, d]
-    const void* k_table;      // [lines, hkv, d]
+    const void* k_table;      // [pages, hkv, page_size, d]
     const void* v_table;
     const int* block_table;   // [entries, table_width]
     const int* row_entry;     // [rows]
@@ -127,7 +127,7 @@ rows_kernel(const AttParams p) {
         for (int v = 0; v < VPL; ++v) {
             const int vi = li + v * LPK;
             if (line >= 0 && vi < nvec) {
-                Vec<T>::load(kt + ((size_t)line * p.hkv + kvh) * d + vi * VN, kv[v]);
+                Vec<T>::load(kt + kv_row(line, kvh, p.hkv, p.page_size) * d + vi * VN, kv[v]);
             } else {
 #pragma unroll
                 for (int e = 0; e < VN; ++e) kv[v][e] = 0.f;
@@ -186,7 +186,7 @@ rows_kernel(const AttParams p) {
             for (int j = jstart; j < nkeys; j += tgroups) {
                 const int line = sline[j];
                 if (line < 0) continue;
-                const T* vp = vt + ((size_t)line * p.hkv + kvh) * d + 2 * pi;
+                const T* vp = vt + kv_row(line, kvh, p.hkv, p.page_size) * d + 2 * pi;
                 const float v0 = Elem<T>::load(vp), v1 = Elem<T>::load(vp + 1);
 #pragma unroll
                 for (int g = 0; g < GMAX; ++g) {

@@ -47,6 +47,14 @@ template <typename T> struct Src {
     }
 };
 
+// The cache tables are [pages, kv_heads, page_size, head_dim]: the keys of one kv head in one page
+// lie together. A "line" is page * page_size + offset; this is the row of that line's kv head.
+__device__ __forceinline__ size_t kv_row(long long line, int kvh, int hkv, int page_size) {
+    const long long page = line / page_size;
+    const int off = (int)(line - page * page_size);
+    return (size_t)(page * hkv + kvh) * page_size + off;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

@@ -41,14 +41,15 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
 // ---------------------------------------------------------------------------------------
 // One thread a pair of components of one head vector of one row of the stacked q|k|v product.
 // Heads [0, Hq) are queries (rotated, written to q_out), [Hq, Hq+Hkv) keys (rotated, written to
-// the key table at the row's line), [Hq+Hkv, Hq+2Hkv) values (copied to the value table).
+// the key table at the row's line), [Hq+Hkv, Hq+2Hkv) values (copied to the value table). The
+// tables are [pages, Hkv, page_size, D]; a line is page * page_size + offset.
 // Pairing "half": (j, j + rotary/2) for j < rotary/2; components from `rotary` on pass through.
 // A row whose line is negative writes no key and no value (a padding row).
 template <typename TI, typename T>
 __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__ cos_sin,
                                    const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
                                    T* __restrict__ v_table, int rows, int hq, int hkv, int d, int rotary,
-                                   int write_kv, long long table_lines) {
+                                   int write_kv, long long table_lines, int page_size) {
     const int half_d = d >> 1, half_r = rotary >> 1;
     const int heads = hq + 2 * hkv;
     const long long total = (long long)rows * heads * half_d;
@@ -74,7 +75,7 @@ __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__
         if (line < 0 || line >= table_lines) return;
         const bool is_key = h < hq + hkv;
         const int kvh = is_key ? h - hq : h - hq - hkv;
-        dst = (is_key ? k_table : v_table) + ((size_t)line * hkv + kvh) * d;
+        dst = (is_key ? k_table : v_table) + kv_row(line, kvh, hkv, page_size) * d;
         if (!is_key) rotate = false;
     }
     float a = qkv.at(src + ia), b = qkv.at(src + ib);      // read only by the threads that write
@@ -154,10 +155,12 @@ extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int
 // added up on the way in; q_out and the tables: `out_dt`.
 extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long split_stride, const float* cos_sin,
                               const int* lines, void* q_out, void* k_table, void* v_table, int out_dt, int rows,
-                              int hq, int hkv, int d, int rotary, int write_kv, long long table_lines, void* stream) {
+                              int hq, int hkv, int d, int rotary, int write_kv, long long table_lines, int page_size,
+                              void* stream) {
     KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && d > 0 && d % 2 == 0, "rope_append: rows %d, heads %d/%d, head_dim %d", rows, hq, hkv, d);
     KB_REQUIRE(rotary >= 0 && rotary <= d && rotary % 2 == 0, "rope_append: rotary %d must be even and at most head_dim %d", rotary, d);
     KB_REQUIRE(splits >= 1, "rope_append: %d slices", splits);
+    KB_REQUIRE(!write_kv || page_size > 0, "rope_append: page_size %d", page_size);
     if (rows == 0) return 0;
     const long long total = (long long)rows * (hq + 2 * hkv) * (d / 2);
     const unsigned blocks = (unsigned)((total + 255) / 256);
@@ -165,7 +168,7 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
 #define KB_ROPE(TI, T)                                                                                              \
     rope_append_kernel<TI, T><<<blocks, 256, 0, s>>>(Src<TI>{(const TI*)qkv, splits, (size_t)split_stride},          \
                                                      (const float2*)cos_sin, lines, (T*)q_out, (T*)k_table,         \
-                                                     (T*)v_table, rows, hq, hkv, d, rotary, write_kv, table_lines)
+                                                     (T*)v_table, rows, hq, hkv, d, rotary, write_kv, table_lines, page_size > 0 ? page_size : 1)
     if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ROPE(float, float);
     else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_ROPE(float, bf16);
     else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_ROPE(bf16, bf16);

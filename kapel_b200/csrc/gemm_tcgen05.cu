@@ -19,11 +19,8 @@
 // Every wait on an mbarrier gives up after about a second: the waiter raises a flag that
 // `kb_tcgen05_error` reports, skips its remaining work, and the block still meets at its final
 // barrier, frees its TMEM and returns.
-#include <cuda.h>
-#include <mutex>
-#include <unordered_map>
-
 #include "common.cuh"
+#include "tensor_map.cuh"
 
 namespace kb {
 
@@ -212,36 +209,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
-// ---- tensor maps
-typedef CUresult (*EncodeTiledFn)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
-                                  const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
-                                  CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
-static EncodeTiledFn g_encode = nullptr;
-
-static int get_encoder() {
-    if (g_encode != nullptr) return 0;
-    void* fn = nullptr;
-    cudaDriverEntryPointQueryResult res;
-    const cudaError_t e = cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &fn, cudaEnableDefault, &res);
-    if (e != cudaSuccess || fn == nullptr || res != cudaDriverEntryPointSuccess)
-        return fail("gemm_tcgen05: the driver does not give cuTensorMapEncodeTiled (%s)", cudaGetErrorString(e));
-    g_encode = reinterpret_cast<EncodeTiledFn>(fn);
-    return 0;
-}
-
-// A [rows, k] bfloat16 row-major matrix seen in boxes of box_rows x 64 elements, 128-byte swizzle.
-static int make_map(CUtensorMap* map, const void* base, int rows, int k, int box_rows) {
-    const cuuint64_t dims[2] = {(cuuint64_t)k, (cuuint64_t)rows};
-    const cuuint64_t strides[1] = {(cuuint64_t)k * sizeof(bf16)};
-    const cuuint32_t box[2] = {(cuuint32_t)TC_BK, (cuuint32_t)box_rows};
-    const cuuint32_t elem[2] = {1, 1};
-    const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 2, const_cast<void*>(base), dims, strides, box, elem,
-                                CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,
-                                CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
-    if (r != CUDA_SUCCESS) return fail("gemm_tcgen05: cuTensorMapEncodeTiled failed with code %d for [%d, %d]", (int)r, rows, k);
-    return 0;
-}
-
 }  // namespace kb
 
 using namespace kb;
@@ -262,10 +229,9 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
     KB_REQUIRE(c_dt == KB_DT_F32 || c_dt == KB_DT_BF16, "gemm_tcgen05: output dtype code %d is not known", c_dt);
     KB_REQUIRE(epilogue == 0 || (epilogue == 1 && cap > 0.f), "gemm_tcgen05: epilogue %d with cap %g", epilogue, cap);
     KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)c & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
-    if (int e = get_encoder()) return e;
     CUtensorMap map_a, map_w;
-    if (int e = make_map(&map_a, a, m, k, TC_BM)) return e;
-    if (int e = make_map(&map_w, w, n, k, TC_BN)) return e;
+    if (int e = encode_map_bf16(&map_a, a, m, k, k, TC_BM)) return e;
+    if (int e = encode_map_bf16(&map_w, w, n, k, k, TC_BN)) return e;
     static bool attr_set = false;
     if (!attr_set) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);

@@ -1,0 +1,13 @@
+// TMA tensor maps over row-major bfloat16 matrices, shared by the kernels that load through them.
+#pragma once
+#include <cuda.h>
+
+namespace kb {
+
+// A [rows, cols] bfloat16 matrix whose rows are `pitch_elems` elements apart, seen in boxes of
+// box_rows x 64 elements (128 bytes) under the 128-byte swizzle; elements outside the matrix read
+// as zero. Returns 0, or 1 after storing a message.
+int encode_map_bf16(CUtensorMap* map, const void* base, unsigned long long rows, unsigned long long cols,
+                    unsigned long long pitch_elems, unsigned box_rows);
+
+}  // namespace kb

@@ -120,16 +120,18 @@ class StepBatch:
             self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
 
     def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None):
-        """How the tensor-core attention kernel cuts this step: (decode mode, (tile_entry, tile_row0,
-        tile_nq) on the device, split, slots). Decode mode when every request's rows fit 16; the
-        keys are split across blocks when the tiles alone are too few to fill the GPU."""
+        """How the tensor-core attention kernel cuts this step: (decode, (tile_entry, tile_row0,
+        tile_nq) on the device, split, slots). `decode` is the most rows (tokens x query heads of a
+        kv head) of any request when that is at most 16, which selects the decode kernel, else 0.
+        The keys are split across blocks when the tiles alone are too few to fill the GPU."""
         key = ("tiles", heads_per_kv, kv_heads, window)
         if key not in self.memo:
             from .. import kernels as K
 
             plan = self.plan
-            decode = int(plan.q_len.max()) * heads_per_kv <= K.attention_mma_rows(True)
-            per_tile = max(1, K.attention_mma_rows(decode) // heads_per_kv)
+            most = int(plan.q_len.max()) * heads_per_kv
+            decode = most if most <= K.attention_mma_rows(True) else 0      # rows a tile in decode mode, else 0
+            per_tile = max(1, K.attention_mma_rows(bool(decode)) // heads_per_kv)
             arrays = cut_tiles(plan.q_start, plan.q_len, per_tile)
             n = arrays[0].size
             host = torch.from_numpy(np.concatenate(arrays)).pin_memory() if self.ids.is_cuda else torch.from_numpy(np.concatenate(arrays))

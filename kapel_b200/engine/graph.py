@@ -62,7 +62,7 @@ class StaticBatch:
         if (kv_heads, window) not in self._mma:
             self._mma[(kv_heads, window)] = decode_split(self.rows * kv_heads, self._longest, sm_count(self._device), window)
         split, slots = self._mma[(kv_heads, window)]
-        return True, self._tiles, split, slots
+        return heads_per_kv, self._tiles, split, slots        # one token a row: heads_per_kv rows a tile
 
     def fill(self, plan, ids) -> None:
         """Writes a plan of at most `rows` single-token entries into the buffers; the rest are

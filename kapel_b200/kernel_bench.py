@@ -120,7 +120,7 @@ def main(argv=None) -> int:
     pages_per_seq = -(-(ctx + 1) // page)
     n_layers_rot = 2
     n_pages = B * pages_per_seq
-    tables = [(torch.randn(n_pages, page, Hkv, D, device=dev).to(bf), torch.randn(n_pages, page, Hkv, D, device=dev).to(bf))
+    tables = [(torch.randn(n_pages, Hkv, page, D, device=dev).to(bf), torch.randn(n_pages, Hkv, page, D, device=dev).to(bf))
               for _ in range(n_layers_rot)]
     perm = torch.randperm(n_pages).to(torch.int32).reshape(B, pages_per_seq)
     bt = perm.to(dev)
@@ -138,7 +138,7 @@ def main(argv=None) -> int:
         split, slots = decode_split(B * Hkv, ctx + 1, sm_count(dev), window)
         seen = min(ctx + 1, window) if window else ctx + 1
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
-                                                   True, split, slots), args.iters)
+                                                   Hq // Hkv, split, slots), args.iters)
         report(f"{name} split={split}x{slots}", us, B * seen * Hkv * D * 2 * 2)
 
     decode_case(None)
@@ -158,7 +158,7 @@ def main(argv=None) -> int:
         slots = max(1, -(-t // split)) if split else 1
         pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
-                                                   False, split, slots), max(3, args.iters // 4))
+                                                   0, split, slots), max(3, args.iters // 4))
         report(f"{name} [{t} tokens]", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
 
     if args.prompt <= ctx:

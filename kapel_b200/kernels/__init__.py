@@ -182,8 +182,8 @@ def rope_table(positions: torch.Tensor, rotary: int, theta: float) -> torch.Tens
 def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int, rotary: int, write_kv: bool = True,
                 out_dtype: Optional[torch.dtype] = None):
     """Rotates the q and k heads of the stacked product `qkv` [rows, (hq + 2 hkv) d] (a tensor or a
-    SplitSum), returns q [rows, hq, d], and writes k and v at each row's line of the tables
-    [lines, hkv, d]."""
+    SplitSum), returns q [rows, hq, d], and writes k and v at each row's line (page * page_size +
+    offset) of the tables [pages, hkv, page_size, d]."""
     src, in_dt, splits, stride = _src(qkv, "rope_append qkv")
     rows = qkv.shape[0]
     if tuple(qkv.shape) != (rows, (hq + 2 * hkv) * d):
@@ -192,19 +192,20 @@ def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int
     if rotary:
         _need(cos_sin, "rope_append cos_sin", torch.float32, (rows, rotary // 2, 2))
     q = torch.empty((rows, hq, d), dtype=out_dtype, device=src.device)
-    table_lines = 0
+    table_lines, page_size = 0, 0
     if write_kv:
         _need(lines, "rope_append lines", torch.int32, (rows,))
         _need(k_table, "rope_append k table", out_dtype)
         _need(v_table, "rope_append v table", out_dtype)
-        if k_table.shape[-2:] != (hkv, d) or v_table.shape != k_table.shape:
-            raise KernelError(f"rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} do not end in ({hkv}, {d})")
-        table_lines = k_table.numel() // (hkv * d)
+        if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[3] != d or v_table.shape != k_table.shape:
+            raise KernelError(f"rope_append: tables {tuple(k_table.shape)} / {tuple(v_table.shape)} are not [pages, {hkv}, page_size, {d}]")
+        table_lines = k_table.shape[0] * k_table.shape[2]
+        page_size = k_table.shape[2]
     _check(
         library().kb_rope_append(
             _ptr(src), in_dt, splits, ctypes.c_longlong(stride), _ptr(cos_sin if rotary else None),
             _ptr(lines if write_kv else None), _ptr(q), _ptr(k_table if write_kv else None), _ptr(v_table if write_kv else None),
-            _dt(q, "rope_append output"), rows, hq, hkv, d, int(rotary), int(bool(write_kv)), ctypes.c_longlong(table_lines), _stream(),
+            _dt(q, "rope_append output"), rows, hq, hkv, d, int(rotary), int(bool(write_kv)), ctypes.c_longlong(table_lines), int(page_size), _stream(),
         )
     )
     return q
@@ -335,10 +336,9 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
     _need(q, "attention q")
     _need(k_table, "attention k table", q.dtype)
     _need(v_table, "attention v table", q.dtype)
-    hkv = k_table.shape[-2]
-    if k_table.shape[-1] != d or v_table.shape != k_table.shape:
-        raise KernelError(f"attention: tables {tuple(k_table.shape)} against head_dim {d}")
-    n_pages = k_table.numel() // (page_size * hkv * d)
+    if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.shape != k_table.shape:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
+    n_pages, hkv = k_table.shape[0], k_table.shape[1]
     _need(block_table, "attention block table", torch.int32)
     _need(row_entry, "attention row_entry", torch.int32, (rows,))
     _need(row_count, "attention row_count", torch.int32, (rows,))
@@ -365,19 +365,19 @@ def attention_mma_takes(dtype, d: int, heads_per_kv: int) -> bool:
 
 
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
-                        scale: float, softcap: Optional[float], decode: bool, split: int, slots: int) -> torch.Tensor:
+                        scale: float, softcap: Optional[float], decode: int, split: int, slots: int) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
-    one request at consecutive positions. `split` > 0 cuts the keys at absolute multiples of it
-    over `slots` blocks (slots >= ceil(longest count / split))."""
+    one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
+    (tokens x query heads of a kv head) any tile holds, at most 16. `split` > 0 cuts the keys at
+    absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split))."""
     rows, hq, d = q.shape
     _need(q, "attention q", torch.bfloat16)
     _need(k_table, "attention k table", torch.bfloat16)
     _need(v_table, "attention v table", torch.bfloat16)
-    hkv = k_table.shape[-2]
-    if k_table.shape[-1] != d or v_table.shape != k_table.shape:
-        raise KernelError(f"attention: tables {tuple(k_table.shape)} against head_dim {d}")
-    n_pages = k_table.numel() // (page_size * hkv * d)
+    if k_table.dim() != 4 or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.shape != k_table.shape:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} are not [pages, kv_heads, {page_size}, {d}]")
+    n_pages, hkv = k_table.shape[0], k_table.shape[1]
     tile_entry, tile_row0, tile_nq = tiles
     n_tiles = tile_entry.numel()
     for t in tiles:
@@ -392,7 +392,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
         lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                              _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
                              int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                             _f(softcap or 0.0), int(bool(decode)), _ptr(scratch), _stream())
+                             _f(softcap or 0.0), int(decode), _ptr(scratch), _stream())
     )
     return out
 

@@ -127,7 +127,7 @@ def test_slots_and_fresh():
     needs = {0: CacheNeeds(state=StateSpec((4,))), 1: CacheNeeds(PagedKV(1, 16))}
     made = []
     m = CacheManager(needs, 16, 4, 2, allocate=lambda shape, dtype: made.append((shape, dtype)) or object(), dtype="bf16")
-    assert ((3, 4), "float32") in made and ((4, 16, 1, 16), "bf16") in made
+    assert ((3, 4), "float32") in made and ((4, 1, 16, 16), "bf16") in made
     a, b = m.add_sequence("a"), m.add_sequence("b")
     assert {a, b} == {1, 2}
     with pytest.raises(CacheFull):

@@ -53,12 +53,13 @@ def test_rope_table():
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hq,hkv,d,rotary", [(4, 2, 16, 16), (6, 1, 32, 32), (3, 3, 48, 48), (2, 1, 64, 32)])
 def test_rope_append(dtype, hq, hkv, d, rotary):
-    rows, lines_total = 9, 40
+    rows, page, pages = 9, 8, 5
+    lines_total = page * pages
     qkv = rnd(rows, (hq + 2 * hkv) * d, seed=2, dtype=DT[dtype])
     pos = torch.tensor([0, 1, 2, 3, 50, 51, 7, 1000, 0], dtype=torch.int32)
     lines = torch.tensor([5, 6, 7, 39, 0, 1, 17, -1, 20], dtype=torch.int32)
-    kt = torch.full((lines_total, hkv, d), 7.0, dtype=DT[dtype])
-    vt = torch.full((lines_total, hkv, d), 7.0, dtype=DT[dtype])
+    kt = torch.full((pages, hkv, page, d), 7.0, dtype=DT[dtype])      # [pages, kv heads, page, d]
+    vt = torch.full((pages, hkv, page, d), 7.0, dtype=DT[dtype])
     kd, vd = dev(kt), dev(vt)
     cs = K().rope_table(dev(pos), rotary, 10000.0)
     q = K().rope_append(dev(qkv), cs, dev(lines), kd, vd, hq, hkv, d, rotary).cpu()
@@ -71,7 +72,9 @@ def test_rope_append(dtype, hq, hkv, d, rotary):
     tol = 1e-6 if dtype == "float32" else 1e-2
     assert rel_err(q.double().numpy(), rot(x[:, :hq]).numpy()) < tol
     k_want, v_want = rot(x[:, hq : hq + hkv]), x[:, hq + hkv :]
-    kc, vc = kd.cpu().double(), vd.cpu().double()
+    # line = page * page_size + offset; bring the tables to [lines, kv heads, d] to look lines up
+    kc = kd.cpu().double().permute(0, 2, 1, 3).reshape(lines_total, hkv, d)
+    vc = vd.cpu().double().permute(0, 2, 1, 3).reshape(lines_total, hkv, d)
     written = set()
     for r in range(rows):
         l = int(lines[r])
@@ -205,9 +208,10 @@ def test_glu(dtype, act):
 def paged_reference(q, k_table, v_table, block_table, row_entry, row_count, page, window, scale, cap):
     """Row by row in 64-bit, as crates/kapel-ref/src/paged.rs:28-92."""
     rows, hq, d = q.shape
-    hkv = k_table.shape[-2]
+    hkv = k_table.shape[1]                      # tables are [pages, kv heads, page, d]
     group = hq // hkv
-    kt, vt = k_table.double().reshape(-1, hkv, d), v_table.double().reshape(-1, hkv, d)
+    kt = k_table.double().permute(0, 2, 1, 3).reshape(-1, hkv, d)        # [lines, kv heads, d]
+    vt = v_table.double().permute(0, 2, 1, 3).reshape(-1, hkv, d)
     out = torch.zeros(rows, hq, d, dtype=torch.float64)
     for r in range(rows):
         e, c = int(row_entry[r]), int(row_count[r])
@@ -234,8 +238,8 @@ def make_paged_case(dtype, hq, hkv, d, lengths, q_lens, page=16, seed=0, n_pages
     perm = torch.randperm(n_pages, generator=g).tolist()
     width = max(-(-n // page) for n in lengths)
     bt = torch.full((len(lengths), width), -1, dtype=torch.int32)
-    k_table = torch.randn(n_pages, page, hkv, d, generator=g).to(DT[dtype])
-    v_table = torch.randn(n_pages, page, hkv, d, generator=g).to(DT[dtype])
+    k_table = torch.randn(n_pages, hkv, page, d, generator=g).to(DT[dtype])
+    v_table = torch.randn(n_pages, hkv, page, d, generator=g).to(DT[dtype])
     for i, n in enumerate(lengths):
         for p in range(-(-n // page)):
             bt[i, p] = perm.pop()
@@ -278,9 +282,8 @@ def test_paged_attention_far_key_and_window_edge(dtype):
 
     def plant(pos):
         kt2, vt2 = kt.clone(), vt.clone()
-        line = int(bt[0, pos // page]) * page + pos % page
-        kt2.reshape(-1, hkv, d)[line, 0] = (q[0, 0].float() * 400).to(kt.dtype)      # a score far above the rest
-        vt2.reshape(-1, hkv, d)[line, 0] = 5.0
+        kt2[int(bt[0, pos // page]), 0, pos % page] = (q[0, 0].float() * 400).to(kt.dtype)      # a score far above the rest
+        vt2[int(bt[0, pos // page]), 0, pos % page] = 5.0
         return kt2, vt2
 
     tol = 1e-5 if dtype == "float32" else 1.5e-2
@@ -342,13 +345,14 @@ def test_sample_temperature_follows_plain_rule_and_probabilities():
 def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split):
     from kapel_b200.engine.batch import cut_tiles
 
-    hq, hkv = q.shape[1], kt.shape[-2]
+    hq, hkv = q.shape[1], kt.shape[1]
     per_tile = max(1, K().attention_mma_rows(decode) // (hq // hkv))
     q_len = np.asarray(q_lens, np.int32)
     q_start = np.concatenate(([0], np.cumsum(q_len)[:-1])).astype(np.int32)
     tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(q_start, q_len, per_tile))
     slots = max(1, -(-int(rc.max()) // split)) if split else 1
-    return K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, window, scale, cap, decode, split, slots).cpu()
+    rows = int(q_len.max()) * (hq // hkv) if decode else 0
+    return K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, window, scale, cap, rows, split, slots).cpu()
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 1, 64), (8, 4, 128), (8, 4, 256), (5, 1, 80)])
@@ -387,9 +391,8 @@ def test_paged_attention_mma_far_key_and_window_edge(decode):
 
     def plant(pos):
         kt2, vt2 = kt.clone(), vt.clone()
-        line = int(bt[0, pos // page]) * page + pos % page
-        kt2.reshape(-1, hkv, d)[line, 0] = (q[0, 0].float() * 400).to(kt.dtype)
-        vt2.reshape(-1, hkv, d)[line, 0] = 5.0
+        kt2[int(bt[0, pos // page]), 0, pos % page] = (q[0, 0].float() * 400).to(kt.dtype)
+        vt2[int(bt[0, pos // page]), 0, pos % page] = 5.0
         return kt2, vt2
 
     for pos, win, seen in [(3, None, True), (n - window, window, True), (n - window - 1, window, False)]:
@@ -441,14 +444,14 @@ def test_split_sums_are_added_up_by_their_readers():
     assert isinstance(split, K().SplitSum)
     pos = torch.tensor([0, 3, 9, 100, 7], dtype=torch.int32)
     lines = torch.tensor([4, 0, 9, -1, 2], dtype=torch.int32)
-    kt = torch.zeros(10, hkv, d, dtype=torch.bfloat16).cuda()
-    vt = torch.zeros(10, hkv, d, dtype=torch.bfloat16).cuda()
+    kt = torch.zeros(1, hkv, 10, d, dtype=torch.bfloat16).cuda()         # one page of 10 lines
+    vt = torch.zeros(1, hkv, 10, d, dtype=torch.bfloat16).cuda()
     cs = K().rope_table(dev(pos), d, 10000.0)
     q = K().rope_append(split, cs, dev(lines), kt, vt, hq, hkv, d, d, out_dtype=torch.bfloat16).cpu().double()
     x = (a.double() @ w.double().T).reshape(m, hq + 2 * hkv, d)
     assert rel_err(q.numpy(), P.rope(x[:, :hq], pos, 10000.0).numpy()) < 1e-2
-    assert rel_err(kt.cpu().double()[4].numpy(), P.rope(x[:, hq : hq + hkv], pos, 10000.0)[0].numpy()) < 1e-2
-    assert rel_err(vt.cpu().double()[9].numpy(), x[2, hq + hkv :].numpy()) < 1e-2
+    assert rel_err(kt.cpu().double()[0, :, 4].numpy(), P.rope(x[:, hq : hq + hkv], pos, 10000.0)[0].numpy()) < 1e-2
+    assert rel_err(vt.cpu().double()[0, :, 9].numpy(), x[2, hq + hkv :].numpy()) < 1e-2
 
 
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 16])
