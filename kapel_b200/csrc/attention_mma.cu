@@ -403,23 +403,24 @@ attention_mma_kernel(const AttMmaParams p) {
         const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
         am_cp_async16(sQ + r * ld + ch * 8, src, valid);
     }
-    // A tile's 64 lines (page * page_size + offset, or -1) wait in shared memory, written one
-    // iteration ahead by the first 64 threads; then consecutive threads copy consecutive 16-byte
-    // pieces of a key row, so a warp's copy instruction covers whole rows.
+    // A tile's 64 table rows (of this kv head, or -1) wait in shared memory, written one iteration
+    // ahead by the first 64 threads; then consecutive threads copy consecutive 16-byte pieces of a
+    // key row, so a warp's copy instruction covers whole rows.
     int* sLine = reinterpret_cast<int*>(sV + 2 * AM_KT * ld);          // [2][KT]
     auto find_lines = [&](int kt) {
         if (tid < AM_KT) {
             const int j = k_begin + kt * AM_KT + tid;
-            sLine[(kt & 1) * AM_KT + tid] = (kt < n_tiles && j >= klo && j < khi) ? (int)am_line(p, x.entry, j) : -1;
+            const long long line = (kt < n_tiles && j >= klo && j < khi) ? am_line(p, x.entry, j) : -1;
+            sLine[(kt & 1) * AM_KT + tid] = line >= 0 ? (int)kv_row(line, kvh, p.hkv, p.page_size) : -1;
         }
     };
     auto load_tile = [&](int stage, int kt) {
         const int* lines = sLine + (kt & 1) * AM_KT;
         for (int idx = tid; idx < AM_KT * chunks; idx += AM_THREADS) {
             const int r = idx / chunks, ch = idx - r * chunks;
-            const int line = lines[r];
-            const bool valid = line >= 0;
-            const size_t off = kv_row(valid ? line : 0, kvh, p.hkv, p.page_size) * d + ch * 8;
+            const int row = lines[r];
+            const bool valid = row >= 0;
+            const size_t off = (size_t)(valid ? row : 0) * d + ch * 8;
             am_cp_async16(sK + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.k_table + off, valid);
             am_cp_async16(sV + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.v_table + off, valid);
         }

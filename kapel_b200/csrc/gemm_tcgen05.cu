@@ -108,7 +108,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m0 = blockIdx.y * TC_BM, n0 = blockIdx.x * TC_BN;
+    const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
     const int k_tiles = (k + TC_BK - 1) / TC_BK;
 
     if (threadIdx.x == 0) {
@@ -238,8 +238,11 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", TC_SMEM_BYTES, cudaGetErrorString(e));
         attr_set = true;
     }
-    dim3 grid((n + TC_BN - 1) / TC_BN, (m + TC_BM - 1) / TC_BM);
-    KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d rows is too many for one launch", m);
+    // Row tiles are the fast grid dimension: the blocks of a wave share a few weight tiles (each
+    // read from memory once) and what a wave reads again is the activations, small beside L2.
+    // Measured on the gate|up product of a 2,048-token prompt: 187 us against 227 us the other way.
+    dim3 grid((m + TC_BM - 1) / TC_BM, (n + TC_BN - 1) / TC_BN);
+    KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d columns is too many for one launch", n);
     gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
     return check_launch("gemm_tcgen05");
 }
