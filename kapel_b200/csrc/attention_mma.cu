@@ -546,27 +546,39 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     // range arrive too (they are masked): what a page holds beyond a sequence's end is what an
     // earlier sequence left there, finite values that meet a weight of exactly zero.
     const uint32_t tile_bytes = stage_bytes;
-    auto load_tile = [&](int stage, int tile) {
-        const int j = k_begin + tile * AD_WK;
-        const long long line = am_line(p, x.entry, max(j, klo));       // the tile's page, by a position the block owns
+    // The pages of this warp's next 32 tiles wait in registers, one a lane, so that the loop does
+    // not stall on the block table: lane l holds the page of the warp's tile number base + l.
+    int pages32 = -1;
+    auto fetch_pages = [&](int base) {
+        const int tile = warp + 4 * (base + lane);
+        pages32 = -1;
+        if (tile < n_tiles) {
+            const int lp = max(k_begin + tile * AD_WK, klo) / p.page_size;     // by a position the block owns
+            if (lp < p.table_width) pages32 = p.block_table[(size_t)x.entry * p.table_width + lp];
+            if (pages32 >= p.n_pages) pages32 = -1;
+        }
+    };
+    auto load_tile = [&](int stage, int i) {                 // the warp's tile number i
+        const int j = k_begin + (warp + 4 * i) * AD_WK;
+        const int page = __shfl_sync(0xffffffffu, pages32, i & 31);
         const uint32_t dst = my_pipe + (uint32_t)stage * stage_bytes;
-        if (line >= 0) {
-            const long long page = line / p.page_size;
-            const int row = (int)((page * p.hkv + kvh) * p.page_size + j % p.page_size);
+        if (page >= 0) {
+            const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
             if (lane == 0) am_mbar_expect_tx(bars + stage, tile_bytes);
             __syncwarp();                                   // the expectation is set before a copy can complete
             if (lane < nbox) am_tma_box(dst + lane * 2048u, &map_k, lane * 64, row, bars + stage);
             else if (lane < 2 * nbox) am_tma_box(dst + lane * 2048u, &map_v, (lane - nbox) * 64, row, bars + stage);
         } else {
             uint4* z = reinterpret_cast<uint4*>(pipes_ptr + (size_t)(warp * AD_STAGES + stage) * stage_bytes);
-            for (uint32_t i = lane; i < stage_bytes / 16; i += 32) z[i] = make_uint4(0u, 0u, 0u, 0u);
+            for (uint32_t k = lane; k < stage_bytes / 16; k += 32) z[k] = make_uint4(0u, 0u, 0u, 0u);
             __syncwarp();
             if (lane == 0) am_mbar_expect_tx(bars + stage, 0u);         // nothing to wait for: the phase completes
         }
     };
+    fetch_pages(0);
 #pragma unroll
     for (int s = 0; s < AD_STAGES; ++s)
-        if (warp + 4 * s < n_tiles) load_tile(s, warp + 4 * s);
+        if (warp + 4 * s < n_tiles) load_tile(s, s);
     am_wait<0>();                                           // this thread's part of Q has landed
     __syncthreads();                                        // and everyone else's
 
@@ -617,7 +629,10 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
         ad_tile<HD, NB, FULL>(bq, tk, tk + nbox * 2048u, d, k_begin + tile * AD_WK, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap,
                               ot, m_run, l_run, lane);
         __syncwarp();                                       // every lane has read the stage
-        if (tile + 4 * AD_STAGES < n_tiles) load_tile(stage, tile + 4 * AD_STAGES);
+        if (tile + 4 * AD_STAGES < n_tiles) {
+            if (((i + AD_STAGES) & 31) == 0) fetch_pages(i + AD_STAGES);
+            load_tile(stage, i + AD_STAGES);
+        }
     }
     if (failed) {
         // A copy never completed. Give the others in flight the same bounded chance to land (they
