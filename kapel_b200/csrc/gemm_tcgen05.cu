@@ -209,6 +209,177 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Up to 64 rows (decoding): the operands change places. A block owns 128 rows of the weight
+// matrix, which are the MMA's M (D^T[128 x NP] = W_tile . X^T), and the few activation rows, padded
+// to NP = 16, 32 or 64, are its N. The weights stream through shared memory once, by TMA, four or
+// five stages deep in each of two blocks a multiprocessor; work is split over K across blockIdx.y when the weight rows alone give too few
+// blocks, and each split leaves float32 partial sums [split, m, n] for the reader to add up.
+constexpr int SK2_BM = 128, SK2_BK = 64;
+// Stages so that two blocks fit a multiprocessor (about 100 KB each): while one starts or stores its
+// results the other streams.
+template <int NP> struct Sk2 { static constexpr int STAGES = NP <= 32 ? 5 : 4; };
+constexpr int SK2_A_BYTES = SK2_BM * SK2_BK * 2;                 // 16 KB of weights a stage
+
+template <int NP>
+__global__ void __launch_bounds__(TC_THREADS, 2)
+gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                           void* __restrict__ c, int c_dt, float* __restrict__ partial, int m, int n, int k,
+                           int k_tiles_per_split, int epi, float cap) {
+    constexpr int B_BYTES = NP * SK2_BK * 2;
+    constexpr int STAGE = SK2_A_BYTES + (B_BYTES < 1024 ? 1024 : B_BYTES);        // stages stay 1024-byte aligned
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(SK2_BM >> 4) << 24);
+    constexpr int COLS = NP < 32 ? 32 : NP;                                        // TMEM columns: a power of two >= 32
+    constexpr int SK2_STAGES = Sk2<NP>::STAGES;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + SK2_STAGES * STAGE);
+    uint64_t* empty = full + SK2_STAGES;
+    uint64_t* accum = empty + SK2_STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * SK2_BM;
+    const int split = blockIdx.y;
+    const int k_tiles_all = (k + SK2_BK - 1) / SK2_BK;
+    const int kt0 = split * k_tiles_per_split;
+    const int k_tiles = min(k_tiles_per_split, k_tiles_all - kt0);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < SK2_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
+        tc_mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % SK2_STAGES;
+                if (kt >= SK2_STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / SK2_STAGES) - 1) & 1u)) { failed = true; break; }
+                unsigned char* dst = smem + s * STAGE;
+                tc_mbar_expect_tx(full + s, SK2_A_BYTES + B_BYTES);
+                tc_tma_load_2d(dst, &map_w, (kt0 + kt) * SK2_BK, n0, full + s);
+                tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % SK2_STAGES;
+                if (!tc_mbar_wait(full + s, (uint32_t)(kt / SK2_STAGES) & 1u)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t a_addr = tc_saddr(smem + s * STAGE);
+                const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + SK2_A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < SK2_BK / 16; ++kk) {
+                    const uint32_t accumulate = (kt | kk) != 0 ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem), "l"(adesc + (uint64_t)(kk * 2)), "l"(bdesc + (uint64_t)(kk * 2)), "r"(IDESC), "r"(accumulate) : "memory");
+                }
+                tc_commit(empty + s);
+            }
+            if (!failed) tc_commit(accum);
+        }
+    } else {
+        const int quarter = warp & 3;
+        if (!__all_sync(0xffffffffu, tc_mbar_wait(accum, 0u))) {
+            failed = true;
+        } else {
+            tc_fence_after();
+            // lane l of this warp holds output column n0 + 32 quarter + l for every activation row
+            const int col = n0 + quarter * 32 + lane;
+            float* pdst = partial ? partial + (size_t)split * m * n : nullptr;
+#pragma unroll
+            for (int c0 = 0; c0 < NP; c0 += 16) {
+                uint32_t r[16];
+                __syncwarp();
+                asm volatile(
+                    "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                    : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+                      "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+                    : "r"(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0) : "memory");
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (col < n) {
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) {
+                        const int row = c0 + j;
+                        if (row < m) {
+                            float v = __uint_as_float(r[j]);
+                            if (pdst != nullptr) {
+                                pdst[(size_t)row * n + col] = v;
+                            } else {
+                                if (epi == 1) v = cap * tanhf(v / cap);
+                                if (c_dt == KB_DT_F32) static_cast<float*>(c)[(size_t)row * n + col] = v;
+                                else static_cast<bf16*>(c)[(size_t)row * n + col] = __float2bfloat16_rn(v);
+                            }
+                        }
+                    }
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(&g_tcgen05_error, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(COLS) : "memory");
+    }
+}
+
+// (splits, k tiles a split) for a weight [n, k]: about two blocks a multiprocessor, a
+// split at least four k tiles long. Depends on n and k only.
+static void skinny_plan(int n, int k, int sms, int* splits, int* k_tiles_per_split) {
+    const int n_tiles = (n + SK2_BM - 1) / SK2_BM;
+    const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
+    int s = (2 * sms + n_tiles / 2) / n_tiles;
+    const int max_splits = (k_tiles + 3) / 4;
+    if (s > max_splits) s = max_splits;
+    if (s < 1) s = 1;
+    const int per = (k_tiles + s - 1) / s;
+    *k_tiles_per_split = per;
+    *splits = (k_tiles + per - 1) / per;
+}
+
+static int skinny_sms() {
+    static int sms = 0;
+    if (sms == 0) {
+        int dev = 0;
+        cudaGetDevice(&dev);
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev);
+        if (sms <= 0) sms = 148;
+    }
+    return sms;
+}
+
+template <int NP>
+static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, void* c, int c_dt, float* partial, int m, int n,
+                         int k, int splits, int per, int epi, float cap, cudaStream_t s) {
+    constexpr int B_BYTES = NP * SK2_BK * 2;
+    constexpr int STAGE = SK2_A_BYTES + (B_BYTES < 1024 ? 1024 : B_BYTES);
+    constexpr int SMEM = Sk2<NP>::STAGES * STAGE + 1024 + 256;
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_skinny_tcgen05_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SMEM);
+        if (e != cudaSuccess) return fail("gemm_skinny: cannot have %d bytes of shared memory: %s", SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    dim3 grid((n + SK2_BM - 1) / SK2_BM, splits);
+    gemm_skinny_tcgen05_kernel<NP><<<grid, TC_THREADS, SMEM, s>>>(map_w, map_x, c, c_dt, splits > 1 ? partial : nullptr, m, n, k, per, epi, cap);
+    return check_launch("gemm_skinny_tcgen05");
+}
+
 }  // namespace kb
 
 using namespace kb;
@@ -245,4 +416,34 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
     KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d columns is too many for one launch", n);
     gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
     return check_launch("gemm_tcgen05");
+}
+
+// Partial sums the skinny kernel leaves for a weight [n, k] (1: it writes the result itself).
+extern "C" int kb_gemm_skinny_splits(int n, int k) {
+    int splits, per;
+    skinny_plan(n, k, skinny_sms(), &splits, &per);
+    return splits;
+}
+
+// a: bf16 [m,k], m <= 64; w: bf16 [n,k]. With one split: c (bf16 or f32 [m,n]) gets the result with
+// its epilogue. With more: `partial` (f32 [splits, m, n]) gets the partial sums and c is not touched.
+extern "C" int kb_gemm_skinny(void* c, int c_dt, float* partial, const void* a, const void* w, int m, int n, int k,
+                              int epilogue, float cap, void* stream) {
+    KB_REQUIRE(m > 0 && m <= 64 && n > 0 && k > 0, "gemm_skinny: m %d (1..64), n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_skinny: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(epilogue == 0 || (epilogue == 1 && cap > 0.f), "gemm_skinny: epilogue %d with cap %g", epilogue, cap);
+    KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_skinny: operands must be 16-byte aligned");
+    int splits, per;
+    skinny_plan(n, k, skinny_sms(), &splits, &per);
+    KB_REQUIRE(splits == 1 || partial != nullptr, "gemm_skinny: %d splits over K need room for partial sums", splits);
+    KB_REQUIRE(splits > 1 || (c != nullptr && (c_dt == KB_DT_F32 || c_dt == KB_DT_BF16)), "gemm_skinny: no output");
+    KB_REQUIRE(splits == 1 || epilogue == 0, "gemm_skinny: an epilogue cannot be applied to partial sums");
+    const int np = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    CUtensorMap map_w, map_x;
+    if (int e = encode_map_bf16(&map_w, w, n, k, k, SK2_BM)) return e;
+    if (int e = encode_map_bf16(&map_x, a, m, k, k, np)) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (np == 16) return launch_skinny<16>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
+    if (np == 32) return launch_skinny<32>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
+    return launch_skinny<64>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
 }

@@ -63,6 +63,54 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const Src<TB> b
     }
 }
 
+// The same with each thread's components kept in registers between the passes (at most EPT a
+// thread): the branch, possibly many split-K slices, is read once, and the residual once.
+template <typename TB, typename TW, typename TH, int EPT>
+__global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const Src<TB> branch,
+                                       const TW* __restrict__ w_post, float eps_post, float off_post,
+                                       const TW* __restrict__ w_next, float eps_next, float off_next,
+                                       TH* __restrict__ h, int width) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    float b[EPT], r[EPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int i = threadIdx.x + e * blockDim.x;
+        b[e] = 0.f;
+        r[e] = 0.f;
+        if (i < width) {
+            b[e] = branch.at(base + i);
+            r[e] = residual[base + i];
+            ss += b[e] * b[e];
+        }
+    }
+    float inv = 1.f;
+    if (w_post != nullptr) {
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int i = threadIdx.x + e * blockDim.x;
+        if (i < width) {
+            const float add = w_post != nullptr ? b[e] * inv * (off_post + Elem<TW>::load(w_post + i)) : b[e];
+            r[e] += add;
+            residual[base + i] = r[e];
+            ss2 += r[e] * r[e];
+        }
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+#pragma unroll
+    for (int e = 0; e < EPT; ++e) {
+        const int i = threadIdx.x + e * blockDim.x;
+        if (i < width) Elem<TH>::store(h + base + i, r[e] * inv2 * (off_next + Elem<TW>::load(w_next + i)));
+    }
+}
+
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
 
 }  // namespace kb
@@ -108,9 +156,15 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
     cudaStream_t s = (cudaStream_t)stream;
     const int t = threads_for(width);
 #define KB_ADDNORM(TB, TW, TH)                                                                                   \
-    add_rmsnorm_kernel<TB, TW, TH><<<rows, t, 0, s>>>(residual, Src<TB>{(const TB*)branch, splits, (size_t)split_stride}, \
-                                                      (const TW*)w_post, eps_post, off_post, (const TW*)w_next,    \
-                                                      eps_next, off_next, (TH*)h, width)
+    do {                                                                                                         \
+        const Src<TB> src{(const TB*)branch, splits, (size_t)split_stride};                                      \
+        if (width <= 8 * t && rows <= 256)              /* few rows: latency counts, not occupancy */                \
+            add_rmsnorm_reg_kernel<TB, TW, TH, 8><<<rows, t, 0, s>>>(residual, src, (const TW*)w_post, eps_post, off_post, \
+                                                                     (const TW*)w_next, eps_next, off_next, (TH*)h, width); \
+        else                                                                                                     \
+            add_rmsnorm_kernel<TB, TW, TH><<<rows, t, 0, s>>>(residual, src, (const TW*)w_post, eps_post, off_post, \
+                                                              (const TW*)w_next, eps_next, off_next, (TH*)h, width); \
+    } while (0)
     const int code = branch_dt * 4 + w_dt * 2 + h_dt;
     switch (code) {
         case 0: KB_ADDNORM(float, float, float); break;

@@ -26,6 +26,10 @@ ACT_CODES = {"gelu_tanh": 0, "silu": 1}
 import os as _os
 
 GEMM_LARGE = _os.environ.get("KAPEL_B200_GEMM_LARGE", "tcgen05")
+# Which kernel multiplies up to 64 rows of bfloat16: "skinny" (tcgen05 with the operands swapped: the
+# weights stream through shared memory by TMA) or "stream" (the mma.sync kernels that read the weights
+# straight into registers).
+GEMM_SMALL = _os.environ.get("KAPEL_B200_GEMM_SMALL", "skinny")
 
 
 class KernelError(RuntimeError):
@@ -302,6 +306,18 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             out = cast(out, out_dtype)
         return out
     out_dtype = out_dtype or torch.bfloat16
+    if 0 < m <= 64 and GEMM_SMALL == "skinny":
+        splits = int(lib.kb_gemm_skinny_splits(n, k))
+        if splits == 1:
+            out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+            _check(lib.kb_gemm_skinny(_ptr(out), _dt(out, "gemm output"), None, _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
+            return out
+        if softcap is None:
+            partials = torch.empty((splits, m, n), dtype=torch.float32, device=a.device)
+            _check(lib.kb_gemm_skinny(None, 0, _ptr(partials), _ptr(a), _ptr(w), m, n, k, 0, _f(0.0), _stream()))
+            split_sum = SplitSum(partials)
+            return split_sum if keep_split else finish(split_sum, out_dtype)
+        # a soft cap over partial sums: the streaming kernels' reduction applies it
     if keep_split and softcap is None and 0 < m <= 16:
         splits = int(lib.kb_gemm_bf16_row16_splits(n, k))
         if splits > 1:

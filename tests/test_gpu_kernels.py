@@ -173,6 +173,28 @@ def test_gemm_tcgen05(m, n, k):
     assert rel_err(got.numpy(), want.numpy()) < 2e-5
 
 
+@pytest.mark.parametrize("small", ["skinny", "stream"])
+@pytest.mark.parametrize("m", [1, 8, 16, 17, 32, 50, 64])
+@pytest.mark.parametrize("n,k", [(8, 8), (136, 72), (2304, 2048), (4096, 2304), (1000, 520)])
+def test_gemm_bf16_up_to_64_rows_both_kernels(small, m, n, k):
+    import kapel_b200.kernels as KK
+
+    a, w = rnd(m, k, seed=42, dtype=torch.bfloat16), rnd(n, k, seed=43, dtype=torch.bfloat16, scale=0.1)
+    want = a.double() @ w.double().T
+    old = KK.GEMM_SMALL
+    KK.GEMM_SMALL = small
+    try:
+        got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+        capped = K().gemm(dev(a), dev(w), out_dtype=torch.float32, softcap=30.0).cpu().double()
+        kept = K().gemm(dev(a), dev(w), keep_split=True)
+    finally:
+        KK.GEMM_SMALL = old
+    K().check_async_errors()
+    assert rel_err(got.numpy(), want.numpy()) < 2e-5
+    assert rel_err(capped.numpy(), (30.0 * torch.tanh(want / 30.0)).numpy()) < 2e-5
+    assert rel_err(K().finish(kept, torch.float32).cpu().double().numpy(), want.numpy()) < (2e-5 if isinstance(kept, K().SplitSum) else 1e-2)
+
+
 def test_gemm_bf16_refuses_what_it_cannot_take():
     a, w = rnd(4, 12, dtype=torch.bfloat16), rnd(8, 12, dtype=torch.bfloat16)
     with pytest.raises(K().KernelError, match="multiple of 8"):

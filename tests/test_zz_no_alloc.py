@@ -45,7 +45,16 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         out = torch.full((ashape[0], wshape[0]), float("nan"), dtype=odt, device="cuda")
         code, msg = _call(lib, out, a, w, cap)
         assert code == 0, msg
-        want = K.gemm(a, w, out_dtype=odt, softcap=cap)
+        # the existing entry point, kb_gemm_bf16, with scratch memory that the caller allocates
+        need = lib.kb_gemm_bf16_scratch_floats(ashape[0], wshape[0], ashape[1])
+        scratch = torch.empty((need,), dtype=torch.float32, device="cuda")
+        want = torch.empty_like(out)
+        code = lib.kb_gemm_bf16(
+            ctypes.c_void_p(want.data_ptr()), 1 if odt == torch.bfloat16 else 0, ctypes.c_void_p(a.data_ptr()),
+            ctypes.c_void_p(w.data_ptr()), ashape[0], wshape[0], ashape[1], 1 if cap else 0, ctypes.c_float(cap or 0.0),
+            ctypes.c_void_p(scratch.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+        )
+        assert code == 0, lib.kb_last_error().decode()
         torch.cuda.synchronize()
         assert torch.isfinite(out).all()
         ref = a.double().cpu() @ w.double().cpu().T
