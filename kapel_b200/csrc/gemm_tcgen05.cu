@@ -6,7 +6,8 @@
 //
 // One block computes one 128 x 256 tile of C. Six warps:
 //   warp 0    one lane walks K in steps of 64 and asks TMA for the A and W tiles of each step, four
-//             stages deep; a stage is free again when the MMAs that read it have completed
+//             stages deep (two, in each of two blocks a multiprocessor, for products of many
+//             tiles); a stage is free again when the MMAs that read it have completed
 //             (tcgen05.commit on the stage's "empty" mbarrier)
 //   warp 1    allocates 256 TMEM columns; one lane waits for a stage to fill and issues four
 //             128 x 256 x 16 MMAs on it (the shared-memory descriptors step 32 bytes through the
@@ -26,12 +27,12 @@ namespace kb {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64, TC_STAGES = 4;
+constexpr int TC_BM = 128, TC_BN = 256, TC_BK = 64;
 constexpr int TC_THREADS = 192;
 constexpr int TC_A_BYTES = TC_BM * TC_BK * 2;                  // 16 KB
 constexpr int TC_B_BYTES = TC_BN * TC_BK * 2;                  // 32 KB
 constexpr int TC_STAGE_BYTES = TC_A_BYTES + TC_B_BYTES;
-constexpr int TC_SMEM_BYTES = TC_STAGES * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */;
+constexpr int tc_smem_bytes(int stages) { return stages * TC_STAGE_BYTES + 1024 /* alignment slack */ + 256 /* barriers */; }
 constexpr int TC_TMEM_COLS = 256;
 
 __device__ int g_tcgen05_error = 0;
@@ -96,7 +97,11 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
-__global__ void __launch_bounds__(TC_THREADS, 1)
+// TC_STAGES = 4: one block a multiprocessor, for products of about one tile a multiprocessor.
+// TC_STAGES = 2: two blocks a multiprocessor, for products of many tiles: while one block stores
+// its tile or starts the next, the other keeps the tensor cores busy.
+template <int TC_STAGES>
+__global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
                     void* __restrict__ c, int c_dt, int m, int n, int k, int epi, float cap) {
     extern __shared__ unsigned char tc_smem_raw[];
@@ -405,8 +410,9 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
     if (int e = encode_map_bf16(&map_w, w, n, k, k, TC_BN)) return e;
     static bool attr_set = false;
     if (!attr_set) {
-        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, TC_SMEM_BYTES);
-        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", TC_SMEM_BYTES, cudaGetErrorString(e));
+        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(4));
+        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(2));
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", tc_smem_bytes(4), cudaGetErrorString(e));
         attr_set = true;
     }
     // Row tiles are the fast grid dimension: the blocks of a wave share a few weight tiles (each
@@ -414,7 +420,10 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
     // Measured on the gate|up product of a 2,048-token prompt: 187 us against 227 us the other way.
     dim3 grid((m + TC_BM - 1) / TC_BM, (n + TC_BN - 1) / TC_BN);
     KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d columns is too many for one launch", n);
-    gemm_tcgen05_kernel<<<grid, TC_THREADS, TC_SMEM_BYTES, (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
+    if ((long long)grid.x * grid.y > 3 * (long long)skinny_sms() / 2)
+        gemm_tcgen05_kernel<2><<<grid, TC_THREADS, tc_smem_bytes(2), (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
+    else
+        gemm_tcgen05_kernel<4><<<grid, TC_THREADS, tc_smem_bytes(4), (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
     return check_launch("gemm_tcgen05");
 }
 
