@@ -7,8 +7,8 @@
 //
 //  * a tile is up to MROWS rows of one request and one kv head; a row is (token, query head of
 //    the kv head's group), so the group shares every key and value it loads;
-//  * `attention_mma_kernel` (prompt portions, 64 rows): keys and values arrive 64 positions at a
-//    time by cp.async in two stages; each of 4 warps owns 16 rows and walks all keys;
+//  * `attention_mma_kernel` (prompt portions, 128 rows): keys and values arrive 64 positions at a
+//    time as TMA boxes in two stages; each of 8 warps owns 16 rows and walks all keys;
 //  * `attention_decode_kernel` (16 rows: a few tokens of one request): the 4 warps share the rows;
 //    each warp streams its own tiles of 16 keys through a three-stage pipeline of its own, filled
 //    by TMA: the cache tables are [pages, kv heads, page size, head_dim], so the 16 keys of a kv
@@ -49,6 +49,7 @@ struct AttMmaParams {
     int rows, hq, hkv, d, page_size, table_width, n_pages;
     int window, split, slots;
     int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
+    int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
     float scale, cap;
 };
 
@@ -130,106 +131,8 @@ __device__ __forceinline__ bool am_mbar_wait(uint64_t* bar, uint32_t parity) {
     }
 }
 
-// One warp's work on one tile part: 16 query rows against NKEYS keys that lie in shared memory.
-// S = Q K^T, scale, soft cap, mask, online softmax, O += P V. HD sizes the registers; d <= HD.
-//   q16: the warp's 16 query rows; tK, tV: the first of the NKEYS key and value rows; j0: the
-//   absolute position of the first key; cnt/fst: count and first visible key of rows g and g+8
-//   (a row beyond the tile's own has count INT_MAX: what it computes is never written).
-//   FULL: d == HD, known when the kernel is compiled, so the loops carry no size tests.
-template <int HD, int NKEYS, bool FULL>
-__device__ __forceinline__ void am_tile(const bf16* q16, const bf16* tK, const bf16* tV, int ld, int d, int j0,
-                                        const int (&cnt)[2], const int (&fst)[2], int fst_hi, int cnt_lo, int klo,
-                                        int khi, float sc, float cap, float (&o)[HD / 8][4], float (&m_run)[2],
-                                        float (&l_run)[2], int lane) {
-    constexpr int NT_S = NKEYS / 8;
-    constexpr int NT_O = HD / 8;
-    const int t = lane & 3;
-    const float LOG2E = 1.4426950408889634f;
-    float s[NT_S][4];
-#pragma unroll
-    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
-#pragma unroll
-    for (int ks = 0; ks < HD / 16; ++ks) {
-        if (FULL || ks * 16 < d) {
-            uint32_t a[4];
-            am_ldmatrix_x4(a, q16 + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + ks * 16 + (lane >> 4) * 8);
-#pragma unroll
-            for (int nb = 0; nb < NT_S / 2; ++nb) {
-                uint32_t b[4];
-                am_ldmatrix_x4(b, tK + (nb * 16 + (lane & 7) + (lane >> 4) * 8) * ld + ks * 16 + ((lane >> 3) & 1) * 8);
-                am_mma(s[2 * nb], a, b[0], b[1]);
-                am_mma(s[2 * nb + 1], a, b[2], b[3]);
-            }
-        }
-    }
-    float mx[2] = {-INFINITY, -INFINITY};
-    // Only a tile at an edge (of the causal triangle, of a window, of the block's key range) needs
-    // the mask: fst_hi and cnt_lo are the warp's largest first-visible key and smallest count.
-    const bool inner = j0 >= fst_hi && j0 + NKEYS <= cnt_lo && j0 >= klo && j0 + NKEYS <= khi;
-#pragma unroll
-    for (int nt = 0; nt < NT_S; ++nt)
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int h = e >> 1;
-            float v = s[nt][e] * sc;
-            if (cap > 0.f) v = cap * am_tanh(v);
-            if (!inner) {
-                const int j = j0 + nt * 8 + t * 2 + (e & 1);
-                const bool seen = j >= fst[h] && j < cnt[h] && j >= klo && j < khi;
-                v = seen ? v : -INFINITY;
-            }
-            s[nt][e] = v;
-            mx[h] = fmaxf(mx[h], v);
-        }
-    float alpha[2];
-#pragma unroll
-    for (int h = 0; h < 2; ++h) {
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
-        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
-        const float m_new = fmaxf(m_run[h], mx[h]);
-        alpha[h] = (m_new == -INFINITY) ? 1.f : am_exp2((m_run[h] - m_new) * LOG2E);
-        m_run[h] = m_new;
-        l_run[h] *= alpha[h];
-    }
-    // p = exp(s - m); the row sums stay per thread until the end
-    uint32_t pa[NT_S / 2][4];
-#pragma unroll
-    for (int nt = 0; nt < NT_S; ++nt) {
-        float pv[4];
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-            const int h = e >> 1;
-            pv[e] = (s[nt][e] == -INFINITY) ? 0.f : am_exp2((s[nt][e] - m_run[h]) * LOG2E);
-            l_run[h] += pv[e];
-        }
-        // the C layout of two neighbouring n-tiles is the A layout of one k16 step
-        pa[nt >> 1][(nt & 1) * 2] = am_pack(pv[0], pv[1]);
-        pa[nt >> 1][(nt & 1) * 2 + 1] = am_pack(pv[2], pv[3]);
-    }
-    // The running maximum settles after a few tiles; then there is nothing to rescale.
-    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
-#pragma unroll
-        for (int i = 0; i < NT_O; ++i) {
-            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
-            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
-        }
-    }
-#pragma unroll
-    for (int kb = 0; kb < NT_S / 2; ++kb) {
-#pragma unroll
-        for (int nd = 0; nd < HD / 16; ++nd) {
-            if (FULL || nd * 16 < d) {
-                uint32_t b[4];
-                am_ldmatrix_x4_trans(b, tV + (kb * 16 + (lane & 7) + ((lane >> 3) & 1) * 8) * ld + nd * 16 + (lane >> 4) * 8);
-                am_mma(o[2 * nd], pa[kb], b[0], b[1]);
-                am_mma(o[2 * nd + 1], pa[kb], b[2], b[3]);
-            }
-        }
-    }
-}
-
-// The same work with the operands swapped, for the decode kernel, where only a few of the 16
-// rows exist: S^T = K Q^T and O^T = V^T P^T. The 16 keys are the MMAs' M; the rows ("heads" here:
+// One warp's work on one tile of 16 keys with the operands swapped, for the decode kernel, where
+// only a few of the 16 rows exist: S^T = K Q^T and O^T = V^T P^T. The 16 keys are the MMAs' M; the rows ("heads" here:
 // (token, query head) pairs) are their N, eight a block, NB blocks. Q waits in registers as B
 // fragments (`bq`), so it costs no load in the loop; O^T is 16 x NB x 4 registers instead of 128;
 // and 16 keys cost 16 + 16 MMAs and ldmatrix instead of 32 + 32 and 48.
@@ -366,28 +269,142 @@ __device__ __forceinline__ AmTile am_tile_info(const AttMmaParams& p, int tile, 
     return x;
 }
 
-// Prompt portions: 64 rows a block, each warp 16 of them over all the block's keys.
+// One warp's 16 query rows against 64 keys that TMA left in shared memory as boxes of 16 keys x 64
+// elements (2 KB, 128-byte swizzle): box (sub, x) of the keys holds keys 16 sub .. and elements
+// 64 x .., boxes in (sub, x) order, `nbox` of them along head_dim; the values likewise.
+// S = Q K^T, scale, soft cap, mask, online softmax, O += P V. HD sizes the registers; d <= HD.
+//   q16: the warp's 16 query rows (rows `ld` elements apart); j0: the absolute position of the
+//   first key; cnt/fst: count and first visible key of rows g and g+8 (a row beyond the tile's own
+//   has count INT_MAX: what it computes is never written); fst_hi/cnt_lo: the warp's largest
+//   first-visible key and smallest count, so that only tiles at an edge are masked.
+//   FULL: d == HD, known when the kernel is compiled, so the loops carry no size tests.
 template <int HD, bool FULL>
-__global__ void __launch_bounds__(AM_THREADS)
-attention_mma_kernel(const AttMmaParams p) {
-    constexpr int MROWS = 64;
+__device__ __forceinline__ void am_tile_boxes(const bf16* q16, uint32_t tK, uint32_t tV, int ld, int d, int nbox, int j0,
+                                              const int (&cnt)[2], const int (&fst)[2], int fst_hi, int cnt_lo, int klo,
+                                              int khi, float sc, float cap, float (&o)[HD / 8][4], float (&m_run)[2],
+                                              float (&l_run)[2], int lane) {
+    constexpr int NKEYS = 64;
+    constexpr int NT_S = NKEYS / 8;
+    constexpr int NT_O = HD / 8;
+    const int t = lane & 3;
+    const float LOG2E = 1.4426950408889634f;
+    float s[NT_S][4];
+#pragma unroll
+    for (int i = 0; i < NT_S; ++i) s[i][0] = s[i][1] = s[i][2] = s[i][3] = 0.f;
+    const int kr = (lane & 7) + (lane >> 4) * 8;              // key row within a box, for the score product
+    const uint32_t kbase = tK + kr * 128;
+#pragma unroll
+    for (int ks = 0; ks < HD / 16; ++ks) {
+        if (FULL || ks * 16 < d) {
+            uint32_t a[4];
+            am_ldmatrix_x4(a, q16 + ((lane & 7) + ((lane >> 3) & 1) * 8) * ld + ks * 16 + (lane >> 4) * 8);
+            const uint32_t koff = (uint32_t)(ks >> 2) * 2048u + (uint32_t)(((((ks & 3) << 1) + ((lane >> 3) & 1)) ^ (kr & 7)) << 4);
+#pragma unroll
+            for (int nb = 0; nb < NT_S / 2; ++nb) {             // keys 16 nb ..: box row `sub` = nb
+                uint32_t b[4];
+                am_ldmatrix_x4_at(b, kbase + (uint32_t)(nb * nbox) * 2048u + koff);
+                am_mma(s[2 * nb], a, b[0], b[1]);
+                am_mma(s[2 * nb + 1], a, b[2], b[3]);
+            }
+        }
+    }
+    float mx[2] = {-INFINITY, -INFINITY};
+    const bool inner = j0 >= fst_hi && j0 + NKEYS <= cnt_lo && j0 >= klo && j0 + NKEYS <= khi;
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            float v = s[nt][e] * sc;
+            if (cap > 0.f) v = cap * am_tanh(v);
+            if (!inner) {
+                const int j = j0 + nt * 8 + t * 2 + (e & 1);
+                const bool seen = j >= fst[h] && j < cnt[h] && j >= klo && j < khi;
+                v = seen ? v : -INFINITY;
+            }
+            s[nt][e] = v;
+            mx[h] = fmaxf(mx[h], v);
+        }
+    float alpha[2];
+#pragma unroll
+    for (int h = 0; h < 2; ++h) {
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 1));
+        mx[h] = fmaxf(mx[h], __shfl_xor_sync(0xffffffffu, mx[h], 2));
+        const float m_new = fmaxf(m_run[h], mx[h]);
+        alpha[h] = (m_new == -INFINITY) ? 1.f : am_exp2((m_run[h] - m_new) * LOG2E);
+        m_run[h] = m_new;
+        l_run[h] *= alpha[h];
+    }
+    uint32_t pa[NT_S / 2][4];
+#pragma unroll
+    for (int nt = 0; nt < NT_S; ++nt) {
+        float pv[4];
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+            const int h = e >> 1;
+            pv[e] = (s[nt][e] == -INFINITY) ? 0.f : am_exp2((s[nt][e] - m_run[h]) * LOG2E);
+            l_run[h] += pv[e];
+        }
+        pa[nt >> 1][(nt & 1) * 2] = am_pack(pv[0], pv[1]);
+        pa[nt >> 1][(nt & 1) * 2 + 1] = am_pack(pv[2], pv[3]);
+    }
+    if (__any_sync(0xffffffffu, alpha[0] != 1.f || alpha[1] != 1.f)) {
+#pragma unroll
+        for (int i = 0; i < NT_O; ++i) {
+            o[i][0] *= alpha[0]; o[i][1] *= alpha[0];
+            o[i][2] *= alpha[1]; o[i][3] *= alpha[1];
+        }
+    }
+    const int vr = (lane & 7) + ((lane >> 3) & 1) * 8;        // key row within a box, for the value product
+    const uint32_t vbase = tV + vr * 128;
+#pragma unroll
+    for (int kb = 0; kb < NT_S / 2; ++kb) {
+#pragma unroll
+        for (int nd = 0; nd < HD / 16; ++nd) {
+            if (FULL || nd * 16 < d) {
+                uint32_t b[4];
+                const uint32_t voff = (uint32_t)(kb * nbox + (nd >> 2)) * 2048u + (uint32_t)(((((nd & 3) << 1) + (lane >> 4)) ^ (vr & 7)) << 4);
+                am_ldmatrix_x4_trans_at(b, vbase + voff);
+                am_mma(o[2 * nd], pa[kb], b[0], b[1]);
+                am_mma(o[2 * nd + 1], pa[kb], b[2], b[3]);
+            }
+        }
+    }
+}
+
+// Prompt portions: 128 rows a block, each of 8 warps 16 of them over all the block's keys, which
+// arrive 64 positions at a time as TMA boxes, two stages.
+constexpr int AP_THREADS = 256;
+constexpr int AP_ROWS = 128;
+
+template <int HD, bool FULL>
+__global__ void __launch_bounds__(AP_THREADS)
+attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap map_k,
+                     const __grid_constant__ CUtensorMap map_v) {
     constexpr int NT_O = HD / 8;
     extern __shared__ __align__(128) unsigned char am_smem[];
     const int d = p.d;
     const int ld = d + AM_PAD;
-    bf16* sQ = reinterpret_cast<bf16*>(am_smem);
-    bf16* sK = sQ + MROWS * ld;                             // [2][KT][ld]
-    bf16* sV = sK + 2 * AM_KT * ld;                         // [2][KT][ld]
+    const int nbox = (d + 63) / 64;
+    bf16* sQ = reinterpret_cast<bf16*>(am_smem);                     // [128][ld]
+    const uint32_t half_bytes = 4u * nbox * 2048u;                   // a tile's keys (or values): 4 x nbox boxes
+    const uint32_t stage_bytes = 2u * half_bytes;
+    const uint32_t smem0 = am_saddr(am_smem);
+    const uint32_t stages = (smem0 + AP_ROWS * ld * (uint32_t)sizeof(bf16) + 1023u) & ~1023u;
+    unsigned char* stages_ptr = am_smem + (stages - smem0);
+    uint64_t* bars = reinterpret_cast<uint64_t*>(stages_ptr + 2 * stage_bytes);    // [2] stage full
+    int* sPage = reinterpret_cast<int*>(bars + 2);                   // [2][4] pages of a tile's four groups of 16 keys
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int g = lane >> 2, t = lane & 3;
-    const int kvh = blockIdx.y, slot = blockIdx.z;
-    // Later tiles of a prompt see more keys: they start first.
-    const AmTile x = am_tile_info(p, gridDim.x - 1 - blockIdx.x, slot);
+    const int kvh = blockIdx.x, slot = blockIdx.y;
+    // Later tiles of a prompt see more keys: they start first, all their heads and slots together,
+    // so that blocks are handed out roughly by falling length.
+    const AmTile x = am_tile_info(p, gridDim.z - 1 - blockIdx.z, slot);
     const int group = x.group, row0 = x.row0, rows_valid = x.rows_valid, klo = x.klo, khi = x.khi;
     if (klo >= khi) {
         if (p.slots == 1 && x.c_first <= 0)
-            for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
+            for (int i = tid; i < rows_valid * d; i += AP_THREADS) {
                 const int r = i / d, c = i % d;
                 p.out[((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + c] = __float2bfloat16_rn(0.f);
             }
@@ -396,40 +413,68 @@ attention_mma_kernel(const AttMmaParams p) {
     const int k_begin = klo / AM_KT * AM_KT;               // tiles are cut at multiples of KT
     const int n_tiles = (khi - k_begin + AM_KT - 1) / AM_KT;
 
+    if (tid == 0) {
+        am_mbar_init(bars, 1);
+        am_mbar_init(bars + 1, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
     const int chunks = d / 8;                               // 16-byte chunks a row
-    for (int i = tid; i < MROWS * chunks; i += AM_THREADS) {
+    for (int i = tid; i < AP_ROWS * chunks; i += AP_THREADS) {
         const int r = i / chunks, ch = i % chunks;
         const bool valid = r < rows_valid;
         const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
         am_cp_async16(sQ + r * ld + ch * 8, src, valid);
     }
-    // A tile's 64 table rows (of this kv head, or -1) wait in shared memory, written one iteration
-    // ahead by the first 64 threads; then consecutive threads copy consecutive 16-byte pieces of a
-    // key row, so a warp's copy instruction covers whole rows.
-    int* sLine = reinterpret_cast<int*>(sV + 2 * AM_KT * ld);          // [2][KT]
-    auto find_lines = [&](int kt) {
-        if (tid < AM_KT) {
-            const int j = k_begin + kt * AM_KT + tid;
-            const long long line = (kt < n_tiles && j >= klo && j < khi) ? am_line(p, x.entry, j) : -1;
-            sLine[(kt & 1) * AM_KT + tid] = line >= 0 ? (int)kv_row(line, kvh, p.hkv, p.page_size) : -1;
-        }
-    };
-    auto load_tile = [&](int stage, int kt) {
-        const int* lines = sLine + (kt & 1) * AM_KT;
-        for (int idx = tid; idx < AM_KT * chunks; idx += AM_THREADS) {
-            const int r = idx / chunks, ch = idx - r * chunks;
-            const int row = lines[r];
-            const bool valid = row >= 0;
-            const size_t off = (size_t)(valid ? row : 0) * d + ch * 8;
-            am_cp_async16(sK + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.k_table + off, valid);
-            am_cp_async16(sV + ((size_t)stage * AM_KT + r) * ld + ch * 8, p.v_table + off, valid);
-        }
-    };
-    find_lines(0);
-    find_lines(1);
-    __syncthreads();
-    load_tile(0, 0);
     am_commit();
+    // The pages of tile kt's four groups of 16 keys, written one iteration ahead by four threads.
+    auto find_pages = [&](int kt) {
+        if (tid < 4) {
+            const int j = k_begin + kt * AM_KT + tid * 16;
+            int page = -1;
+            if (kt < n_tiles && j < khi && j + 16 > klo) {
+                const int lp = max(j, klo) / p.page_size;
+                if (lp < p.table_width) page = p.block_table[(size_t)x.entry * p.table_width + lp];
+                if (page >= p.n_pages) page = -1;
+            }
+            sPage[(kt & 1) * 4 + tid] = page;
+        }
+    };
+    // Warp 0 asks TMA for the boxes of tile kt: operation o is group o / (2 nbox), and of that group
+    // the keys' box o % (2 nbox) or, from nbox on, the values' box. Groups without a page are cleared
+    // by everyone instead.
+    auto load_tile = [&](int kt) {
+        const int stage = kt & 1;
+        const int* pages = sPage + stage * 4;
+        const uint32_t dst = stages + (uint32_t)stage * stage_bytes;
+        int live = 0;
+#pragma unroll
+        for (int sub = 0; sub < 4; ++sub) live += pages[sub] >= 0 ? 1 : 0;
+        if (tid == 0) am_mbar_expect_tx(bars + stage, (uint32_t)live * 2u * nbox * 2048u);
+        __syncwarp();
+        if (warp == 0) {
+            for (int op = lane; op < 8 * nbox; op += 32) {
+                const int sub = op / (2 * nbox), bx = op % (2 * nbox);
+                const int page = pages[sub];
+                if (page < 0) continue;
+                const int j = k_begin + kt * AM_KT + sub * 16;
+                const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                if (bx < nbox) am_tma_box(dst + (uint32_t)(sub * nbox + bx) * 2048u, &map_k, bx * 64, row, bars + stage);
+                else am_tma_box(dst + half_bytes + (uint32_t)(sub * nbox + bx - nbox) * 2048u, &map_v, (bx - nbox) * 64, row, bars + stage);
+            }
+        }
+        if (live < 4) {
+            for (int sub = 0; sub < 4; ++sub) {
+                if (pages[sub] >= 0) continue;
+                uint4* zk = reinterpret_cast<uint4*>(stages_ptr + (size_t)stage * stage_bytes + (size_t)sub * nbox * 2048);
+                uint4* zv = reinterpret_cast<uint4*>(stages_ptr + (size_t)stage * stage_bytes + half_bytes + (size_t)sub * nbox * 2048);
+                for (int i = tid; i < nbox * 128; i += AP_THREADS) { zk[i] = make_uint4(0u, 0u, 0u, 0u); zv[i] = make_uint4(0u, 0u, 0u, 0u); }
+            }
+        }
+    };
+    find_pages(0);
+    find_pages(1);
+    __syncthreads();                                        // barriers initialised, pages of tiles 0 and 1 known
+    load_tile(0);
 
     float o[NT_O][4];
 #pragma unroll
@@ -447,17 +492,22 @@ attention_mma_kernel(const AttMmaParams p) {
     const int fst_hi = __reduce_max_sync(0xffffffffu, max(fst[0], fst[1]));
     const int cnt_lo = __reduce_min_sync(0xffffffffu, min(cnt[0], cnt[1]));
     const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
+    am_wait<0>();                                           // this thread's part of Q has landed
 
+    bool failed = false;
     for (int kt = 0; kt < n_tiles; ++kt) {
-        am_wait<0>();
-        __syncthreads();                                    // tile kt landed; the other stage is free
-        if (kt + 1 < n_tiles) load_tile((kt + 1) & 1, kt + 1);
-        am_commit();
-        find_lines(kt + 2);                                 // read after the next barrier; last read before this one
-        am_tile<HD, AM_KT, FULL>(sQ + wrow * ld, sK + (size_t)(kt & 1) * AM_KT * ld, sV + (size_t)(kt & 1) * AM_KT * ld, ld, d,
-                           k_begin + kt * AM_KT, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap, o, m_run, l_run, lane);
+        if (!am_mbar_wait(bars + (kt & 1), (uint32_t)(kt >> 1) & 1u)) failed = true;
+        if (__syncthreads_or(failed)) { failed = true; break; }       // tile kt landed (and Q); the other stage is free
+        if (kt + 1 < n_tiles) load_tile(kt + 1);
+        find_pages(kt + 2);                                 // read after the next barrier; last read before this one
+        const uint32_t tk = stages + (uint32_t)(kt & 1) * stage_bytes;
+        am_tile_boxes<HD, FULL>(sQ + wrow * ld, tk, tk + half_bytes, ld, d, nbox, k_begin + kt * AM_KT, cnt, fst, fst_hi, cnt_lo,
+                                klo, khi, sc, p.cap, o, m_run, l_run, lane);
     }
-    am_wait<0>();
+    if (failed) {
+        if (tid == 0) atomicExch(&g_attention_error, 1);
+        return;                                             // a copy never completed: nothing is written
+    }
 #pragma unroll
     for (int h = 0; h < 2; ++h) {
         l_run[h] += __shfl_xor_sync(0xffffffffu, l_run[h], 1);
@@ -468,18 +518,22 @@ attention_mma_kernel(const AttMmaParams p) {
         const int r = wrow + g + h * 8;
         if (r >= rows_valid) continue;
         const int row = row0 + r / group, head = kvh * group + r % group;
-        if (p.slots == 1) {
+        // With several slots, a row whose keys all lie in one slot is finished by that slot's block.
+        const int z0 = p.slots > 1 ? fst[h] / p.split : 0;
+        const int z1 = p.slots > 1 ? min(p.slots - 1, (cnt[h] - 1) / p.split) : 0;
+        if (z0 == z1) {
+            if (slot != z0) continue;
             const float inv = l_run[h] > 0.f ? 1.f / l_run[h] : 0.f;
             bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
 #pragma unroll
             for (int i = 0; i < NT_O; ++i)
-                if (i * 8 < d)
+                if (FULL || i * 8 < d)
                     *reinterpret_cast<uint32_t*>(dst + i * 8 + t * 2) = am_pack(o[i][h * 2] * inv, o[i][h * 2 + 1] * inv);
         } else {
             float* dst = p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2);
 #pragma unroll
             for (int i = 0; i < NT_O; ++i)
-                if (i * 8 < d) { dst[i * 8 + t * 2] = o[i][h * 2]; dst[i * 8 + t * 2 + 1] = o[i][h * 2 + 1]; }
+                if (FULL || i * 8 < d) { dst[i * 8 + t * 2] = o[i][h * 2]; dst[i * 8 + t * 2 + 1] = o[i][h * 2 + 1]; }
             if (t == 0) { dst[d] = m_run[h]; dst[d + 1] = l_run[h]; }
         }
     }
@@ -719,6 +773,7 @@ attention_mma_combine_kernel(const AttMmaParams p) {
     const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
     const int z0 = first / p.split, z1 = min(p.slots - 1, (count - 1) / p.split);
     const int nz = z1 - z0 + 1;
+    if (nz == 1 && p.direct) return;
     const int stride = p.d + 2;
     const float* base = p.partial + (((size_t)row * p.hq + head) * p.slots + z0) * stride;
     if (threadIdx.x < 32) {
@@ -738,26 +793,37 @@ attention_mma_combine_kernel(const AttMmaParams p) {
         for (int z = lane; z < nz; z += 32) cw[z] *= inv;
     }
     __syncthreads();
-    for (int i = threadIdx.x; i < p.d; i += blockDim.x) {
-        float acc = 0.f;
+    for (int i = threadIdx.x * 2; i < p.d; i += blockDim.x * 2) {      // d and the stride are even
+        float a0 = 0.f, a1 = 0.f;
 #pragma unroll 4
-        for (int z = 0; z < nz; ++z) acc = fmaf(cw[z], base[(size_t)z * stride + i], acc);
-        o[i] = __float2bfloat16_rn(acc);
+        for (int z = 0; z < nz; ++z) {
+            const float2 v = *reinterpret_cast<const float2*>(base + (size_t)z * stride + i);
+            a0 = fmaf(cw[z], v.x, a0);
+            a1 = fmaf(cw[z], v.y, a1);
+        }
+        *reinterpret_cast<uint32_t*>(o + i) = am_pack(a0, a1);
     }
 }
 
 template <int HD>
 static int launch_prompt(const AttMmaParams& p, int tiles, cudaStream_t s) {
+    if (p.page_size % 16 != 0) return fail("attention_mma: pages must hold a multiple of 16 positions, got %d", p.page_size);
     const int ld = p.d + AM_PAD;
-    const size_t smem = ((size_t)64 * ld + 4 * (size_t)AM_KT * ld) * sizeof(bf16) + 2 * AM_KT * sizeof(int);
-    if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
-    dim3 grid(tiles, p.hkv, p.slots);
+    const int nbox = (p.d + 63) / 64;
+    const size_t smem = (size_t)AP_ROWS * ld * sizeof(bf16) + 2048 + 2 * (size_t)8 * nbox * 2048 + 2 * sizeof(uint64_t) + 8 * sizeof(int) + 16;
+    if (smem > 225 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
+    const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
+    CUtensorMap map_k, map_v;
+    if (int e = encode_map_bf16(&map_k, p.k_table, rows, p.d, p.d, 16)) return e;
+    if (int e = encode_map_bf16(&map_v, p.v_table, rows, p.d, p.d, 16)) return e;
+    if (tiles > 65535 || p.slots > 65535) return fail("attention_mma: %d tiles in %d slots is too many for one launch", tiles, p.slots);
+    dim3 grid(p.hkv, p.slots, tiles);
     if (p.d == HD) {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mma_kernel<HD, true>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_mma_kernel<HD, true><<<grid, AM_THREADS, smem, s>>>(p);
+        attention_mma_kernel<HD, true><<<grid, AP_THREADS, smem, s>>>(p, map_k, map_v);
     } else {
         if (smem > 48 * 1024) cudaFuncSetAttribute(attention_mma_kernel<HD, false>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem);
-        attention_mma_kernel<HD, false><<<grid, AM_THREADS, smem, s>>>(p);
+        attention_mma_kernel<HD, false><<<grid, AP_THREADS, smem, s>>>(p, map_k, map_v);
     }
     return check_launch("attention_mma");
 }
@@ -802,7 +868,7 @@ static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStr
 using namespace kb;
 
 // Rows a tile may hold in each mode; the host cuts requests into tiles of rows / group tokens.
-extern "C" int kb_attention_mma_rows(int decode) { return decode ? 16 : 64; }
+extern "C" int kb_attention_mma_rows(int decode) { return decode ? 16 : AP_ROWS; }
 
 // 1 if a wait inside an attention kernel ever ran out (and clears the flag); synchronises the device.
 extern "C" int kb_attention_error() {
@@ -825,7 +891,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     // holds, at most 16.
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_mma: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
     KB_REQUIRE(d > 0 && d % 16 == 0 && d <= 256, "attention_mma: head_dim %d must be a multiple of 16, at most 256", d);
-    KB_REQUIRE(hq / hkv <= (decode ? 16 : 64), "attention_mma: %d query heads a kv head do not fit a tile of %d rows", hq / hkv, decode ? 16 : 64);
+    KB_REQUIRE(hq / hkv <= (decode ? 16 : AP_ROWS), "attention_mma: %d query heads a kv head do not fit a tile of %d rows", hq / hkv, decode ? 16 : AP_ROWS);
     KB_REQUIRE(decode >= 0 && decode <= 16 && (decode == 0 || decode >= hq / hkv), "attention_mma: decode mode with %d rows a tile (1..16, at least the group of %d)", decode, hq / hkv);
     KB_REQUIRE(page_size > 0 && table_width > 0 && n_pages > 0, "attention_mma: page_size %d, table width %d, pages %d", page_size, table_width, n_pages);
     KB_REQUIRE(window >= 0 && cap >= 0.f, "attention_mma: window %d, cap %g", window, cap);
@@ -842,6 +908,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width;
     p.n_pages = n_pages; p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
     p.decode_bar_offset = 0;
+    p.direct = decode ? 0 : 1;
     cudaStream_t s = (cudaStream_t)stream;
     int e;
     if (d <= 64) e = decode ? launch_decode<64>(p, tiles, decode, s) : launch_prompt<64>(p, tiles, s);

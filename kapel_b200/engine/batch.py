@@ -31,7 +31,6 @@ def _chunks_touched(row_count: np.ndarray, window: Optional[int], chunk: int) ->
     return int(((c - 1) // chunk - first // chunk + 1).max())
 
 
-PROMPT_SPLIT = 1024      # keys a block of the prompt attention kernel when the tiles alone would leave most of the GPU idle
 SPLIT_STEP = 64          # splits are multiples of the kernels' key tile
 
 
@@ -54,6 +53,43 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
             best = (cost, split)
     split = best[1]
     return split, max(1, -(-longest // split))
+
+
+def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, window: Optional[int], rows: int, hq: int, d: int):
+    """(split, slots) of the prompt attention kernel. A tile of a long prompt walks all the keys
+    before it, so late tiles work many times longer than early ones; cutting the keys into slots
+    of `split` positions evens the blocks out at the price of partial sums that a second kernel
+    merges. The choice minimises an estimate of the time: the longest block or the mean load of a
+    multiprocessor, whichever is larger, plus the merge, all counted in 64-key steps."""
+    first = np.asarray(first_counts, np.int64)
+    last = np.asarray(last_counts, np.int64)
+    lo = np.maximum(0, first - window) if window else np.zeros_like(first)
+    longest = int(last.max()) if last.size else 0
+    best = None
+    for split in (0, 4096, 2048, 1024, 512, 256, 128):
+        if split == 0:
+            steps = -(-(last - lo // 64 * 64) // 64)
+            work = steps.astype(np.float64)
+            slots = 1
+            merge = 0.0
+        else:
+            if split >= longest:
+                continue
+            slots = -(-longest // split)
+            z = np.arange(slots)[None, :]
+            a = np.maximum(lo[:, None], z * split)
+            b = np.minimum(last[:, None], (z + 1) * split)
+            steps = np.where(b > a, -(-(b - a // 64 * 64) // 64), 0)
+            work = steps.astype(np.float64).reshape(-1)
+            # what the partial sums cost to write and read back (at ~5 TB/s), in steps of ~4.5 us, plus a launch
+            merge = 1.0 + slots * rows * hq * (d + 2) * 8 / 5e12 / 4.5e-6
+        work = work[work > 0] + 0.5                      # half a step to start and finish a block
+        if work.size == 0:
+            continue
+        cost = max(float(work.max()), float(work.sum()) * pairs_per_tile / sms * 1.1) + merge
+        if best is None or cost < best[0]:
+            best = (cost, split, slots)
+    return (best[1], best[2]) if best else (0, 1)
 
 
 _SMS = {}
@@ -141,8 +177,9 @@ class StepBatch:
             if decode:
                 split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window)
             else:
-                split = 0 if n * kv_heads >= 96 else PROMPT_SPLIT
-                slots = max(1, -(-longest // split)) if split else 1
+                firsts = plan.row_count[arrays[1]]
+                split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,
+                                            plan.rows, heads_per_kv * kv_heads, 256)
             self.memo[key] = (decode, tiles, split, slots, host)
         return self.memo[key][:4]
 

@@ -63,7 +63,7 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
 
     from . import kernels as K
-    from .engine.batch import PROMPT_SPLIT, cut_tiles, decode_split, sm_count
+    from .engine.batch import cut_tiles, decode_split, prompt_split, sm_count
 
     dev = torch.device("cuda", torch.cuda.current_device())
     K.library()
@@ -153,13 +153,12 @@ def main(argv=None) -> int:
         rc = torch.arange(1, t + 1, dtype=torch.int32, device=dev)
         per_tile = max(1, K.attention_mma_rows(False) // (Hq // Hkv))
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
-        n = tiles[0].numel()
-        split = 0 if n * Hkv >= 96 else PROMPT_SPLIT
-        slots = max(1, -(-t // split)) if split else 1
+        firsts = tiles[1].cpu().numpy() + 1
+        split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D)
         pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
                                                    0, split, slots), max(3, args.iters // 4))
-        report(f"{name} [{t} tokens]", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
+        report(f"{name} [{t} tokens] split={split}x{slots}", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
 
     if args.prompt <= ctx:
         prompt_case(None)
