@@ -1,0 +1,75 @@
+"""The engine at the layer sizes of Gemma 2 2B, 9B and 27B against the plain implementation.
+
+Two layers of the real widths, head counts, head sizes and scale factors (one windowed, one
+global), with a small vocabulary and a short window so that the plain implementation on the CPU
+finishes in seconds and the window's edge lies inside the prompts. Each request is run whole, and
+again cut into portions beside another request's portions and decoded tokens.
+"""
+import shutil
+
+import numpy as np
+import pytest
+
+import helpers
+from helpers import TOL, TraceBuilder, compare_trace, embed_scale_for, make_model_dir, plain_logits, random_tokens, run_trace_engine
+
+pytestmark = pytest.mark.gpu
+
+
+def _config(hidden, heads, kv_heads, head_dim, intermediate, scalar):
+    return dict(
+        architectures=["Gemma2ForCausalLM"], model_type="gemma2",
+        num_hidden_layers=2, hidden_size=hidden, num_attention_heads=heads, num_key_value_heads=kv_heads,
+        head_dim=head_dim, intermediate_size=intermediate, vocab_size=4096, rope_theta=10000.0, sliding_window=64,
+        query_pre_attn_scalar=scalar, attn_logit_softcapping=50.0, final_logit_softcapping=30.0,
+        rms_norm_eps=1e-6, hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True,
+        max_position_embeddings=8192,
+    )
+
+
+SHAPES = {
+    "2b": _config(2304, 8, 4, 256, 9216, 256),
+    "9b": _config(3584, 16, 8, 256, 14336, 256),
+    "27b": _config(4608, 32, 16, 128, 36864, 144),
+}
+
+
+@pytest.fixture(scope="module", params=list(SHAPES))
+def case(request):
+    name = request.param
+    raw = SHAPES[name]
+    folder = make_model_dir(raw, seed=3)
+    rng = np.random.default_rng(21)
+    reqs = {"a": random_tokens(rng, 100, raw["vocab_size"]), "b": random_tokens(rng, 70, raw["vocab_size"])}
+    plain = {}
+    for dtype in ("float32", "bfloat16"):
+        scale = embed_scale_for(raw, dtype)
+        plain[dtype] = {rid: plain_logits(folder, toks, embed_scale=scale) for rid, toks in reqs.items()}
+    yield name, raw, folder, reqs, plain
+    shutil.rmtree(folder, ignore_errors=True)
+    helpers._PLAIN_CACHE.clear()                            # the plain weights in 64-bit are several GB
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_layer_sizes(case, dtype):
+    from kapel_b200.engine import Engine
+
+    name, raw, folder, reqs, plain = case
+    engine = Engine.from_dir(folder, dtype=dtype, max_tokens=256, max_sequences=4)
+    a, b = reqs["a"], reqs["b"]
+
+    whole = TraceBuilder()
+    for rid, toks in reqs.items():
+        whole.step([(rid, toks, [0, len(toks) // 2, len(toks) - 1])], end=[rid])
+    worst = compare_trace(run_trace_engine(engine, whole.steps), whole, plain[dtype], TOL[dtype], f"{name} whole {dtype}")
+
+    cut = TraceBuilder()
+    cut.step([("a", a[:50], [49]), ("b", b[:2], [1])])
+    cut.step([("a", a[50:92], [0, 41]), ("b", b[2:62], [59])])
+    for i in range(8):
+        last = i == 7
+        cut.step([("a", [a[92 + i]], [0]), ("b", [b[62 + i]], [0])], end=["a", "b"] if last else [])
+    worst = max(worst, compare_trace(run_trace_engine(engine, cut.steps), cut, plain[dtype], TOL[dtype], f"{name} cut {dtype}"))
+    print(f"{name} {dtype}: worst {worst:.2e}")
+    engine.cache.check()
+    assert engine.cache.free_pages() == engine.cache.total_pages()
