@@ -42,6 +42,12 @@ GEMMA2_2B = dict(
     rms_norm_eps=1e-6, hidden_activation="gelu_pytorch_tanh", tie_word_embeddings=True,
     max_position_embeddings=8192,
 )
+# The other two sizes, for `--size`; the line the contract asks for is the 2B one.
+GEMMA2_9B = dict(GEMMA2_2B, num_hidden_layers=42, hidden_size=3584, num_attention_heads=16, num_key_value_heads=8,
+                 intermediate_size=14336)
+GEMMA2_27B = dict(GEMMA2_2B, num_hidden_layers=46, hidden_size=4608, num_attention_heads=32, num_key_value_heads=16, head_dim=128,
+                  intermediate_size=36864, query_pre_attn_scalar=144)
+SIZES = {"2b": (GEMMA2_2B, 6144), "9b": (GEMMA2_9B, 6144), "27b": (GEMMA2_27B, 2048)}      # configuration, tokens of history
 FULL_LAYERS = GEMMA2_2B["num_hidden_layers"]
 HISTORY = 6144
 CONTEXT = 8192
@@ -62,38 +68,47 @@ def peaks():
 
 
 class ClockSampler:
-    """Samples SM clocks and throttle reasons with nvidia-smi while `active`."""
+    """Samples SM clocks and throttle reasons while `active`: one nvidia-smi process that prints a
+    line every 50 ms, read by a thread."""
 
     QUERY = ("clocks.sm,clocks.max.sm,clocks_event_reasons.hw_slowdown,clocks_event_reasons.hw_thermal_slowdown,"
              "clocks_event_reasons.sw_thermal_slowdown,clocks_event_reasons.sw_power_cap")
+    NAMES = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
 
     def __init__(self, index=0):
         self.samples, self.reasons, self.max_mhz = [], set(), None
         self.active = False
-        self._stop = threading.Event()
-        self.index = index
+        self.proc = None
+        try:
+            self.proc = subprocess.Popen(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(index), "-lms", "50"],
+                                         stdout=subprocess.PIPE, stderr=subprocess.DEVNULL, text=True)
+        except OSError:
+            return
         self._thread = threading.Thread(target=self._run, daemon=True)
         self._thread.start()
 
     def _run(self):
-        names = ["hw_slowdown", "hw_thermal_slowdown", "sw_thermal_slowdown", "sw_power_cap"]
-        while not self._stop.is_set():
+        for line in self.proc.stdout:
+            out = line.strip().split(",")
+            if not self.active or len(out) < 6:
+                continue
             try:
-                out = subprocess.run(["nvidia-smi", f"--query-gpu={self.QUERY}", "--format=csv,noheader,nounits", "-i", str(self.index)],
-                                     capture_output=True, text=True, timeout=5).stdout.strip().split(",")
-                if self.active and len(out) >= 6:
-                    self.samples.append(float(out[0]))
-                    self.max_mhz = float(out[1])
-                    for name, v in zip(names, out[2:6]):
-                        if v.strip().lower().startswith("active"):
-                            self.reasons.add(name)
-            except Exception:
-                pass
-            self._stop.wait(0.1)
+                self.samples.append(float(out[0]))
+                self.max_mhz = float(out[1])
+            except ValueError:
+                continue
+            for name, v in zip(self.NAMES, out[2:6]):
+                if v.strip().lower().startswith("active"):
+                    self.reasons.add(name)
 
     def close(self):
-        self._stop.set()
-        self._thread.join(timeout=2)
+        if self.proc is not None:
+            self.proc.terminate()                     # this object's own child, by its handle
+            try:
+                self.proc.wait(timeout=5)
+            except subprocess.TimeoutExpired:
+                self.proc.kill()
+            self._thread.join(timeout=2)
 
     def summary(self):
         return {"sm_mhz": statistics.median(self.samples) if self.samples else None, "sm_max_mhz": self.max_mhz,
@@ -167,10 +182,11 @@ def breakdown(model, batch, tokens) -> int:
 def main() -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=20)
+    ap.add_argument("--steps", type=int, default=100)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the configuration has (both numbers are reported)")
+    ap.add_argument("--size", default="2b", choices=sorted(SIZES), help="layer sizes: Gemma 2 2B (the default and the contract's line), 9B or 27B")
+    ap.add_argument("--layers", type=int, default=0, help="fewer layers than the configuration has (both numbers are reported)")
     ap.add_argument("--batch", type=int, default=8)
     ap.add_argument("--skip-points", action="store_true", help="leave out decode at batch 1 and 64")
     ap.add_argument("--breakdown", action="store_true",
@@ -197,7 +213,11 @@ def main() -> int:
 
     torch.cuda.set_device(0)
     pk = peaks()
-    cfg = dict(GEMMA2_2B, num_hidden_layers=args.layers)
+    global HISTORY, FULL_LAYERS
+    base, HISTORY = SIZES[args.size]
+    FULL_LAYERS = base["num_hidden_layers"]
+    args.layers = args.layers or FULL_LAYERS
+    cfg = dict(base, num_hidden_layers=args.layers)
     batches = [args.batch] if args.skip_points else sorted({1, args.batch, 64})
     room = max(batches) * (-(-(HISTORY + 4 * (warmup + steps) + 64) // 64) * 64) + PREFILL_TOKENS + 64
     model = Model.random(cfg, seed=0, dtype="bf16", max_tokens_cached=room, max_sequences=max(batches) + 1)
@@ -276,18 +296,18 @@ def main() -> int:
     step_bytes = weight_bytes(cfg, args.layers) + args.batch * kv_bytes_seen(cfg, args.layers, HISTORY + warmup + steps)
     achieved = step_bytes / (dev_ms * 1e-3) / 1e9
     line = {
-        "metric": "decode tok/s at batch 8 (Gemma 2 2B sizes, bf16, 6144 tokens of history per sequence)",
+        "metric": f"decode tok/s at batch {args.batch} (Gemma 2 {args.size.upper()} sizes, bf16, {HISTORY} tokens of history per sequence)",
         "value": args.batch / dev_ms * 1e3,
         "unit": "tokens/s",
         "n_gpus": 1, "steps": steps, "warmup": warmup, "ms_per_step": dev_ms,
         "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "bf16",
         "data": "synthetic: seeded random weights and uniform-random token ids",
         "config": {
-            "model": "gemma2-2b-shape", "global_batch": args.batch, "seq_len": CONTEXT, "history": HISTORY, "parallelism": "single-gpu",
+            "model": f"gemma2-{args.size}-shape", "global_batch": args.batch, "seq_len": CONTEXT, "history": HISTORY, "parallelism": "single-gpu",
             "layers": args.layers, "layers_of_config": FULL_LAYERS, "hidden": cfg["hidden_size"], "heads": cfg["num_attention_heads"],
             "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"],
             "vocab": cfg["vocab_size"], "window": cfg["sliding_window"], "page": engine.cache.page_size,
-            "l2": "inputs larger than L2 (5.2 GB of weights a step)", "peaks": pk["source"],
+            "l2": f"inputs larger than L2 ({weight_bytes(cfg, args.layers) / 1e9:.1f} GB of weights a step)", "peaks": pk["source"],
         },
         "e2e": {"value": args.batch / e2e_ms * 1e3, "unit": "tokens/s", "ms_per_step": e2e_ms, "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h},
         "gpu_launches": int(round(launches * steps)),
