@@ -45,6 +45,15 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
 // tables are [pages, Hkv, page_size, D]; a line is page * page_size + offset.
 // Pairing "half": (j, j + rotary/2) for j < rotary/2; components from `rotary` on pass through.
 // A row whose line is negative writes no key and no value (a padding row).
+// (a, b) turned by the angle whose (cos, sin) is cs; the roundings are spelled out so that every
+// kernel that rotates gives the same bits.
+__device__ __forceinline__ void rope_rotate(float& a, float& b, const float2 cs) {
+    const float ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
+    const float rb = __fmaf_rn(b, cs.x, __fmul_rn(a, cs.y));
+    a = ra;
+    b = rb;
+}
+
 template <typename TI, typename T>
 __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__ cos_sin,
                                    const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
@@ -79,14 +88,58 @@ __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__
         if (!is_key) rotate = false;
     }
     float a = qkv.at(src + ia), b = qkv.at(src + ib);      // read only by the threads that write
-    if (rotate) {
-        const float2 cs = cos_sin[(size_t)r * half_r + i];
-        const float ra = a * cs.x - b * cs.y;
-        const float rb = b * cs.x + a * cs.y;
-        a = ra; b = rb;
-    }
+    if (rotate) rope_rotate(a, b, cos_sin[(size_t)r * half_r + i]);
     Elem<T>::store(dst + ia, a);
     Elem<T>::store(dst + ib, b);
+}
+
+// The same for bfloat16 in and out with the whole head rotated (rotary == d, d a multiple of 16):
+// one thread takes eight components of the first half and their eight partners of the second, with
+// 16-byte loads and stores.
+__global__ void rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv, const float2* __restrict__ cos_sin,
+                                          const int* __restrict__ lines, __nv_bfloat16* __restrict__ q_out,
+                                          __nv_bfloat16* __restrict__ k_table, __nv_bfloat16* __restrict__ v_table, int rows,
+                                          int hq, int hkv, int d, int write_kv, long long table_lines, int page_size) {
+    const int half_d = d >> 1, cpr = half_d >> 3;           // chunks of eight in half a head
+    const int heads = hq + 2 * hkv;
+    const long long total = (long long)rows * heads * cpr;
+    const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (idx >= total) return;
+    const int c = (int)(idx % cpr);
+    const int h = (int)((idx / cpr) % heads);
+    const int r = (int)(idx / ((long long)cpr * heads));
+    const __nv_bfloat16* src = qkv + ((size_t)r * heads + h) * d + c * 8;
+    __nv_bfloat16* dst;
+    bool rotate = true;
+    if (h < hq) {
+        dst = q_out + ((size_t)r * hq + h) * d;
+    } else {
+        if (!write_kv) return;
+        const int line = lines[r];
+        if (line < 0 || line >= table_lines) return;
+        const bool is_key = h < hq + hkv;
+        const int kvh = is_key ? h - hq : h - hq - hkv;
+        dst = (is_key ? k_table : v_table) + kv_row(line, kvh, hkv, page_size) * d;
+        rotate = is_key;
+    }
+    uint4 ua = *reinterpret_cast<const uint4*>(src);
+    uint4 ub = *reinterpret_cast<const uint4*>(src + half_d);
+    if (rotate) {
+        const float4* cs4 = reinterpret_cast<const float4*>(cos_sin + (size_t)r * half_d + c * 8);
+        __nv_bfloat162* pa = reinterpret_cast<__nv_bfloat162*>(&ua);
+        __nv_bfloat162* pb = reinterpret_cast<__nv_bfloat162*>(&ub);
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const float4 cs = cs4[j];                       // (cos, sin) of two neighbouring components
+            float2 a = __bfloat1622float2(pa[j]), b = __bfloat1622float2(pb[j]);
+            rope_rotate(a.x, b.x, make_float2(cs.x, cs.y));
+            rope_rotate(a.y, b.y, make_float2(cs.z, cs.w));
+            pa[j] = __floats2bfloat162_rn(a.x, a.y);
+            pb[j] = __floats2bfloat162_rn(b.x, b.y);
+        }
+    }
+    *reinterpret_cast<uint4*>(dst + c * 8) = ua;
+    *reinterpret_cast<uint4*>(dst + half_d + c * 8) = ub;
 }
 
 // ---------------------------------------------------------------------------------------
@@ -192,7 +245,14 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
     rope_append_kernel<TI, T><<<blocks, 256, 0, s>>>(Src<TI>{(const TI*)qkv, splits, (size_t)split_stride},          \
                                                      (const float2*)cos_sin, lines, (T*)q_out, (T*)k_table,         \
                                                      (T*)v_table, rows, hq, hkv, d, rotary, write_kv, table_lines, page_size > 0 ? page_size : 1)
-    if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ROPE(float, float);
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_table | (uintptr_t)v_table | (uintptr_t)cos_sin) & 15) == 0;
+    if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16 && splits == 1 && rotary == d && d % 16 == 0 && aligned) {
+        const long long vec = (long long)rows * (hq + 2 * hkv) * (d / 16);
+        rope_append_bf16x8_kernel<<<(unsigned)((vec + 255) / 256), 256, 0, s>>>(
+            (const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out, (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d,
+            write_kv, table_lines, page_size > 0 ? page_size : 1);
+    }
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ROPE(float, float);
     else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_ROPE(float, bf16);
     else if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16) KB_ROPE(bf16, bf16);
     else return fail("rope_append: dtype codes %d -> %d are not known", in_dt, out_dt);

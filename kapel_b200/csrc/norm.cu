@@ -111,6 +111,87 @@ __global__ void add_rmsnorm_reg_kernel(float* __restrict__ residual, const Src<T
     }
 }
 
+// bfloat16 branch, weights and output with a width that is a multiple of eight: a thread keeps up
+// to CPT chunks of eight components in registers and moves them with 16-byte loads and stores.
+template <int CPT>
+__global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __nv_bfloat16* __restrict__ branch,
+                                          const __nv_bfloat16* __restrict__ w_post, float eps_post, float off_post,
+                                          const __nv_bfloat16* __restrict__ w_next, float eps_next, float off_next,
+                                          __nv_bfloat16* __restrict__ h, int width) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    const int chunks = width >> 3;
+    float b[CPT][8], r[CPT][8];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            const uint4 ub = *reinterpret_cast<const uint4*>(branch + base + ci * 8);
+            const __nv_bfloat162* pb = reinterpret_cast<const __nv_bfloat162*>(&ub);
+            const float4 r0 = *reinterpret_cast<const float4*>(residual + base + ci * 8);
+            const float4 r1 = *reinterpret_cast<const float4*>(residual + base + ci * 8 + 4);
+            r[c][0] = r0.x; r[c][1] = r0.y; r[c][2] = r0.z; r[c][3] = r0.w;
+            r[c][4] = r1.x; r[c][5] = r1.y; r[c][6] = r1.z; r[c][7] = r1.w;
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 v = __bfloat1622float2(pb[j]);
+                b[c][2 * j] = v.x;
+                b[c][2 * j + 1] = v.y;
+                ss += v.x * v.x + v.y * v.y;
+            }
+        }
+    }
+    float inv = 1.f;
+    if (w_post != nullptr) {
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            if (w_post != nullptr) {
+                const uint4 uw = *reinterpret_cast<const uint4*>(w_post + ci * 8);
+                const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&uw);
+#pragma unroll
+                for (int j = 0; j < 4; ++j) {
+                    const float2 w = __bfloat1622float2(pw[j]);
+                    r[c][2 * j] += b[c][2 * j] * inv * (off_post + w.x);
+                    r[c][2 * j + 1] += b[c][2 * j + 1] * inv * (off_post + w.y);
+                }
+            } else {
+#pragma unroll
+                for (int j = 0; j < 8; ++j) r[c][j] += b[c][j];
+            }
+#pragma unroll
+            for (int j = 0; j < 8; ++j) ss2 += r[c][j] * r[c][j];
+            *reinterpret_cast<float4*>(residual + base + ci * 8) = make_float4(r[c][0], r[c][1], r[c][2], r[c][3]);
+            *reinterpret_cast<float4*>(residual + base + ci * 8 + 4) = make_float4(r[c][4], r[c][5], r[c][6], r[c][7]);
+        }
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            const uint4 uw = *reinterpret_cast<const uint4*>(w_next + ci * 8);
+            const __nv_bfloat162* pw = reinterpret_cast<const __nv_bfloat162*>(&uw);
+            uint4 uo;
+            __nv_bfloat162* po = reinterpret_cast<__nv_bfloat162*>(&uo);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+                const float2 w = __bfloat1622float2(pw[j]);
+                po[j] = __floats2bfloat162_rn(r[c][2 * j] * inv2 * (off_next + w.x), r[c][2 * j + 1] * inv2 * (off_next + w.y));
+            }
+            *reinterpret_cast<uint4*>(h + base + ci * 8) = uo;
+        }
+    }
+}
+
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
 
 }  // namespace kb
@@ -166,6 +247,17 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
                                                               (const TW*)w_next, eps_next, off_next, (TH*)h, width); \
     } while (0)
     const int code = branch_dt * 4 + w_dt * 2 + h_dt;
+    const bool aligned = (((uintptr_t)residual | (uintptr_t)branch | (uintptr_t)w_post | (uintptr_t)w_next | (uintptr_t)h) & 15) == 0;
+    if (code == 7 && splits == 1 && width % 8 == 0 && width <= 4 * 8 * 1024 && aligned) {
+        const int chunks = width / 8;
+        const int cpt = chunks <= 1024 ? 1 : (chunks <= 2048 ? 2 : 4);
+        const int tv = min(1024, ((chunks + cpt - 1) / cpt + 31) / 32 * 32);
+        const bf16 *b = (const bf16*)branch, *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
+        if (cpt == 1) add_rmsnorm_bf16x8_kernel<1><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        else if (cpt == 2) add_rmsnorm_bf16x8_kernel<2><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        else add_rmsnorm_bf16x8_kernel<4><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        return check_launch("add_rmsnorm");
+    }
     switch (code) {
         case 0: KB_ADDNORM(float, float, float); break;
         case 1: KB_ADDNORM(float, float, bf16); break;
