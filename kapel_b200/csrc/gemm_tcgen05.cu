@@ -97,13 +97,109 @@ __device__ __forceinline__ void tc_ld32(uint32_t taddr, uint32_t (&r)[32]) {
     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
 }
 
+__device__ __forceinline__ void tc_ld16(uint32_t taddr, uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15])
+        : "r"(taddr) : "memory");
+}
+
+// Epilogues, chosen at compile time so that each kernel carries only its own code:
+// 0 none, 1 soft cap c * tanh(x / c), 2 and 3 the gated unit gelu_tanh(gate) * up and silu(gate) * up.
+constexpr int EPI_NONE = 0, EPI_SOFTCAP = 1, EPI_GLU_GELU = 2, EPI_GLU_SILU = 3;
+
+__device__ __forceinline__ uint4 tc_pack8(const float (&v)[8]) {
+    uint4 o;
+    __nv_bfloat162 p0 = __floats2bfloat162_rn(v[0], v[1]), p1 = __floats2bfloat162_rn(v[2], v[3]);
+    __nv_bfloat162 p2 = __floats2bfloat162_rn(v[4], v[5]), p3 = __floats2bfloat162_rn(v[6], v[7]);
+    o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
+    o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
+    return o;
+}
+
+// Eight neighbouring results of one row, from column `col` on, to a row of `n` columns. Every index
+// is a compile-time constant, so the values stay in registers.
+__device__ __forceinline__ void tc_store8(void* __restrict__ c, int c_dt, size_t at, int col, int n, bool whole, const float (&v)[8]) {
+    if (c_dt == KB_DT_BF16) {
+        bf16* dst = static_cast<bf16*>(c) + at;
+        if (whole) {
+            *reinterpret_cast<uint4*>(dst) = tc_pack8(v);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (col + j < n) dst[j] = __float2bfloat16_rn(v[j]);
+        }
+    } else {
+        float* dst = static_cast<float*>(c) + at;
+        if (whole) {
+            *reinterpret_cast<float4*>(dst) = make_float4(v[0], v[1], v[2], v[3]);
+            *reinterpret_cast<float4*>(dst + 4) = make_float4(v[4], v[5], v[6], v[7]);
+        } else {
+#pragma unroll
+            for (int j = 0; j < 8; ++j)
+                if (col + j < n) dst[j] = v[j];
+        }
+    }
+}
+
+// One warp's share of a 128 x 256 accumulator: its 32 TMEM lanes start at `lanes`, this thread's
+// row of C is `row`, the accumulator's first column is column `n0` of C. For the gated unit the
+// accumulator's columns 0-127 are gates and 128-255 the matching ups, C is [m, n] with n the unit's
+// width, and n0 counts in outputs.
+template <int EPI>
+__device__ __forceinline__ void tc_epilogue(uint32_t lanes, int row, int n0, void* __restrict__ c, int c_dt, int m, int n, float cap) {
+    const bool vec = (c_dt == KB_DT_BF16) ? (n % 8 == 0) : (n % 4 == 0);
+    if constexpr (EPI == EPI_GLU_GELU || EPI == EPI_GLU_SILU) {
+        for (int c0 = 0; c0 < 128; c0 += 16) {
+            if (n0 + c0 >= n) break;                            // the same for the whole warp
+            uint32_t g[16], u[16];
+            __syncwarp();                                       // lanes that skipped their stores rejoin here
+            tc_ld16(lanes + (uint32_t)c0, g);
+            tc_ld16(lanes + (uint32_t)(128 + c0), u);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            if (row >= m) continue;
+#pragma unroll
+            for (int h = 0; h < 16; h += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    const float x = __uint_as_float(g[h + j]);
+                    v[j] = (EPI == EPI_GLU_GELU ? gelu_tanh(x) : silu(x)) * __uint_as_float(u[h + j]);
+                }
+                const int col = n0 + c0 + h;
+                tc_store8(c, c_dt, (size_t)row * n + col, col, n, vec && col + 8 <= n, v);
+            }
+        }
+    } else {
+        for (int c0 = 0; c0 < 256; c0 += 32) {
+            if (n0 + c0 >= n) break;
+            uint32_t r[32];
+            __syncwarp();
+            tc_ld32(lanes + (uint32_t)c0, r);
+            if (row >= m) continue;
+#pragma unroll
+            for (int h = 0; h < 32; h += 8) {
+                float v[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    v[j] = __uint_as_float(r[h + j]);
+                    if (EPI == EPI_SOFTCAP) v[j] = cap * tanhf(v[j] / cap);
+                }
+                const int col = n0 + c0 + h;
+                tc_store8(c, c_dt, (size_t)row * n + col, col, n, vec && col + 8 <= n, v);
+            }
+        }
+    }
+}
+
 // TC_STAGES = 4: one block a multiprocessor, for products of about one tile a multiprocessor.
 // TC_STAGES = 2: two blocks a multiprocessor, for products of many tiles: while one block stores
 // its tile or starts the next, the other keeps the tensor cores busy.
-template <int TC_STAGES>
+template <int TC_STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    void* __restrict__ c, int c_dt, int m, int n, int k, int epi, float cap) {
+                    void* __restrict__ c, int c_dt, int m, int n, int k, float cap) {
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -164,45 +260,7 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
             failed = true;
         } else {
             tc_fence_after();
-            const int row = m0 + quarter * 32 + lane;
-            const bool vec = (c_dt == KB_DT_BF16) ? (n % 8 == 0) : (n % 4 == 0);
-            for (int c0 = 0; c0 < TC_BN; c0 += 32) {
-                uint32_t r[32];
-                __syncwarp();                                       // lanes that skipped their stores rejoin here
-                tc_ld32(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
-                const int col = n0 + c0;
-                if (row >= m || col >= n) continue;
-                float v[32];
-#pragma unroll
-                for (int j = 0; j < 32; ++j) {
-                    v[j] = __uint_as_float(r[j]);
-                    if (epi == 1) v[j] = cap * tanhf(v[j] / cap);
-                }
-                if (c_dt == KB_DT_BF16) {
-                    bf16* dst = static_cast<bf16*>(c) + (size_t)row * n + col;
-                    if (vec && col + 32 <= n) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 8) {
-                            uint4 o;
-                            __nv_bfloat162 p0 = __floats2bfloat162_rn(v[j], v[j + 1]), p1 = __floats2bfloat162_rn(v[j + 2], v[j + 3]);
-                            __nv_bfloat162 p2 = __floats2bfloat162_rn(v[j + 4], v[j + 5]), p3 = __floats2bfloat162_rn(v[j + 6], v[j + 7]);
-                            o.x = *reinterpret_cast<uint32_t*>(&p0); o.y = *reinterpret_cast<uint32_t*>(&p1);
-                            o.z = *reinterpret_cast<uint32_t*>(&p2); o.w = *reinterpret_cast<uint32_t*>(&p3);
-                            *reinterpret_cast<uint4*>(dst + j) = o;
-                        }
-                    } else {
-                        for (int j = 0; j < 32 && col + j < n; ++j) dst[j] = __float2bfloat16_rn(v[j]);
-                    }
-                } else {
-                    float* dst = static_cast<float*>(c) + (size_t)row * n + col;
-                    if (vec && col + 32 <= n) {
-#pragma unroll
-                        for (int j = 0; j < 32; j += 4) *reinterpret_cast<float4*>(dst + j) = make_float4(v[j], v[j + 1], v[j + 2], v[j + 3]);
-                    } else {
-                        for (int j = 0; j < 32 && col + j < n; ++j) dst[j] = v[j];
-                    }
-                }
-            }
+            tc_epilogue<EPI>(tmem + ((uint32_t)(quarter * 32) << 16), m0 + quarter * 32 + lane, n0, c, c_dt, m, n, cap);
         }
     }
     if (failed) atomicExch(&g_tcgen05_error, 1);
@@ -211,6 +269,168 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
     if (warp == 1) {
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TC_TMEM_COLS) : "memory");
+    }
+}
+
+// ---------------------------------------------------------------------------------------
+// The same product by pairs of blocks (a cluster of two, on the two multiprocessors of a pair):
+// tcgen05.mma.cta_group::2 computes a 256 x 256 tile, rows 0-127 accumulated in the first block's
+// TMEM and rows 128-255 in the second's. Each block stages its own 128 rows of A and only half of
+// the weight tile (128 of its 256 rows), so a k step costs a block 32 KB of shared memory instead
+// of 48 KB and the weights cross from L2 half as often.
+//   * both blocks' TMA copies complete on the first block's "full" barrier (the copy names that
+//     barrier by its address in the cluster's shared window with the block-rank bit cleared);
+//   * the first block's warp 1 issues the MMAs for both; tcgen05.commit with a two-block mask
+//     arrives on the "empty" barrier of the stage, and at the end on the "accumulator" barrier, in
+//     both blocks;
+//   * each block's warps 2-5 read their own TMEM and store their own 128 rows;
+//   * the blocks meet at a cluster barrier after the barriers are initialised and before TMEM is
+//     freed, so neither signals a block that is not there yet or has left.
+// With a gated-unit epilogue the weight is a stacked gate|up matrix [2 n, k]: the first block
+// stages 128 gate rows and the second the 128 up rows of the same outputs, the accumulator's
+// columns 0-127 and 128-255 are then gate and up of one output each, and the epilogue stores
+// act(gate) * up, [m, n].
+constexpr int TP_BN_HALF = 128;
+constexpr int TP_B_BYTES = TP_BN_HALF * TC_BK * 2;             // 16 KB: this block's half of the weight tile
+constexpr int TP_STAGE_BYTES = TC_A_BYTES + TP_B_BYTES;        // 32 KB
+constexpr int tp_smem_bytes(int stages) { return stages * TP_STAGE_BYTES + 1024 + 256; }
+constexpr uint32_t TP_IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(256 >> 3) << 17) | ((uint32_t)(256 >> 4) << 24);
+constexpr uint32_t TP_PEER_MASK = 0xFEFFFFFFu;                 // clears the bit that tells the two blocks' shared windows apart
+
+__device__ __forceinline__ void tp_tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint32_t bar_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(tc_saddr(dst)), "l"(map), "r"(bar_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void tp_commit_both(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(tc_saddr(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void tp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+// The kernel is persistent: a cluster walks 256 x 256 tiles (cluster i takes tiles i, i + clusters,
+// ...; row tiles are the fast index), each block's TMEM holds two accumulators (512 columns), and
+// the epilogue of a tile runs while the MMAs of the next fill the other accumulator. Six stages of
+// 32 KB in one block a multiprocessor. An accumulator is free again when the four epilogue warps
+// of both blocks have arrived on the first block's "accumulator empty" barrier.
+constexpr int TPP_STAGES = 6;
+constexpr int TPP_TMEM_COLS = 512;
+
+__device__ __forceinline__ void tp_arrive_on_first(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(tc_saddr(bar)) : "memory");
+}
+
+template <int EPI>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(TC_THREADS, 1)
+gemm_tcgen05_pair_persistent_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
+                                    void* __restrict__ c, int c_dt, int m, int n, int k, float cap) {
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + TPP_STAGES * TP_STAGE_BYTES);
+    uint64_t* empty = full + TPP_STAGES;
+    uint64_t* acc_full = empty + TPP_STAGES;             // [2] accumulator complete (MMA -> both blocks' epilogues)
+    uint64_t* acc_empty = acc_full + 2;                  // [2] accumulator read out (both blocks' epilogues -> MMA), first block's
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    constexpr bool glu = EPI == EPI_GLU_GELU || EPI == EPI_GLU_SILU;
+    constexpr int tile_cols = glu ? TP_BN_HALF : 2 * TP_BN_HALF;
+    const int m_pairs = (m + 2 * TC_BM - 1) / (2 * TC_BM), n_tiles = (n + tile_cols - 1) / tile_cols;
+    const int tiles = m_pairs * n_tiles;
+    const int cluster = blockIdx.x >> 1, clusters = gridDim.x >> 1;
+    const int k_tiles = (k + TC_BK - 1) / TC_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < TPP_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
+        for (int a = 0; a < 2; ++a) { tc_mbar_init(acc_full + a, 1); tc_mbar_init(acc_empty + a, 8); }
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(TPP_TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tp_cluster_sync();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool failed = false;
+
+    // A wait on a barrier nobody has arrived at yet passes with parity 1: the waiters that ask for
+    // room (the producer for a stage, the MMA lane for an accumulator) start there.
+    if (warp == 0) {
+        if (lane == 0) {
+            int it = 0;
+            for (int t = cluster; t < tiles && !failed; t += clusters) {
+                const int m0 = ((t % m_pairs) * 2 + (int)rank) * TC_BM;
+                const int n0 = (t / m_pairs) * tile_cols;
+                const int w_row = glu ? (rank == 0 ? n0 : n + n0) : n0 + (int)rank * TP_BN_HALF;
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % TPP_STAGES;
+                    if (!tc_mbar_wait(empty + s, ((uint32_t)(it / TPP_STAGES) & 1u) ^ 1u)) { failed = true; break; }
+                    unsigned char* a_dst = smem + s * TP_STAGE_BYTES;
+                    if (rank == 0) tc_mbar_expect_tx(full + s, 2 * TP_STAGE_BYTES);
+                    const uint32_t bar = tc_saddr(full + s) & TP_PEER_MASK;
+                    tp_tma_load_2d(a_dst, &map_a, kt * TC_BK, m0, bar);
+                    tp_tma_load_2d(a_dst + TC_A_BYTES, &map_w, kt * TC_BK, w_row, bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0 && rank == 0) {
+            int it = 0, i = 0;
+            for (int t = cluster; t < tiles && !failed; t += clusters, ++i) {
+                const int acc = i & 1;
+                if (!tc_mbar_wait(acc_empty + acc, ((uint32_t)(i >> 1) & 1u) ^ 1u)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t d_tmem = tmem + (uint32_t)(acc * 256);
+                for (int kt = 0; kt < k_tiles; ++kt, ++it) {
+                    const int s = it % TPP_STAGES;
+                    if (!tc_mbar_wait(full + s, (uint32_t)(it / TPP_STAGES) & 1u)) { failed = true; break; }
+                    tc_fence_after();
+                    const uint32_t a_addr = tc_saddr(smem + s * TP_STAGE_BYTES);
+                    const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + TC_A_BYTES);
+#pragma unroll
+                    for (int kk = 0; kk < TC_BK / 16; ++kk) {
+                        const uint32_t accumulate = (kt | kk) != 0 ? 1u : 0u;
+                        asm volatile(
+                            "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                            "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                            ::"r"(d_tmem), "l"(adesc + (uint64_t)(kk * 2)), "l"(bdesc + (uint64_t)(kk * 2)), "r"(TP_IDESC), "r"(accumulate) : "memory");
+                    }
+                    tp_commit_both(empty + s);
+                }
+                if (!failed) tp_commit_both(acc_full + acc);
+            }
+        }
+    } else {
+        const int quarter = warp & 3;
+        int i = 0;
+        for (int t = cluster; t < tiles; t += clusters, ++i) {
+            const int acc = i & 1;
+            const int m0 = ((t % m_pairs) * 2 + (int)rank) * TC_BM;
+            const int n0 = (t / m_pairs) * tile_cols;
+            if (!__all_sync(0xffffffffu, tc_mbar_wait(acc_full + acc, (uint32_t)(i >> 1) & 1u))) { failed = true; break; }
+            tc_fence_after();
+            tc_epilogue<EPI>(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)(acc * 256), m0 + quarter * 32 + lane, n0, c, c_dt, m, n, cap);
+            tc_fence_before();
+            __syncwarp();
+            if (lane == 0) tp_arrive_on_first(acc_empty + acc);
+        }
+    }
+    if (failed) atomicExch(&g_tcgen05_error, 1);
+    tc_fence_before();
+    __syncthreads();
+    tp_cluster_sync();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(TPP_TMEM_COLS) : "memory");
     }
 }
 
@@ -385,6 +605,37 @@ static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
     return check_launch("gemm_skinny_tcgen05");
 }
 
+template <int STAGES, int EPI>
+static int launch_single(const CUtensorMap& map_a, const CUtensorMap& map_w, void* c, int c_dt, int m, int n, int k, float cap,
+                         dim3 grid, cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(STAGES));
+        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", tc_smem_bytes(STAGES), cudaGetErrorString(e));
+        attr_set = true;
+    }
+    gemm_tcgen05_kernel<STAGES, EPI><<<grid, TC_THREADS, tc_smem_bytes(STAGES), s>>>(map_a, map_w, c, c_dt, m, n, k, cap);
+    return check_launch("gemm_tcgen05");
+}
+
+// n counts output columns (the gated unit's width with a gated epilogue).
+template <int EPI>
+static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, void* c, int c_dt, int m, int n, int k, float cap,
+                       cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_pair_persistent_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, tp_smem_bytes(TPP_STAGES));
+        if (e != cudaSuccess) return fail("gemm_tcgen05_pair: cannot have %d bytes of shared memory: %s", tp_smem_bytes(TPP_STAGES), cudaGetErrorString(e));
+        attr_set = true;
+    }
+    constexpr int tile_cols = (EPI == EPI_GLU_GELU || EPI == EPI_GLU_SILU) ? TP_BN_HALF : 2 * TP_BN_HALF;
+    const long long tiles = (long long)((m + 2 * TC_BM - 1) / (2 * TC_BM)) * ((n + tile_cols - 1) / tile_cols);
+    const int pairs = skinny_sms() / 2;
+    const int clusters = tiles < pairs ? (int)tiles : pairs;
+    gemm_tcgen05_pair_persistent_kernel<EPI><<<2 * clusters, TC_THREADS, tp_smem_bytes(TPP_STAGES), s>>>(map_a, map_w, c, c_dt, m, n, k, cap);
+    return check_launch("gemm_tcgen05_pair");
+}
+
 }  // namespace kb
 
 using namespace kb;
@@ -398,33 +649,55 @@ extern "C" int kb_tcgen05_error() {
 }
 
 // a: bf16 [m,k]; w: bf16 [n,k]; c: bf16 or f32 [m,n]. Any m, n; k a multiple of 8.
+// kernel: 0 chooses, 1 the one-block kernel, 2 the persistent pair kernel.
 extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, int m, int n, int k, int epilogue,
-                               float cap, void* stream) {
+                               float cap, int kernel, void* stream) {
     KB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_tcgen05: m %d, n %d, k %d", m, n, k);
     KB_REQUIRE(k % 8 == 0, "gemm_tcgen05: k = %d must be a multiple of 8 (16-byte rows)", k);
     KB_REQUIRE(c_dt == KB_DT_F32 || c_dt == KB_DT_BF16, "gemm_tcgen05: output dtype code %d is not known", c_dt);
     KB_REQUIRE(epilogue == 0 || (epilogue == 1 && cap > 0.f), "gemm_tcgen05: epilogue %d with cap %g", epilogue, cap);
+    KB_REQUIRE(kernel >= 0 && kernel <= 2, "gemm_tcgen05: kernel choice %d (0 to 2)", kernel);
     KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)c & 15) == 0, "gemm_tcgen05: operands must be 16-byte aligned");
+    cudaStream_t s = (cudaStream_t)stream;
     CUtensorMap map_a, map_w;
     if (int e = encode_map_bf16(&map_a, a, m, k, k, TC_BM)) return e;
-    if (int e = encode_map_bf16(&map_w, w, n, k, k, TC_BN)) return e;
-    static bool attr_set = false;
-    if (!attr_set) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(4));
-        if (e == cudaSuccess) e = cudaFuncSetAttribute(gemm_tcgen05_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(2));
-        if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", tc_smem_bytes(4), cudaGetErrorString(e));
-        attr_set = true;
-    }
     // Row tiles are the fast grid dimension: the blocks of a wave share a few weight tiles (each
     // read from memory once) and what a wave reads again is the activations, small beside L2.
     // Measured on the gate|up product of a 2,048-token prompt: 187 us against 227 us the other way.
     dim3 grid((m + TC_BM - 1) / TC_BM, (n + TC_BN - 1) / TC_BN);
     KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05: %d columns is too many for one launch", n);
-    if ((long long)grid.x * grid.y > 3 * (long long)skinny_sms() / 2)
-        gemm_tcgen05_kernel<2><<<grid, TC_THREADS, tc_smem_bytes(2), (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
-    else
-        gemm_tcgen05_kernel<4><<<grid, TC_THREADS, tc_smem_bytes(4), (cudaStream_t)stream>>>(map_a, map_w, c, c_dt, m, n, k, epilogue, cap);
-    return check_launch("gemm_tcgen05");
+    const long long tiles = (long long)grid.x * grid.y;
+    // About one 128 x 256 tile a multiprocessor and a short K: pairs would leave half the tiles'
+    // worth of multiprocessors idle and there is no second tile whose MMAs could hide an epilogue.
+    if (kernel == 0) kernel = (tiles <= 3 * (long long)skinny_sms() / 2 && k <= 4096) ? 1 : 2;
+    if (kernel == 2) {
+        if (int e = encode_map_bf16(&map_w, w, n, k, k, TP_BN_HALF)) return e;
+        return epilogue == 0 ? launch_pair<EPI_NONE>(map_a, map_w, c, c_dt, m, n, k, cap, s)
+                             : launch_pair<EPI_SOFTCAP>(map_a, map_w, c, c_dt, m, n, k, cap, s);
+    }
+    if (int e = encode_map_bf16(&map_w, w, n, k, k, TC_BN)) return e;
+    const bool many = tiles > 3 * (long long)skinny_sms() / 2;
+    if (epilogue == 0)
+        return many ? launch_single<2, EPI_NONE>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s)
+                    : launch_single<4, EPI_NONE>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s);
+    return many ? launch_single<2, EPI_SOFTCAP>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s)
+                : launch_single<4, EPI_SOFTCAP>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s);
+}
+
+// The gated unit in the product's epilogue: a bf16 [m,k]; w bf16 [2 n, k], gate rows then up rows;
+// c = act(a . gate^T) * (a . up^T), bf16 [m, n]; act 0 gelu_tanh, 1 silu. The gate and the up sums
+// meet in 32-bit, before any rounding to bfloat16.
+extern "C" int kb_gemm_tcgen05_glu(void* c, const void* a, const void* w, int m, int n, int k, int act, void* stream) {
+    KB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_tcgen05_glu: m %d, n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_tcgen05_glu: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(act == 0 || act == 1, "gemm_tcgen05_glu: activation code %d is not known (0 gelu_tanh, 1 silu)", act);
+    KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)c & 15) == 0, "gemm_tcgen05_glu: operands must be 16-byte aligned");
+    CUtensorMap map_a, map_w;
+    if (int e = encode_map_bf16(&map_a, a, m, k, k, TC_BM)) return e;
+    if (int e = encode_map_bf16(&map_w, w, 2ull * n, k, k, TP_BN_HALF)) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    return act == 0 ? launch_pair<EPI_GLU_GELU>(map_a, map_w, c, KB_DT_BF16, m, n, k, 0.f, s)
+                    : launch_pair<EPI_GLU_SILU>(map_a, map_w, c, KB_DT_BF16, m, n, k, 0.f, s);
 }
 
 // Partial sums the skinny kernel leaves for a weight [n, k] (1: it writes the result itself).

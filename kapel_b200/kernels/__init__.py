@@ -21,8 +21,10 @@ _CODES = {torch.float32: F32, torch.bfloat16: BF16}
 
 ACT_CODES = {"gelu_tanh": 0, "silu": 1}
 
-# Which kernel multiplies more than 64 rows of bfloat16: "tcgen05" (TMA, TMEM, tcgen05.mma) or
-# "mma" (the warp-level mma.sync tile kernel, kept as the yardstick the tcgen05 kernel is measured against).
+# Which kernel multiplies more than 64 rows of bfloat16: "tcgen05" (TMA, TMEM, tcgen05.mma; the
+# library picks between one block a tile and persistent pairs of blocks, "single" and "pair" force
+# one) or "mma" (the warp-level mma.sync tile kernel, kept as the yardstick the tcgen05 kernels are
+# measured against).
 import os as _os
 
 GEMM_LARGE = _os.environ.get("KAPEL_B200_GEMM_LARGE", "tcgen05")
@@ -325,12 +327,35 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             _check(lib.kb_gemm_bf16_partial(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
             return SplitSum(partials)
     out = torch.empty((m, n), dtype=out_dtype, device=a.device)
-    if m > 64 and GEMM_LARGE == "tcgen05":
-        _check(lib.kb_gemm_tcgen05(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
+    if m > 64 and GEMM_LARGE in _TCGEN05_KERNELS:
+        _check(lib.kb_gemm_tcgen05(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap),
+                                   _TCGEN05_KERNELS[GEMM_LARGE], _stream()))
         return out
     need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
     scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
     _check(lib.kb_gemm_bf16(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _ptr(scratch), _stream()))
+    return out
+
+
+_TCGEN05_KERNELS = {"tcgen05": 0, "single": 1, "pair": 2}       # the kernel chooses; one block a tile; persistent pairs
+
+
+def gemm_glu_fused(a: torch.Tensor, w: torch.Tensor, act: str) -> Optional[torch.Tensor]:
+    """act(a . gate^T) * (a . up^T) for a stacked gate|up weight w [2 n, k], in one kernel whose
+    epilogue applies the gated unit to the 32-bit sums; None where that kernel does not apply
+    (few rows, 32-bit operands) and the caller multiplies and gates in two steps."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[0] <= 64 or GEMM_LARGE not in ("tcgen05", "pair"):
+        return None
+    if act not in ACT_CODES:
+        raise KernelError(f"gemm_glu: activation {act!r} is not known")
+    _need(a, "gemm input")
+    _need(w, "gemm weight")
+    m, k = a.shape
+    n2, k2 = w.shape
+    if k != k2 or n2 % 2:
+        raise KernelError(f"gemm_glu: input [{m}, {k}] against stacked weight [{n2}, {k2}]")
+    out = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=a.device)
+    _check(library().kb_gemm_tcgen05_glu(_ptr(out), _ptr(a), _ptr(w), m, n2 // 2, k, ACT_CODES[act], _stream()))
     return out
 
 

@@ -37,6 +37,9 @@ class GatedMLP(Part):
         self.w_down = matrix_for(self.ctx, tensors[w["down"]])
 
     def forward(self, h):
-        gu = linear(self.ctx, h, self.w_gate_up, keep_split=True)
-        inner = K.glu(gu, self.spec.activation, out_dtype=self.ctx.dtype)
+        # many rows of bfloat16: the gated unit is the epilogue of the gate|up product
+        inner = K.gemm_glu_fused(h, self.w_gate_up, self.spec.activation) if h.dtype == self.w_gate_up.dtype else None
+        if inner is None:
+            gu = linear(self.ctx, h, self.w_gate_up, keep_split=True)
+            inner = K.glu(gu, self.spec.activation, out_dtype=self.ctx.dtype)
         return linear(self.ctx, inner, self.w_down, keep_split=True)

@@ -152,25 +152,50 @@ def test_gemm_bf16(m, n, k):
     assert rel_err(got.numpy(), (30.0 * torch.tanh(want / 30.0)).numpy()) < 2e-5
 
 
-@pytest.mark.parametrize("m,n,k", [(65, 256, 64), (128, 256, 128), (129, 300, 200), (2048, 2304, 2048), (300, 4104, 72), (1000, 18432, 2304)])
-def test_gemm_tcgen05(m, n, k):
-    """The tcgen05 kernel (more than 64 rows) and, as a yardstick, the mma.sync tile kernel."""
-    a, w = rnd(m, k, seed=40, dtype=torch.bfloat16), rnd(n, k, seed=41, dtype=torch.bfloat16, scale=0.1)
-    want = a.double() @ w.double().T
-    got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
-    K().check_async_errors()
-    assert rel_err(got.numpy(), want.numpy()) < 2e-5
-    got = K().gemm(dev(a), dev(w)).cpu().double()
-    assert rel_err(got.numpy(), want.numpy()) < 1e-2
+@pytest.mark.parametrize("kernel", ["tcgen05", "single", "pair", "mma"])
+@pytest.mark.parametrize("m,n,k", [(65, 256, 64), (128, 256, 128), (129, 300, 200), (257, 520, 136), (2048, 2304, 2048), (300, 4104, 72),
+                                   (1000, 18432, 2304), (700, 2304, 9216)])
+def test_gemm_tcgen05(kernel, m, n, k):
+    """More than 64 rows: the tcgen05 kernels (one block a tile; persistent pairs of blocks; the
+    library's choice between them) and, as a yardstick, the mma.sync tile kernel."""
     import kapel_b200.kernels as KK
 
+    a, w = rnd(m, k, seed=40, dtype=torch.bfloat16), rnd(n, k, seed=41, dtype=torch.bfloat16, scale=0.1)
+    want = a.double() @ w.double().T
     old = KK.GEMM_LARGE
-    KK.GEMM_LARGE = "mma"
+    KK.GEMM_LARGE = kernel
     try:
         got = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+        K().check_async_errors()
+        assert rel_err(got.numpy(), want.numpy()) < 2e-5
+        got = K().gemm(dev(a), dev(w)).cpu().double()
+        assert rel_err(got.numpy(), want.numpy()) < 1e-2
+        got = K().gemm(dev(a), dev(w), out_dtype=torch.float32, softcap=30.0).cpu().double()
+        assert rel_err(got.numpy(), (30.0 * torch.tanh(want / 30.0)).numpy()) < 2e-5
     finally:
         KK.GEMM_LARGE = old
-    assert rel_err(got.numpy(), want.numpy()) < 2e-5
+    K().check_async_errors()
+
+
+@pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
+@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (300, 328, 200), (129, 100, 72), (2048, 9216, 2304), (513, 1000, 520)])
+def test_gemm_with_the_gated_unit_in_its_epilogue(act, m, n, k):
+    """act(a . gate^T) * (a . up^T) from the stacked weight in one kernel, against the two products
+    in 64-bit; and against the two-step path, which rounds both products to bfloat16 first."""
+    a, w = rnd(m, k, seed=44, dtype=torch.bfloat16), rnd(2 * n, k, seed=45, dtype=torch.bfloat16, scale=0.1)
+    prod = a.double() @ w.double().T
+    gate, up = prod[:, :n], prod[:, n:]
+    if act == "gelu_tanh":
+        want = 0.5 * gate * (1.0 + torch.tanh(0.7978845608028654 * (gate + 0.044715 * gate ** 3))) * up
+    else:
+        want = gate / (1.0 + torch.exp(-gate)) * up
+    got = K().gemm_glu_fused(dev(a), dev(w), act)
+    K().check_async_errors()
+    assert got is not None and got.dtype == torch.bfloat16 and tuple(got.shape) == (m, n)
+    assert rel_err(got.cpu().double().numpy(), want.numpy()) < 6e-3          # one rounding to bfloat16
+    two_step = K().glu(K().gemm(dev(a), dev(w)), act)
+    assert rel_err(two_step.cpu().double().numpy(), want.numpy()) < 2e-2
+    assert K().gemm_glu_fused(dev(a[:64]), dev(w), act) is None              # few rows: the caller takes two steps
 
 
 @pytest.mark.parametrize("small", ["skinny", "stream"])
