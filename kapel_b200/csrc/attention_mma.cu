@@ -882,6 +882,21 @@ extern "C" long long kb_attention_mma_scratch_floats(int rows, int hq, int d, in
     return slots > 1 ? (long long)rows * hq * slots * (d + 2) : 0;
 }
 
+// Merges the partial sums [rows, hq, slots, d + 2] that a prompt kernel left in `scratch`; rows whose
+// keys all lie in one slot were finished by that slot's block and are left alone.
+extern "C" int kb_attention_mma_combine(void* out, const int* row_count, const float* scratch, int rows, int hq, int d,
+                                        int window, int split, int slots, void* stream) {
+    KB_REQUIRE(rows >= 0 && hq > 0 && d > 0 && d % 2 == 0, "attention combine: rows %d, heads %d, head_dim %d", rows, hq, d);
+    KB_REQUIRE(split > 0 && slots > 1 && scratch != nullptr, "attention combine: split %d, %d slots", split, slots);
+    if (rows == 0) return 0;
+    AttMmaParams p = {};
+    p.row_count = row_count; p.out = (bf16*)out; p.partial = const_cast<float*>(scratch);
+    p.rows = rows; p.hq = hq; p.d = d; p.window = window; p.split = split; p.slots = slots; p.direct = 1;
+    dim3 grid(rows, hq);
+    attention_mma_combine_kernel<<<grid, 128, (size_t)slots * sizeof(float), (cudaStream_t)stream>>>(p);
+    return check_launch("attention_mma combine");
+}
+
 extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, const void* v_table,
                                 const int* block_table, const int* row_count, const int* tile_entry,
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,

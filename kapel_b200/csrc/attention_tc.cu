@@ -1,0 +1,481 @@
+// Paged attention for prompt portions on the fifth-generation tensor cores (bfloat16, soft cap).
+//
+// One block takes a tile of 128 rows — (token, query head) pairs of one kv head, the same tiles as
+// the mma.sync kernel — and walks its keys 64 at a time:
+//   S = Q K^T      tcgen05.mma, Q [128 x d] and the key tile [64 x d] K-major in shared memory
+//                  (128-byte swizzle), S [128 x 64] float32 in tensor memory (TMEM);
+//   P = exp(cap tanh(S scale / cap)), masked, read from TMEM and written back to TMEM as bfloat16
+//                  by four warps, one row a thread;
+//   O += P V       tcgen05.mma with P as the A operand straight from TMEM and the value tile
+//                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM throughout.
+// Keys and values arrive as TMA boxes of 16 keys x 64 elements (one page of one kv head) in two
+// rings of slots, one for key tiles and one for value tiles, each slot freed by the tcgen05.commit
+// of the product that read it. S and P are double-buffered so the exponentials of one tile run under the
+// products of its neighbours.
+//
+// The soft cap bounds every score by +-cap, so exp(s) itself is safe in float32 and bfloat16 for
+// cap <= 64 (e^64 times 2^17 keys < 3e38, e^-64 > 1e-38): the softmax uses the fixed reference 0
+// instead of a running maximum, and O never has to be rescaled. Without a soft cap, with a larger
+// cap, or with a head size other than 64, 128 or 256 the mma.sync kernel runs instead.
+//
+// Six warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
+// every MMA; warps 2-5 are the softmax and the epilogue. Every wait on an mbarrier gives up after
+// about a second, raises a flag that `kb_attention_tc_error` reports, and the block still meets at
+// its final barrier, frees its TMEM and returns.
+#include "common.cuh"
+#include "tensor_map.cuh"
+
+namespace kb {
+
+typedef __nv_bfloat16 bf16;
+
+constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 192;
+
+__device__ int g_attention_tc_error = 0;
+
+struct AttTcParams {
+    const bf16* q;             // [rows, hq, d]
+    const int* block_table;    // [entries, table_width]
+    const int* row_count;      // [rows]
+    const int* tile_entry;     // [tiles]
+    const int* tile_row0;      // [tiles] first row (token) of the tile in the batch
+    const int* tile_nq;        // [tiles] tokens in the tile
+    bf16* out;                 // [rows, hq, d]
+    float* partial;            // [rows, hq, slots, d + 2] when slots > 1: (sum p v, reference 0, sum p)
+    int rows, hq, hkv, d, page_size, table_width, n_pages;
+    int window, split, slots;
+    float scale, cap;
+};
+
+__device__ __forceinline__ uint32_t at_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ void at_mbar_init(uint64_t* bar, int count) {
+    asm volatile("mbarrier.init.shared::cta.b64 [%0], %1;" ::"r"(at_saddr(bar)), "r"(count) : "memory");
+}
+__device__ __forceinline__ void at_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
+    asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(at_saddr(bar)), "r"(bytes) : "memory");
+}
+__device__ __forceinline__ void at_mbar_arrive(uint64_t* bar) {
+    asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(at_saddr(bar)) : "memory");
+}
+// false if the phase with this parity did not complete within ~1 s
+__device__ __forceinline__ bool at_mbar_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = at_saddr(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - start > 2000000000ll) return false;
+    }
+}
+__device__ __forceinline__ void at_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(at_saddr(bar)), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void at_commit(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void at_fence_before() { asm volatile("tcgen05.fence::before_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::after_thread_sync;" ::: "memory"); }
+__device__ __forceinline__ void at_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
+// Shared-memory matrix descriptors, 128-byte swizzle (layout type 2 at bit 61, version 1 at bit 46).
+// K-major (Q, keys): rows of 128 bytes, eight-row groups 1024 bytes apart (stride offset); the
+// leading offset is not used. MN-major (values, [key][element]): blocks of 64 elements `lead` bytes
+// apart along N (leading offset), eight-key groups 1024 bytes apart along K (stride offset).
+__device__ __forceinline__ uint64_t at_desc_kmajor(uint32_t saddr) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
+           ((uint64_t)2 << 61);
+}
+__device__ __forceinline__ uint64_t at_desc_mnmajor(uint32_t saddr, uint32_t lead) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lead >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+           ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
+}
+// Instruction descriptor, kind::f16: D float32 (bit 4), A and B bfloat16 (bits 7, 10), A K-major,
+// B K-major or MN-major (bit 16), N / 8 at [17,23), M / 16 at [24,29).
+__host__ __device__ constexpr uint32_t at_idesc(int m, int n, bool b_mn) {
+    return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
+}
+__device__ __forceinline__ void at_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void at_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::1.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+__device__ __forceinline__ void at_ld32(uint32_t taddr, uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.ld.sync.aligned.32x32b.x32.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,"
+        "%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+        : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]), "=r"(r[8]),
+          "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]), "=r"(r[16]),
+          "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]), "=r"(r[24]),
+          "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+        : "r"(taddr) : "memory");
+}
+__device__ __forceinline__ void at_st16(uint32_t taddr, const uint32_t (&r)[16]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
+}
+__device__ __forceinline__ float at_tanh(float x) {
+    float y;
+    asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ float at_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+__device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+
+// Slots of the key/value ring and TMEM columns by head size.
+template <int HD> struct AtCfg {
+    static constexpr int NBOX = HD / 64;                        // boxes of 64 elements along the head
+    static constexpr int SLOT_BYTES = AT_KEYS * HD * 2;         // a key tile or a value tile
+    static constexpr int Q_BYTES = AT_ROWS * HD * 2;
+    // Keys and values have rings of their own: a key slot is free as soon as its scores are
+    // complete, two tiles before the next key tile is needed in it, and a value slot when its
+    // product is, so both are loaded two tiles ahead.
+    static constexpr int K_SLOTS = HD == 256 ? 2 : (HD == 128 ? 4 : 3);
+    static constexpr int V_SLOTS = HD == 256 ? 3 : (HD == 128 ? 6 : 5);
+    static constexpr int SLOTS = K_SLOTS + V_SLOTS;
+    static constexpr int COL_O = 0, COL_S = HD, COL_P = HD + 2 * AT_KEYS;
+    static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // HD + 192 rounded up to a power of two
+    static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024 /* alignment */ + 256 /* barriers */ + 64 /* pages */;
+};
+
+template <int HD>
+__global__ void __launch_bounds__(AT_THREADS, 1)
+attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+    using C = AtCfg<HD>;
+    constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS;
+    extern __shared__ unsigned char at_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* sQ = smem;                                    // NBOX chunks of [128 rows x 128 bytes]
+    unsigned char* ring = smem + C::Q_BYTES;
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] a slot's boxes have landed
+    uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete
+    uint64_t* s_full = empty + NS;                               // [2] S complete (MMA -> softmax)
+    uint64_t* p_full = s_full + 2;                               // [2] P written (softmax -> MMA), four warps arrive
+    uint64_t* pv_done = p_full + 2;                              // [2] the product that read P is complete
+    uint64_t* o_full = pv_done + 2;                              // [1] O complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x, slot = blockIdx.y;
+    // Later tiles of a prompt see more keys: they start first, all their heads and slots together.
+    const int tile = gridDim.z - 1 - blockIdx.z;
+    const int group = p.hq / p.hkv;
+    const int row0 = p.tile_row0[tile], nq = p.tile_nq[tile];
+    const int entry = p.tile_entry[tile];
+    const int rows_valid = nq * group;
+    const int c_first = p.row_count[row0];
+    int klo = (p.window > 0 && c_first > p.window) ? c_first - p.window : 0;
+    int khi = c_first > 0 ? c_first + nq - 1 : 0;                // a padding row sees nothing
+    if (p.split > 0) {
+        klo = max(klo, slot * p.split);
+        khi = min(khi, (slot + 1) * p.split);
+    }
+    const int d = HD;
+    if (klo >= khi) {                                            // nothing for this block: before anything is allocated
+        if (p.slots == 1 && c_first <= 0)
+            for (int i = tid; i < rows_valid * d; i += AT_THREADS) {
+                const int r = i / d, c = i % d;
+                p.out[((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + c] = __float2bfloat16_rn(0.f);
+            }
+        return;
+    }
+    const int k_begin = klo / AT_KEYS * AT_KEYS;
+    const int n_tiles = (khi - k_begin + AT_KEYS - 1) / AT_KEYS;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 1); at_mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 4); at_mbar_init(pv_done + b, 1); }
+        at_mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_saddr(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    // Q: 16-byte pieces to the swizzled K-major layout (piece c of row r of a chunk at r * 128 + ((c ^ (r & 7)) * 16)).
+    for (int i = tid; i < AT_ROWS * (HD / 8); i += AT_THREADS) {
+        const int r = i / (HD / 8), piece = i % (HD / 8);
+        uint4 v = make_uint4(0u, 0u, 0u, 0u);
+        if (r < rows_valid)
+            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + piece * 8);
+        const int chunk = piece >> 3, c = piece & 7;
+        *reinterpret_cast<uint4*>(sQ + chunk * (AT_ROWS * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
+    }
+    at_fence_async_smem();                                       // generic-proxy writes, read by the tensor cores
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        // ---------------------------------------------------------------- pages and boxes
+        // The keys of tile kt go to key slot kt % KS, its values to value slot KS + kt % VS. The pages
+        // of eight tiles are looked up at once, lane 4 t + sub for keys 16 sub .. of the batch's tile
+        // t, and one batch ahead of their use. A group without a page (before the window, past the
+        // end) is cleared instead when it holds values: 0 * garbage could be NaN.
+        auto lookup = [&](int kt_first) -> int {
+            const int kt = kt_first + (lane >> 2);
+            const int j = k_begin + kt * AT_KEYS + (lane & 3) * 16;
+            int page = -1;
+            if (kt < n_tiles && j < khi && j + 16 > klo) {
+                const int lp = max(j, klo) / p.page_size;
+                if (lp < p.table_width) page = p.block_table[(size_t)entry * p.table_width + lp];
+                if (page >= p.n_pages) page = -1;
+            }
+            return page;
+        };
+        int pages_now = 0, pages_next = lookup(0);
+        const int my_sub = (lane / NBOX) & 3, my_bx = lane % NBOX;                  // the box this lane asks for
+        for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+            if ((kt & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
+            const int j0 = k_begin + kt * AT_KEYS;
+            const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
+            const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
+            const int live = __popc(have);
+            const int my_page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + my_sub);
+            for (int half = 0; half < 2; ++half) {               // keys, then values
+                const int s = half == 0 ? kt % KS : KS + kt % VS;
+                const int round = half == 0 ? kt / KS : kt / VS;
+                bool ok = true;
+                if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
+                if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
+                unsigned char* dst = ring + s * C::SLOT_BYTES;
+                if (half == 1 && live < 4) {
+                    for (int sub = 0; sub < 4; ++sub) {
+                        if (have & (1u << sub)) continue;
+                        for (int bx = 0; bx < NBOX; ++bx) {
+                            uint4* z = reinterpret_cast<uint4*>(dst + (bx * 4 + sub) * 2048);
+                            for (int e = lane; e < 128; e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
+                        }
+                    }
+                    at_fence_async_smem();
+                    __syncwarp();
+                }
+                if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * NBOX * 2048u);
+                __syncwarp();
+                if (lane < 4 * NBOX && my_page >= 0) {
+                    const int j = j0 + my_sub * 16;
+                    const int row = (my_page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                    at_tma_box(at_saddr(dst) + (uint32_t)(my_bx * 4 + my_sub) * 2048u, half == 0 ? &map_k : &map_v, my_bx * 64, row, full + s);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- every MMA, from one lane
+        if (lane == 0) {
+            constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS, false);
+            constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
+            const uint32_t q_addr = at_saddr(sQ), ring_addr = at_saddr(ring);
+            auto issue_s = [&](int kt) -> bool {                 // S[kt & 1] = Q K(kt)^T
+                const int s = kt % KS;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) return false;
+                at_fence_after();
+                const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
+                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (kt & 1) * AT_KEYS);
+#pragma unroll
+                for (int bx = 0; bx < NBOX; ++bx) {
+                    const uint64_t adesc = at_desc_kmajor(q_addr + bx * (AT_ROWS * 128));
+                    const uint64_t bdesc = at_desc_kmajor(k_addr + bx * (AT_KEYS * 128));
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        at_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                }
+                at_commit(empty + s);                            // the key slot is free when S is complete
+                at_commit(s_full + (kt & 1));
+                return true;
+            };
+            if (!issue_s(0)) failed = true;
+            for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+                const int b = kt & 1;
+                if (kt + 1 < n_tiles && !issue_s(kt + 1)) { failed = true; break; }
+                const int s = KS + kt % VS;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / VS) & 1u)) { failed = true; break; }
+                if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
+                at_fence_after();
+                const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
+                const uint64_t bdesc = at_desc_mnmajor(v_addr, 4 * 2048);
+                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_P + b * (AT_KEYS / 2));
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk)                   // 16 keys a step: 2 KB further in V, 8 columns in P
+                    at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * (2048 >> 4)), IDESC_O, (kt | kk) != 0 ? 1u : 0u);
+                at_commit(empty + s);
+                at_commit(pv_done + b);
+            }
+            if (!failed) at_commit(o_full);
+        }
+    } else {
+        // ---------------------------------------------------------------- softmax and epilogue, one row a thread
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;                       // the row of the tile, and the TMEM lane
+        const bool own = r < rows_valid;
+        const int cnt = own ? c_first + r / group : 0;
+        const int fst = (own && p.window > 0 && cnt > p.window) ? cnt - p.window : 0;
+        const int lo = max(fst, klo), hi = min(cnt, khi);        // this row sees keys [lo, hi) of this block's
+        const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
+        const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float c1 = p.scale / p.cap, c2 = p.cap * 1.4426950408889634f;
+        float l = 0.f;
+        for (int kt = 0; kt < n_tiles; ++kt) {
+            const int b = kt & 1;
+            const int j0 = k_begin + kt * AT_KEYS;
+            if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
+            // the product that read this P buffer two tiles ago must be complete before it is overwritten
+            if (kt >= 2 && !__all_sync(0xffffffffu, at_mbar_wait(pv_done + b, (uint32_t)((kt >> 1) - 1) & 1u))) { failed = true; break; }
+            at_fence_after();
+            uint32_t s0[32], s1[32], pr[16];
+            const bool edge = j0 < lo_max || j0 + AT_KEYS > hi_min;      // the same for the whole warp
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS), s0);
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + 32), s1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float la = 0.f, lb = 0.f;                            // two chains of additions
+#pragma unroll
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
+                    float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
+                    if (edge) {
+                        const int jj = j0 + h * 32 + j;
+                        if (jj < lo || jj >= hi) p0 = 0.f;
+                        if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
+                    }
+                    la += p0;
+                    lb += p1;
+                    pr[j >> 1] = at_pack(p0, p1);
+                }
+                at_st16(lanes + (uint32_t)(C::COL_P + b * (AT_KEYS / 2) + h * 16), pr);
+            }
+            l += la + lb;
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            at_fence_before();
+            __syncwarp();
+            if (lane == 0) at_mbar_arrive(p_full + b);
+        }
+        if (!failed && !__all_sync(0xffffffffu, at_mbar_wait(o_full, 0u))) failed = true;
+        if (!failed) {
+            at_fence_after();
+            // With several slots, a row whose keys all lie in one slot is finished by that slot's block.
+            const int z0 = p.slots > 1 ? fst / p.split : 0;
+            const int z1 = p.slots > 1 ? min(p.slots - 1, (max(cnt, 1) - 1) / p.split) : 0;
+            const bool direct = z0 == z1;
+            const bool writes = own && (!direct || slot == z0);
+            const int row = row0 + r / group, head = kvh * group + r % group;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
+            float* pdst = p.partial ? p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2) : nullptr;
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                __syncwarp();
+                at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!writes) continue;
+                if (direct) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 v;
+                        v.x = at_pack(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                        v.y = at_pack(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                        v.z = at_pack(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                        v.w = at_pack(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + j) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2*>(pdst + c0 + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
+                }
+            }
+            if (writes && !direct) { pdst[d] = 0.f; pdst[d + 1] = l; }
+        }
+    }
+    if (failed) atomicExch(&g_attention_tc_error, 1);
+    at_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_table, int tiles, cudaStream_t s) {
+    using C = AtCfg<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(attention_tc_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return fail("attention_tc: cannot have %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
+    CUtensorMap map_k, map_v;
+    if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
+    if (int e = encode_map_bf16(&map_v, v_table, rows, p.d, p.d, 16)) return e;
+    dim3 grid(p.hkv, p.slots, tiles);
+    attention_tc_kernel<HD><<<grid, AT_THREADS, C::SMEM, s>>>(p, map_k, map_v);
+    return check_launch("attention_tc");
+}
+
+}  // namespace kb
+
+using namespace kb;
+
+// 1 if a wait inside the kernel ever ran out (and clears the flag); synchronises the device.
+extern "C" int kb_attention_tc_error() {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_attention_tc_error, sizeof(int)) != cudaSuccess) return -1;
+    if (flag) cudaMemcpyToSymbol(g_attention_tc_error, &zero, sizeof(int));
+    return flag;
+}
+
+// 1 where the kernel applies: head sizes 64, 128 and 256, a soft cap of at most 64, pages of a
+// multiple of 16 positions, at most 128 query heads a kv head.
+extern "C" int kb_attention_tc_takes(int hq, int hkv, int d, int page_size, float cap) {
+    return (d == 64 || d == 128 || d == 256) && cap > 0.f && cap <= 64.f && page_size > 0 && page_size % 16 == 0 && hkv > 0 &&
+           hq % hkv == 0 && hq / hkv <= AT_ROWS;
+}
+
+// Prompt portions; arguments as kb_attention_mma's with decode = 0. With slots > 1, `scratch` holds
+// [rows, hq, slots, d + 2] floats and the caller merges it (kb_attention_mma_combine).
+extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, const void* v_table, const int* block_table,
+                               const int* row_count, const int* tile_entry, const int* tile_row0, const int* tile_nq, int tiles,
+                               int rows, int hq, int hkv, int d, int page_size, int table_width, int n_pages, int window,
+                               int split, int slots, float scale, float cap, float* scratch, void* stream) {
+    KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0, "attention_tc: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
+    KB_REQUIRE(kb_attention_tc_takes(hq, hkv, d, page_size, cap), "attention_tc: head_dim %d, %d heads over %d, pages of %d, cap %g are not taken",
+               d, hq, hkv, page_size, cap);
+    KB_REQUIRE(table_width > 0 && n_pages > 0 && window >= 0, "attention_tc: table width %d, pages %d, window %d", table_width, n_pages, window);
+    KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AT_KEYS == 0 && slots >= 1 && slots <= 65535),
+               "attention_tc: split %d (a multiple of %d) with %d slots", split, AT_KEYS, slots);
+    KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_tc: %d slots need scratch memory", slots);
+    KB_REQUIRE(tiles <= 65535 && hkv <= 65535, "attention_tc: %d tiles, %d kv heads is too many for one launch", tiles, hkv);
+    KB_REQUIRE((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_table | (uintptr_t)v_table) & 15) == 0, "attention_tc: operands must be 16-byte aligned");
+    if (rows == 0 || tiles == 0) return 0;
+    AttTcParams p;
+    p.q = (const bf16*)q; p.block_table = block_table; p.row_count = row_count; p.tile_entry = tile_entry;
+    p.tile_row0 = tile_row0; p.tile_nq = tile_nq; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
+    p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width; p.n_pages = n_pages;
+    p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (d == 64) return launch_tc<64>(p, k_table, v_table, tiles, s);
+    if (d == 128) return launch_tc<128>(p, k_table, v_table, tiles, s);
+    return launch_tc<256>(p, k_table, v_table, tiles, s);
+}

@@ -32,6 +32,10 @@ GEMM_LARGE = _os.environ.get("KAPEL_B200_GEMM_LARGE", "tcgen05")
 # weights stream through shared memory by TMA) or "stream" (the mma.sync kernels that read the weights
 # straight into registers).
 GEMM_SMALL = _os.environ.get("KAPEL_B200_GEMM_SMALL", "skinny")
+# Which kernel runs attention over prompt portions where both apply: "tcgen05" (products by
+# tcgen05.mma, scores and probabilities in tensor memory) or "mma" (the mma.sync flash kernel, which
+# also takes what the first does not: no soft cap, other head sizes).
+ATTENTION_PROMPT = _os.environ.get("KAPEL_B200_ATTENTION_PROMPT", "tcgen05")
 
 
 class KernelError(RuntimeError):
@@ -65,6 +69,8 @@ def check_async_errors() -> None:
         bad.append("paged attention (a bulk copy into shared memory never completed)")
     if lib.kb_tcgen05_error() != 0:
         bad.append("tcgen05 product (a TMA load or an MMA commit never arrived)")
+    if lib.kb_attention_tc_error() != 0:
+        bad.append("tcgen05 attention (a TMA load, an MMA commit or a softmax warp never arrived)")
     if bad:
         raise KernelError("a wait inside a kernel gave up after its time limit: " + "; ".join(bad))
 
@@ -429,6 +435,17 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     lib = library()
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
     scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    if not decode and ATTENTION_PROMPT == "tcgen05" and lib.kb_attention_tc_takes(hq, hkv, d, int(page_size), _f(softcap or 0.0)):
+        _check(
+            lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
+                                _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
+                                int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
+                                _f(softcap or 0.0), _ptr(scratch), _stream())
+        )
+        if slots > 1:
+            _check(lib.kb_attention_mma_combine(_ptr(out), _ptr(row_count), _ptr(scratch), rows, hq, d, int(window or 0), int(split),
+                                                int(slots), _stream()))
+        return out
     _check(
         lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                              _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),

@@ -405,13 +405,47 @@ def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split):
 @pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 1, 64), (8, 4, 128), (8, 4, 256), (5, 1, 80)])
 @pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0)])
 @pytest.mark.parametrize("split", [0, 64, 256])
-def test_paged_attention_mma_prompt_mode(hq, hkv, d, window, cap, split):
+@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+def test_paged_attention_mma_prompt_mode(kernel, hq, hkv, d, window, cap, split):
+    """Prompt portions: the tcgen05 kernel where it applies (head sizes 64, 128, 256 with a soft
+    cap) and the mma.sync kernel everywhere."""
+    import kapel_b200.kernels as KK
+
+    takes = d in (64, 128, 256) and cap is not None
+    if kernel == "tcgen05" and not takes:
+        pytest.skip("the mma.sync kernel runs these sizes under either setting")
     lengths, q_lens = [1, 37, 300, 700], [1, 37, 130, 33]
     q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d)
     scale = 1.0 / math.sqrt(d * 1.5)
-    got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, False, split).double()
+    old = KK.ATTENTION_PROMPT
+    KK.ATTENTION_PROMPT = kernel
+    try:
+        got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, False, split).double()
+    finally:
+        KK.ATTENTION_PROMPT = old
+    K().check_async_errors()
     want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
     assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("d", [64, 128, 256])
+def test_paged_attention_tcgen05_far_key_and_window_edge(d):
+    """One key among hundreds carries the weight: seen at the far end and at the window's first
+    position, not one position before it. Scores are capped, so the planted key stands out by
+    about e^(2 cap) only."""
+    hq, hkv, n, page, window, cap = 2, 1, 600, 16, 128, 12.0
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, [n], [70], seed=5)
+    q = q * 0.05
+    first = n - 70 + 1                                  # keys the first of the 70 tokens sees
+    for pos, win, seen in [(3, None, True), (first - window, window, True), (first - window - 1, window, False)]:
+        kt2, vt2 = kt.clone(), vt.clone()
+        kt2[int(bt[0, pos // page]), 0, pos % page] = (q[0, 0].float() * 4000).to(kt.dtype)
+        vt2[int(bt[0, pos // page]), 0, pos % page] = 5.0
+        got = run_mma(q, kt2, vt2, bt, rc, [70], page, win, 1.0, cap, False, 0).double()
+        K().check_async_errors()
+        want = paged_reference(q, kt2, vt2, bt, re, rc, page, win, 1.0, cap)
+        assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+        assert (abs(float(got[0, 0].mean()) - 5.0) < 0.5) == seen
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (16, 1, 64), (8, 4, 128), (8, 4, 256), (2, 2, 96)])
