@@ -8,9 +8,14 @@
 //                  by four warps, one row a thread;
 //   O += P V       tcgen05.mma with P as the A operand straight from TMEM and the value tile
 //                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM throughout.
-// Keys and values arrive as TMA boxes of 16 keys x 64 elements (one page of one kv head) in two
-// rings of slots, one for key tiles and one for value tiles, each slot freed by the tcgen05.commit
-// of the product that read it. S and P are double-buffered so the exponentials of one tile run under the
+// Keys and values arrive by TMA, one copy for the 16 keys of a page of one kv head (a
+// three-dimensional box that lands as head_dim / 64 chunks of [16 keys x 128 bytes]), in two rings of
+// slots, one for key tiles and one for value tiles, each slot freed by the tcgen05.commit of the
+// product that read it. A tile is therefore laid out page by page, [4 pages][chunks][16 keys], and
+// eight-key groups are evenly spaced only from page to page. The products take them that way: the
+// scores are two MMAs of 32 keys each, the first halves of the four pages and then the second
+// halves, so column c of S is key 16 ((c >> 3) & 3) + 8 (c >> 5) + (c & 7) of the tile; P keeps that
+// order, and each 16-key step of P V pairs the same halves of two neighbouring pages. S and P are double-buffered so the exponentials of one tile run under the
 // products of its neighbours.
 //
 // The soft cap bounds every score by +-cap, so exp(s) itself is safe in float32 and bfloat16 for
@@ -69,9 +74,11 @@ __device__ __forceinline__ bool at_mbar_wait(uint64_t* bar, uint32_t parity) {
         if (clock64() - start > 2000000000ll) return false;
     }
 }
-__device__ __forceinline__ void at_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
-    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
-                 ::"r"(dst), "l"(map), "r"(at_saddr(bar)), "r"(x), "r"(y) : "memory");
+// the 16 rows from `row` on, all chunks
+__device__ __forceinline__ void at_tma_page(uint32_t dst, const CUtensorMap* map, int row, uint64_t* bar) {
+    const int zero = 0;
+    asm volatile("cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %3}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(at_saddr(bar)), "r"(zero), "r"(row) : "memory");
 }
 __device__ __forceinline__ void at_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_saddr(bar)) : "memory");
@@ -81,15 +88,11 @@ __device__ __forceinline__ void at_fence_after() { asm volatile("tcgen05.fence::
 __device__ __forceinline__ void at_fence_async_smem() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
 // Shared-memory matrix descriptors, 128-byte swizzle (layout type 2 at bit 61, version 1 at bit 46).
-// K-major (Q, keys): rows of 128 bytes, eight-row groups 1024 bytes apart (stride offset); the
-// leading offset is not used. MN-major (values, [key][element]): blocks of 64 elements `lead` bytes
-// apart along N (leading offset), eight-key groups 1024 bytes apart along K (stride offset).
-__device__ __forceinline__ uint64_t at_desc_kmajor(uint32_t saddr) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)1 << 16) | ((uint64_t)(1024 >> 4) << 32) | ((uint64_t)1 << 46) |
-           ((uint64_t)2 << 61);
-}
-__device__ __forceinline__ uint64_t at_desc_mnmajor(uint32_t saddr, uint32_t lead) {
-    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lead >> 4) & 0x3FFFu) << 16) | ((uint64_t)(1024 >> 4) << 32) |
+// K-major (Q, keys): rows of 128 bytes, eight-row groups `stride` bytes apart; the leading offset
+// is not used. MN-major (values, [key][element]): blocks of 64 elements `lead` bytes apart along
+// N, eight-key groups `stride` bytes apart along K.
+__device__ __forceinline__ uint64_t at_desc(uint32_t saddr, uint32_t lead, uint32_t stride) {
+    return (uint64_t)((saddr & 0x3FFFFu) >> 4) | ((uint64_t)((lead >> 4) & 0x3FFFu) << 16) | ((uint64_t)((stride >> 4) & 0x3FFFu) << 32) |
            ((uint64_t)1 << 46) | ((uint64_t)2 << 61);
 }
 // Instruction descriptor, kind::f16: D float32 (bit 4), A and B bfloat16 (bits 7, 10), A K-major,
@@ -244,14 +247,13 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             return page;
         };
         int pages_now = 0, pages_next = lookup(0);
-        const int my_sub = (lane / NBOX) & 3, my_bx = lane % NBOX;                  // the box this lane asks for
+        constexpr uint32_t PAGE_BYTES = NBOX * 2048u;                                // a page's keys (or values) of one kv head
         for (int kt = 0; kt < n_tiles && !failed; ++kt) {
             if ((kt & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
             const int j0 = k_begin + kt * AT_KEYS;
             const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
             const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
             const int live = __popc(have);
-            const int my_page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + my_sub);
             for (int half = 0; half < 2; ++half) {               // keys, then values
                 const int s = half == 0 ? kt % KS : KS + kt % VS;
                 const int round = half == 0 ? kt / KS : kt / VS;
@@ -262,27 +264,26 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 if (half == 1 && live < 4) {
                     for (int sub = 0; sub < 4; ++sub) {
                         if (have & (1u << sub)) continue;
-                        for (int bx = 0; bx < NBOX; ++bx) {
-                            uint4* z = reinterpret_cast<uint4*>(dst + (bx * 4 + sub) * 2048);
-                            for (int e = lane; e < 128; e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
-                        }
+                        uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_BYTES);
+                        for (int e = lane; e < (int)(PAGE_BYTES / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
                     }
                     at_fence_async_smem();
                     __syncwarp();
                 }
-                if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * NBOX * 2048u);
+                if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_BYTES);
                 __syncwarp();
-                if (lane < 4 * NBOX && my_page >= 0) {
-                    const int j = j0 + my_sub * 16;
-                    const int row = (my_page * p.hkv + kvh) * p.page_size + j % p.page_size;
-                    at_tma_box(at_saddr(dst) + (uint32_t)(my_bx * 4 + my_sub) * 2048u, half == 0 ? &map_k : &map_v, my_bx * 64, row, full + s);
+                if (lane < 4 && page >= 0) {                     // lane = sub: one copy a page
+                    const int j = j0 + lane * 16;
+                    const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                    at_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_BYTES, half == 0 ? &map_k : &map_v, row, full + s);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- every MMA, from one lane
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS, false);
+            constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS / 2, false);
+            constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
             constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
             const uint32_t q_addr = at_saddr(sQ), ring_addr = at_saddr(ring);
             auto issue_s = [&](int kt) -> bool {                 // S[kt & 1] = Q K(kt)^T
@@ -293,11 +294,15 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (kt & 1) * AT_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
-                    const uint64_t adesc = at_desc_kmajor(q_addr + bx * (AT_ROWS * 128));
-                    const uint64_t bdesc = at_desc_kmajor(k_addr + bx * (AT_KEYS * 128));
+                    const uint64_t adesc = at_desc(q_addr + bx * (AT_ROWS * 128), 16, 1024);
+                    // the first (then the second) eight keys of each of the four pages: groups a page apart
+                    const uint64_t bdesc0 = at_desc(k_addr + bx * 2048, 16, PAGE_BYTES);
+                    const uint64_t bdesc1 = at_desc(k_addr + bx * 2048 + 1024, 16, PAGE_BYTES);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk)
-                        at_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                    for (int kk = 0; kk < 4; ++kk) {
+                        at_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc0 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                        at_mma_ss(d_tmem + 32, adesc + (uint64_t)(kk * 2), bdesc1 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                    }
                 }
                 at_commit(empty + s);                            // the key slot is free when S is complete
                 at_commit(s_full + (kt & 1));
@@ -312,11 +317,13 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint64_t bdesc = at_desc_mnmajor(v_addr, 4 * 2048);
                 const uint32_t a_tmem = tmem + (uint32_t)(C::COL_P + b * (AT_KEYS / 2));
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk)                   // 16 keys a step: 2 KB further in V, 8 columns in P
-                    at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * (2048 >> 4)), IDESC_O, (kt | kk) != 0 ? 1u : 0u);
+                for (int kk = 0; kk < 4; ++kk) {
+                    // columns 16 kk .. of P: half kk >> 1 of pages 2 (kk & 1) and 2 (kk & 1) + 1; chunks 2 KB apart
+                    const uint64_t bdesc = at_desc(v_addr + (uint32_t)(kk & 1) * 2 * PAGE_BYTES + (uint32_t)(kk >> 1) * 1024, 2048, PAGE_BYTES);
+                    at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
+                }
                 at_commit(empty + s);
                 at_commit(pv_done + b);
             }
@@ -354,7 +361,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
                     float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
                     if (edge) {
-                        const int jj = j0 + h * 32 + j;
+                        const int jj = j0 + (j >> 3) * 16 + h * 8 + (j & 7);     // column 32 h + j of S is this key
                         if (jj < lo || jj >= hi) p0 = 0.f;
                         if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
                     }
@@ -427,8 +434,8 @@ static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_ta
     }
     const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
     CUtensorMap map_k, map_v;
-    if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
-    if (int e = encode_map_bf16(&map_v, v_table, rows, p.d, p.d, 16)) return e;
+    if (int e = encode_map_bf16_chunks(&map_k, k_table, rows, p.d, 16)) return e;
+    if (int e = encode_map_bf16_chunks(&map_v, v_table, rows, p.d, 16)) return e;
     dim3 grid(p.hkv, p.slots, tiles);
     attention_tc_kernel<HD><<<grid, AT_THREADS, C::SMEM, s>>>(p, map_k, map_v);
     return check_launch("attention_tc");

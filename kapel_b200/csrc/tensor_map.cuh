@@ -10,4 +10,10 @@ namespace kb {
 int encode_map_bf16(CUtensorMap* map, const void* base, unsigned long long rows, unsigned long long cols,
                     unsigned long long pitch_elems, unsigned box_rows);
 
+// A dense [rows, cols] bfloat16 matrix (cols a multiple of 64) seen as three dimensions: 64 elements,
+// rows, chunks of 64 columns. A box of box_rows rows lands in shared memory chunk by chunk:
+// [cols / 64][box_rows][128 bytes] under the 128-byte swizzle, one copy for rows of any width.
+// Coordinates are (0, row, 0).
+int encode_map_bf16_chunks(CUtensorMap* map, const void* base, unsigned long long rows, unsigned cols, unsigned box_rows);
+
 }  // namespace kb
