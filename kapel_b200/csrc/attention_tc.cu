@@ -2,12 +2,17 @@
 //
 // One block takes a tile of 128 rows — (token, query head) pairs of one kv head, the same tiles as
 // the mma.sync kernel — and walks its keys 64 at a time:
-//   S = Q K^T      tcgen05.mma, Q [128 x d] and the key tile [64 x d] K-major in shared memory
-//                  (128-byte swizzle), S [128 x 64] float32 in tensor memory (TMEM);
-//   P = exp(cap tanh(S scale / cap)), masked, read from TMEM and written back to TMEM as bfloat16
+//   S = Q K^T      tcgen05.mma with Q [128 x d] as the A operand from tensor memory (TMEM), where
+//                  it is put once (read from shared memory, Q would cost every product 4 KB), the
+//                  key tile [64 x d] K-major in shared memory (128-byte swizzle), S [128 x 64]
+//                  float32 in TMEM;
+//   P = exp(cap tanh(S scale / cap)), masked, read from TMEM and written back over S as bfloat16
 //                  by four warps, one row a thread;
 //   O += P V       tcgen05.mma with P as the A operand straight from TMEM and the value tile
 //                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM throughout.
+// TMEM columns: O (d), two S buffers (64 each; P lies over the first 32 columns of its S), Q (d / 2).
+// One thread issues every MMA and they run in the order issued, so the scores of tile kt + 2 land on
+// their buffer only after the product that read tile kt's P from it.
 // Keys and values arrive by TMA, one copy for the 16 keys of a page of one kv head (a
 // three-dimensional box that lands as head_dim / 64 chunks of [16 keys x 128 bytes]), in two rings of
 // slots, one for key tiles and one for value tiles, each slot freed by the tcgen05.commit of the
@@ -100,12 +105,6 @@ __device__ __forceinline__ uint64_t at_desc(uint32_t saddr, uint32_t lead, uint3
 __host__ __device__ constexpr uint32_t at_idesc(int m, int n, bool b_mn) {
     return (1u << 4) | (1u << 7) | (1u << 10) | (b_mn ? (1u << 16) : 0u) | ((uint32_t)(n >> 3) << 17) | ((uint32_t)(m >> 4) << 24);
 }
-__device__ __forceinline__ void at_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
-    asm volatile(
-        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
-        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
-        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
-}
 __device__ __forceinline__ void at_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
     asm volatile(
         "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
@@ -128,6 +127,15 @@ __device__ __forceinline__ void at_st16(uint32_t taddr, const uint32_t (&r)[16])
         ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
           "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]) : "memory");
 }
+__device__ __forceinline__ void at_st32(uint32_t taddr, const uint32_t (&r)[32]) {
+    asm volatile(
+        "tcgen05.st.sync.aligned.32x32b.x32.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,"
+        "%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31,%32};"
+        ::"r"(taddr), "r"(r[0]), "r"(r[1]), "r"(r[2]), "r"(r[3]), "r"(r[4]), "r"(r[5]), "r"(r[6]), "r"(r[7]), "r"(r[8]),
+          "r"(r[9]), "r"(r[10]), "r"(r[11]), "r"(r[12]), "r"(r[13]), "r"(r[14]), "r"(r[15]), "r"(r[16]), "r"(r[17]),
+          "r"(r[18]), "r"(r[19]), "r"(r[20]), "r"(r[21]), "r"(r[22]), "r"(r[23]), "r"(r[24]), "r"(r[25]), "r"(r[26]),
+          "r"(r[27]), "r"(r[28]), "r"(r[29]), "r"(r[30]), "r"(r[31]) : "memory");
+}
 __device__ __forceinline__ float at_tanh(float x) {
     float y;
     asm("tanh.approx.f32 %0, %1;" : "=f"(y) : "f"(x));
@@ -147,16 +155,15 @@ __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
 template <int HD> struct AtCfg {
     static constexpr int NBOX = HD / 64;                        // boxes of 64 elements along the head
     static constexpr int SLOT_BYTES = AT_KEYS * HD * 2;         // a key tile or a value tile
-    static constexpr int Q_BYTES = AT_ROWS * HD * 2;
     // Keys and values have rings of their own: a key slot is free as soon as its scores are
     // complete, two tiles before the next key tile is needed in it, and a value slot when its
     // product is, so both are loaded two tiles ahead.
-    static constexpr int K_SLOTS = HD == 256 ? 2 : (HD == 128 ? 4 : 3);
-    static constexpr int V_SLOTS = HD == 256 ? 3 : (HD == 128 ? 6 : 5);
+    static constexpr int K_SLOTS = HD == 256 ? 3 : (HD == 128 ? 5 : 3);
+    static constexpr int V_SLOTS = HD == 256 ? 4 : (HD == 128 ? 8 : 5);
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
-    static constexpr int COL_O = 0, COL_S = HD, COL_P = HD + 2 * AT_KEYS;
-    static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // HD + 192 rounded up to a power of two
-    static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024 /* alignment */ + 256 /* barriers */ + 64 /* pages */;
+    static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
+    static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // 3 HD / 2 + 128 rounded up to a power of two
+    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
 
 template <int HD>
@@ -166,14 +173,12 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS;
     extern __shared__ unsigned char at_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* sQ = smem;                                    // NBOX chunks of [128 rows x 128 bytes]
-    unsigned char* ring = smem + C::Q_BYTES;
+    unsigned char* ring = smem;
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] a slot's boxes have landed
     uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete
     uint64_t* s_full = empty + NS;                               // [2] S complete (MMA -> softmax)
     uint64_t* p_full = s_full + 2;                               // [2] P written (softmax -> MMA), four warps arrive
-    uint64_t* pv_done = p_full + 2;                              // [2] the product that read P is complete
-    uint64_t* o_full = pv_done + 2;                              // [1] O complete
+    uint64_t* o_full = p_full + 2;                               // [1] O complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
@@ -205,7 +210,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 1); at_mbar_init(empty + s, 1); }
-        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 4); at_mbar_init(pv_done + b, 1); }
+        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 4); }
         at_mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -213,20 +218,29 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_saddr(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
-    // Q: 16-byte pieces to the swizzled K-major layout (piece c of row r of a chunk at r * 128 + ((c ^ (r & 7)) * 16)).
-    for (int i = tid; i < AT_ROWS * (HD / 8); i += AT_THREADS) {
-        const int r = i / (HD / 8), piece = i % (HD / 8);
-        uint4 v = make_uint4(0u, 0u, 0u, 0u);
-        if (r < rows_valid)
-            v = *reinterpret_cast<const uint4*>(p.q + ((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + piece * 8);
-        const int chunk = piece >> 3, c = piece & 7;
-        *reinterpret_cast<uint4*>(sQ + chunk * (AT_ROWS * 128) + r * 128 + ((c ^ (r & 7)) << 4)) = v;
-    }
-    at_fence_async_smem();                                       // generic-proxy writes, read by the tensor cores
     at_fence_before();
     __syncthreads();
     at_fence_after();
     const uint32_t tmem = *tmem_slot;
+    // Q into TMEM as the A operand of the score products: row r in lane r, two elements a column.
+    if (warp >= 2) {
+        const int r = (warp & 3) * 32 + lane;
+        const bf16* src = p.q + ((size_t)(row0 + (r < rows_valid ? r / group : 0)) * p.hq + kvh * group + (r < rows_valid ? r % group : 0)) * d;
+        for (int c0 = 0; c0 < HD; c0 += 64) {
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
     bool failed = false;
 
     if (warp == 0) {
@@ -285,7 +299,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS / 2, false);
             constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
             constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
-            const uint32_t q_addr = at_saddr(sQ), ring_addr = at_saddr(ring);
+            const uint32_t ring_addr = at_saddr(ring);
             auto issue_s = [&](int kt) -> bool {                 // S[kt & 1] = Q K(kt)^T
                 const int s = kt % KS;
                 if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) return false;
@@ -294,14 +308,14 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (kt & 1) * AT_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
-                    const uint64_t adesc = at_desc(q_addr + bx * (AT_ROWS * 128), 16, 1024);
+                    const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
                     // the first (then the second) eight keys of each of the four pages: groups a page apart
                     const uint64_t bdesc0 = at_desc(k_addr + bx * 2048, 16, PAGE_BYTES);
                     const uint64_t bdesc1 = at_desc(k_addr + bx * 2048 + 1024, 16, PAGE_BYTES);
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk) {
-                        at_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc0 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
-                        at_mma_ss(d_tmem + 32, adesc + (uint64_t)(kk * 2), bdesc1 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                        at_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc0 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                        at_mma_ts(d_tmem + 32, a_tmem + (uint32_t)(kk * 8), bdesc1 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
                     }
                 }
                 at_commit(empty + s);                            // the key slot is free when S is complete
@@ -317,7 +331,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_P + b * (AT_KEYS / 2));
+                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
                     // columns 16 kk .. of P: half kk >> 1 of pages 2 (kk & 1) and 2 (kk & 1) + 1; chunks 2 KB apart
@@ -325,7 +339,6 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);
-                at_commit(pv_done + b);
             }
             if (!failed) at_commit(o_full);
         }
@@ -345,8 +358,6 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             const int b = kt & 1;
             const int j0 = k_begin + kt * AT_KEYS;
             if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
-            // the product that read this P buffer two tiles ago must be complete before it is overwritten
-            if (kt >= 2 && !__all_sync(0xffffffffu, at_mbar_wait(pv_done + b, (uint32_t)((kt >> 1) - 1) & 1u))) { failed = true; break; }
             at_fence_after();
             uint32_t s0[32], s1[32], pr[16];
             const bool edge = j0 < lo_max || j0 + AT_KEYS > hi_min;      // the same for the whole warp
@@ -369,7 +380,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     lb += p1;
                     pr[j >> 1] = at_pack(p0, p1);
                 }
-                at_st16(lanes + (uint32_t)(C::COL_P + b * (AT_KEYS / 2) + h * 16), pr);
+                at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + h * 16), pr);
             }
             l += la + lb;
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
