@@ -13,14 +13,12 @@
 // TMEM columns: O (d), two S buffers (64 each; P lies over the first 32 columns of its S), Q (d / 2).
 // One thread issues every MMA and they run in the order issued, so the scores of tile kt + 2 land on
 // their buffer only after the product that read tile kt's P from it.
-// Keys and values arrive by TMA, one copy for the 16 keys of a page of one kv head (a
-// three-dimensional box that lands as head_dim / 64 chunks of [16 keys x 128 bytes]), in two rings of
-// slots, one for key tiles and one for value tiles, each slot freed by the tcgen05.commit of the
-// product that read it. A tile is therefore laid out page by page, [4 pages][chunks][16 keys], and
-// eight-key groups are evenly spaced only from page to page. The products take them that way: the
-// scores are two MMAs of 32 keys each, the first halves of the four pages and then the second
-// halves, so column c of S is key 16 ((c >> 3) & 3) + 8 (c >> 5) + (c & 7) of the tile; P keeps that
-// order, and each 16-key step of P V pairs the same halves of two neighbouring pages. S and P are double-buffered so the exponentials of one tile run under the
+// Keys and values arrive by TMA in two rings of slots, one for key tiles and one for value tiles,
+// each slot freed by the tcgen05.commit of the product that read it. A product costs the tensor
+// cores about 50 cycles beyond its arithmetic, so the scores take all 64 keys in one product a
+// 16-element step: the key tile is laid out [chunk of 64 elements][64 keys], boxes of 16 keys x 64
+// elements, one a (page, chunk). The values, whose products step through the keys 16 at a time,
+// come as one three-dimensional copy a page: [page][chunk][16 keys]. S and P are double-buffered so the exponentials of one tile run under the
 // products of its neighbours.
 //
 // The soft cap bounds every score by +-cap, so exp(s) itself is safe in float32 and bfloat16 for
@@ -78,6 +76,10 @@ __device__ __forceinline__ bool at_mbar_wait(uint64_t* bar, uint32_t parity) {
         if (ok) return true;
         if (clock64() - start > 2000000000ll) return false;
     }
+}
+__device__ __forceinline__ void at_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
+    asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(at_saddr(bar)), "r"(x), "r"(y) : "memory");
 }
 // the 16 rows from `row` on, all chunks
 __device__ __forceinline__ void at_tma_page(uint32_t dst, const CUtensorMap* map, int row, uint64_t* bar) {
@@ -286,17 +288,27 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 }
                 if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_BYTES);
                 __syncwarp();
-                if (lane < 4 && page >= 0) {                     // lane = sub: one copy a page
+                if (half == 0) {
+                    // keys: a box of 16 keys x 64 elements a lane, chunk by chunk [chunk][page][16 keys], so that
+                    // the tile's eight-key groups are 1 KB apart and one product takes all 64 keys
+                    const int sub = (lane / NBOX) & 3, bx = lane % NBOX;
+                    const int pg = __shfl_sync(0xffffffffu, page, sub);
+                    if (lane < 4 * NBOX && pg >= 0) {
+                        const int j = j0 + sub * 16;
+                        const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
+                        at_tma_box(at_saddr(dst) + (uint32_t)(bx * 4 + sub) * 2048u, &map_k, bx * 64, row, full + s);
+                    }
+                } else if (lane < 4 && page >= 0) {              // values: one copy a page, [page][chunk][16 keys]
                     const int j = j0 + lane * 16;
                     const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
-                    at_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_BYTES, half == 0 ? &map_k : &map_v, row, full + s);
+                    at_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_BYTES, &map_v, row, full + s);
                 }
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- every MMA, from one lane
         if (lane == 0) {
-            constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS / 2, false);
+            constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS, false);
             constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
             constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
             const uint32_t ring_addr = at_saddr(ring);
@@ -309,14 +321,10 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
                     const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
-                    // the first (then the second) eight keys of each of the four pages: groups a page apart
-                    const uint64_t bdesc0 = at_desc(k_addr + bx * 2048, 16, PAGE_BYTES);
-                    const uint64_t bdesc1 = at_desc(k_addr + bx * 2048 + 1024, 16, PAGE_BYTES);
+                    const uint64_t bdesc = at_desc(k_addr + bx * (AT_KEYS * 128), 16, 1024);
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        at_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc0 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
-                        at_mma_ts(d_tmem + 32, a_tmem + (uint32_t)(kk * 8), bdesc1 + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
-                    }
+                    for (int kk = 0; kk < 4; ++kk)
+                        at_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);                            // the key slot is free when S is complete
                 at_commit(s_full + (kt & 1));
@@ -334,8 +342,8 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
 #pragma unroll
                 for (int kk = 0; kk < 4; ++kk) {
-                    // columns 16 kk .. of P: half kk >> 1 of pages 2 (kk & 1) and 2 (kk & 1) + 1; chunks 2 KB apart
-                    const uint64_t bdesc = at_desc(v_addr + (uint32_t)(kk & 1) * 2 * PAGE_BYTES + (uint32_t)(kk >> 1) * 1024, 2048, PAGE_BYTES);
+                    // keys 16 kk ..: page kk of the tile, its two eight-key groups 1 KB apart, chunks 2 KB apart
+                    const uint64_t bdesc = at_desc(v_addr + (uint32_t)kk * PAGE_BYTES, 2048, 1024);
                     at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);
@@ -372,7 +380,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
                     float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
                     if (edge) {
-                        const int jj = j0 + (j >> 3) * 16 + h * 8 + (j & 7);     // column 32 h + j of S is this key
+                        const int jj = j0 + h * 32 + j;
                         if (jj < lo || jj >= hi) p0 = 0.f;
                         if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
                     }
@@ -445,7 +453,7 @@ static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_ta
     }
     const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
     CUtensorMap map_k, map_v;
-    if (int e = encode_map_bf16_chunks(&map_k, k_table, rows, p.d, 16)) return e;
+    if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
     if (int e = encode_map_bf16_chunks(&map_v, v_table, rows, p.d, 16)) return e;
     dim3 grid(p.hkv, p.slots, tiles);
     attention_tc_kernel<HD><<<grid, AT_THREADS, C::SMEM, s>>>(p, map_k, map_v);
