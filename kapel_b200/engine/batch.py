@@ -55,12 +55,21 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
     return split, max(1, -(-longest // split))
 
 
-def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, window: Optional[int], rows: int, hq: int, d: int):
+# What a block costs beyond its 64-key steps, what the merge of partial sums costs beyond its traffic
+# (both in steps), and microseconds a step, by prompt kernel; from sweeps of the split at Gemma 2 2B
+# head sizes. The tcgen05 kernel's steps are short, so its fixed costs weigh more and it is cut into
+# slots only when a few tiles face a long history.
+PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5), "tcgen05": (8.0, 15.0, 1.34)}
+
+
+def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, window: Optional[int], rows: int, hq: int, d: int,
+                 kernel: str = "mma"):
     """(split, slots) of the prompt attention kernel. A tile of a long prompt walks all the keys
     before it, so late tiles work many times longer than early ones; cutting the keys into slots
     of `split` positions evens the blocks out at the price of partial sums that a second kernel
     merges. The choice minimises an estimate of the time: the longest block or the mean load of a
     multiprocessor, whichever is larger, plus the merge, all counted in 64-key steps."""
+    block_cost, merge_cost, step_us = PROMPT_KERNEL_COSTS[kernel]
     first = np.asarray(first_counts, np.int64)
     last = np.asarray(last_counts, np.int64)
     lo = np.maximum(0, first - window) if window else np.zeros_like(first)
@@ -81,9 +90,9 @@ def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, windo
             b = np.minimum(last[:, None], (z + 1) * split)
             steps = np.where(b > a, -(-(b - a // 64 * 64) // 64), 0)
             work = steps.astype(np.float64).reshape(-1)
-            # what the partial sums cost to write and read back (at ~5 TB/s), in steps of ~4.5 us, plus a launch
-            merge = 1.0 + slots * rows * hq * (d + 2) * 8 / 5e12 / 4.5e-6
-        work = work[work > 0] + 0.5                      # half a step to start and finish a block
+            # what the partial sums cost to write and read back (at ~5 TB/s), in steps, plus a launch
+            merge = merge_cost + slots * rows * hq * (d + 2) * 8 / 5e12 / (step_us * 1e-6)
+        work = work[work > 0] + block_cost               # what it costs to start and finish a block
         if work.size == 0:
             continue
         cost = max(float(work.max()), float(work.sum()) * pairs_per_tile / sms * 1.1) + merge
@@ -155,12 +164,14 @@ class StepBatch:
         for i, shape in enumerate(table_shapes):
             self.groups.append(GroupBatch(views[6 + 2 * i], views[7 + 2 * i].view(shape)))
 
-    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None):
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
+                        prompt_kernel: str = "mma"):
         """How the tensor-core attention kernel cuts this step: (decode, (tile_entry, tile_row0,
         tile_nq) on the device, split, slots). `decode` is the most rows (tokens x query heads of a
         kv head) of any request when that is at most 16, which selects the decode kernel, else 0.
-        The keys are split across blocks when the tiles alone are too few to fill the GPU."""
-        key = ("tiles", heads_per_kv, kv_heads, window)
+        The keys are split across blocks when the tiles alone are too few to fill the GPU;
+        `prompt_kernel` names the kernel whose costs decide that for prompt portions."""
+        key = ("tiles", heads_per_kv, kv_heads, window, head_dim, prompt_kernel)
         if key not in self.memo:
             from .. import kernels as K
 
@@ -179,7 +190,7 @@ class StepBatch:
             else:
                 firsts = plan.row_count[arrays[1]]
                 split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,
-                                            plan.rows, heads_per_kv * kv_heads, 256)
+                                            plan.rows, heads_per_kv * kv_heads, head_dim, prompt_kernel)
             self.memo[key] = (decode, tiles, split, slots, host)
         return self.memo[key][:4]
 

@@ -58,7 +58,8 @@ class StaticBatch:
             n = min(n, (window - 1) // self.chunk + 2)
         return max(1, n)
 
-    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None):
+    def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
+                        prompt_kernel: str = "mma"):
         if (kv_heads, window) not in self._mma:
             self._mma[(kv_heads, window)] = decode_split(self.rows * kv_heads, self._longest, sm_count(self._device), window)
         split, slots = self._mma[(kv_heads, window)]

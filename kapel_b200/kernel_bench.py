@@ -154,7 +154,8 @@ def main(argv=None) -> int:
         per_tile = max(1, K.attention_mma_rows(False) // (Hq // Hkv))
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
         firsts = tiles[1].cpu().numpy() + 1
-        split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D)
+        split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D,
+                                    K.attention_prompt_kernel(Hq, Hkv, D, page, cap))
         pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
                                                    0, split, slots), max(3, args.iters // 4))

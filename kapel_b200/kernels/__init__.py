@@ -411,6 +411,13 @@ def attention_mma_takes(dtype, d: int, heads_per_kv: int) -> bool:
     return dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and heads_per_kv <= 16
 
 
+def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: Optional[float]) -> str:
+    """Which kernel `paged_attention_mma` runs for prompt portions of these sizes: "tcgen05" or "mma"."""
+    if ATTENTION_PROMPT == "tcgen05" and library().kb_attention_tc_takes(int(hq), int(hkv), int(d), int(page_size), _f(softcap or 0.0)):
+        return "tcgen05"
+    return "mma"
+
+
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
@@ -435,7 +442,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     lib = library()
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
     scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
-    if not decode and ATTENTION_PROMPT == "tcgen05" and lib.kb_attention_tc_takes(hq, hkv, d, int(page_size), _f(softcap or 0.0)):
+    if not decode and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
         _check(
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                                 _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
