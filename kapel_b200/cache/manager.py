@@ -83,12 +83,57 @@ class Plan:
         return int(self.kv_len.max()) if len(self.kv_len) else 0
 
 
+class PageList:
+    """A sequence's logical pages in one group, as a list that is also an int32 array: a step's
+    block-table row is a slice of it, not a conversion of a Python list every step."""
+
+    __slots__ = ("a", "n")
+
+    def __init__(self):
+        self.a = np.empty(16, np.int32)
+        self.n = 0
+
+    def __len__(self) -> int:
+        return self.n
+
+    def __iter__(self):
+        return iter(self.a[: self.n].tolist())
+
+    def __reversed__(self):
+        return iter(self.a[: self.n][::-1].tolist())
+
+    def __getitem__(self, i: int) -> int:
+        if not -self.n <= i < self.n:
+            raise IndexError(i)
+        return int(self.a[i if i >= 0 else self.n + i])
+
+    def __setitem__(self, i: int, page: int) -> None:
+        if not 0 <= i < self.n:
+            raise IndexError(i)
+        self.a[i] = page
+
+    def append(self, page: int) -> None:
+        if self.n == self.a.size:
+            self.a = np.concatenate([self.a, np.empty(self.a.size, np.int32)])
+        self.a[self.n] = page
+        self.n += 1
+
+    def pop(self) -> int:
+        if self.n == 0:
+            raise IndexError("pop from no pages")
+        self.n -= 1
+        return int(self.a[self.n])
+
+    def array(self) -> np.ndarray:
+        return self.a[: self.n]
+
+
 class _Sequence:
     __slots__ = ("length", "pages", "released", "slot", "fresh")
 
     def __init__(self, n_groups: int, slot: int):
         self.length = 0
-        self.pages: List[List[int]] = [[] for _ in range(n_groups)]   # -1 where given back
+        self.pages: List[PageList] = [PageList() for _ in range(n_groups)]   # -1 where given back
         self.released = [0] * n_groups     # logical pages below this index were given back
         self.slot = slot
         self.fresh = True
@@ -286,19 +331,25 @@ class CacheManager:
             start, end = seq.length, seq.length + count
             q_start[e], q_len[e], kv_len[e] = r, count, end
             slots[e], fresh[e] = seq.slot, seq.fresh
-            positions[r : r + count] = np.arange(start, end, dtype=np.int32)
-            row_entry[r : r + count] = e
-            row_count[r : r + count] = np.arange(start + 1, end + 1, dtype=np.int32)
+            if count == 1:
+                positions[r], row_entry[r], row_count[r] = start, e, end
+            else:
+                positions[r : r + count] = np.arange(start, end, dtype=np.int32)
+                row_entry[r : r + count] = e
+                row_count[r : r + count] = np.arange(start + 1, end + 1, dtype=np.int32)
             for g, group in enumerate(self.groups):
                 pages = seq.pages[g]
                 while len(pages) < self._pages_for(end):
                     page = group.pool.take()
                     taken.append((g, seq_id, len(pages), page))
                     pages.append(page)
-                table = np.asarray(pages, np.int32)
+                table = pages.array()
                 group_plans[g].block_table[e, : len(pages)] = table
-                pos = positions[r : r + count]
-                group_plans[g].lines[r : r + count] = table[pos // ps] * ps + pos % ps
+                if count == 1:                                   # a decoded token: no arrays to build
+                    group_plans[g].lines[r] = int(table[start // ps]) * ps + start % ps
+                else:
+                    pos = positions[r : r + count]
+                    group_plans[g].lines[r : r + count] = table[pos // ps] * ps + pos % ps
             r += count
         return Plan(list(entries), positions, row_entry, row_count, q_start, q_len, kv_len, slots, fresh, group_plans, taken)
 

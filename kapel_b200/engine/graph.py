@@ -34,7 +34,10 @@ class StaticBatch:
         self.memo: Dict[object, object] = {}
         sizes = [rows] * 6 + [rows, rows * width] * n_groups
         self.total = sum(sizes)
-        self.host = torch.empty((self.total,), dtype=torch.int32, pin_memory=True)
+        # Two pinned staging buffers taken in turn: the next pass can be written while the copy of
+        # the last one may still be in flight.
+        self.hosts = [torch.empty((self.total,), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.turn = 0
         self.dev = torch.empty((self.total,), dtype=torch.int32, device=device)
         views, at = [], 0
         for n in sizes:
@@ -68,10 +71,28 @@ class StaticBatch:
     def fill(self, plan, ids) -> None:
         """Writes a plan of at most `rows` single-token entries into the buffers; the rest are
         padding rows."""
+        which = self.fill_host(plan)
+        self.set_ids(which, ids, plan.rows)
+        self.upload(which)
+
+    def set_ids(self, which: int, ids, n: int) -> None:
+        flat = self.hosts[which].numpy()
+        flat[:n] = np.asarray(ids, np.int32)
+        flat[n : self.rows] = 0
+
+    def upload(self, which: int) -> None:
+        """One copy of everything a pass reads; the other staging buffer takes the next pass."""
+        self.dev.copy_(self.hosts[which], non_blocking=True)
+        self.turn = which ^ 1
+
+    def fill_host(self, plan) -> int:
+        """Everything of a plan but its token ids into the staging buffer whose turn it is; returns
+        which. Nothing is copied to the device yet."""
         n = plan.rows
         rows, width = self.rows, self.width
-        flat = self.host.numpy()
-        at = 0
+        which = self.turn
+        flat = self.hosts[which].numpy()
+        at = rows                                            # the ids come first
 
         def put(values, pad):
             nonlocal at
@@ -79,7 +100,6 @@ class StaticBatch:
             flat[at + n : at + rows] = pad
             at += rows
 
-        put(np.asarray(ids, np.int32), 0)
         put(plan.positions, 0)
         put(plan.row_entry, 0)
         flat[at - rows + n : at] = np.arange(n, rows, dtype=np.int32)     # a padding row is its own entry
@@ -94,7 +114,7 @@ class StaticBatch:
             w = g.block_table.shape[1]
             table[:n, :w] = g.block_table
             at += rows * width
-        self.dev.copy_(self.host, non_blocking=True)
+        return which
 
 
 class DecodeGraphs:
@@ -114,6 +134,28 @@ class DecodeGraphs:
             if b >= rows:
                 return b, -(-width // WIDTH_STEP) * WIDTH_STEP
         return None
+
+    def prepare(self, plan):
+        """Stages a decode-only plan whose token ids are not known yet: (plan, bucket, staging
+        buffer), or None if its bucket has no recording so far."""
+        width = max(g.block_table.shape[1] for g in plan.groups) if plan.groups else 1
+        key = self.bucket(plan.rows, width)
+        if key is None or key not in self.graphs:
+            return None
+        return plan, key, self.graphs[key][1].fill_host(plan)
+
+    def run_prepared(self, prepared, ids) -> torch.Tensor:
+        """The staged pass with its token ids: one copy, one replay."""
+        plan, key, which = prepared
+        graph, static, out = self.graphs[key]
+        static.set_ids(which, ids, plan.rows)
+        static.upload(which)
+        graph.replay()
+        self.replays += 1
+        self.replayed_kernels += static.kernels
+        eng = self._engine()
+        eng.last_h2d_bytes = static.h2d_bytes
+        return out[: plan.rows]
 
     def run(self, plan, ids) -> Optional[torch.Tensor]:
         """Logits [rows, vocab] of a decode-only plan through a recording, or None if no bucket

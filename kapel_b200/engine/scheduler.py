@@ -98,6 +98,8 @@ class Scheduler:
         self._ids = itertools.count()
         self.preemptions = 0
         self.passes = 0
+        self.staged = None            # (request ids, engine handle) of a decode pass staged ahead of its tokens
+        self.staged_passes = 0        # passes that ran from a staged plan
 
     # ------------------------------------------------------------------ requests
     def add(self, request: Request) -> int:
@@ -215,6 +217,14 @@ class Scheduler:
         """One pass of the model: a token of every decoding request and portions of prompts.
         Returns the tokens it gave and the requests that ended; nothing when there is no work."""
         events = self._admit()
+        staged, self.staged = self.staged, None
+        if staged is not None:
+            # The pass staged while the last one ran is this pass if nothing changed since: the same
+            # requests run, each with exactly its new token to feed.
+            rids, handle = staged
+            if rids == self.running and all(self._pending(r) == 1 for r in rids):
+                return self._finish_pass(events, [(r, 1) for r in rids], handle)
+            self._discard(handle)
         while True:
             pass_ = self._plan()
             need = [0] * len(self.cache.groups)
@@ -235,6 +245,29 @@ class Scheduler:
             self._suspend_last()
         if not pass_:
             return events
+        return self._finish_pass(events, pass_, None)
+
+    def _discard(self, handle) -> None:
+        discard = getattr(self.engine, "discard", None)
+        if discard is not None:
+            discard(handle)
+
+    def _stage_next(self, pass_, producing) -> None:
+        """While the pass just launched runs: if it was decoding only and every request is sure to
+        go on unless it meets an end-of-sequence or stop token, take the next pass's pages and
+        write its inputs now, so that only the token ids remain to be filled in."""
+        prepare = getattr(self.engine, "prepare_decode", None)
+        if prepare is None or self.waiting or len(producing) != len(pass_) or [r for r, _ in pass_] != self.running:
+            return
+        for rid in producing:
+            entry = self.entries[rid]
+            if entry.generated + 1 >= entry.request.max_tokens:
+                return
+        handle = prepare(list(self.running))
+        if handle is not None:
+            self.staged = (list(self.running), handle)
+
+    def _finish_pass(self, events, pass_, handle) -> List[Event]:
         producing = [rid for rid, count in pass_ if count == self._pending(rid)]
         entries = []
         for rid, count in pass_:
@@ -243,10 +276,18 @@ class Scheduler:
             tokens = entry.sequence[at : at + count]
             entries.append(StepEntry(rid, tokens, [count - 1] if count == self._pending(rid) else []))
         try:
-            logits = self.engine.step(entries)
+            if handle is not None:
+                logits = self.engine.step_prepared(handle, [e.tokens[0] for e in entries])
+                self.staged_passes += 1
+            else:
+                logits = self.engine.step(entries)
             self.passes += 1
+            self._stage_next(pass_, producing)
             tokens = self._choose(logits, producing)
         except Exception as e:                      # the pass failed: every running request ends
+            staged, self.staged = self.staged, None
+            if staged is not None:
+                self._discard(staged[1])
             for rid in list(self.running):
                 self.cancel(rid)
                 events.append(Event(rid, None, "error", f"{type(e).__name__}: {e}"))

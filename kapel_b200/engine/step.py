@@ -185,6 +185,54 @@ class Engine:
         self.steps += 1
         return logits
 
+    # ------------------------------------------------------------------ a pass staged ahead of its tokens
+    def prepare_decode(self, seq_ids):
+        """Takes the pages and stages the inputs of a pass in which each of `seq_ids` brings one
+        token, before the tokens are known (while the pass that chooses them still runs). Returns a
+        handle for `step_prepared` / `discard`, or None when such a pass cannot be staged now (no
+        recording for its size yet, no pages, a sequence at its limit): then nothing is held."""
+        if self.graphs is None or not seq_ids:
+            return None
+        limit = self.spec.max_positions
+        for s in seq_ids:
+            if s not in self.cache or (limit is not None and self.cache.length(s) + 1 > limit):
+                return None
+        try:
+            plan = self.cache.plan([(s, 1) for s in seq_ids])
+        except CacheFull:
+            return None
+        if plan.fresh.any():
+            self.cache.abort(plan)
+            return None
+        prepared = self.graphs.prepare(plan)
+        if prepared is None:
+            self.cache.abort(plan)
+        return prepared
+
+    def step_prepared(self, prepared, ids) -> torch.Tensor:
+        """Runs a staged pass with its token ids (one a sequence, in the staged order); logits as
+        `step` returns them, every row wanted."""
+        plan = prepared[0]
+        vocab = self.spec.vocab_size
+        try:
+            if len(ids) != plan.rows:
+                raise ValueError(f"{len(ids)} tokens for a staged pass of {plan.rows}")
+            for t in ids:
+                if not 0 <= int(t) < vocab:
+                    raise ValueError(f"token {t} is outside the vocabulary (0..{vocab - 1})")
+            logits = self.graphs.run_prepared(prepared, ids)
+        except Exception:
+            self.cache.abort(plan)
+            raise
+        self.cache.commit(plan)
+        self.steps += 1
+        return logits
+
+    def discard(self, prepared) -> None:
+        """The staged pass will not run: its pages go back."""
+        if prepared is not None and not prepared[0].committed:
+            self.cache.abort(prepared[0])
+
     def _clear_fresh_state(self, plan) -> None:
         if not self.cache.states or not plan.fresh.any():
             return

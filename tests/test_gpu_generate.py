@@ -104,6 +104,47 @@ def test_scheduler_with_few_pages_suspends_and_still_gives_each_its_tokens(folde
     small.engine.cache.check()
 
 
+def test_passes_staged_ahead_give_the_same_tokens_and_hold_no_page_afterwards(folders):
+    """While a decode pass runs the scheduler stages the next one (pages taken, inputs written,
+    only the token ids open). The tokens are those of each request alone; a request that meets
+    its end-of-sequence token, one that is cancelled and one that joins late all make a staged
+    pass stale, which must give its pages back."""
+    import kapel_b200
+    from kapel_b200.engine.scheduler import Request
+
+    raw, _ = TINY["A"]
+    rng = np.random.default_rng(29)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (20, 31, 9, 14)]
+    model = kapel_b200.Model(str(folders["A"]), dtype="f32", max_tokens_cached=1024, max_sequences=8)
+    want = [model.generate(p, max_tokens=40) for p in prompts]
+    eos = want[1][17]                                   # request 1 stops where this token first appears
+    cut = want[1].index(eos) + 1
+    sched = model.scheduler(max_pass_tokens=64)
+    ids = [sched.add(Request(prompts[0], max_tokens=40)), sched.add(Request(prompts[1], max_tokens=40, eos_ids=[eos])),
+           sched.add(Request(prompts[2], max_tokens=40))]
+    out = {r: [] for r in ids}
+    passes = 0
+    while sched.has_work():
+        passes += 1
+        if passes == 12:                                # a request joins while others decode
+            ids.append(sched.add(Request(prompts[3], max_tokens=40)))
+            out[ids[-1]] = []
+        if passes == 25:
+            sched.cancel(ids[2])
+        for ev in sched.step():
+            assert ev.finish != "error", ev.error
+            if ev.token is not None:
+                out[ev.id].append(ev.token)
+        model.engine.cache.check()
+    assert out[ids[0]] == want[0]
+    assert out[ids[1]] == want[1][:cut]
+    assert out[ids[2]] == want[2][: len(out[ids[2]])] and 0 < len(out[ids[2]]) < 40
+    assert out[ids[3]] == want[3]
+    assert sched.staged_passes > 10, "decode passes ran from staged plans"
+    assert sched.staged is None or not model.engine.cache._sequences
+    assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(folders, dtype):
     """A one-token prompt, then every token one by one up to the model's limit: first tokens of a
