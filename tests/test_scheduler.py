@@ -53,6 +53,43 @@ class FakeEngine:
         self.fed.pop(seq_id, None)
 
 
+class StagingEngine(FakeEngine):
+    """The stand-in with the three calls that let the scheduler stage a decode pass ahead."""
+
+    def __init__(self, *a, **kw):
+        super().__init__(*a, **kw)
+        self.staged = self.ran_staged = self.discarded = 0
+
+    def prepare_decode(self, seq_ids):
+        from kapel_b200.cache import CacheFull
+
+        try:
+            plan = self.cache.plan([(s, 1) for s in seq_ids])
+        except CacheFull:
+            return None
+        self.staged += 1
+        return (plan, list(seq_ids))
+
+    def step_prepared(self, handle, ids):
+        plan, seq_ids = handle
+        rows = []
+        for s, t in zip(seq_ids, ids):
+            self.fed[s].append(t)
+            assert len(self.fed[s]) == self.cache.length(s) + 1
+            row = np.full(VOCAB, -5.0)
+            row[self.next_token(self.fed[s])] = 5.0
+            rows.append(row)
+        self.cache.commit(plan)
+        self.passes.append([(s, 1) for s in seq_ids])
+        self.ran_staged += 1
+        return np.array(rows).reshape(-1, VOCAB)
+
+    def discard(self, handle):
+        if not handle[0].committed:
+            self.cache.abort(handle[0])
+            self.discarded += 1
+
+
 def expected(prompt, n):
     seq = list(prompt)
     for _ in range(n):
@@ -77,6 +114,33 @@ def run(sched, limit=10000):
 
 def prompts(rng, lengths):
     return [[int(t) for t in rng.integers(0, VOCAB, size=n)] for n in lengths]
+
+
+def test_a_staged_pass_runs_if_nothing_changed_and_gives_its_pages_back_if_something_did():
+    eng = StagingEngine(pages=64)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=64))
+    a, b = [3, 9, 27, 4], [5] * 20
+    eos = expected(b, 12)[7]
+    n_b = expected(b, 12).index(eos) + 1
+    ra = sched.add(Request(a, max_tokens=30))
+    rb = sched.add(Request(b, max_tokens=12, eos_ids=[eos]))          # ends early: a staged pass goes stale
+    out = {ra: [], rb: []}
+    late = None
+    passes = 0
+    while sched.has_work():
+        passes += 1
+        if passes == 15:
+            late = sched.add(Request([8, 8], max_tokens=5))           # joins: another stale pass
+            out[late] = []
+        for ev in sched.step():
+            assert ev.finish != "error"
+            if ev.token is not None:
+                out[ev.id].append(ev.token)
+        eng.cache.check()
+    assert out[ra] == expected(a, 30) and out[rb] == expected(b, 12)[:n_b] and out[late] == expected([8, 8], 5)
+    assert eng.ran_staged > 10 and eng.discarded >= 2
+    assert eng.staged == eng.ran_staged + eng.discarded or sched.staged is not None
+    assert eng.cache.free_pages() == eng.cache.total_pages()
 
 
 def test_portions_under_a_token_budget_decodes_first():
