@@ -563,6 +563,142 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// Up to 64 rows with the gated unit in the epilogue: the weight is a stacked gate|up matrix
+// [2 n, k]. A block owns 64 outputs: its 128 MMA rows are the 64 gate rows and the 64 up rows of
+// the same outputs (two TMA boxes a stage), it walks all of K (no split: the gate and the up sums
+// must meet in one block), and the epilogue's upper two warps hand their up values to the lower two
+// through shared memory, which store act(gate) * up. One block a multiprocessor for Gemma-sized
+// units, so the pipeline is deeper than the plain kernel's.
+constexpr int SKG_ROWS = 64;                                    // outputs a block
+template <int NP> struct SkGlu {
+    static constexpr int B_BYTES = NP * SK2_BK * 2;
+    static constexpr int STAGE = SK2_A_BYTES + (B_BYTES < 1024 ? 1024 : B_BYTES);
+    static constexpr int STAGES = NP <= 16 ? 10 : (NP <= 32 ? 9 : 8);
+    static constexpr int XCH_BYTES = SKG_ROWS * NP * 4;         // up values on their way to the gate warps
+    static constexpr int SMEM = STAGES * STAGE + XCH_BYTES + 1024 + 256;
+};
+
+template <int NP>
+__global__ void __launch_bounds__(TC_THREADS, 1)
+gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
+                       bf16* __restrict__ c, int m, int n, int k, int act) {
+    using G = SkGlu<NP>;
+    constexpr int STAGES = G::STAGES, STAGE = G::STAGE;
+    constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(SK2_BM >> 4) << 24);
+    constexpr int COLS = NP < 32 ? 32 : NP;
+    extern __shared__ unsigned char tc_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
+    float* xch = reinterpret_cast<float*>(smem + STAGES * STAGE);                  // [64 outputs][NP rows]
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE + G::XCH_BYTES);
+    uint64_t* empty = full + STAGES;
+    uint64_t* accum = empty + STAGES;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(accum + 1);
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int n0 = blockIdx.x * SKG_ROWS;
+    const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
+        tc_mbar_init(accum, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    tc_fence_before();
+    __syncthreads();
+    tc_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    bool failed = false;
+
+    if (warp == 0) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % STAGES;
+                if (kt >= STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / STAGES) - 1) & 1u)) { failed = true; break; }
+                unsigned char* dst = smem + s * STAGE;
+                tc_mbar_expect_tx(full + s, SK2_A_BYTES + G::B_BYTES);
+                tc_tma_load_2d(dst, &map_w, kt * SK2_BK, n0, full + s);                           // 64 gate rows
+                tc_tma_load_2d(dst + SK2_A_BYTES / 2, &map_w, kt * SK2_BK, n + n0, full + s);     // the same outputs' up rows
+                tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, kt * SK2_BK, 0, full + s);
+            }
+        }
+    } else if (warp == 1) {
+        if (lane == 0) {
+            for (int kt = 0; kt < k_tiles; ++kt) {
+                const int s = kt % STAGES;
+                if (!tc_mbar_wait(full + s, (uint32_t)(kt / STAGES) & 1u)) { failed = true; break; }
+                tc_fence_after();
+                const uint32_t a_addr = tc_saddr(smem + s * STAGE);
+                const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + SK2_A_BYTES);
+#pragma unroll
+                for (int kk = 0; kk < SK2_BK / 16; ++kk) {
+                    const uint32_t accumulate = (kt | kk) != 0 ? 1u : 0u;
+                    asm volatile(
+                        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+                        "tcgen05.mma.cta_group::1.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+                        ::"r"(tmem), "l"(adesc + (uint64_t)(kk * 2)), "l"(bdesc + (uint64_t)(kk * 2)), "r"(IDESC), "r"(accumulate) : "memory");
+                }
+                tc_commit(empty + s);
+            }
+            if (!failed) tc_commit(accum);
+        }
+    } else {
+        const int quarter = warp & 3;                       // TMEM lanes 32 quarter ..: 0, 1 gates; 2, 3 ups
+        const bool ok = __all_sync(0xffffffffu, tc_mbar_wait(accum, 0u));
+        if (!ok) failed = true;
+        const int f = (quarter & 1) * 32 + lane;            // the output within the block's 64
+        float v[NP];
+        if (ok) {
+            tc_fence_after();
+#pragma unroll
+            for (int c0 = 0; c0 < NP; c0 += 16) {
+                uint32_t r[16];
+                tc_ld16(tmem + ((uint32_t)(quarter * 32) << 16) + (uint32_t)c0, r);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+                for (int j = 0; j < 16; ++j) v[c0 + j] = __uint_as_float(r[j]);
+            }
+            if (quarter >= 2) {
+#pragma unroll
+                for (int j = 0; j < NP; ++j) xch[j * SKG_ROWS + f] = v[j];          // a row's 64 outputs side by side
+            }
+        }
+        asm volatile("bar.sync 1, 128;" ::: "memory");      // the four epilogue warps; reached whether or not the wait ran out
+        if (ok && quarter < 2 && n0 + f < n) {
+#pragma unroll
+            for (int j = 0; j < NP; ++j) {
+                if (j < m) {
+                    const float g = v[j];
+                    c[(size_t)j * n + n0 + f] = __float2bfloat16_rn((act == 0 ? gelu_tanh(g) : silu(g)) * xch[j * SKG_ROWS + f]);
+                }
+            }
+        }
+    }
+    if (failed) atomicExch(&g_tcgen05_error, 1);
+    tc_fence_before();
+    __syncthreads();
+    if (warp == 1) {
+        tc_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(COLS) : "memory");
+    }
+}
+
+template <int NP>
+static int launch_skinny_glu(const CUtensorMap& map_w, const CUtensorMap& map_x, bf16* c, int m, int n, int k, int act, cudaStream_t s) {
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(gemm_skinny_glu_kernel<NP>, cudaFuncAttributeMaxDynamicSharedMemorySize, SkGlu<NP>::SMEM);
+        if (e != cudaSuccess) return fail("gemm_skinny_glu: cannot have %d bytes of shared memory: %s", SkGlu<NP>::SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    gemm_skinny_glu_kernel<NP><<<(n + SKG_ROWS - 1) / SKG_ROWS, TC_THREADS, SkGlu<NP>::SMEM, s>>>(map_w, map_x, c, m, n, k, act);
+    return check_launch("gemm_skinny_glu");
+}
+
 // (splits, k tiles a split) for a weight [n, k]: about two blocks a multiprocessor, a
 // split at least four k tiles long. Depends on n and k only.
 static void skinny_plan(int n, int k, int sms, int* splits, int* k_tiles_per_split) {
@@ -698,6 +834,23 @@ extern "C" int kb_gemm_tcgen05_glu(void* c, const void* a, const void* w, int m,
     cudaStream_t s = (cudaStream_t)stream;
     return act == 0 ? launch_pair<EPI_GLU_GELU>(map_a, map_w, c, KB_DT_BF16, m, n, k, 0.f, s)
                     : launch_pair<EPI_GLU_SILU>(map_a, map_w, c, KB_DT_BF16, m, n, k, 0.f, s);
+}
+
+// The gated unit for up to 64 rows: a bf16 [m,k]; w bf16 [2 n, k], gate rows then up rows;
+// c = act(a . gate^T) * (a . up^T), bf16 [m, n]; act 0 gelu_tanh, 1 silu.
+extern "C" int kb_gemm_skinny_glu(void* c, const void* a, const void* w, int m, int n, int k, int act, void* stream) {
+    KB_REQUIRE(m > 0 && m <= 64 && n > 0 && k > 0, "gemm_skinny_glu: m %d (1..64), n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_skinny_glu: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(act == 0 || act == 1, "gemm_skinny_glu: activation code %d is not known (0 gelu_tanh, 1 silu)", act);
+    KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_skinny_glu: operands must be 16-byte aligned");
+    const int np = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    CUtensorMap map_w, map_x;
+    if (int e = encode_map_bf16(&map_w, w, 2ull * n, k, k, SKG_ROWS)) return e;
+    if (int e = encode_map_bf16(&map_x, a, m, k, k, np)) return e;
+    cudaStream_t s = (cudaStream_t)stream;
+    if (np == 16) return launch_skinny_glu<16>(map_w, map_x, (bf16*)c, m, n, k, act, s);
+    if (np == 32) return launch_skinny_glu<32>(map_w, map_x, (bf16*)c, m, n, k, act, s);
+    return launch_skinny_glu<64>(map_w, map_x, (bf16*)c, m, n, k, act, s);
 }
 
 // Partial sums the skinny kernel leaves for a weight [n, k] (1: it writes the result itself).

@@ -348,9 +348,12 @@ _TCGEN05_KERNELS = {"tcgen05": 0, "single": 1, "pair": 2}       # the kernel cho
 
 def gemm_glu_fused(a: torch.Tensor, w: torch.Tensor, act: str) -> Optional[torch.Tensor]:
     """act(a . gate^T) * (a . up^T) for a stacked gate|up weight w [2 n, k], in one kernel whose
-    epilogue applies the gated unit to the 32-bit sums; None where that kernel does not apply
-    (few rows, 32-bit operands) and the caller multiplies and gates in two steps."""
-    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[0] <= 64 or GEMM_LARGE not in ("tcgen05", "pair"):
+    epilogue applies the gated unit to the 32-bit sums; None where no such kernel applies
+    (32-bit operands, the mma.sync yardsticks selected) and the caller multiplies and gates in two steps."""
+    if a.dtype != torch.bfloat16 or w.dtype != torch.bfloat16 or a.shape[0] == 0:
+        return None
+    few = a.shape[0] <= 64
+    if (few and GEMM_SMALL != "skinny") or (not few and GEMM_LARGE not in ("tcgen05", "pair")):
         return None
     if act not in ACT_CODES:
         raise KernelError(f"gemm_glu: activation {act!r} is not known")
@@ -361,6 +364,9 @@ def gemm_glu_fused(a: torch.Tensor, w: torch.Tensor, act: str) -> Optional[torch
     if k != k2 or n2 % 2:
         raise KernelError(f"gemm_glu: input [{m}, {k}] against stacked weight [{n2}, {k2}]")
     out = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=a.device)
+    if few:
+        _check(library().kb_gemm_skinny_glu(_ptr(out), _ptr(a), _ptr(w), m, n2 // 2, k, ACT_CODES[act], _stream()))
+        return out
     _check(library().kb_gemm_tcgen05_glu(_ptr(out), _ptr(a), _ptr(w), m, n2 // 2, k, ACT_CODES[act], _stream()))
     return out
 

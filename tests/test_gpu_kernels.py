@@ -178,7 +178,8 @@ def test_gemm_tcgen05(kernel, m, n, k):
 
 
 @pytest.mark.parametrize("act", ["gelu_tanh", "silu"])
-@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (300, 328, 200), (129, 100, 72), (2048, 9216, 2304), (513, 1000, 520)])
+@pytest.mark.parametrize("m,n,k", [(65, 128, 64), (300, 328, 200), (129, 100, 72), (2048, 9216, 2304), (513, 1000, 520),
+                                   (1, 64, 64), (8, 9216, 2304), (17, 328, 200), (40, 100, 72), (64, 1000, 520)])
 def test_gemm_with_the_gated_unit_in_its_epilogue(act, m, n, k):
     """act(a . gate^T) * (a . up^T) from the stacked weight in one kernel, against the two products
     in 64-bit; and against the two-step path, which rounds both products to bfloat16 first."""
@@ -195,7 +196,7 @@ def test_gemm_with_the_gated_unit_in_its_epilogue(act, m, n, k):
     assert rel_err(got.cpu().double().numpy(), want.numpy()) < 6e-3          # one rounding to bfloat16
     two_step = K().glu(K().gemm(dev(a), dev(w)), act)
     assert rel_err(two_step.cpu().double().numpy(), want.numpy()) < 2e-2
-    assert K().gemm_glu_fused(dev(a[:64]), dev(w), act) is None              # few rows: the caller takes two steps
+    assert K().gemm_glu_fused(dev(a.float()), dev(w.float()), act) is None    # 32-bit operands: the caller takes two steps
 
 
 @pytest.mark.parametrize("small", ["skinny", "stream"])
