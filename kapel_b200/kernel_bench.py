@@ -101,6 +101,20 @@ def main(argv=None) -> int:
         gemm_case(f"gemm down {tag}", m, H, I)
     gemm_case("gemm head decode", B, V, H, out_dtype=torch.float32, softcap=30.0)
 
+    def glu_case(name, m):
+        """The gate|up product with the gated unit in its epilogue, as the feed-forward part calls it."""
+        if not want(name):
+            return
+        ws = [torch.randn(2 * I, H, device=dev, dtype=torch.float32).mul_(0.02).to(bf) for _ in range(4)]
+        a = torch.randn(m, H, device=dev).to(bf)
+        if K.gemm_glu_fused(a, ws[0], "gelu_tanh") is None:
+            return
+        us = _time(lambda i: K.gemm_glu_fused(a, ws[i % 4], "gelu_tanh"), args.iters)
+        report(f"{name} [{m}x{H}]x[{2 * I}x{H}]", us, 2 * I * H * 2 + m * H * 2 + m * I * 2, 4.0 * m * I * H)
+
+    glu_case("gemm gate_up+glu decode", B)
+    glu_case("gemm gate_up+glu prompt", args.prompt)
+
     # ------------------------------------------------------------------ small kernels
     for m, tag in ((B, "decode"), (args.prompt, "prompt")):
         if want(f"add_rmsnorm {tag}"):
