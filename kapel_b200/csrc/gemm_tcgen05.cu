@@ -474,6 +474,14 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         for (int s = 0; s < SK2_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
         tc_mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        // The first stages are asked for at once, before the block meets: the copies are on their
+        // way while TMEM is allocated. This thread made the barriers, so it may use them already.
+        for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt) {
+            unsigned char* dst = smem + kt * STAGE;
+            tc_mbar_expect_tx(full + kt, SK2_A_BYTES + B_BYTES);
+            tc_tma_load_2d(dst, &map_w, (kt0 + kt) * SK2_BK, n0, full + kt);
+            tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + kt);
+        }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
@@ -487,9 +495,9 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kt = 0; kt < k_tiles; ++kt) {
+            for (int kt = SK2_STAGES; kt < k_tiles; ++kt) {
                 const int s = kt % SK2_STAGES;
-                if (kt >= SK2_STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / SK2_STAGES) - 1) & 1u)) { failed = true; break; }
+                if (!tc_mbar_wait(empty + s, (uint32_t)((kt / SK2_STAGES) - 1) & 1u)) { failed = true; break; }
                 unsigned char* dst = smem + s * STAGE;
                 tc_mbar_expect_tx(full + s, SK2_A_BYTES + B_BYTES);
                 tc_tma_load_2d(dst, &map_w, (kt0 + kt) * SK2_BK, n0, full + s);
@@ -599,10 +607,19 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int n0 = blockIdx.x * SKG_ROWS;
     const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
 
+    auto load_stage = [&](int kt) {
+        const int s = kt % STAGES;
+        unsigned char* dst = smem + s * STAGE;
+        tc_mbar_expect_tx(full + s, SK2_A_BYTES + G::B_BYTES);
+        tc_tma_load_2d(dst, &map_w, kt * SK2_BK, n0, full + s);                           // 64 gate rows
+        tc_tma_load_2d(dst + SK2_A_BYTES / 2, &map_w, kt * SK2_BK, n + n0, full + s);     // the same outputs' up rows
+        tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, kt * SK2_BK, 0, full + s);
+    };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
         tc_mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_stage(kt);        // on their way while TMEM is allocated
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
@@ -616,14 +633,9 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
 
     if (warp == 0) {
         if (lane == 0) {
-            for (int kt = 0; kt < k_tiles; ++kt) {
-                const int s = kt % STAGES;
-                if (kt >= STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / STAGES) - 1) & 1u)) { failed = true; break; }
-                unsigned char* dst = smem + s * STAGE;
-                tc_mbar_expect_tx(full + s, SK2_A_BYTES + G::B_BYTES);
-                tc_tma_load_2d(dst, &map_w, kt * SK2_BK, n0, full + s);                           // 64 gate rows
-                tc_tma_load_2d(dst + SK2_A_BYTES / 2, &map_w, kt * SK2_BK, n + n0, full + s);     // the same outputs' up rows
-                tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, kt * SK2_BK, 0, full + s);
+            for (int kt = STAGES; kt < k_tiles; ++kt) {
+                if (!tc_mbar_wait(empty + kt % STAGES, (uint32_t)((kt / STAGES) - 1) & 1u)) { failed = true; break; }
+                load_stage(kt);
             }
         }
     } else if (warp == 1) {
