@@ -50,6 +50,7 @@ struct AttMmaParams {
     int window, split, slots;
     int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
     int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
+    int relative;              // 1: slots are counted from the tile's first visible key (every tile is one token), else from key 0
     float scale, cap;
 };
 
@@ -263,8 +264,11 @@ __device__ __forceinline__ AmTile am_tile_info(const AttMmaParams& p, int tile, 
     x.klo = (p.window > 0 && x.c_first > p.window) ? x.c_first - p.window : 0;
     x.khi = x.c_first > 0 ? x.c_first + x.nq - 1 : 0;       // a padding row sees nothing
     if (p.split > 0) {
-        x.klo = max(x.klo, slot * p.split);
-        x.khi = min(x.khi, (slot + 1) * p.split);
+        // Counted from the window's start, a windowed row's keys fill whole slots: window / split of
+        // them, not one more with a sliver at each end.
+        const int base = p.relative ? x.klo : 0;
+        x.klo = max(x.klo, base + slot * p.split);
+        x.khi = min(x.khi, base + (slot + 1) * p.split);
     }
     return x;
 }
@@ -771,7 +775,8 @@ attention_mma_combine_kernel(const AttMmaParams p) {
         return;
     }
     const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
-    const int z0 = first / p.split, z1 = min(p.slots - 1, (count - 1) / p.split);
+    const int origin = p.relative ? first : 0;
+    const int z0 = (first - origin) / p.split, z1 = min(p.slots - 1, (count - 1 - origin) / p.split);
     const int nz = z1 - z0 + 1;
     if (nz == 1 && p.direct) return;
     const int stride = p.d + 2;
@@ -901,7 +906,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
                                 const int* block_table, const int* row_count, const int* tile_entry,
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
                                 int page_size, int table_width, int n_pages, int window, int split, int slots,
-                                float scale, float cap, int decode, float* scratch, void* stream) {
+                                float scale, float cap, int decode, int relative, float* scratch, void* stream) {
     // decode: 0 for prompt portions; else the most rows (tokens x query heads of a kv head) any tile
     // holds, at most 16.
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_mma: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
@@ -914,6 +919,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
                "attention_mma: split %d (a multiple of %d) with %d slots (at most 8192)", split, AM_KT, slots);
     KB_REQUIRE(!(decode && split == 0 && slots != 1), "attention_mma: decode mode without a split has one slot");
     KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_mma: %d slots need scratch memory", slots);
+    KB_REQUIRE(relative == 0 || relative == 1, "attention_mma: relative %d (0 or 1: slots counted from each tile's first visible key, for tiles of one token)", relative);
     KB_REQUIRE(hkv <= 65535, "attention_mma: %d kv heads is too many for one launch", hkv);
     if (rows == 0 || tiles == 0) return 0;
     AttMmaParams p;
@@ -924,6 +930,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.n_pages = n_pages; p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
     p.decode_bar_offset = 0;
     p.direct = decode ? 0 : 1;
+    p.relative = (decode && relative) ? 1 : 0;
     cudaStream_t s = (cudaStream_t)stream;
     int e;
     if (d <= 64) e = decode ? launch_decode<64>(p, tiles, decode, s) : launch_prompt<64>(p, tiles, s);

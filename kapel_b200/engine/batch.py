@@ -34,10 +34,11 @@ def _chunks_touched(row_count: np.ndarray, window: Optional[int], chunk: int) ->
 SPLIT_STEP = 64          # splits are multiples of the kernels' key tile
 
 
-def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = None):
+def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = None, relative: bool = False):
     """(split, slots) of the decode attention kernel, which runs one block a multiprocessor.
-    Keys are cut at absolute multiples of `split`; `slots` covers the longest request
-    (`longest` positions). A row reads at most `window` keys, so only about window / split of the
+    Keys are cut at multiples of `split`, counted from key 0 (`slots` then covers the longest
+    request, `longest` positions) or, with `relative`, from each row's first visible key (`slots`
+    covers what a row can see). A row reads at most `window` keys, so only about window / split of the
     slots do work. The split is chosen so that the working blocks (`pairs` (tile, kv head)
     pairs times working slots) take as little time as possible: waves of blocks times the keys a
     block walks plus what a block costs to start and to merge (about 192 keys' worth)."""
@@ -47,12 +48,12 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
     most = max(1, -(-span // SPLIT_STEP))
     for want in range(1, min(most, 4 * sms) + 1):
         split = max(SPLIT_STEP, -(-(-(-span // want)) // SPLIT_STEP) * SPLIT_STEP)
-        working = -(-span // split) + (1 if (window and longest > window) else 0)
+        working = -(-span // split) + (1 if (window and longest > window and not relative) else 0)
         cost = -(-(pairs * working) // sms) * (split + 192)
         if best is None or cost < best[0]:
             best = (cost, split)
     split = best[1]
-    return split, max(1, -(-longest // split))
+    return split, max(1, -(-(span if relative else longest) // split))
 
 
 # What a block costs beyond its 64-key steps, what the merge of partial sums costs beyond its traffic
@@ -170,7 +171,9 @@ class StepBatch:
         tile_nq) on the device, split, slots). `decode` is the most rows (tokens x query heads of a
         kv head) of any request when that is at most 16, which selects the decode kernel, else 0.
         The keys are split across blocks when the tiles alone are too few to fill the GPU;
-        `prompt_kernel` names the kernel whose costs decide that for prompt portions."""
+        `prompt_kernel` names the kernel whose costs decide that for prompt portions. A fifth
+        value says whether the slots are counted from each row's first visible key (every
+        request brings one token) or from key 0."""
         key = ("tiles", heads_per_kv, kv_heads, window, head_dim, prompt_kernel)
         if key not in self.memo:
             from .. import kernels as K
@@ -185,14 +188,15 @@ class StepBatch:
             dev = host.to(self.ids.device, non_blocking=True)
             tiles = (dev[:n], dev[n : 2 * n], dev[2 * n :])
             longest = int(plan.row_count.max())
+            relative = bool(decode) and int(plan.q_len.max()) == 1
             if decode:
-                split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window)
+                split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window, relative)
             else:
                 firsts = plan.row_count[arrays[1]]
                 split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,
                                             plan.rows, heads_per_kv * kv_heads, head_dim, prompt_kernel)
-            self.memo[key] = (decode, tiles, split, slots, host)
-        return self.memo[key][:4]
+            self.memo[key] = (decode, tiles, split, slots, relative, host)
+        return self.memo[key][:5]
 
     def attention_slots(self, window: Optional[int]) -> int:
         """Chunk slots the row-wise attention kernel needs for a layer with this window."""

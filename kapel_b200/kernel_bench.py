@@ -149,10 +149,10 @@ def main(argv=None) -> int:
         q_start, q_len = np.arange(B, dtype=np.int32), np.ones(B, np.int32)
         per_tile = max(1, K.attention_mma_rows(True) // (Hq // Hkv))
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(q_start, q_len, per_tile))
-        split, slots = decode_split(B * Hkv, ctx + 1, sm_count(dev), window)
+        split, slots = decode_split(B * Hkv, ctx + 1, sm_count(dev), window, True)
         seen = min(ctx + 1, window) if window else ctx + 1
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
-                                                   Hq // Hkv, split, slots), args.iters)
+                                                   Hq // Hkv, split, slots, True), args.iters)
         report(f"{name} split={split}x{slots}", us, B * seen * Hkv * D * 2 * 2)
 
     decode_case(None)

@@ -425,12 +425,15 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
 
 
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
-                        scale: float, softcap: Optional[float], decode: int, split: int, slots: int) -> torch.Tensor:
+                        scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
+                        relative: bool = False) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
     one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
     (tokens x query heads of a kv head) any tile holds, at most 16. `split` > 0 cuts the keys at
-    absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split))."""
+    absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split)). With
+    `relative` (decode mode, every tile one token) the multiples are counted from each row's first
+    visible key, so a windowed row needs ceil(window / split) slots however long its history."""
     rows, hq, d = q.shape
     _need(q, "attention q", torch.bfloat16)
     _need(k_table, "attention k table", torch.bfloat16)
@@ -463,7 +466,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
         lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                              _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
                              int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                             _f(softcap or 0.0), int(decode), _ptr(scratch), _stream())
+                             _f(softcap or 0.0), int(decode), int(bool(relative) and bool(decode)), _ptr(scratch), _stream())
     )
     return out
 

@@ -390,7 +390,7 @@ def test_sample_temperature_follows_plain_rule_and_probabilities():
 
 
 # ------------------------------------------------------------------------------------------
-def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split):
+def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split, relative=False):
     from kapel_b200.engine.batch import cut_tiles
 
     hq, hkv = q.shape[1], kt.shape[1]
@@ -398,9 +398,13 @@ def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split):
     q_len = np.asarray(q_lens, np.int32)
     q_start = np.concatenate(([0], np.cumsum(q_len)[:-1])).astype(np.int32)
     tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(q_start, q_len, per_tile))
-    slots = max(1, -(-int(rc.max()) // split)) if split else 1
+    longest = int(rc.max())
+    if relative and window:
+        longest = min(longest, window)                  # slots counted from each row's first visible key
+    slots = max(1, -(-longest // split)) if split else 1
     rows = int(q_len.max()) * (hq // hkv) if decode else 0
-    return K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, window, scale, cap, rows, split, slots).cpu()
+    return K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, window, scale, cap, rows, split, slots,
+                                   relative).cpu()
 
 
 @pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 1, 64), (8, 4, 128), (8, 4, 256), (5, 1, 80)])
@@ -460,6 +464,23 @@ def test_paged_attention_mma_decode_mode(hq, hkv, d, window, cap, split):
     rc[0] = 0                      # a padding row: sees nothing, gives zeros
     scale = 1.0 / math.sqrt(d * 1.5)
     got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, True, split).double()
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
+    assert (got[0] == 0).all()
+    assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (16, 1, 64), (8, 4, 128), (8, 4, 256)])
+@pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0), (128, 50.0)])
+@pytest.mark.parametrize("split", [64, 128, 256])
+def test_paged_attention_decode_slots_counted_from_the_windows_start(hq, hkv, d, window, cap, split):
+    """One token a request: the key slots may be counted from each row's first visible key, so a
+    windowed row fills ceil(window / split) slots however long its history."""
+    lengths = [1, 37, 300, 700, 64, 65, 129, 428]
+    q_lens = [1] * len(lengths)
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d + 2)
+    rc[0] = 0                      # a padding row
+    scale = 1.0 / math.sqrt(d * 1.5)
+    got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, True, split, relative=True).double()
     want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
     assert (got[0] == 0).all()
     assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
