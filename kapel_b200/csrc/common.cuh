@@ -40,9 +40,19 @@ template <typename T> struct Src {
     const T* p;
     int splits;
     size_t stride;
+    // Eight slices are loaded before they are added, so that their latencies overlap; the order of
+    // the additions is the slices' order all the same.
     __device__ __forceinline__ float at(size_t i) const {
         float v = Elem<T>::load(p + i);
-        for (int s = 1; s < splits; ++s) v += Elem<T>::load(p + (size_t)s * stride + i);
+        int s = 1;
+        for (; s + 8 <= splits; s += 8) {
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = Elem<T>::load(p + (size_t)(s + j) * stride + i);
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v += t[j];
+        }
+        for (; s < splits; ++s) v += Elem<T>::load(p + (size_t)s * stride + i);
         return v;
     }
 };

@@ -192,6 +192,90 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
     }
 }
 
+// Float32 partial sums of a product split over K (few rows: a decode step), bfloat16 weights and
+// output, a width that is a multiple of four: a thread owns up to CPT groups of four components,
+// reads each slice's four with one 16-byte load, eight slices in flight, and adds them in slice
+// order. The rest is the register-resident kernel's.
+template <int CPT>
+__global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const float* __restrict__ parts, int splits, size_t stride,
+                                          const __nv_bfloat16* __restrict__ w_post, float eps_post, float off_post,
+                                          const __nv_bfloat16* __restrict__ w_next, float eps_next, float off_next,
+                                          __nv_bfloat16* __restrict__ h, int width) {
+    __shared__ float scratch[32];
+    const size_t base = (size_t)blockIdx.x * width;
+    const int chunks = width >> 2;
+    float4 b[CPT], r[CPT];
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        b[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        r[c] = b[c];
+        if (ci < chunks) {
+            const float* src = parts + base + ci * 4;
+            float4 v = *reinterpret_cast<const float4*>(src);
+            int s = 1;
+            for (; s + 8 <= splits; s += 8) {
+                float4 t[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) t[j] = *reinterpret_cast<const float4*>(src + (size_t)(s + j) * stride);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
+            }
+            for (; s < splits; ++s) {
+                const float4 t = *reinterpret_cast<const float4*>(src + (size_t)s * stride);
+                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            }
+            b[c] = v;
+            r[c] = *reinterpret_cast<const float4*>(residual + base + ci * 4);
+            ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
+        }
+    }
+    float inv = 1.f;
+    if (w_post != nullptr) {
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            if (w_post != nullptr) {
+                const uint2 uw = *reinterpret_cast<const uint2*>(w_post + ci * 4);
+                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.x));
+                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.y));
+                r[c].x += b[c].x * inv * (off_post + w0.x);
+                r[c].y += b[c].y * inv * (off_post + w0.y);
+                r[c].z += b[c].z * inv * (off_post + w1.x);
+                r[c].w += b[c].w * inv * (off_post + w1.y);
+            } else {
+                r[c].x += b[c].x; r[c].y += b[c].y; r[c].z += b[c].z; r[c].w += b[c].w;
+            }
+            ss2 += r[c].x * r[c].x + r[c].y * r[c].y + r[c].z * r[c].z + r[c].w * r[c].w;
+            *reinterpret_cast<float4*>(residual + base + ci * 4) = r[c];
+        }
+    }
+    if (w_next == nullptr) return;
+    ss2 = block_sum(ss2, scratch);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            const uint2 uw = *reinterpret_cast<const uint2*>(w_next + ci * 4);
+            const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.x));
+            const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.y));
+            uint2 uo;
+            __nv_bfloat162 o0 = __floats2bfloat162_rn(r[c].x * inv2 * (off_next + w0.x), r[c].y * inv2 * (off_next + w0.y));
+            __nv_bfloat162 o1 = __floats2bfloat162_rn(r[c].z * inv2 * (off_next + w1.x), r[c].w * inv2 * (off_next + w1.y));
+            uo.x = *reinterpret_cast<uint32_t*>(&o0);
+            uo.y = *reinterpret_cast<uint32_t*>(&o1);
+            *reinterpret_cast<uint2*>(h + base + ci * 4) = uo;
+        }
+    }
+}
+
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
 
 }  // namespace kb
@@ -256,6 +340,20 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         if (cpt == 1) add_rmsnorm_bf16x8_kernel<1><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
         else if (cpt == 2) add_rmsnorm_bf16x8_kernel<2><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
         else add_rmsnorm_bf16x8_kernel<4><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        return check_launch("add_rmsnorm");
+    }
+    // float32 partial sums of few rows (a decode step): the kernel that keeps many slices in flight
+    if (branch_dt == KB_DT_F32 && w_dt == KB_DT_BF16 && h_dt == KB_DT_BF16 && rows <= 256 && width % 4 == 0 && width <= 4 * 4 * 1024 &&
+        (split_stride % 4) == 0 && (((uintptr_t)residual | (uintptr_t)branch | (uintptr_t)h) & 15) == 0 &&
+        (((uintptr_t)w_post | (uintptr_t)w_next) & 7) == 0) {
+        const int chunks = width / 4;
+        const int cpt = chunks <= 1024 ? 1 : (chunks <= 2048 ? 2 : 4);
+        const int tv = min(1024, ((chunks + cpt - 1) / cpt + 31) / 32 * 32);
+        const float* b = (const float*)branch;
+        const bf16 *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
+        if (cpt == 1) add_rmsnorm_splits_kernel<1><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        else if (cpt == 2) add_rmsnorm_splits_kernel<2><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        else add_rmsnorm_splits_kernel<4><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
         return check_launch("add_rmsnorm");
     }
     switch (code) {

@@ -123,6 +123,13 @@ def main(argv=None) -> int:
             w1, w2 = torch.randn(H, device=dev).to(bf), torch.randn(H, device=dev).to(bf)
             us = _time(lambda i: K.add_rmsnorm(res, br, (w1, 1e-6, 1.0), (w2, 1e-6, 1.0), bf), args.iters)
             report(f"add_rmsnorm {tag} [{m}x{H}]", us, m * H * (4 + 4 + 2 + 2))
+        if m <= 64 and want(f"add_rmsnorm {tag} of partial sums"):
+            for splits in (8, 16):                           # what the o and down products of a decode step leave
+                res = torch.randn(m, H, device=dev)
+                parts = K.SplitSum(torch.randn(splits, m, H, device=dev))
+                w1, w2 = torch.randn(H, device=dev).to(bf), torch.randn(H, device=dev).to(bf)
+                us = _time(lambda i: K.add_rmsnorm(res, parts, (w1, 1e-6, 1.0), (w2, 1e-6, 1.0), bf), args.iters)
+                report(f"add_rmsnorm {tag} of partial sums [{splits}x{m}x{H}]", us, m * H * (4 * splits + 4 + 4 + 2))
         if want(f"glu {tag}"):
             x = torch.randn(m, 2 * I, device=dev).to(bf)
             us = _time(lambda i: K.glu(x, "gelu_tanh"), args.iters)
@@ -187,6 +194,10 @@ def main(argv=None) -> int:
             lines = torch.arange(m, dtype=torch.int32, device=dev)
             us = _time(lambda i: K.rope_append(qkv, cs, lines, tables[0][0], tables[0][1], Hq, Hkv, D, D), args.iters)
             report(f"rope_append {tag} [{m}]", us, m * (Hq + 2 * Hkv) * D * 4)
+            if m <= 64:                                      # as a decode step has it: the q|k|v product's partial sums
+                parts = K.SplitSum(torch.randn(9, m, (Hq + 2 * Hkv) * D, device=dev))
+                us = _time(lambda i: K.rope_append(parts, cs, lines, tables[0][0], tables[0][1], Hq, Hkv, D, D, out_dtype=bf), args.iters)
+                report(f"rope_append {tag} of partial sums [9x{m}]", us, m * (Hq + 2 * Hkv) * D * (4 * 9 + 2))
     return 0
 
 
