@@ -14,6 +14,8 @@ int fail(const char* fmt, ...) {
 }
 
 static unsigned long long g_launches = 0;
+static bool g_pdl = false;
+bool pdl_enabled() { return g_pdl; }
 
 int check_launch(const char* what) {
     ++g_launches;                         // every kernel launch of this library passes here once
@@ -28,6 +30,9 @@ extern "C" const char* kb_last_error() { return kb::g_error; }
 
 // Kernels this library has launched (or recorded into a graph under capture) so far.
 extern "C" unsigned long long kb_launch_count() { return kb::g_launches; }
+
+// 1: the kernels of a decode step are launched as programmatic dependents of one another.
+extern "C" void kb_set_pdl(int on) { kb::g_pdl = on != 0; }
 
 // The compute capability this library was built for, as major * 10 + minor.
 extern "C" int kb_built_for() { return 100; }

@@ -569,6 +569,8 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     uint64_t* bars = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + warp * AD_STAGES;
 
     const int kvh = blockIdx.y, slot = blockIdx.z;
+    dependent_wait();                                       // the queries and the newest keys are the kernel before's
+    dependent_trigger();
     const AmTile x = am_tile_info(p, blockIdx.x, slot);
     const int group = x.group, row0 = x.row0, rows_valid = x.rows_valid, klo = x.klo, khi = x.khi;
     if (klo >= khi) {                                       // nothing here: the merge kernel skips this slot
@@ -768,6 +770,8 @@ __global__ void __launch_bounds__(128)
 attention_mma_combine_kernel(const AttMmaParams p) {
     extern __shared__ float cw[];                           // [slots] weights
     const int row = blockIdx.x, head = blockIdx.y;
+    dependent_wait();
+    dependent_trigger();
     const int count = p.row_count[row];
     bf16* o = p.out + ((size_t)row * p.hq + head) * p.d;
     if (count <= 0) {
@@ -860,7 +864,7 @@ static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStr
     do {                                                                                                                       \
         if (smem > 48 * 1024)                                                                                                  \
             cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        attention_decode_kernel<HD, NB, FULL><<<grid, AM_THREADS, smem, s>>>(q, map_k, map_v);                                 \
+        launch_dependent(attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v);     \
     } while (0)
     if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true); else KB_DECODE(1, false); }
     else               { if (p.d == HD) KB_DECODE(2, true); else KB_DECODE(2, false); }
@@ -939,7 +943,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     if (e) return e;
     if (slots > 1) {
         dim3 grid(rows, hq);
-        attention_mma_combine_kernel<<<grid, 128, (size_t)slots * sizeof(float), s>>>(p);
+        launch_dependent(attention_mma_combine_kernel, grid, dim3(128), (size_t)slots * sizeof(float), s, p);
         return check_launch("attention_mma combine");
     }
     return 0;

@@ -19,6 +19,31 @@ namespace kb {
 int fail(const char* fmt, ...);          // stores the message, returns 1
 int check_launch(const char* what);      // cudaGetLastError -> fail(...)
 
+// Programmatic dependent launch. A kernel started through `launch_dependent` may begin while the
+// kernel before it on the stream still runs: it must call `dependent_wait()` before it reads what
+// that kernel wrote or writes anything at all, and it lets the kernel after it begin once all its
+// blocks have called `dependent_trigger()` (or ended). What does not depend on the kernel before
+// (barriers, TMEM, the first tiles of weights) goes ahead of the wait. Off unless `kb_set_pdl(1)`.
+bool pdl_enabled();
+template <typename... KArgs, typename... Args>
+inline void launch_dependent(void (*kernel)(KArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream, Args... args) {
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = grid;
+    cfg.blockDim = block;
+    cfg.dynamicSmemBytes = smem;
+    cfg.stream = stream;
+    cudaLaunchAttribute attr[1];
+    attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attr[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = attr;
+    cfg.numAttrs = pdl_enabled() ? 1 : 0;
+    cudaLaunchKernelEx(&cfg, kernel, static_cast<KArgs>(args)...);      // the caller checks with check_launch
+}
+#ifdef __CUDACC__
+__device__ __forceinline__ void dependent_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void dependent_trigger() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+#endif
+
 #define KB_REQUIRE(cond, ...)                 \
     do {                                      \
         if (!(cond)) return kb::fail(__VA_ARGS__); \

@@ -476,16 +476,20 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
         // The first stages are asked for at once, before the block meets: the copies are on their
         // way while TMEM is allocated. This thread made the barriers, so it may use them already.
+        // The weights do not depend on the kernel before this one: they are asked for ahead of the wait.
         for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt) {
-            unsigned char* dst = smem + kt * STAGE;
             tc_mbar_expect_tx(full + kt, SK2_A_BYTES + B_BYTES);
-            tc_tma_load_2d(dst, &map_w, (kt0 + kt) * SK2_BK, n0, full + kt);
-            tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + kt);
+            tc_tma_load_2d(smem + kt * STAGE, &map_w, (kt0 + kt) * SK2_BK, n0, full + kt);
         }
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
+    }
+    dependent_wait();                                       // the activations are the kernel before's to finish
+    if (threadIdx.x == 0) {
+        for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt)
+            tc_tma_load_2d(smem + kt * STAGE + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + kt);
     }
     tc_fence_before();
     __syncthreads();
@@ -504,6 +508,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
                 tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + s);
             }
         }
+        dependent_trigger();                                // everything this block reads has been asked for
     } else if (warp == 1) {
         if (lane == 0) {
             for (int kt = 0; kt < k_tiles; ++kt) {
@@ -524,9 +529,12 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             }
             if (!failed) tc_commit(accum);
         }
+        dependent_trigger();
     } else {
         const int quarter = warp & 3;
-        if (!__all_sync(0xffffffffu, tc_mbar_wait(accum, 0u))) {
+        const bool complete = __all_sync(0xffffffffu, tc_mbar_wait(accum, 0u));
+        dependent_trigger();
+        if (!complete) {
             failed = true;
         } else {
             tc_fence_after();
@@ -607,24 +615,28 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int n0 = blockIdx.x * SKG_ROWS;
     const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
 
-    auto load_stage = [&](int kt) {
+    auto load_weights = [&](int kt) {
         const int s = kt % STAGES;
         unsigned char* dst = smem + s * STAGE;
         tc_mbar_expect_tx(full + s, SK2_A_BYTES + G::B_BYTES);
         tc_tma_load_2d(dst, &map_w, kt * SK2_BK, n0, full + s);                           // 64 gate rows
         tc_tma_load_2d(dst + SK2_A_BYTES / 2, &map_w, kt * SK2_BK, n + n0, full + s);     // the same outputs' up rows
-        tc_tma_load_2d(dst + SK2_A_BYTES, &map_x, kt * SK2_BK, 0, full + s);
     };
+    auto load_rows = [&](int kt) { tc_tma_load_2d(smem + (kt % STAGES) * STAGE + SK2_A_BYTES, &map_x, kt * SK2_BK, 0, full + kt % STAGES); };
+    auto load_stage = [&](int kt) { load_weights(kt); load_rows(kt); };
     if (threadIdx.x == 0) {
         for (int s = 0; s < STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
         tc_mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_stage(kt);        // on their way while TMEM is allocated
+        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_weights(kt);      // on their way ahead of the wait
     }
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
+    dependent_wait();
+    if (threadIdx.x == 0)
+        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_rows(kt);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
@@ -638,6 +650,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
                 load_stage(kt);
             }
         }
+        dependent_trigger();
     } else if (warp == 1) {
         if (lane == 0) {
             for (int kt = 0; kt < k_tiles; ++kt) {
@@ -658,9 +671,11 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             }
             if (!failed) tc_commit(accum);
         }
+        dependent_trigger();
     } else {
         const int quarter = warp & 3;                       // TMEM lanes 32 quarter ..: 0, 1 gates; 2, 3 ups
         const bool ok = __all_sync(0xffffffffu, tc_mbar_wait(accum, 0u));
+        dependent_trigger();
         if (!ok) failed = true;
         const int f = (quarter & 1) * 32 + lane;            // the output within the block's 64
         float v[NP];
@@ -707,7 +722,7 @@ static int launch_skinny_glu(const CUtensorMap& map_w, const CUtensorMap& map_x,
         if (e != cudaSuccess) return fail("gemm_skinny_glu: cannot have %d bytes of shared memory: %s", SkGlu<NP>::SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    gemm_skinny_glu_kernel<NP><<<(n + SKG_ROWS - 1) / SKG_ROWS, TC_THREADS, SkGlu<NP>::SMEM, s>>>(map_w, map_x, c, m, n, k, act);
+    launch_dependent(gemm_skinny_glu_kernel<NP>, dim3((n + SKG_ROWS - 1) / SKG_ROWS), dim3(TC_THREADS), (size_t)SkGlu<NP>::SMEM, s, map_w, map_x, c, m, n, k, act);
     return check_launch("gemm_skinny_glu");
 }
 
@@ -749,7 +764,7 @@ static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
         attr_set = true;
     }
     dim3 grid((n + SK2_BM - 1) / SK2_BM, splits);
-    gemm_skinny_tcgen05_kernel<NP><<<grid, TC_THREADS, SMEM, s>>>(map_w, map_x, c, c_dt, splits > 1 ? partial : nullptr, m, n, k, per, epi, cap);
+    launch_dependent(gemm_skinny_tcgen05_kernel<NP>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map_w, map_x, c, c_dt, splits > 1 ? partial : (float*)nullptr, m, n, k, per, epi, cap);
     return check_launch("gemm_skinny_tcgen05");
 }
 

@@ -204,6 +204,8 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * width;
     const int chunks = width >> 2;
+    dependent_wait();
+    dependent_trigger();                                    // a few blocks with little to read: the next kernel may set up
     float4 b[CPT], r[CPT];
     float ss = 0.f;
 #pragma unroll
@@ -351,9 +353,11 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const int tv = min(1024, ((chunks + cpt - 1) / cpt + 31) / 32 * 32);
         const float* b = (const float*)branch;
         const bf16 *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
-        if (cpt == 1) add_rmsnorm_splits_kernel<1><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
-        else if (cpt == 2) add_rmsnorm_splits_kernel<2><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
-        else add_rmsnorm_splits_kernel<4><<<rows, tv, 0, s>>>(residual, b, splits, (size_t)split_stride, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        const size_t stride = (size_t)split_stride;
+        bf16* out = (bf16*)h;
+        if (cpt == 1) launch_dependent(add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else if (cpt == 2) launch_dependent(add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else launch_dependent(add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
         return check_launch("add_rmsnorm");
     }
     switch (code) {

@@ -36,6 +36,9 @@ GEMM_SMALL = _os.environ.get("KAPEL_B200_GEMM_SMALL", "skinny")
 # tcgen05.mma, scores and probabilities in tensor memory) or "mma" (the mma.sync flash kernel, which
 # also takes what the first does not: no soft cap, other head sizes).
 ATTENTION_PROMPT = _os.environ.get("KAPEL_B200_ATTENTION_PROMPT", "tcgen05")
+# Whether the kernels of a decode step are launched as programmatic dependents of one another, so
+# that a kernel sets up (and asks for its first weights) while the one before it finishes.
+PDL = _os.environ.get("KAPEL_B200_PDL", "1") == "1"
 
 
 class KernelError(RuntimeError):
@@ -56,6 +59,7 @@ def library():
                 for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
+                lib.kb_set_pdl(1 if PDL else 0)
                 _lib = lib
     return _lib
 
