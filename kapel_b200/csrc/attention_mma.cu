@@ -569,11 +569,12 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     uint64_t* bars = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + warp * AD_STAGES;
 
     const int kvh = blockIdx.y, slot = blockIdx.z;
-    dependent_wait();                                       // the queries and the newest keys are the kernel before's
-    dependent_trigger();
+    // Counts, tiles and block tables were copied in before the step began: they may be read ahead of
+    // the wait on the kernel before this one, whose work the queries and the newest keys are.
     const AmTile x = am_tile_info(p, blockIdx.x, slot);
     const int group = x.group, row0 = x.row0, rows_valid = x.rows_valid, klo = x.klo, khi = x.khi;
     if (klo >= khi) {                                       // nothing here: the merge kernel skips this slot
+        dependent_wait();
         if (p.slots == 1 && x.c_first <= 0)                 // a padding row without a merge kernel: zeros
             for (int i = tid; i < rows_valid * d; i += AM_THREADS) {
                 const int r = i / d, c = i % d;
@@ -589,16 +590,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
         for (int s = 0; s < AD_STAGES; ++s) am_mbar_init(bars + s, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
-    const int chunks = d / 8;
-    for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
-        const int r = i / chunks, ch = i % chunks;
-        const bool valid = r < rows_valid;
-        const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
-        am_cp_async16(sQ + r * ld + ch * 8, src, valid);
-    }
-    am_commit();
-    __syncthreads();                                        // every warp's barriers are initialised
-
+    __syncwarp();                                           // a warp's barriers are its own
     // A tile is 16 consecutive positions from a multiple of 16: with pages of a multiple of 16
     // positions it lies in one page, where the kv head's rows are consecutive. Lane i < nbox asks
     // TMA for box i of the keys, lane nbox + i for box i of the values. A tile whose page the
@@ -636,9 +628,27 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
         }
     };
     fetch_pages(0);
+    // The kernel before this one wrote the newest key of every row and nothing older: a first tile
+    // that ends below the first row's last position is asked for ahead of the wait.
+    bool early[AD_STAGES];
+#pragma unroll
+    for (int s = 0; s < AD_STAGES; ++s) {
+        early[s] = warp + 4 * s < n_tiles && k_begin + (warp + 4 * s) * AD_WK + AD_WK < x.c_first;
+        if (early[s]) load_tile(s, s);
+    }
+    dependent_wait();
+    dependent_trigger();
+    const int chunks = d / 8;
+    for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
+        const int r = i / chunks, ch = i % chunks;
+        const bool valid = r < rows_valid;
+        const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
+        am_cp_async16(sQ + r * ld + ch * 8, src, valid);
+    }
+    am_commit();
 #pragma unroll
     for (int s = 0; s < AD_STAGES; ++s)
-        if (warp + 4 * s < n_tiles) load_tile(s, s);
+        if (!early[s] && warp + 4 * s < n_tiles) load_tile(s, s);
     am_wait<0>();                                           // this thread's part of Q has landed
     __syncthreads();                                        // and everyone else's
 
