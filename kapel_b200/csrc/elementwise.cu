@@ -106,6 +106,8 @@ __global__ void rope_append_bf16x8_kernel(const __nv_bfloat16* __restrict__ qkv,
     const int heads = hq + 2 * hkv;
     const long long total = (long long)rows * heads * cpr;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    dependent_wait();
+    dependent_trigger();
     if (idx >= total) return;
     const int c = (int)(idx % cpr);
     const int h = (int)((idx / cpr) % heads);
@@ -250,7 +252,7 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_table | (uintptr_t)v_table | (uintptr_t)cos_sin) & 15) == 0;
     if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16 && splits == 1 && rotary == d && d % 16 == 0 && aligned) {
         const long long vec = (long long)rows * (hq + 2 * hkv) * (d / 16);
-        rope_append_bf16x8_kernel<<<(unsigned)((vec + 255) / 256), 256, 0, s>>>(
+        launch_dependent(rope_append_bf16x8_kernel, dim3((unsigned)((vec + 255) / 256)), dim3(256), 0, s,
             (const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out, (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d,
             write_kv, table_lines, page_size > 0 ? page_size : 1);
     }

@@ -121,6 +121,8 @@ __global__ void add_rmsnorm_bf16x8_kernel(float* __restrict__ residual, const __
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * width;
     const int chunks = width >> 3;
+    dependent_wait();
+    dependent_trigger();
     float b[CPT][8], r[CPT][8];
     float ss = 0.f;
 #pragma unroll
@@ -339,9 +341,10 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const int cpt = chunks <= 1024 ? 1 : (chunks <= 2048 ? 2 : 4);
         const int tv = min(1024, ((chunks + cpt - 1) / cpt + 31) / 32 * 32);
         const bf16 *b = (const bf16*)branch, *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
-        if (cpt == 1) add_rmsnorm_bf16x8_kernel<1><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
-        else if (cpt == 2) add_rmsnorm_bf16x8_kernel<2><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
-        else add_rmsnorm_bf16x8_kernel<4><<<rows, tv, 0, s>>>(residual, b, wp, eps_post, off_post, wn, eps_next, off_next, (bf16*)h, width);
+        bf16* out = (bf16*)h;
+        if (cpt == 1) launch_dependent(add_rmsnorm_bf16x8_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else if (cpt == 2) launch_dependent(add_rmsnorm_bf16x8_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else launch_dependent(add_rmsnorm_bf16x8_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
         return check_launch("add_rmsnorm");
     }
     // float32 partial sums of few rows (a decode step): the kernel that keeps many slices in flight
