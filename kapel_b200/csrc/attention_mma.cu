@@ -3,7 +3,9 @@
 //
 // Kapel's counterparts: the cutile FlashAttention forward after a gather of the pages
 // (crates/kapel-cuda/src/attention.rs:107-247, crates/kapel-cuda/src/paged.rs:66-114) for prompts, and
-// paged_attention_16 (kernels/src/lib.rs:2949) for decoding. Here one kernel does both:
+// paged_attention_16 (kernels/src/lib.rs:2949) for decoding. Here one file does both (prompt
+// portions with a soft cap and a head size of 64, 128 or 256 go to the tcgen05 kernel of
+// attention_tc.cu instead; this file's prompt kernel takes the rest):
 //
 //  * a tile is up to MROWS rows of one request and one kv head; a row is (token, query head of
 //    the kv head's group), so the group shares every key and value it loads;
@@ -22,8 +24,11 @@
 //    the block leaves without writing;
 //  * score = scale * q.k, then cap * tanh(score / cap) (tanh.approx), then the mask: a row that
 //    has seen c positions reads keys [max(0, c - window), c);
-//  * with `split` > 0 the keys are also cut at absolute multiples of `split` across blockIdx.z;
-//    each block writes (sum p.v, max, sum p) to scratch memory and a second kernel merges them.
+//  * with `split` > 0 the keys are also cut at multiples of `split` across blocks (counted from
+//    key 0 or, when every tile is one token, from the row's first visible key); each block writes
+//    (sum p.v, max, sum p) to scratch memory and a second kernel merges them;
+//  * the decode kernel and the merge are launched as programmatic dependents: they wait for the
+//    kernel before them only where they first touch what it wrote.
 #include "common.cuh"
 #include "tensor_map.cuh"
 

@@ -1,10 +1,15 @@
 // C[M,N] = A[M,K] . W[N,K]^T for bfloat16 inputs on the fifth-generation tensor cores:
 // tcgen05.mma issued by one thread, operands staged in shared memory by TMA (cp.async.bulk.tensor,
 // 128-byte swizzle, no multicast), the 128 x 256 accumulator in tensor memory (TMEM), read back
-// with tcgen05.ld for the epilogue. Used for prompt portions (M > 64); Kapel's counterpart is the
-// cutile `batched_matmul_nt` (crates/kapel-cuda/src/tile.rs:65-87), which has no sm_100 path.
+// with tcgen05.ld for the epilogue. Kapel's counterpart is the cutile `batched_matmul_nt`
+// (crates/kapel-cuda/src/tile.rs:65-87), which has no sm_100 path. Four kernels, below in this order:
+// one block a 128 x 256 tile (products of about one tile a multiprocessor); persistent pairs of
+// blocks with cta_group::2 and two accumulators (all other products of more than 64 rows, also with
+// the gated unit in the epilogue); operands swapped for up to 64 rows, split over K; the same with
+// the gated unit. All are launched as programmatic dependents and wait for the kernel before them
+// only before they touch the activations.
 //
-// One block computes one 128 x 256 tile of C. Six warps:
+// The first: one block computes one 128 x 256 tile of C. Six warps:
 //   warp 0    one lane walks K in steps of 64 and asks TMA for the A and W tiles of each step, four
 //             stages deep (two, in each of two blocks a multiprocessor, for products of many
 //             tiles); a stage is free again when the MMAs that read it have completed
