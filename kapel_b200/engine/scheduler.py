@@ -159,6 +159,8 @@ class Scheduler:
     # ------------------------------------------------------------------ admission
     def _admit(self) -> List[Event]:
         events: List[Event] = []
+        if not self.waiting:                                # nobody to admit: nothing to count
+            return events
         n_groups = len(self.cache.groups)
         promised = [0] * n_groups
         for rid in self.running:
@@ -223,7 +225,7 @@ class Scheduler:
             # requests run, each with exactly its new token to feed.
             rids, handle = staged
             if rids == self.running and all(self._pending(r) == 1 for r in rids):
-                return self._finish_pass(events, [(r, 1) for r in rids], handle)
+                return self._finish_staged(events, rids, handle)
             self._discard(handle)
         while True:
             pass_ = self._plan()
@@ -245,7 +247,7 @@ class Scheduler:
             self._suspend_last()
         if not pass_:
             return events
-        return self._finish_pass(events, pass_, None)
+        return self._finish_pass(events, pass_)
 
     def _discard(self, handle) -> None:
         discard = getattr(self.engine, "discard", None)
@@ -267,31 +269,29 @@ class Scheduler:
         if handle is not None:
             self.staged = (list(self.running), handle)
 
-    def _finish_pass(self, events, pass_, handle) -> List[Event]:
-        producing = [rid for rid, count in pass_ if count == self._pending(rid)]
-        entries = []
-        for rid, count in pass_:
-            entry = self.entries[rid]
-            at = self._cached(rid)
-            tokens = entry.sequence[at : at + count]
-            entries.append(StepEntry(rid, tokens, [count - 1] if count == self._pending(rid) else []))
+    def _finish_staged(self, events, rids, handle) -> List[Event]:
+        """The staged pass: each request feeds its newest token and gets the next."""
         try:
-            if handle is not None:
-                logits = self.engine.step_prepared(handle, [e.tokens[0] for e in entries])
-                self.staged_passes += 1
-            else:
-                logits = self.engine.step(entries)
+            logits = self.engine.step_prepared(handle, [self.entries[r].sequence[-1] for r in rids])
+            self.staged_passes += 1
             self.passes += 1
-            self._stage_next(pass_, producing)
-            tokens = self._choose(logits, producing)
+            pass_ = [(r, 1) for r in rids]
+            self._stage_next(pass_, rids)
+            tokens = self._choose(logits, rids)
         except Exception as e:                      # the pass failed: every running request ends
-            staged, self.staged = self.staged, None
-            if staged is not None:
-                self._discard(staged[1])
-            for rid in list(self.running):
-                self.cancel(rid)
-                events.append(Event(rid, None, "error", f"{type(e).__name__}: {e}"))
-            return events
+            return self._fail_pass(events, e)
+        return self._give(events, rids, tokens)
+
+    def _fail_pass(self, events, e) -> List[Event]:
+        staged, self.staged = self.staged, None
+        if staged is not None:
+            self._discard(staged[1])
+        for rid in list(self.running):
+            self.cancel(rid)
+            events.append(Event(rid, None, "error", f"{type(e).__name__}: {e}"))
+        return events
+
+    def _give(self, events, producing, tokens) -> List[Event]:
         for rid, token in zip(producing, tokens):
             entry = self.entries[rid]
             entry.sequence.append(int(token))
@@ -301,6 +301,23 @@ class Scheduler:
             if finish is not None:
                 self.cancel(rid)
         return events
+
+    def _finish_pass(self, events, pass_) -> List[Event]:
+        producing = [rid for rid, count in pass_ if count == self._pending(rid)]
+        entries = []
+        for rid, count in pass_:
+            entry = self.entries[rid]
+            at = self._cached(rid)
+            tokens = entry.sequence[at : at + count]
+            entries.append(StepEntry(rid, tokens, [count - 1] if count == self._pending(rid) else []))
+        try:
+            logits = self.engine.step(entries)
+            self.passes += 1
+            self._stage_next(pass_, producing)
+            tokens = self._choose(logits, producing)
+        except Exception as e:                      # the pass failed: every running request ends
+            return self._fail_pass(events, e)
+        return self._give(events, producing, tokens)
 
     def _finish_reason(self, entry: _Entry, token: int) -> Optional[str]:
         req = entry.request
