@@ -73,3 +73,33 @@ def test_real_layer_sizes(case, dtype):
     print(f"{name} {dtype}: worst {worst:.2e}")
     engine.cache.check()
     assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+def test_decoding_twice_gives_the_same_bits(case):
+    """Eight requests decoded 48 steps through recorded passes, twice over: every logit of every
+    step is the same bit for bit. Kernels of a step start while the ones before them finish
+    (programmatic dependent launch); one that read too early would show here sooner or later."""
+    import torch
+
+    from kapel_b200.engine import Engine, StepEntry
+
+    name, raw, folder, reqs, _ = case
+    if name != "2b":
+        pytest.skip("one size is enough for this")
+    rng = np.random.default_rng(5)
+    prompts = [random_tokens(rng, 30 + 7 * i, raw["vocab_size"]) for i in range(8)]
+
+    def run():
+        engine = Engine.from_dir(folder, dtype="bfloat16", max_tokens=2048, max_sequences=8)
+        logits = engine.step([StepEntry(i, p, [len(p) - 1]) for i, p in enumerate(prompts)])
+        rows = [logits.clone()]
+        for _ in range(48):
+            tokens = logits.argmax(dim=-1).tolist()
+            logits = engine.step([StepEntry(i, [t], [0]) for i, t in enumerate(tokens)])
+            rows.append(logits.clone())
+        assert engine.recorded_passes >= 40
+        engine.check()
+        return torch.stack(rows)
+
+    first, second = run(), run()
+    assert torch.equal(first, second)
