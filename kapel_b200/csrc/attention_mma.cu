@@ -829,6 +829,67 @@ attention_mma_combine_kernel(const AttMmaParams p) {
     }
 }
 
+
+// The same with one warp a (row, head), four to a block, for the tens of thousands of pairs of a
+// prompt, where a block each would be bound by the rate at which blocks can be started.
+constexpr int AC_WARPS = 4;
+__global__ void __launch_bounds__(AC_WARPS * 32)
+attention_mma_combine_warp_kernel(const AttMmaParams p) {
+    extern __shared__ float cw_all[];                       // [AC_WARPS][slots] weights
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const long long pair = (long long)blockIdx.x * AC_WARPS + warp;
+    dependent_wait();
+    dependent_trigger();
+    if (pair >= (long long)p.rows * p.hq) return;
+    const int row = (int)(pair / p.hq), head = (int)(pair % p.hq);
+    float* cw = cw_all + warp * p.slots;
+    const int count = p.row_count[row];
+    bf16* o = p.out + ((size_t)row * p.hq + head) * p.d;
+    if (count <= 0) {
+        for (int i = lane; i < p.d; i += 32) o[i] = __float2bfloat16_rn(0.f);
+        return;
+    }
+    const int first = (p.window > 0 && count > p.window) ? count - p.window : 0;
+    const int origin = p.relative ? first : 0;
+    const int z0 = (first - origin) / p.split, z1 = min(p.slots - 1, (count - 1 - origin) / p.split);
+    const int nz = z1 - z0 + 1;
+    if (nz == 1 && p.direct) return;
+    const int stride = p.d + 2;
+    const float* base = p.partial + (((size_t)row * p.hq + head) * p.slots + z0) * stride;
+    float mx = -INFINITY;
+    for (int z = lane; z < nz; z += 32) mx = fmaxf(mx, base[(size_t)z * stride + p.d]);
+    mx = warp_max(mx);
+    float denom = 0.f;
+    for (int z = lane; z < nz; z += 32) {
+        const float m = base[(size_t)z * stride + p.d];
+        const float w = (m == -INFINITY) ? 0.f : __expf(m - mx);
+        cw[z] = w;
+        denom += w * base[(size_t)z * stride + p.d + 1];
+    }
+    denom = warp_sum(denom);
+    const float inv = denom > 0.f ? 1.f / denom : 0.f;
+    __syncwarp();
+    for (int i = lane * 2; i < p.d; i += 64) {              // d and the stride are even
+        float a0 = 0.f, a1 = 0.f;
+#pragma unroll 4
+        for (int z = 0; z < nz; ++z) {
+            const float2 v = *reinterpret_cast<const float2*>(base + (size_t)z * stride + i);
+            a0 = fmaf(cw[z], v.x, a0);
+            a1 = fmaf(cw[z], v.y, a1);
+        }
+        *reinterpret_cast<uint32_t*>(o + i) = am_pack(a0 * inv, a1 * inv);
+    }
+}
+
+// The merge kernel's weights: beyond 48 KB of shared memory the kernel has to be told.
+static int combine_smem(int slots) {
+    const size_t bytes = (size_t)AC_WARPS * slots * sizeof(float);
+    if (bytes <= 48 * 1024) return 0;
+    const cudaError_t e = cudaFuncSetAttribute(attention_mma_combine_warp_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)bytes);
+    if (e != cudaSuccess) return fail("attention merge: %d slots need %zu bytes of shared memory: %s", slots, bytes, cudaGetErrorString(e));
+    return 0;
+}
+
 template <int HD>
 static int launch_prompt(const AttMmaParams& p, int tiles, cudaStream_t s) {
     if (p.page_size % 16 != 0) return fail("attention_mma: pages must hold a multiple of 16 positions, got %d", p.page_size);
@@ -916,8 +977,9 @@ extern "C" int kb_attention_mma_combine(void* out, const int* row_count, const f
     AttMmaParams p = {};
     p.row_count = row_count; p.out = (bf16*)out; p.partial = const_cast<float*>(scratch);
     p.rows = rows; p.hq = hq; p.d = d; p.window = window; p.split = split; p.slots = slots; p.direct = 1;
-    dim3 grid(rows, hq);
-    attention_mma_combine_kernel<<<grid, 128, (size_t)slots * sizeof(float), (cudaStream_t)stream>>>(p);
+    const unsigned blocks = (unsigned)(((long long)rows * hq + AC_WARPS - 1) / AC_WARPS);
+    if (int e = combine_smem(slots)) return e;
+    attention_mma_combine_warp_kernel<<<blocks, AC_WARPS * 32, (size_t)AC_WARPS * slots * sizeof(float), (cudaStream_t)stream>>>(p);
     return check_launch("attention_mma combine");
 }
 
@@ -957,8 +1019,13 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     else e = decode ? launch_decode<256>(p, tiles, decode, s) : launch_prompt<256>(p, tiles, s);
     if (e) return e;
     if (slots > 1) {
-        dim3 grid(rows, hq);
-        launch_dependent(attention_mma_combine_kernel, grid, dim3(128), (size_t)slots * sizeof(float), s, p);
+        if ((long long)rows * hq >= 4096) {                 // many pairs: a warp each
+            const unsigned blocks = (unsigned)(((long long)rows * hq + AC_WARPS - 1) / AC_WARPS);
+            if (int e2 = combine_smem(slots)) return e2;
+            launch_dependent(attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
+        } else {                                            // few (a decode step): a block each, for the latency
+            launch_dependent(attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p);
+        }
         return check_launch("attention_mma combine");
     }
     return 0;

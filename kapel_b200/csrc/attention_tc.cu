@@ -243,8 +243,9 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
+    // The MMA warp must see Q in place; the copying warp need not, and asks for keys meanwhile.
     at_fence_before();
-    __syncthreads();
+    if (warp >= 1) asm volatile("bar.sync 1, 160;" ::: "memory");
     at_fence_after();
     bool failed = false;
 
