@@ -18,8 +18,8 @@
 // cores about 50 cycles beyond its arithmetic, so the scores take all 64 keys in one product a
 // 16-element step: the key tile is laid out [chunk of 64 elements][64 keys], boxes of 16 keys x 64
 // elements, one a (page, chunk). The values, whose products step through the keys 16 at a time,
-// come as one three-dimensional copy a page: [page][chunk][16 keys]. S and P are double-buffered so the exponentials of one tile run under the
-// products of its neighbours.
+// come as one three-dimensional copy a page: [page][chunk][16 keys]. S and P are double-buffered so
+// the exponentials of one tile run under the products of its neighbours.
 //
 // The soft cap bounds every score by +-cap, so exp(s) itself is safe in float32 and bfloat16 for
 // cap <= 64 (e^64 times 2^17 keys < 3e38, e^-64 > 1e-38): the softmax uses the fixed reference 0
