@@ -940,7 +940,7 @@ static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStr
     do {                                                                                                                       \
         if (smem > 48 * 1024)                                                                                                  \
             cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_dependent(attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v);     \
+        launch_dependent_if(p.rows <= DEPENDENT_ROWS, attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v);     \
     } while (0)
     if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true); else KB_DECODE(1, false); }
     else               { if (p.d == HD) KB_DECODE(2, true); else KB_DECODE(2, false); }
@@ -1022,9 +1022,9 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
         if ((long long)rows * hq >= 4096) {                 // many pairs: a warp each
             const unsigned blocks = (unsigned)(((long long)rows * hq + AC_WARPS - 1) / AC_WARPS);
             if (int e2 = combine_smem(slots)) return e2;
-            launch_dependent(attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
+            launch_dependent_if(false, attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
         } else {                                            // few (a decode step): a block each, for the latency
-            launch_dependent(attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p);
+            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p);
         }
         return check_launch("attention_mma combine");
     }

@@ -246,13 +246,13 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
     const unsigned blocks = (unsigned)((total + 255) / 256);
     cudaStream_t s = (cudaStream_t)stream;
 #define KB_ROPE(TI, T)                                                                                              \
-    launch_dependent(rope_append_kernel<TI, T>, dim3(blocks), dim3(256), 0, s, Src<TI>{(const TI*)qkv, splits, (size_t)split_stride}, \
+    launch_dependent_if(rows <= DEPENDENT_ROWS, rope_append_kernel<TI, T>, dim3(blocks), dim3(256), 0, s, Src<TI>{(const TI*)qkv, splits, (size_t)split_stride}, \
                      (const float2*)cos_sin, lines, (T*)q_out, (T*)k_table, (T*)v_table, rows, hq, hkv, d, rotary, write_kv,       \
                      table_lines, page_size > 0 ? page_size : 1)
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_table | (uintptr_t)v_table | (uintptr_t)cos_sin) & 15) == 0;
     if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16 && splits == 1 && rotary == d && d % 16 == 0 && aligned) {
         const long long vec = (long long)rows * (hq + 2 * hkv) * (d / 16);
-        launch_dependent(rope_append_bf16x8_kernel, dim3((unsigned)((vec + 255) / 256)), dim3(256), 0, s,
+        launch_dependent_if(rows <= DEPENDENT_ROWS, rope_append_bf16x8_kernel, dim3((unsigned)((vec + 255) / 256)), dim3(256), 0, s,
             (const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out, (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d,
             write_kv, table_lines, page_size > 0 ? page_size : 1);
     }

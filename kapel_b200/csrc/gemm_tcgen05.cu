@@ -244,7 +244,6 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 tc_tma_load_2d(a_dst + TC_A_BYTES, &map_w, kt * TC_BK, n0, full + s);
             }
         }
-        dependent_trigger();
     } else if (warp == 1) {
         if (lane == 0) {
             for (int kt = 0; kt < k_tiles; ++kt) {
@@ -368,7 +367,7 @@ gemm_tcgen05_pair_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
     tc_fence_after();
     const uint32_t tmem = *tmem_slot;
     bool failed = false;
-    dependent_wait();                                       // barriers, TMEM and the cluster are set up while the kernel before ends
+    dependent_wait();                                       // returns at once after a plain launch
 
     // A wait on a barrier nobody has arrived at yet passes with parity 1: the waiters that ask for
     // room (the producer for a stage, the MMA lane for an accumulator) start there.
@@ -390,7 +389,6 @@ gemm_tcgen05_pair_persistent_kernel(const __grid_constant__ CUtensorMap map_a, c
                 }
             }
         }
-        dependent_trigger();                                // everything this block reads has been asked for
     } else if (warp == 1) {
         if (lane == 0 && rank == 0) {
             int it = 0, i = 0;
@@ -786,7 +784,7 @@ static int launch_single(const CUtensorMap& map_a, const CUtensorMap& map_w, voi
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", tc_smem_bytes(STAGES), cudaGetErrorString(e));
         attr_set = true;
     }
-    launch_dependent(gemm_tcgen05_kernel<STAGES, EPI>, grid, dim3(TC_THREADS), (size_t)tc_smem_bytes(STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap);
+    launch_dependent_if(false, gemm_tcgen05_kernel<STAGES, EPI>, grid, dim3(TC_THREADS), (size_t)tc_smem_bytes(STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap);
     return check_launch("gemm_tcgen05");
 }
 
@@ -804,7 +802,7 @@ static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, void*
     const long long tiles = (long long)((m + 2 * TC_BM - 1) / (2 * TC_BM)) * ((n + tile_cols - 1) / tile_cols);
     const int pairs = skinny_sms() / 2;
     const int clusters = tiles < pairs ? (int)tiles : pairs;
-    launch_dependent(gemm_tcgen05_pair_persistent_kernel<EPI>, dim3(2 * clusters), dim3(TC_THREADS), (size_t)tp_smem_bytes(TPP_STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap);
+    launch_dependent_if(false, gemm_tcgen05_pair_persistent_kernel<EPI>, dim3(2 * clusters), dim3(TC_THREADS), (size_t)tp_smem_bytes(TPP_STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap);
     return check_launch("gemm_tcgen05_pair");
 }
 

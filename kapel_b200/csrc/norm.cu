@@ -342,9 +342,9 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const int tv = min(1024, ((chunks + cpt - 1) / cpt + 31) / 32 * 32);
         const bf16 *b = (const bf16*)branch, *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
         bf16* out = (bf16*)h;
-        if (cpt == 1) launch_dependent(add_rmsnorm_bf16x8_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else if (cpt == 2) launch_dependent(add_rmsnorm_bf16x8_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else launch_dependent(add_rmsnorm_bf16x8_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        if (cpt == 1) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_bf16x8_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else if (cpt == 2) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_bf16x8_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_bf16x8_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
         return check_launch("add_rmsnorm");
     }
     // float32 partial sums of few rows (a decode step): the kernel that keeps many slices in flight
@@ -358,9 +358,9 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const bf16 *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
         const size_t stride = (size_t)split_stride;
         bf16* out = (bf16*)h;
-        if (cpt == 1) launch_dependent(add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else if (cpt == 2) launch_dependent(add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else launch_dependent(add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        if (cpt == 1) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else if (cpt == 2) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
         return check_launch("add_rmsnorm");
     }
     switch (code) {
