@@ -6,8 +6,8 @@
 // one block a 128 x 256 tile (products of about one tile a multiprocessor); persistent pairs of
 // blocks with cta_group::2 and two accumulators (all other products of more than 64 rows, also with
 // the gated unit in the epilogue); operands swapped for up to 64 rows, split over K; the same with
-// the gated unit. All are launched as programmatic dependents and wait for the kernel before them
-// only before they touch the activations.
+// the gated unit. The last two (decoding) are launched as programmatic dependents and wait for the
+// kernel before them only before they touch the activations; the first two are launched plainly.
 //
 // The first: one block computes one 128 x 256 tile of C. Six warps:
 //   warp 0    one lane walks K in steps of 64 and asks TMA for the A and W tiles of each step, four
