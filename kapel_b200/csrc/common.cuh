@@ -28,8 +28,8 @@ int check_launch(const char* what);      // cudaGetLastError -> fail(...)
 // Only the kernels of a step of at most DEPENDENT_ROWS rows (decoding) are chained this way. The
 // kernels of a prompt are launched plainly: chained, two-layer and 46-layer passes of 2,048 tokens
 // at hidden 4608, 32 heads over 16 of size 128 and intermediate 36864 stopped now and then in the
-// middle of a pass (no wait of the kernels' own ran out; the multiprocessors stayed busy until the
-// process ended), which the same passes launched plainly never did.
+// middle of a pass (the stream stood still until the process ended; a copy on another stream still
+// ran), which the same passes launched plainly never did.
 constexpr int DEPENDENT_ROWS = 64;
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>
