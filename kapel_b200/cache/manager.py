@@ -14,7 +14,9 @@ cache.rs:141-144,846-897): slot 0 belongs to padding rows, a request gets a slot
 for its lifetime, and `Plan.fresh` says which slots a step must clear.
 
 The manager is host code only. Device tables are made by an `allocate(shape, dtype)` function
-given by the engine, so every decision here can be tested without a GPU.
+given by the engine, so every decision here can be tested without a GPU. The bookkeeping (free
+lists, page lists, the arrays of a step) runs in the host library, `csrc/host/cache_core.cpp`;
+this class owns its handle, names the sequences and raises the typed errors.
 """
 from __future__ import annotations
 
@@ -23,7 +25,9 @@ from typing import Callable, Dict, Hashable, List, Optional, Sequence, Tuple
 
 import numpy as np
 
-from .pages import CacheFull, PagePool
+import ctypes
+
+from .pages import CacheFull, host_library
 
 
 @dataclass(frozen=True)
@@ -73,6 +77,7 @@ class Plan:
     groups: List[GroupPlan]
     taken: List[Tuple[int, Hashable, int, int]] = field(default_factory=list)  # (group, id, logical, physical)
     committed: bool = False
+    native: object = None        # the manager's own: the entries as the host library takes them
 
     @property
     def rows(self) -> int:
@@ -83,67 +88,13 @@ class Plan:
         return int(self.kv_len.max()) if len(self.kv_len) else 0
 
 
-class PageList:
-    """A sequence's logical pages in one group, as a list that is also an int32 array: a step's
-    block-table row is a slice of it, not a conversion of a Python list every step."""
-
-    __slots__ = ("a", "n")
-
-    def __init__(self):
-        self.a = np.empty(16, np.int32)
-        self.n = 0
-
-    def __len__(self) -> int:
-        return self.n
-
-    def __iter__(self):
-        return iter(self.a[: self.n].tolist())
-
-    def __reversed__(self):
-        return iter(self.a[: self.n][::-1].tolist())
-
-    def __getitem__(self, i: int) -> int:
-        if not -self.n <= i < self.n:
-            raise IndexError(i)
-        return int(self.a[i if i >= 0 else self.n + i])
-
-    def __setitem__(self, i: int, page: int) -> None:
-        if not 0 <= i < self.n:
-            raise IndexError(i)
-        self.a[i] = page
-
-    def append(self, page: int) -> None:
-        if self.n == self.a.size:
-            self.a = np.concatenate([self.a, np.empty(self.a.size, np.int32)])
-        self.a[self.n] = page
-        self.n += 1
-
-    def pop(self) -> int:
-        if self.n == 0:
-            raise IndexError("pop from no pages")
-        self.n -= 1
-        return int(self.a[self.n])
-
-    def array(self) -> np.ndarray:
-        return self.a[: self.n]
-
-
-class _Sequence:
-    __slots__ = ("length", "pages", "released", "slot", "fresh")
-
-    def __init__(self, n_groups: int, slot: int):
-        self.length = 0
-        self.pages: List[PageList] = [PageList() for _ in range(n_groups)]   # -1 where given back
-        self.released = [0] * n_groups     # logical pages below this index were given back
-        self.slot = slot
-        self.fresh = True
-
-
 class CacheGroup:
     def __init__(self, needs: PagedKV, n_pages: int):
+        if n_pages < 0:
+            raise ValueError(f"a pool cannot have {n_pages} pages")
         self.needs = needs
         self.window = needs.window
-        self.pool = PagePool(n_pages)
+        self.n_pages = n_pages
         self.layers: List[int] = []
         self.keys: Dict[int, object] = {}      # layer -> table [pages, kv_heads, page_size, head_dim]
         self.values: Dict[int, object] = {}
@@ -152,6 +103,10 @@ class CacheGroup:
     def name(self) -> str:
         w = "all" if self.window is None else f"window{self.window}"
         return f"{w}/h{self.needs.kv_heads}/d{self.needs.head_dim}"
+
+
+def _ptr(a: np.ndarray) -> int:
+    return a.ctypes.data
 
 
 class CacheManager:
@@ -190,11 +145,31 @@ class CacheManager:
             self.group_of_layer[layer] = g
         self.state_specs: Dict[int, StateSpec] = {l: n.state for l, n in needs.items() if n.state is not None}
         self.states: Dict[int, object] = {}
-        self._sequences: Dict[Hashable, _Sequence] = {}
-        self._free_slots = list(range(max_sequences, 0, -1))     # slot 0 is the padding rows'
-        self.released_pages = 0
+        self._sequences: Dict[Hashable, int] = {}                # sequence -> its slot (1 ..; 0 is the padding rows')
+        self._lib = host_library()
+        n_groups = len(self.groups)
+        counts = np.asarray([g.n_pages for g in self.groups], np.int32)
+        windows = np.asarray([-1 if g.window is None else g.window for g in self.groups], np.int32)
+        ip = ctypes.POINTER(ctypes.c_int)
+        self._h = self._lib.kc_create(n_groups, page_size, counts.ctypes.data_as(ip), windows.ctypes.data_as(ip), max_sequences)
+        if not self._h:
+            raise ValueError(f"a cache of {n_groups} groups, pages {counts.tolist()}, {max_sequences} sequences cannot be made")
+        self._scratch = np.zeros(max(n_groups, 1), np.int32)
+        self._info = np.zeros(7, np.int64)
+        self._info_ptr = self._info.ctypes.data
+        self._names = 0                                          # counts the sequences that have come or gone
         if allocate is not None:
             self.allocate_tables(allocate, dtype)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.kc_destroy(self._h)
+            self._h = None
+
+    @property
+    def released_pages(self) -> int:
+        """Pages that windowed groups have given back so far."""
+        return int(self._lib.kc_released_pages(self._h))
 
     # ------------------------------------------------------------------ device tables
     def allocate_tables(self, allocate: Callable, dtype) -> None:
@@ -202,7 +177,7 @@ class CacheManager:
         head in one page lie together, so a kernel fetches them in one piece), and state
         tables [slots + 1, *shape]; they never move afterwards, so a recorded step stays valid."""
         for g in self.groups:
-            shape = (max(g.pool.n_pages, 1), g.needs.kv_heads, self.page_size, g.needs.head_dim)
+            shape = (max(g.n_pages, 1), g.needs.kv_heads, self.page_size, g.needs.head_dim)
             for layer in g.layers:
                 g.keys[layer] = allocate(shape, dtype)
                 g.values[layer] = allocate(shape, dtype)
@@ -223,39 +198,51 @@ class CacheManager:
     def add_sequence(self, seq_id) -> int:
         if seq_id in self._sequences:
             raise ValueError(f"sequence {seq_id!r} is already in the cache")
-        if not self._free_slots:
+        slot = self._lib.kc_add(self._h)
+        if slot < 1:
             raise CacheFull(1, 0, "slots")
-        slot = self._free_slots.pop()
-        self._sequences[seq_id] = _Sequence(len(self.groups), slot)
+        self._sequences[seq_id] = slot
+        self._names += 1
         return slot
 
     def remove_sequence(self, seq_id) -> None:
         """Gives back everything the sequence holds, last page first."""
-        seq = self._sequences.pop(seq_id)
-        for g, group in enumerate(self.groups):
-            for page in reversed(seq.pages[g]):
-                if page >= 0:
-                    group.pool.give(page)
-        self._free_slots.append(seq.slot)
+        slot = self._sequences.pop(seq_id)
+        self._names += 1
+        if self._lib.kc_remove(self._h, slot) != 0:
+            raise AssertionError(f"sequence {seq_id!r} (slot {slot}) could not give its pages back")
 
     def length(self, seq_id) -> int:
-        return self._sequences[seq_id].length
+        return self._lib.kc_length(self._h, self._sequences[seq_id])
 
     def slot(self, seq_id) -> int:
-        return self._sequences[seq_id].slot
+        return self._sequences[seq_id]
 
     def free_slots(self) -> int:
-        return len(self._free_slots)
+        return self._lib.kc_free_slots(self._h)
+
+    def _ints(self, call, *args) -> List[int]:
+        r = call(self._h, *args, self._scratch.ctypes.data_as(ctypes.POINTER(ctypes.c_int)))
+        if r is not None and r < 0:
+            raise KeyError("no such sequence in the cache")
+        return self._scratch[: len(self.groups)].tolist()
 
     def free_pages(self) -> List[int]:
-        return [g.pool.free for g in self.groups]
+        return self._ints(self._lib.kc_free_pages)
 
     def total_pages(self) -> List[int]:
-        return [g.pool.n_pages for g in self.groups]
+        return [g.n_pages for g in self.groups]
 
     def held_pages(self, seq_id) -> List[int]:
-        seq = self._sequences[seq_id]
-        return [sum(1 for p in seq.pages[g] if p >= 0) for g in range(len(self.groups))]
+        return self._ints(self._lib.kc_held_pages, self._sequences[seq_id])
+
+    def page_list(self, seq_id, group: int) -> List[int]:
+        """The sequence's logical pages in a group, -1 where a page was given back."""
+        slot = self._sequences[seq_id]
+        n = self._lib.kc_pages_of(self._h, slot, group, None, 0)
+        out = np.empty(max(n, 1), np.int32)
+        self._lib.kc_pages_of(self._h, slot, group, out.ctypes.data_as(ctypes.POINTER(ctypes.c_int)), n)
+        return out[:n].tolist()
 
     # ------------------------------------------------------------------ arithmetic
     def _pages_for(self, length: int) -> int:
@@ -265,10 +252,7 @@ class CacheManager:
         """New pages each group must take for `count` more tokens of `seq_id` (a sequence not
         yet in the cache counts from zero): ceil((len + count) / page) - pages held or passed
         (crates/kapel-models/src/cache.rs:481-486, per group)."""
-        seq = self._sequences.get(seq_id)
-        length = seq.length if seq is not None else 0
-        have = [len(seq.pages[g]) if seq is not None else 0 for g in range(len(self.groups))]
-        return [self._pages_for(length + count) - have[g] for g in range(len(self.groups))]
+        return self._ints(self._lib.kc_pages_needed, self._sequences.get(seq_id, 0), int(count))
 
     def pages_for_tokens(self, tokens: int) -> List[int]:
         """Pages a sequence of `tokens` positions holds at most in each group at one time,
@@ -280,7 +264,7 @@ class CacheManager:
         for seq_id, count in entries:
             for g, n in enumerate(self.pages_needed(seq_id, count)):
                 need[g] += n
-        return all(n <= g.pool.free for n, g in zip(need, self.groups))
+        return all(n <= f for n, f in zip(need, self.free_pages()))
 
     # ------------------------------------------------------------------ a step
     def plan(self, entries: Sequence[Tuple[Hashable, int]]) -> Plan:
@@ -291,67 +275,71 @@ class CacheManager:
         Raises `CacheFull` and takes nothing if some group lacks pages. Lengths move only at
         `commit`; `abort` gives the pages back.
         """
+        entries = list(entries)
+        n = len(entries)
+        slot_of = self._sequences
+        sc = np.empty((2, max(n, 1)), np.int32)                  # slots, counts
         seen = set()
-        for seq_id, count in entries:
+        for e, (seq_id, count) in enumerate(entries):
             if seq_id in seen:
                 raise ValueError(f"sequence {seq_id!r} appears twice in one step")
             seen.add(seq_id)
             if count <= 0:
                 raise ValueError(f"sequence {seq_id!r} brings no token")
-            if seq_id not in self._sequences:
+            slot = slot_of.get(seq_id)
+            if slot is None:
                 raise KeyError(f"sequence {seq_id!r} is not in the cache")
-        need = [0] * len(self.groups)
-        for seq_id, count in entries:
-            for g, n in enumerate(self.pages_needed(seq_id, count)):
-                need[g] += n
-        for g, group in enumerate(self.groups):
-            if need[g] > group.pool.free:
-                raise CacheFull(need[g], group.pool.free, group.name)
-
-        ps = self.page_size
-        n_rows = sum(c for _, c in entries)
-        n_entries = len(entries)
-        positions = np.empty(n_rows, np.int32)
-        row_entry = np.empty(n_rows, np.int32)
-        row_count = np.empty(n_rows, np.int32)
-        q_start = np.empty(n_entries, np.int32)
-        q_len = np.empty(n_entries, np.int32)
-        kv_len = np.empty(n_entries, np.int32)
-        slots = np.empty(n_entries, np.int32)
-        fresh = np.zeros(n_entries, bool)
-        widest = max((self._pages_for(self._sequences[s].length + c) for s, c in entries), default=0)
-        group_plans = [
-            GroupPlan(np.empty(n_rows, np.int32), np.full((n_entries, max(widest, 1)), -1, np.int32))
-            for _ in self.groups
-        ]
+            sc[0, e], sc[1, e] = slot, count
+        sc_ptr = sc.ctypes.data
+        stride = 4 * sc.shape[1]
+        info = self._info
+        status = self._lib.kc_plan_prepare(self._h, n, sc_ptr, sc_ptr + stride, self._info_ptr)
+        if status == 1:
+            raise CacheFull(int(info[5]), int(info[6]), self.groups[int(info[4])].name)
+        if status != 0:
+            raise AssertionError("the cache's bookkeeping does not know a sequence this manager holds")
+        n_rows, widest, n_take = int(info[1]), int(info[2]), int(info[3])
+        width = max(widest, 1)
+        n_groups = len(self.groups)
+        # One buffer for every array of the step: three by row, four by entry, the lines and the
+        # block tables of each group, the pages taken, and a byte an entry for `fresh`.
+        at_entry = 3 * n_rows
+        at_lines = at_entry + 4 * n
+        at_tables = at_lines + n_groups * n_rows
+        at_taken = at_tables + n_groups * n * width
+        at_fresh = at_taken + 4 * n_take
+        buf = np.empty(at_fresh + (n + 3) // 4 + 1, np.int32)
+        buf[at_tables:at_taken] = -1
+        buf[at_fresh:] = 0
+        base = buf.ctypes.data
+        at = lambda words: base + 4 * words
+        line_ptrs = (ctypes.c_void_p * max(n_groups, 1))(*[at(at_lines + g * n_rows) for g in range(n_groups)])
+        table_ptrs = (ctypes.c_void_p * max(n_groups, 1))(*[at(at_tables + g * n * width) for g in range(n_groups)])
+        got = self._lib.kc_plan_fill(
+            self._h, n, sc_ptr, sc_ptr + stride, base, at(n_rows), at(2 * n_rows),
+            at(at_entry), at(at_entry + n), at(at_entry + 2 * n), at(at_entry + 3 * n), at(at_fresh),
+            ctypes.addressof(line_ptrs), ctypes.addressof(table_ptrs), width, at(at_taken), n_take)
+        if got < 0:
+            raise AssertionError("the cache's bookkeeping could not take the pages it had counted")
         taken: List[Tuple[int, Hashable, int, int]] = []
-        r = 0
-        for e, (seq_id, count) in enumerate(entries):
-            seq = self._sequences[seq_id]
-            start, end = seq.length, seq.length + count
-            q_start[e], q_len[e], kv_len[e] = r, count, end
-            slots[e], fresh[e] = seq.slot, seq.fresh
-            if count == 1:
-                positions[r], row_entry[r], row_count[r] = start, e, end
-            else:
-                positions[r : r + count] = np.arange(start, end, dtype=np.int32)
-                row_entry[r : r + count] = e
-                row_count[r : r + count] = np.arange(start + 1, end + 1, dtype=np.int32)
-            for g, group in enumerate(self.groups):
-                pages = seq.pages[g]
-                while len(pages) < self._pages_for(end):
-                    page = group.pool.take()
-                    taken.append((g, seq_id, len(pages), page))
-                    pages.append(page)
-                table = pages.array()
-                group_plans[g].block_table[e, : len(pages)] = table
-                if count == 1:                                   # a decoded token: no arrays to build
-                    group_plans[g].lines[r] = int(table[start // ps]) * ps + start % ps
-                else:
-                    pos = positions[r : r + count]
-                    group_plans[g].lines[r : r + count] = table[pos // ps] * ps + pos % ps
-            r += count
-        return Plan(list(entries), positions, row_entry, row_count, q_start, q_len, kv_len, slots, fresh, group_plans, taken)
+        if got:
+            name_of = {int(sc[0, e]): entries[e][0] for e in range(n)}
+            taken = [(g, name_of[s], logical, page) for g, s, logical, page in buf[at_taken : at_taken + 4 * got].reshape(-1, 4).tolist()]
+        group_plans = [
+            GroupPlan(buf[at_lines + g * n_rows : at_lines + (g + 1) * n_rows],
+                      buf[at_tables + g * n * width : at_tables + (g + 1) * n * width].reshape(n, width))
+            for g in range(n_groups)
+        ]
+        plan = Plan(entries, buf[:n_rows], buf[n_rows : 2 * n_rows], buf[2 * n_rows : 3 * n_rows],
+                    buf[at_entry : at_entry + n], buf[at_entry + n : at_entry + 2 * n], buf[at_entry + 2 * n : at_entry + 3 * n],
+                    buf[at_entry + 3 * n : at_entry + 4 * n], buf[at_fresh:].view(np.bool_)[:n], group_plans, taken)
+        plan.native = (self._names, sc, n)
+        return plan
+
+    def _entries_arrays(self, entries):
+        live = [(self._sequences[s], c) for s, c in entries]
+        arr = np.asarray(live, np.int32).reshape(-1, 2)
+        return np.ascontiguousarray(arr[:, 0]), np.ascontiguousarray(arr[:, 1])
 
     def commit(self, plan: Plan) -> None:
         """The step's kernels are enqueued: lengths advance, and windowed groups give back the
@@ -359,59 +347,36 @@ class CacheManager:
         if plan.committed:
             raise ValueError("a plan is committed once")
         plan.committed = True
-        for seq_id, count in plan.entries:
-            seq = self._sequences[seq_id]
-            seq.length += count
-            seq.fresh = False
-            for g, group in enumerate(self.groups):
-                if group.window is None:
-                    continue
-                # The next query has seen at least length + 1 positions and reads from
-                # (length + 1) - window on; pages wholly below that are done.
-                first_needed = seq.length + 1 - group.window
-                if first_needed <= 0:
-                    continue
-                upto = min(first_needed // self.page_size, len(seq.pages[g]))
-                for p in range(seq.released[g], upto):
-                    if seq.pages[g][p] >= 0:
-                        group.pool.give(seq.pages[g][p])
-                        seq.pages[g][p] = -1
-                        self.released_pages += 1
-                seq.released[g] = max(seq.released[g], upto)
+        native = plan.native
+        if native is not None and native[0] == self._names:       # no sequence has come or gone since the plan
+            sc, n = native[1], native[2]
+            ptr = sc.ctypes.data
+            r = self._lib.kc_commit(self._h, n, ptr, ptr + 4 * sc.shape[1])
+        else:
+            slots, counts = self._entries_arrays(plan.entries)
+            r = self._lib.kc_commit(self._h, len(plan.entries), _ptr(slots), _ptr(counts))
+        if r < 0:
+            raise AssertionError("a committed plan names a sequence the cache does not hold")
 
     def abort(self, plan: Plan) -> None:
         """The step did not run: the pages it took go back, newest first."""
         if plan.committed:
             raise ValueError("a committed plan cannot be aborted")
-        for g, seq_id, logical, page in reversed(plan.taken):
-            seq = self._sequences.get(seq_id)
-            if seq is not None and len(seq.pages[g]) == logical + 1 and seq.pages[g][logical] == page:
-                seq.pages[g].pop()
-                self.groups[g].pool.give(page)
+        quads = [(g, self._sequences[s], logical, page) for g, s, logical, page in plan.taken if s in self._sequences]
+        if quads:
+            raw = np.asarray(quads, np.int32)
+            self._lib.kc_abort(self._h, len(quads), _ptr(raw))
         plan.taken.clear()
         plan.committed = True
 
     # ------------------------------------------------------------------ checks
     def check(self) -> None:
         """No page lost, none held twice: every held page belongs to exactly one sequence."""
-        for g, group in enumerate(self.groups):
-            group.pool.check()
-            owners: Dict[int, Hashable] = {}
-            for seq_id, seq in self._sequences.items():
-                for page in seq.pages[g]:
-                    if page < 0:
-                        continue
-                    if page in owners:
-                        raise AssertionError(f"group {group.name}: page {page} held by {owners[page]!r} and {seq_id!r}")
-                    if not group.pool.is_held(page):
-                        raise AssertionError(f"group {group.name}: page {page} of {seq_id!r} is on the free list")
-                    owners[page] = seq_id
-            if len(owners) != group.pool.held:
-                raise AssertionError(
-                    f"group {group.name}: {group.pool.held} pages held, {len(owners)} owned: pages lost"
-                )
-        slots = [s.slot for s in self._sequences.values()]
-        if len(set(slots)) != len(slots) or set(slots) & set(self._free_slots) or 0 in slots:
-            raise AssertionError("a slot is held twice, is free while held, or is the padding slot")
-        if len(slots) + len(self._free_slots) != self.max_sequences:
+        msg = ctypes.create_string_buffer(512)
+        if self._lib.kc_check(self._h, msg, 512):
+            raise AssertionError(msg.value.decode())
+        slots = list(self._sequences.values())
+        if len(set(slots)) != len(slots) or 0 in slots:
+            raise AssertionError("a slot is held twice or is the padding slot")
+        if len(slots) + self.free_slots() != self.max_sequences:
             raise AssertionError("a slot was lost")

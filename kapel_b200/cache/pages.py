@@ -3,11 +3,43 @@
 Kapel keeps a free list with reference counts and a typed `CacheFull{needed, free}`
 (crates/kapel-models/src/cache.rs:148-150,419-433; crates/kapel-models/src/lib.rs:70-77).
 Here pages are never shared, so a page is either free or held by exactly one owner; the pool
-checks that on every call.
+checks that on every call. The bookkeeping itself is in the host library
+(`csrc/host/cache_core.cpp`), built with the C++ compiler alone at first use.
 """
 from __future__ import annotations
 
-from typing import List
+import ctypes
+from typing import Optional
+
+_LIB: Optional[ctypes.CDLL] = None
+
+
+def host_library() -> ctypes.CDLL:
+    """The host library, built if need be; raises if it cannot be built or loaded."""
+    global _LIB
+    if _LIB is None:
+        from ..csrc.build import ensure_host_built
+
+        lib = ctypes.CDLL(str(ensure_host_built(verbose=True)))
+        vp, i32, i64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong
+        ip = ctypes.POINTER(ctypes.c_int)
+        sigs = {
+            "kp_create": (vp, [i32]), "kp_destroy": (None, [vp]), "kp_take": (i32, [vp]), "kp_give": (i32, [vp, i32]),
+            "kp_free": (i32, [vp]), "kp_is_held": (i32, [vp, i32]), "kp_check": (i32, [vp, ctypes.c_char_p, i32]),
+            "kc_create": (vp, [i32, i32, ip, ip, i32]), "kc_destroy": (None, [vp]), "kc_add": (i32, [vp]),
+            "kc_remove": (i32, [vp, i32]), "kc_length": (i32, [vp, i32]), "kc_free_slots": (i32, [vp]),
+            "kc_released_pages": (i64, [vp]), "kc_free_pages": (None, [vp, ip]), "kc_held_pages": (i32, [vp, i32, ip]),
+            "kc_pages_of": (i32, [vp, i32, i32, ip, i32]), "kc_pages_needed": (i32, [vp, i32, i32, ip]),
+            "kc_plan_prepare": (i32, [vp, i32, vp, vp, vp]),
+            "kc_plan_fill": (i32, [vp, i32, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, vp, i32, vp, i32]),
+            "kc_commit": (i64, [vp, i32, vp, vp]), "kc_abort": (i32, [vp, i32, vp]),
+            "kc_check": (i32, [vp, ctypes.c_char_p, i32]),
+        }
+        for name, (res, args) in sigs.items():
+            fn = getattr(lib, name)
+            fn.restype, fn.argtypes = res, args
+        _LIB = lib
+    return _LIB
 
 
 class CacheFull(RuntimeError):
@@ -26,43 +58,42 @@ class PagePool:
         if n_pages < 0:
             raise ValueError(f"a pool cannot have {n_pages} pages")
         self.n_pages = n_pages
-        # Pop takes from the end: page 0 first in a fresh pool.
-        self._free: List[int] = list(range(n_pages - 1, -1, -1))
-        self._held = [False] * n_pages
+        self._lib = host_library()
+        self._h = self._lib.kp_create(n_pages)
+
+    def __del__(self):
+        if getattr(self, "_h", None):
+            self._lib.kp_destroy(self._h)
+            self._h = None
 
     @property
     def free(self) -> int:
-        return len(self._free)
+        return self._lib.kp_free(self._h)
 
     @property
     def held(self) -> int:
-        return self.n_pages - len(self._free)
+        return self.n_pages - self.free
 
     def take(self) -> int:
-        if not self._free:
+        page = self._lib.kp_take(self._h)
+        if page == -1:
             raise CacheFull(1, 0)
-        page = self._free.pop()
-        if self._held[page]:
-            raise AssertionError(f"page {page} was on the free list while held")
-        self._held[page] = True
+        if page < 0:
+            raise AssertionError("a page was on the free list while held")
         return page
 
     def give(self, page: int) -> None:
-        if not 0 <= page < self.n_pages:
+        r = self._lib.kp_give(self._h, int(page))
+        if r == -1:
             raise ValueError(f"page {page} is not of this pool (0..{self.n_pages - 1})")
-        if not self._held[page]:
+        if r == -2:
             raise ValueError(f"page {page} is given back twice")
-        self._held[page] = False
-        self._free.append(page)
 
     def is_held(self, page: int) -> bool:
-        return self._held[page]
+        return bool(self._lib.kp_is_held(self._h, int(page)))
 
     def check(self) -> None:
         """Every page is free or held, never both, none lost."""
-        free = set(self._free)
-        if len(free) != len(self._free):
-            raise AssertionError("a page is on the free list twice")
-        for p in range(self.n_pages):
-            if self._held[p] == (p in free):
-                raise AssertionError(f"page {p}: held={self._held[p]} but on the free list={p in free}")
+        msg = ctypes.create_string_buffer(256)
+        if self._lib.kp_check(self._h, msg, 256):
+            raise AssertionError(msg.value.decode())

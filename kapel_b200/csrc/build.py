@@ -1,4 +1,5 @@
-"""Builds the CUDA library of this package for sm_100a with nvcc, once, and finds it again.
+"""Builds the CUDA library of this package for sm_100a with nvcc, once, and finds it again; and the
+small host library (`host/*.cpp`: the cache manager's bookkeeping) with the C++ compiler alone.
 
 `ensure_built()` returns the path of `libkapel_b200.so`. It compiles every `.cu` file of this
 folder in parallel when the library is missing or older than its sources (a stamp beside it
@@ -143,5 +144,60 @@ def ensure_built(verbose: bool = True, force: bool = False) -> Path:
     return out / LIB_NAME
 
 
+# ---------------------------------------------------------------------------------------
+# The host library: no CUDA in it, so it builds (in a second or two) and is tested where there is
+# neither a GPU nor nvcc.
+HOST_LIB_NAME = "libkapel_b200_host.so"
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall"]
+
+
+def host_sources():
+    return sorted((HERE / "host").glob("*.cpp"))
+
+
+def _cxx() -> str:
+    for name in (os.environ.get("CXX"), "g++", "c++", "clang++"):
+        if name and shutil.which(name):
+            return shutil.which(name)
+    raise RuntimeError("kapel_b200: no C++ compiler was found (CXX, g++, c++, clang++); the cache manager cannot be built")
+
+
+def _host_stamp() -> str:
+    h = hashlib.sha256()
+    for f in host_sources():
+        h.update(f.name.encode())
+        h.update(f.read_bytes())
+    h.update(" ".join(HOST_FLAGS).encode())
+    return h.hexdigest()
+
+
+def ensure_host_built(verbose: bool = True, force: bool = False) -> Path:
+    stamp = _host_stamp()
+    candidates = [HERE / "_build"]
+    if os.environ.get("KAPEL_B200_BUILD_DIR"):
+        candidates.insert(0, Path(os.environ["KAPEL_B200_BUILD_DIR"]))
+    candidates.append(Path(tempfile.gettempdir()) / f"kapel_b200-build-{os.getuid()}")
+    if not force:
+        for d in candidates:
+            lib, st = d / HOST_LIB_NAME, d / "stamp_host"
+            try:
+                if lib.is_file() and st.is_file() and st.read_text().strip() == stamp:
+                    return lib
+            except OSError:
+                continue
+    out = build_dir()
+    t0 = time.time()
+    tmp = out / (HOST_LIB_NAME + f".tmp{os.getpid()}")
+    cmd = [_cxx(), *HOST_FLAGS, *[str(s) for s in host_sources()], "-o", str(tmp)]
+    r = subprocess.run(cmd, capture_output=True, text=True)
+    if r.returncode != 0:
+        raise RuntimeError(f"kapel_b200: the host library did not compile:\n{r.stdout}\n{r.stderr}")
+    os.replace(tmp, out / HOST_LIB_NAME)
+    (out / "stamp_host").write_text(stamp)
+    _say(f"built {out / HOST_LIB_NAME} in {time.time() - t0:.0f} s", verbose)
+    return out / HOST_LIB_NAME
+
+
 if __name__ == "__main__":
+    print(ensure_host_built(force="--force" in sys.argv))
     print(ensure_built(force="--force" in sys.argv))
