@@ -1,0 +1,78 @@
+"""What the kernels' launchers refuse, and how they say it. A launcher checks its sizes before it
+touches the device, so a refusal needs no GPU: only the built library (nvcc), which is why these
+tests skip where it cannot be built. Every call here must be refused; nothing is launched.
+"""
+import ctypes
+
+import pytest
+
+vp, i32, i64, f32, f64 = ctypes.c_void_p, ctypes.c_int, ctypes.c_longlong, ctypes.c_float, ctypes.c_double
+
+
+@pytest.fixture(scope="module")
+def lib():
+    try:
+        from kapel_b200 import kernels as K
+
+        lib = K.library()
+    except Exception as err:                                 # no nvcc, no CUDA runtime library
+        pytest.skip(f"the CUDA library cannot be built or loaded here: {err}")
+    lib.kb_gemm_bf16.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, f32, vp, vp]
+    lib.kb_gemm_tcgen05.argtypes = [vp, i32, vp, vp, i32, i32, i32, i32, f32, i32, vp]
+    lib.kb_gemm_skinny.argtypes = [vp, i32, vp, vp, vp, i32, i32, i32, i32, f32, vp]
+    lib.kb_gemm_f32.argtypes = [vp, vp, vp, i32, i32, i32, i32, f32, vp]
+    lib.kb_rope_table.argtypes = [vp, vp, i32, i32, f64, vp]
+    lib.kb_rope_append.argtypes = [vp, i32, i32, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i32, vp]
+    lib.kb_glu.argtypes = [vp, i32, vp, i32, i32, i64, i64, i32, i32, vp]
+    lib.kb_attention_tc.argtypes = [vp] * 9 + [i32] * 11 + [f32, f32, vp, vp]
+    lib.kb_attention_tc_takes.argtypes = [i32, i32, i32, i32, f32]
+    return lib
+
+
+def refused(lib, code, *words):
+    assert code != 0
+    msg = lib.kb_last_error().decode()
+    for w in words:
+        assert w in msg, msg
+    return msg
+
+
+A = 4096                                                     # a 16-byte aligned stand-in address; never dereferenced
+BF16, F32 = 1, 0
+
+
+def test_products_refuse_rows_that_are_no_multiple_of_16_bytes_and_unknown_choices(lib):
+    refused(lib, lib.kb_gemm_bf16(A, BF16, A, A, 4, 64, 36, 0, 0.0, None, None), "gemm_bf16", "multiple of 8")
+    refused(lib, lib.kb_gemm_bf16(A, BF16, A, A, 4, 0, 64, 0, 0.0, None, None), "n 0")
+    refused(lib, lib.kb_gemm_bf16(A, 7, A, A, 4, 64, 64, 0, 0.0, None, None), "dtype code 7")
+    refused(lib, lib.kb_gemm_bf16(A, BF16, A, A, 4, 64, 64, 1, 0.0, None, None), "epilogue 1 with cap 0")
+    refused(lib, lib.kb_gemm_bf16(A, BF16, A + 2, A, 4, 64, 64, 0, 0.0, None, None), "16-byte aligned")
+    refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 128, 64, 36, 0, 0.0, 0, None), "gemm_tcgen05", "multiple of 8")
+    refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 128, 64, 64, 0, 0.0, 5, None), "kernel choice 5")
+    refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 0, 64, 64, 0, 0.0, 0, None), "m 0")
+    refused(lib, lib.kb_gemm_skinny(A, BF16, None, A, A, 65, 64, 64, 0, 0.0, None), "gemm_skinny", "m 65 (1..64)")
+    refused(lib, lib.kb_gemm_skinny(A, BF16, None, A + 8, A, 8, 64, 64, 0, 0.0, None), "16-byte aligned")
+    refused(lib, lib.kb_gemm_f32(A, A, A, 4, 64, 0, 0, 0.0, None), "gemm_f32", "k 0")
+
+
+def test_rotation_refuses_odd_sizes(lib):
+    refused(lib, lib.kb_rope_table(A, A, 4, 7, 10000.0, None), "rope_table", "rotary 7 (must be even)")
+    refused(lib, lib.kb_rope_table(A, A, 4, 8, 0.0, None), "theta 0 must be positive")
+    refused(lib, lib.kb_rope_append(A, BF16, 1, 0, A, A, A, A, A, BF16, 4, 2, 1, 15, 14, 1, 64, 16, None), "rope_append", "head_dim 15")
+    refused(lib, lib.kb_rope_append(A, BF16, 1, 0, A, A, A, A, A, BF16, 4, 2, 1, 16, 18, 1, 64, 16, None), "rotary 18", "at most head_dim 16")
+    refused(lib, lib.kb_rope_append(A, BF16, 0, 0, A, A, A, A, A, BF16, 4, 2, 1, 16, 16, 1, 64, 16, None), "0 slices")
+    refused(lib, lib.kb_rope_append(A, BF16, 1, 0, A, A, A, A, A, BF16, 4, 2, 1, 16, 16, 1, 64, 0, None), "page_size 0")
+    refused(lib, lib.kb_glu(A, BF16, A, BF16, 1, 0, 4, 64, 2, None), "glu", "activation code 2")
+
+
+def test_tcgen05_attention_says_what_it_takes(lib):
+    takes = lib.kb_attention_tc_takes
+    assert takes(8, 4, 256, 16, 50.0) == 1 and takes(32, 16, 128, 16, 50.0) == 1 and takes(4, 2, 64, 16, 30.0) == 1
+    assert takes(8, 4, 96, 16, 50.0) == 0                    # head sizes 64, 128 and 256 only
+    assert takes(8, 4, 128, 16, 0.0) == 0                    # the fixed softmax reference needs a soft cap
+    assert takes(8, 4, 128, 16, 100.0) == 0                  # ... of at most 64
+    assert takes(8, 3, 128, 16, 50.0) == 0                   # heads must divide into kv heads
+    args = [A] * 9 + [1, 64, 8, 4, 96, 16, 8, 8, 0, 0, 1]
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "head_dim 96", "are not taken")
+    args = [A] * 9 + [1, 64, 8, 4, 128, 16, 8, 8, 0, 96, 2]
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "split 96")
