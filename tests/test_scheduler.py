@@ -284,3 +284,38 @@ def test_temperature_uses_the_requests_own_seeded_sampler():
 
     a, b, c = tokens(7), tokens(7), tokens(8)
     assert a == b and a != c and len(set(a)) > 5
+
+
+def test_a_reserve_keeps_a_share_of_the_pool_free_at_admission():
+    """With `reserve`, a newcomer is admitted only if what the running requests will still take, its
+    own need and ceil(reserve x pages) fit what is free (Kapel: engine.rs:355-388); alone, a request
+    takes what there is."""
+    rng = np.random.default_rng(11)
+    ps = prompts(rng, [40, 40, 40])                       # each needs ceil((40 + 1) / 16) = 3 pages to start
+    greedy = Sampling()
+
+    eng = FakeEngine(pages=10)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=256, max_sequences=8, reserve=0.0))
+    rids = [sched.add(Request(prompt=p, sampling=greedy, max_tokens=4)) for p in ps]
+    sched.step()
+    assert sched.stats().running == 3                      # 9 of 10 pages promised: all three fit
+
+    eng = FakeEngine(pages=10)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=256, max_sequences=8, reserve=0.3))
+    rids = [sched.add(Request(prompt=p, sampling=greedy, max_tokens=4)) for p in ps]
+    first = sched.step()
+    st = sched.stats()
+    assert st.running == 2 and st.waiting == 1             # 3 + 3 + margin 3 <= 10, but 9 + 3 > 10
+    out, finishes = run(sched)
+    for ev in reversed(first):                              # the first pass's tokens come before the rest
+        if ev.token is not None:
+            out.setdefault(ev.id, []).insert(0, ev.token)
+    for rid, p in zip(rids, ps):                            # the third ran once the others had ended
+        assert out[rid] == expected(p, 4) and finishes[rid][0] == "length"
+    assert sched.stats().free_pages == sched.stats().pages
+
+    eng = FakeEngine(pages=4)                              # alone: the margin does not keep it out
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=256, max_sequences=8, reserve=0.9))
+    rid = sched.add(Request(prompt=ps[0], sampling=greedy, max_tokens=3))
+    out, finishes = run(sched)
+    assert out[rid] == expected(ps[0], 3)
