@@ -45,6 +45,10 @@ class PlainPlan:
     taken: List[Tuple[int, Hashable, int, int]] = field(default_factory=list)
     committed: bool = False
 
+    @property
+    def rows(self) -> int:
+        return int(self.positions.shape[0])
+
 
 class PlainCacheFull(RuntimeError):
     """A pool has fewer free pages than a step needs."""

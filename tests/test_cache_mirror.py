@@ -159,3 +159,31 @@ def test_a_step_batch_built_from_the_plan_holds_the_plain_arrays():
     m.commit(a)
     p.commit(b)
     same_state(m, p)
+
+
+def test_a_recorded_pass_s_staging_buffer_is_the_same_from_both_plans():
+    """`StaticBatch.fill_host` writes a decode pass (padding rows included) into a staging buffer; the
+    buffer written from the package's plan equals the one written from the plain plan. The staging
+    buffers are pinned in the engine; here plain host tensors stand in, so no GPU is needed."""
+    import torch
+
+    from kapel_b200.engine.graph import StaticBatch
+
+    m, p = pair([None, 40], [20, 20], 16, 6)
+    for c in (m, p):
+        for i, n in enumerate([70, 5, 33]):
+            c.add_sequence(i)
+            c.commit(c.plan([(i, n)]))
+    entries = [(2, 1), (0, 1), (1, 1)]
+    plans = m.plan(entries), p.plan(entries)
+    rows, width, n_groups = 4, 8, 2                              # a bucket of four rows: one padding row
+    buffers = []
+    for plan in plans:
+        static = StaticBatch.__new__(StaticBatch)
+        static.rows, static.width, static.turn = rows, width, 0
+        total = 6 * rows + n_groups * (rows + rows * width)
+        static.hosts = [torch.full((total,), 12345, dtype=torch.int32) for _ in range(2)]
+        assert static.fill_host(plan) == 0
+        buffers.append(static.hosts[0].numpy().copy())
+    assert np.array_equal(buffers[0][rows:], buffers[1][rows:])  # everything but the ids, which come later
+    assert not (buffers[0][rows:] == 12345).any()                # and every word of it was written
