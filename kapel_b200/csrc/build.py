@@ -148,7 +148,7 @@ def ensure_built(verbose: bool = True, force: bool = False) -> Path:
 # The host library: no CUDA in it, so it builds (in a second or two) and is tested where there is
 # neither a GPU nor nvcc.
 HOST_LIB_NAME = "libkapel_b200_host.so"
-HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall"]
+HOST_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-shared", "-Wall", "-pthread"]
 
 
 def host_sources():

@@ -28,7 +28,7 @@ from typing import Deque, Dict, List, Optional, Sequence
 import numpy as np
 
 from ..cache import CacheFull
-from ..sampling import Sampler, Sampling
+from ..sampling import Sampler, Sampling, choose_many
 from .step import StepEntry
 
 
@@ -352,5 +352,5 @@ class Scheduler:
             host = torch.tensor([temps, us], dtype=torch.float32).pin_memory()
             dev = host.to(logits.device, non_blocking=True)
             return K.sample(logits, dev[0], dev[1]).cpu().tolist()
-        rows = np.asarray(logits.detach().cpu().numpy() if hasattr(logits, "detach") else logits, dtype=np.float64)
-        return [e.sampler.choose(rows[i], e.sequence, e.prompt_len) for i, e in enumerate(entries)]
+        rows = logits.detach().cpu().numpy() if hasattr(logits, "detach") else np.asarray(logits)
+        return choose_many([e.sampler for e in entries], rows, [e.sequence for e in entries], [e.prompt_len for e in entries])
