@@ -26,6 +26,7 @@ import numpy as np
 from ..hostlib import host_library
 
 _M = (1 << 64) - 1
+_CPUS = os.cpu_count() or 1
 
 
 @dataclass
@@ -82,12 +83,13 @@ class Rng:
 
     def __init__(self, seed: int):
         self._lib = host_library()
-        self.state = (ctypes.c_ulonglong * 4)()
-        self._lib.ks_seed(seed & _M, ctypes.addressof(self.state))
+        self.state = np.zeros(4, np.uint64)
+        self._ptr = self.state.ctypes.data                  # the array is never replaced, only written
+        self._lib.ks_seed(seed & _M, self._ptr)
 
     @property
     def s(self) -> List[int]:
-        return [int(x) for x in self.state]
+        return self.state.tolist()
 
     @staticmethod
     def _rotl(x: int, k: int) -> int:
@@ -103,12 +105,11 @@ class Rng:
         s[0] ^= s[3]
         s[2] ^= t
         s[3] = self._rotl(s[3], 45)
-        for i in range(4):
-            self.state[i] = s[i]
+        self.state[:] = np.asarray(s, np.uint64)
         return result
 
     def uniform(self) -> float:
-        return self._lib.ks_uniform(ctypes.addressof(self.state))
+        return self._lib.ks_uniform(self._ptr)
 
 
 def _row(logits):
@@ -144,7 +145,7 @@ class Sampler:
         seq = self._sequence(sequence)
         return self.rng._lib.ks_choose(
             row.ctypes.data, code, row.shape[0], self._floats.ctypes.data, self._top_k, seq.ctypes.data, seq.shape[0],
-            int(generated_from), ctypes.addressof(self.rng.state), None if probs is None else probs.ctypes.data, want_draw)
+            int(generated_from), self.rng._ptr, None if probs is None else probs.ctypes.data, want_draw)
 
     def distribution(self, logits, sequence: Sequence[int], generated_from: int):
         """(token, None) when the choice is certain, else (None, probabilities in 64-bit).
@@ -177,16 +178,13 @@ def choose_many(samplers: Sequence[Sampler], rows: np.ndarray, sequences: Sequen
     seq_ptrs = (ctypes.c_void_p * count)(*[q.ctypes.data for q in seqs])
     seq_lens = np.asarray([q.shape[0] for q in seqs], np.int32)
     gen_from = np.asarray([int(g) for g in generated_from], np.int32)
-    states = np.empty((count, 4), np.uint64)
-    for i, s in enumerate(samplers):
-        states[i] = s.rng.s
+    states = np.stack([s.rng.state for s in samplers])
     tokens = np.empty(count, np.int32)
-    if threads is None:
-        threads = min(count, 8, os.cpu_count() or 1)
+    if threads is None:                                     # threads pay from a few hundred thousand logits on
+        threads = min(count, 8, _CPUS) if rows.size >= 200_000 else 1
     lib.ks_choose_many(count, rows.ctypes.data, rows.shape[1], code, rows.shape[1], floats.ctypes.data, top_k.ctypes.data,
                        ctypes.addressof(seq_ptrs), seq_lens.ctypes.data, gen_from.ctypes.data, states.ctypes.data,
                        tokens.ctypes.data, int(threads))
     for i, s in enumerate(samplers):
-        for j in range(4):
-            s.rng.state[j] = int(states[i, j])
+        s.rng.state[:] = states[i]
     return tokens.tolist()
