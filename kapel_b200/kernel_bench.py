@@ -6,6 +6,11 @@ For every kernel: device time by CUDA events (mean of `iters` launches after 3 w
 bytes it has to move, and the bandwidth that makes. Operands rotate through enough copies to
 exceed L2, so a launch never finds its weights or its cache pages in L2 from the launch before.
 Sizes default to Gemma 2 2B's; they are arguments, not constants of the package.
+
+    python -m kapel_b200.kernel_bench --host [--batch 8] [--history 6144] [--vocab 256000]
+
+times the host library instead (no GPU needed): planning and committing a decode step in the cache
+manager, and the host sampler's choice for one request and for the whole batch.
 """
 from __future__ import annotations
 
@@ -46,6 +51,42 @@ def _time(fn, iters, warm=3):
     return best / iters * 1e3
 
 
+def host_bench(args) -> int:
+    """Wall-clock times of the host library's calls at the given batch, history and vocabulary."""
+    import time
+
+    from .cache import CacheManager, CacheNeeds, PagedKV
+    from .sampling import Sampler, Sampling, choose_many
+
+    def clock(fn, n):
+        fn()
+        t0 = time.perf_counter()
+        for _ in range(n):
+            fn()
+        return (time.perf_counter() - t0) / n * 1e6
+
+    B = args.batch
+    needs = {0: CacheNeeds(paged=PagedKV(args.kv_heads, args.head_dim, args.window)), 1: CacheNeeds(paged=PagedKV(args.kv_heads, args.head_dim, None))}
+    pages = B * (-(-(args.history + 1024) // 16))
+    cache = CacheManager(needs, 16, pages, B)
+    for i in range(B):
+        cache.add_sequence(i)
+    cache.commit(cache.plan([(i, args.history) for i in range(B)]))
+    steps = [(i, 1) for i in range(B)]
+    print(f"cache manager, batch {B}, {args.history} positions each: plan + commit of a decode step "
+          f"{clock(lambda: cache.commit(cache.plan(steps)), 300):.1f} us")
+    rows = (np.random.default_rng(0).normal(size=(B, args.vocab)) * 3).astype(np.float32)
+    seq = list(range(100, 400))
+    for name, st in (("top_k 50", Sampling(temperature=1.0, top_k=50)), ("top_p 0.9", Sampling(temperature=0.8, top_p=0.9)),
+                     ("top_k 50, top_p 0.9, min_p 0.05, repetition 1.1", Sampling(temperature=0.8, top_k=50, top_p=0.9, min_p=0.05, repetition_penalty=1.1))):
+        one = Sampler(st)
+        many = [Sampler(st) for _ in range(B)]
+        t_one = clock(lambda: one.choose(rows[0], seq, 50), 10)
+        t_many = clock(lambda: choose_many(many, rows, [seq] * B, [50] * B), 10)
+        print(f"host sampler, {args.vocab} logits, {name}: one request {t_one / 1e3:.2f} ms, {B} at once {t_many / 1e3:.2f} ms")
+    return 0
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__.split("\n\n")[0])
     ap.add_argument("--batch", type=int, default=8)
@@ -60,7 +101,10 @@ def main(argv=None) -> int:
     ap.add_argument("--vocab", type=int, default=256000)
     ap.add_argument("--window", type=int, default=4096)
     ap.add_argument("--only", default="", help="comma-separated substrings of kernel names to run")
+    ap.add_argument("--host", action="store_true", help="time the host library (cache manager, host sampler) instead; no GPU needed")
     args = ap.parse_args(argv)
+    if args.host:
+        return host_bench(args)
 
     from . import kernels as K
     from .engine.batch import cut_tiles, decode_split, prompt_split, sm_count
