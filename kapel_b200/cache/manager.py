@@ -78,6 +78,7 @@ class Plan:
     taken: List[Tuple[int, Hashable, int, int]] = field(default_factory=list)  # (group, id, logical, physical)
     committed: bool = False
     native: object = None        # the manager's own: the entries as the host library takes them
+    added: List[Hashable] = field(default_factory=list)   # the step function's: sequences it added for this step
 
     @property
     def rows(self) -> int:

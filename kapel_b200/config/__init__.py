@@ -5,6 +5,8 @@ from .registry import (
     config_class_for,
     config_from_dir,
     config_from_json,
+    presets,
+    read_config_file,
     register_architecture,
     unregister_architecture,
 )

@@ -66,4 +66,30 @@ def config_from_dir(folder) -> Tuple[object, dict]:
     return config_from_json(raw), raw
 
 
+PRESETS = Path(__file__).resolve().parent / "presets"
+
+
+def presets() -> Tuple[str, ...]:
+    """Names of the config.json files that come with the package (`config/presets/NAME.json`)."""
+    return tuple(sorted(p.stem for p in PRESETS.glob("*.json")))
+
+
+def read_config_file(name_or_path) -> dict:
+    """The raw JSON of a config.json given by path, or of a preset given by name."""
+    path = Path(str(name_or_path))
+    if not path.is_file() and (PRESETS / f"{name_or_path}.json").is_file():
+        path = PRESETS / f"{name_or_path}.json"
+    if path.is_dir():
+        path = path / "config.json"
+    if not path.is_file():
+        raise ConfigError(f"{name_or_path}: neither a config.json nor one of the presets {list(presets())}")
+    try:
+        raw = json.loads(path.read_text())
+    except json.JSONDecodeError as e:
+        raise ConfigError(f"{path}: not JSON ({e})") from None
+    if not isinstance(raw, dict):
+        raise ConfigError(f"{path}: not a JSON object")
+    return raw
+
+
 register_architecture(Gemma2Config, Gemma2Config.architecture, Gemma2Config.model_type)

@@ -27,8 +27,7 @@ from pathlib import Path
 HERE = Path(__file__).resolve().parent
 LIB_NAME = "libkapel_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
-NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC", "--use_fast_math=false"]
-NVCC_FLAGS = [f for f in NVCC_FLAGS if f != "--use_fast_math=false"]
+NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]      # no fast-math: the 32-bit path is exact arithmetic
 
 
 def sources():

@@ -26,10 +26,8 @@ int check_launch(const char* what);      // cudaGetLastError -> fail(...)
 // (barriers, TMEM, the first tiles of weights) goes ahead of the wait. Off unless `kb_set_pdl(1)`.
 //
 // Only the kernels of a step of at most DEPENDENT_ROWS rows (decoding) are chained this way. The
-// kernels of a prompt are launched plainly: chained, two-layer and 46-layer passes of 2,048 tokens
-// at hidden 4608, 32 heads over 16 of size 128 and intermediate 36864 stopped now and then in the
-// middle of a pass (the stream stood still until the process ended; a copy on another stream still
-// ran), which the same passes launched plainly never did.
+// kernels of a prompt are launched plainly (`launch_dependent_if(false, ...)`): that is a rule of
+// this library, not a tuning choice, and it holds for every prompt kernel.
 constexpr int DEPENDENT_ROWS = 64;
 bool pdl_enabled();
 template <typename... KArgs, typename... Args>

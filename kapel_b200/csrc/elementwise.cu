@@ -198,10 +198,51 @@ __global__ void gather_rows_f32_kernel(float* __restrict__ out, const float* __r
         out[(size_t)i * width + c] = (r >= 0 && r < src_rows) ? x[(size_t)r * width + c] : __int_as_float(0x7fc00000);
 }
 
+// table[rows[i], :] = value for the rows listed; a row outside the table is skipped.
+__global__ void fill_rows_f32_kernel(float* __restrict__ table, const int* __restrict__ rows, int n, long long width,
+                                     int table_rows, float value) {
+    const int r = rows[blockIdx.y];
+    if (r < 0 || r >= table_rows) return;
+    const long long c = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (c < width) table[(size_t)r * width + c] = value;
+}
+
+// x[i] = value
+__global__ void fill_u32_kernel(unsigned* __restrict__ x, long long n, unsigned value) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = value;
+}
+__global__ void fill_u16_kernel(unsigned short* __restrict__ x, long long n, unsigned short value) {
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i < n) x[i] = value;
+}
+
 }  // namespace kb
 
 using namespace kb;
 typedef __nv_bfloat16 bf16;
+
+// table [table_rows, width] float32: the rows named in `rows` (n of them, on the device) become `value`.
+extern "C" int kb_fill_rows_f32(float* table, const int* rows, int n, long long width, int table_rows, float value, void* stream) {
+    KB_REQUIRE(n >= 0 && width >= 0 && table_rows >= 0, "fill_rows: n %d, width %lld, table rows %d", n, width, table_rows);
+    if (n == 0 || width == 0) return 0;
+    KB_REQUIRE(n <= 65535 && (width + 255) / 256 < (1ll << 31), "fill_rows: %d rows of %lld is too many for one launch", n, width);
+    fill_rows_f32_kernel<<<dim3((unsigned)((width + 255) / 256), n), 256, 0, (cudaStream_t)stream>>>(table, rows, n, width, table_rows, value);
+    return check_launch("fill_rows");
+}
+
+// Every element of a float32 (dt 0) or bfloat16 (dt 1) buffer becomes NaN: what a debugging run
+// puts into fresh buffers so that a kernel that reads what nobody wrote shows in the result.
+extern "C" int kb_poison(void* x, int dt, long long n, void* stream) {
+    KB_REQUIRE(n >= 0, "poison: %lld elements", n);
+    if (n == 0) return 0;
+    const unsigned blocks = (unsigned)((n + 255) / 256);
+    KB_REQUIRE((n + 255) / 256 < (1ll << 31), "poison: %lld elements is too many for one launch", n);
+    if (dt == KB_DT_F32) fill_u32_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((unsigned*)x, n, 0x7fc00000u);
+    else if (dt == KB_DT_BF16) fill_u16_kernel<<<blocks, 256, 0, (cudaStream_t)stream>>>((unsigned short*)x, n, (unsigned short)0x7fc0);
+    else return fail("poison: dtype code %d is not known", dt);
+    return check_launch("poison");
+}
 
 extern "C" int kb_embed(float* out, const void* table, int table_dt, const int* ids, int rows, int width,
                         int vocab, float scale, void* stream) {

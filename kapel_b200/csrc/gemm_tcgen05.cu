@@ -50,8 +50,8 @@ __device__ __forceinline__ void tc_mbar_init(uint64_t* bar, int count) {
 __device__ __forceinline__ void tc_mbar_expect_tx(uint64_t* bar, uint32_t bytes) {
     asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(tc_saddr(bar)), "r"(bytes) : "memory");
 }
-// false if the phase with this parity did not complete within ~1 s
-__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity) {
+// false if the phase with this parity did not complete within `limit` clocks (by default ~1 s)
+__device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity, long long limit = 2000000000ll) {
     const uint32_t addr = tc_saddr(bar);
     const long long start = clock64();
     for (;;) {
@@ -59,8 +59,24 @@ __device__ __forceinline__ bool tc_mbar_wait(uint64_t* bar, uint32_t parity) {
         asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
                      : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
         if (ok) return true;
-        if (clock64() - start > 2000000000ll) return false;
+        if (clock64() - start > limit) return false;
     }
+}
+
+// For the test of the error path only: one block whose first thread waits, with the products' own
+// wait and a limit given by the caller, on a barrier at which nobody ever arrives. The wait runs
+// out, the flag is raised as a product would raise it, the block meets at its barrier and returns.
+__global__ void wait_probe_kernel(long long limit) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        tc_mbar_init(&bar, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    __syncthreads();
+    bool failed = false;
+    if (threadIdx.x == 0) failed = !tc_mbar_wait(&bar, 0u, limit);
+    if (failed) atomicExch(&g_tcgen05_error, 1);
+    __syncthreads();
 }
 __device__ __forceinline__ void tc_tma_load_2d(void* dst, const CUtensorMap* map, int x, int y, uint64_t* bar) {
     asm volatile("cp.async.bulk.tensor.2d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
@@ -816,6 +832,15 @@ extern "C" int kb_tcgen05_error() {
     if (cudaMemcpyFromSymbol(&flag, g_tcgen05_error, sizeof(int)) != cudaSuccess) return -1;
     if (flag) cudaMemcpyToSymbol(g_tcgen05_error, &zero, sizeof(int));
     return flag;
+}
+
+// Makes a bounded wait run out on purpose, for the test of what follows it: one small block waits
+// `limit_clocks` (at most four million: about two milliseconds) on a barrier nobody arrives at,
+// raises the flag that kb_tcgen05_error reports and returns; the context stays usable.
+extern "C" int kb_wait_probe(long long limit_clocks, void* stream) {
+    KB_REQUIRE(limit_clocks > 0 && limit_clocks <= 4000000ll, "wait_probe: a limit of %lld clocks (1 to 4,000,000)", limit_clocks);
+    wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_clocks);
+    return check_launch("wait_probe");
 }
 
 // a: bf16 [m,k]; w: bf16 [n,k]; c: bf16 or f32 [m,n]. Any m, n; k a multiple of 8.

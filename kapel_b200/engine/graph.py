@@ -35,8 +35,13 @@ class StaticBatch:
         sizes = [rows] * 6 + [rows, rows * width] * n_groups
         self.total = sum(sizes)
         # Two pinned staging buffers taken in turn: the next pass can be written while the copy of
-        # the last one may still be in flight.
+        # the last one may still be in flight. Each has an event recorded behind its copy; the host
+        # waits for it before it writes that buffer again, so a caller that enqueues pass after
+        # pass without synchronising is held back once it is two passes ahead of the device and
+        # never rewrites inputs that a copy has yet to read.
         self.hosts = [torch.empty((self.total,), dtype=torch.int32, pin_memory=True) for _ in range(2)]
+        self.copied = [torch.cuda.Event() for _ in range(2)]
+        self.in_flight = [False, False]
         self.turn = 0
         self.dev = torch.empty((self.total,), dtype=torch.int32, device=device)
         views, at = [], 0
@@ -83,6 +88,8 @@ class StaticBatch:
     def upload(self, which: int) -> None:
         """One copy of everything a pass reads; the other staging buffer takes the next pass."""
         self.dev.copy_(self.hosts[which], non_blocking=True)
+        self.copied[which].record()
+        self.in_flight[which] = True
         self.turn = which ^ 1
 
     def fill_host(self, plan) -> int:
@@ -91,6 +98,9 @@ class StaticBatch:
         n = plan.rows
         rows, width = self.rows, self.width
         which = self.turn
+        if self.in_flight[which]:
+            self.copied[which].synchronize()                 # the copy that last read this buffer is done
+            self.in_flight[which] = False
         flat = self.hosts[which].numpy()
         at = rows                                            # the ids come first
 
@@ -117,6 +127,13 @@ class StaticBatch:
         return which
 
 
+RETRY_AFTER = 256        # passes before a size that could not be recorded is tried again (crates/kapel-infer/src/engine.rs:521-526)
+
+
+class CaptureFailed(RuntimeError):
+    """A decode pass could not be recorded; the pass itself is not lost (it runs eagerly)."""
+
+
 class DecodeGraphs:
     def __init__(self, engine, max_rows: int):
         # A weak reference: an engine and its recordings must not form a cycle, or an engine that
@@ -128,6 +145,12 @@ class DecodeGraphs:
         self.replays = 0
         self.replayed_kernels = 0      # kernels that ran inside replays (the library counts only launches it makes itself)
         self.pool = None
+        self.passes = 0                # decode passes offered to `run`, recorded or not
+        self.unrecordable: Dict[Tuple[int, int], int] = {}     # bucket -> the pass at which its recording failed
+        self.failed_captures = 0
+        self.last_capture_error: Optional[str] = None
+        # Failure injection on the host, for tests: this many of the next recordings raise inside the capture.
+        self.fail_next_captures = 0
 
     def bucket(self, rows: int, width: int) -> Optional[Tuple[int, int]]:
         for b in ROW_BUCKETS:
@@ -152,20 +175,22 @@ class DecodeGraphs:
         static.upload(which)
         graph.replay()
         self.replays += 1
+        self.passes += 1
         self.replayed_kernels += static.kernels
         eng = self._engine()
         eng.last_h2d_bytes = static.h2d_bytes
         return out[: plan.rows]
 
-    def run(self, plan, ids) -> Optional[torch.Tensor]:
-        """Logits [rows, vocab] of a decode-only plan through a recording, or None if no bucket
-        takes it. The result is a view of the recording's output: use it before the next replay."""
-        width = max(g.block_table.shape[1] for g in plan.groups) if plan.groups else 1
-        key = self.bucket(plan.rows, width)
-        if key is None:
-            return None
+    def _record(self, key, plan, ids):
+        """Records the pass of `plan` for bucket `key`. Raises `CaptureFailed` if anything goes wrong
+        between the first eager run and the end of the capture; by then the capture has been ended and
+        what it made has been dropped, so the stream is usable and the pass can run eagerly
+        (Kapel: crates/kapel-cuda/src/graph.rs:107-123, crates/kapel-models/src/model.rs:1169-1181)."""
         eng = self._engine()
-        if key not in self.graphs:
+        from .. import kernels as K
+
+        graph = None
+        try:
             static = StaticBatch(key[0], key[1], len(plan.groups), eng.device, eng.chunk, eng.cache.page_size)
             static.fill(plan, ids)
             # Once eagerly on a side stream (kernels set their attributes, the allocator warms up), then the capture.
@@ -176,21 +201,50 @@ class DecodeGraphs:
             torch.cuda.current_stream().wait_stream(side)
             graph = torch.cuda.CUDAGraph()
             static.memo.clear()
-            from .. import kernels as K
-
             before = K.launch_count()
             collecting = gc.isenabled()
             gc.disable()                   # nothing may be destroyed while the stream is capturing
             try:
                 with torch.cuda.graph(graph, pool=self.pool):
+                    if self.fail_next_captures > 0:
+                        self.fail_next_captures -= 1
+                        raise RuntimeError("injected: the capture was made to fail")
                     out = eng.model.forward(static, eng.cache)
             finally:
                 if collecting:
                     gc.enable()
             static.kernels = K.launch_count() - before
-            if self.pool is None:
-                self.pool = graph.pool()
-            self.graphs[key] = (graph, static, out)
+        except Exception as e:
+            del graph                       # what the capture made so far goes with it
+            static = None
+            raise CaptureFailed(f"{type(e).__name__}: {e}") from e
+        if self.pool is None:
+            self.pool = graph.pool()
+        self.graphs[key] = (graph, static, out)
+
+    def run(self, plan, ids) -> Optional[torch.Tensor]:
+        """Logits [rows, vocab] of a decode-only plan through a recording, or None if no bucket
+        takes it or its bucket cannot be recorded (now): the caller then runs the pass eagerly. A
+        recording that fails loses only itself; its bucket is tried again `RETRY_AFTER` passes later.
+        The result is a view of the recording's output: use it before the next replay."""
+        width = max(g.block_table.shape[1] for g in plan.groups) if plan.groups else 1
+        key = self.bucket(plan.rows, width)
+        self.passes += 1
+        if key is None:
+            return None
+        eng = self._engine()
+        if key not in self.graphs:
+            failed_at = self.unrecordable.get(key)
+            if failed_at is not None and self.passes - failed_at < RETRY_AFTER:
+                return None
+            try:
+                self._record(key, plan, ids)
+            except CaptureFailed as e:
+                self.unrecordable[key] = self.passes
+                self.failed_captures += 1
+                self.last_capture_error = str(e)
+                return None
+            self.unrecordable.pop(key, None)
         graph, static, out = self.graphs[key]
         static.fill(plan, ids)
         graph.replay()

@@ -44,7 +44,7 @@ class ModelParts:
     def cache_needs(self) -> Dict[int, CacheNeeds]:
         """What each cache-owning layer keeps: layers named as `cache_of` in the schedule."""
         owners = sorted({e.cache_of for e in self.spec.schedule})
-        return {l: self.blocks[l].mixer.cache_needs() for l in owners}
+        return {l: self.blocks[l].cache_needs() for l in owners}
 
     def forward(self, batch, cache_manager) -> torch.Tensor:
         """float32 logits [wanted rows, vocab] of a step."""
@@ -53,7 +53,7 @@ class ModelParts:
         h = None
         for i, e in enumerate(schedule):
             block = self.blocks[e.layer]
-            nxt = self.blocks[schedule[i + 1].layer].norms.get("pre_mixer") if i + 1 < len(schedule) else None
+            nxt = self.blocks[schedule[i + 1].layer].first_norm() if i + 1 < len(schedule) else None
             cache = LayerCache(cache_manager, e.cache_of, owns=(e.cache_of == e.layer))
             x, h = block.forward(x, h, batch, cache, nxt)
         rows = K.gather_rows(x, batch.want_rows)

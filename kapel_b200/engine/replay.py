@@ -5,6 +5,11 @@ generation uses, with its cache and kernels. Kapel has no such program; the near
 parity checks (crates/kapel-models/examples/parity.rs:11-58, crates/kapel-models/tests/parity.rs:43-65).
 
     trace_run --model DIR --dtype bfloat16|float32 --out DIR --max-tokens N
+    trace_run --random CONFIG --seed-weights S --dtype ... --out DIR --max-tokens N
+
+`--random` takes the place of `--model`: a model of CONFIG (a config.json, or the name of one
+that comes with the package) with random weights made on the device from the seed, for sizes
+whose folder nobody wants to write.
 
 Steps come on standard input, one JSON object a line:
 
@@ -24,7 +29,9 @@ from pathlib import Path
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(prog="trace_run", description=__doc__.split("\n\n")[0])
-    ap.add_argument("--model", required=True, help="a folder with config.json and model.safetensors")
+    ap.add_argument("--model", help="a folder with config.json and model.safetensors")
+    ap.add_argument("--random", metavar="CONFIG", help="instead of --model: random weights for this config.json (a path, or a preset's name)")
+    ap.add_argument("--seed-weights", type=int, default=0, help="the seed of --random's weights (default 0)")
     ap.add_argument("--dtype", required=True, choices=["bfloat16", "float32"])
     ap.add_argument("--out", required=True, help="the folder that receives <step>.f32")
     ap.add_argument("--max-tokens", type=int, required=True,
@@ -32,14 +39,22 @@ def main(argv=None) -> int:
     args = ap.parse_args(argv)
     if args.max_tokens <= 0:
         ap.error("--max-tokens must be positive")
+    if (args.model is None) == (args.random is None):
+        ap.error("give either --model DIR or --random CONFIG")
 
     out = Path(args.out)
     out.mkdir(parents=True, exist_ok=True)
-    print(f"trace_run: loading {args.model} ({args.dtype}); kernels are compiled at the first call", file=sys.stderr, flush=True)
+    print(f"trace_run: loading {args.model or args.random} ({args.dtype}); kernels are compiled at the first call", file=sys.stderr, flush=True)
 
     from .step import Engine, StepEntry
 
-    engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens, max_sequences=16)
+    if args.random is not None:
+        from ..config import read_config_file
+
+        engine = Engine.random(read_config_file(args.random), seed=args.seed_weights, dtype=args.dtype,
+                               max_tokens=args.max_tokens, max_sequences=16)
+    else:
+        engine = Engine.from_dir(args.model, dtype=args.dtype, max_tokens=args.max_tokens, max_sequences=16)
     print("trace_run: ready", file=sys.stderr, flush=True)
 
     for line in sys.stdin:

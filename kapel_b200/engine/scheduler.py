@@ -15,8 +15,15 @@ The policy is Kapel's `Engine` (crates/kapel-infer/src/engine.rs):
   * if a pass fails every running request ends (:463-476).
 Pages are counted per layer group: a pass fits when every group has the pages it needs.
 
+A model with a limit on positions (`engine.max_positions`, config.json's
+max_position_embeddings; Kapel has no such limit) is handled here, not in the step function: a
+prompt longer than the limit is refused when it is added, and a request whose next token would
+have to be fed beyond the limit ends with "length". The step function's own refusal is thus
+never met, and one long request cannot end the others.
+
 The scheduler needs of its engine only `cache` (a CacheManager), `step(entries)`, `end(id)` and
-`vocab_size`, so its decisions are tested on the CPU with a stand-in.
+`vocab_size` (and reads `max_positions` and `new_request_ids()` where they exist), so its
+decisions are tested on the CPU with a stand-in.
 """
 from __future__ import annotations
 
@@ -95,7 +102,19 @@ class Scheduler:
         self.entries: Dict[int, _Entry] = {}
         self.waiting: Deque[int] = deque()
         self.running: List[int] = []
-        self._ids = itertools.count()
+        # Request ids name sequences in the engine's one cache, so every scheduler over an engine
+        # draws them from the engine's counter: two schedulers alive at once (a stream not yet
+        # exhausted beside another call, a user's scheduler beside generate()) never share a name.
+        ids = getattr(engine, "new_request_ids", None)
+        if ids is not None:
+            self._ids = ids()
+        else:
+            self._ids = getattr(engine, "_request_ids", None) or itertools.count()
+            try:
+                engine._request_ids = self._ids
+            except AttributeError:
+                pass
+        self.limit = getattr(engine, "max_positions", None)
         self.preemptions = 0
         self.passes = 0
         self.staged = None            # (request ids, engine handle) of a decode pass staged ahead of its tokens
@@ -109,6 +128,8 @@ class Scheduler:
         for t in request.prompt:
             if not 0 <= int(t) < vocab:
                 raise ValueError(f"prompt token {t} is outside the vocabulary (0..{vocab - 1})")
+        if self.limit is not None and len(request.prompt) > self.limit:
+            raise ValueError(f"a prompt of {len(request.prompt)} tokens is longer than the {self.limit} positions the model allows")
         rid = next(self._ids)
         self.entries[rid] = _Entry(request)
         self.waiting.append(rid)
@@ -265,6 +286,8 @@ class Scheduler:
             entry = self.entries[rid]
             if entry.generated + 1 >= entry.request.max_tokens:
                 return
+            if self.limit is not None and len(entry.sequence) + 1 > self.limit:
+                return
         handle = prepare(list(self.running))
         if handle is not None:
             self.staged = (list(self.running), handle)
@@ -330,6 +353,8 @@ class Scheduler:
                 return "stop"
         if entry.generated >= req.max_tokens:
             return "length"
+        if self.limit is not None and len(entry.sequence) > self.limit:
+            return "length"                 # the token just given would have to be fed at a position beyond the limit
         return None
 
     # ------------------------------------------------------------------ choosing tokens

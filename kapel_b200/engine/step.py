@@ -8,6 +8,7 @@ enqueued; if anything fails before, the pages the plan took go back.
 """
 from __future__ import annotations
 
+import itertools
 import json
 from dataclasses import dataclass, field
 from pathlib import Path
@@ -19,7 +20,7 @@ from .. import kernels as K
 from ..cache import CacheFull, CacheManager
 from ..config import config_from_dir, config_from_json
 from ..parts import BuildContext
-from ..weights import check_names, load_tensors, random_tensors
+from ..weights import RandomSource, check_names, open_weights
 from .batch import StepBatch
 from .model import ModelParts
 
@@ -67,7 +68,7 @@ class Engine:
 
     def __init__(self, config, tensors, dtype="bfloat16", max_tokens: int = 8192, max_sequences: int = 64,
                  device: Optional[torch.device] = None, pages: Optional[int] = None, raw_config: Optional[dict] = None,
-                 graphs: bool = True):
+                 graphs: bool = True, strict: bool = False):
         self.device = device or require_device()
         self.dtype = parse_dtype(dtype)
         self.config = config
@@ -76,8 +77,17 @@ class Engine:
         ctx = BuildContext(dtype=self.dtype, device=self.device, page_size=PAGE_SIZE)
         self.ctx = ctx
         self.model = ModelParts(self.spec, ctx)
-        check_names(self.model.expected_tensors(), {n: tuple(t.shape) for n, t in tensors.items()}, "the given tensors")
+        # `tensors` is a mapping from name to tensor: a dict of device tensors, or a source that reads
+        # (or makes) a tensor when it is asked for. Names and shapes are checked before anything is
+        # read; tensors the model does not name are an error only when `strict`.
+        expected = self.model.expected_tensors()
+        if hasattr(tensors, "check"):
+            self.unexpected_tensors = list(tensors.check(expected, strict))
+        else:
+            self.unexpected_tensors = check_names(expected, {n: tuple(t.shape) for n, t in tensors.items()},
+                                                  "the given tensors", strict)
         self.model.load(tensors)
+        ctx.prepared.clear()               # the parts hold what they use
         n_pages = pages if pages is not None else -(-max_tokens // PAGE_SIZE)
         self.cache = CacheManager(
             self.model.cache_needs(), PAGE_SIZE, n_pages, max_sequences,
@@ -86,6 +96,7 @@ class Engine:
         self.chunk = K.attention_chunk()
         self.steps = 0
         self.last_h2d_bytes = 0
+        self._request_ids = itertools.count()
         from .graph import DecodeGraphs
 
         self.graphs = DecodeGraphs(self, max_sequences) if (graphs and self.model.graph_safe()) else None
@@ -95,10 +106,11 @@ class Engine:
     def from_dir(cls, folder, dtype="bfloat16", **kw) -> "Engine":
         config, raw = config_from_dir(folder)
         device = kw.pop("device", None) or require_device()
-        from ..parts import expected_tensors
-
-        tensors = load_tensors(folder, expected_tensors(config.to_spec()), device)
-        return cls(config, tensors, dtype=dtype, device=device, raw_config=raw, **kw)
+        source = open_weights(folder, device)
+        try:
+            return cls(config, source, dtype=dtype, device=device, raw_config=raw, **kw)
+        finally:
+            source.close()
 
     @classmethod
     def random(cls, config, seed: int = 0, dtype="bfloat16", **kw) -> "Engine":
@@ -107,8 +119,7 @@ class Engine:
         if isinstance(config, dict):
             config = config_from_json(config)
         device = kw.pop("device", None) or require_device()
-        tensors = random_tensors(config, seed, device=device)
-        return cls(config, tensors, dtype=dtype, device=device, **kw)
+        return cls(config, RandomSource(config, seed, device=device), dtype=dtype, device=device, raw_config=config.to_json(), **kw)
 
     def _allocate(self, shape, dtype):
         if isinstance(dtype, str):
@@ -159,11 +170,19 @@ class Engine:
             for seq_id in added:
                 self.cache.remove_sequence(seq_id)
             raise
+        plan.added = added                 # requests this step brought into the cache: they leave again if it fails
         return plan, ids, want_rows
 
     def step(self, entries: Sequence[StepEntry]) -> torch.Tensor:
         """Runs one batch; returns float32 logits [number of wanted places, vocab] on the device,
-        in the order of the entries and of each entry's `want`."""
+        in the order of the entries and of each entry's `want`.
+
+        The step is enqueued on the current stream and not waited for. The logits of a pass in
+        which every request brings one token may be a view of a recorded step's output buffer,
+        which the next such pass overwrites: read them (or enqueue what reads them, on the same
+        stream) before the next step, or clone them. A caller may enqueue step after step without
+        synchronising; the inputs of recorded steps are staged so that this is safe, and the
+        host is held back once it is two recorded steps ahead of the device."""
         entries = [e if isinstance(e, StepEntry) else StepEntry(*e) for e in entries]
         if not entries:
             return torch.empty((0, self.spec.vocab_size), dtype=torch.float32, device=self.device)
@@ -180,6 +199,9 @@ class Engine:
                 logits = self.model.forward(batch, self.cache)
         except Exception:
             self.cache.abort(plan)
+            for seq_id in getattr(plan, "added", ()):      # a request that came with this step leaves with it
+                if seq_id in self.cache:
+                    self.cache.remove_sequence(seq_id)
             raise
         self.cache.commit(plan)
         self.steps += 1
@@ -236,9 +258,21 @@ class Engine:
     def _clear_fresh_state(self, plan) -> None:
         if not self.cache.states or not plan.fresh.any():
             return
-        slots = torch.as_tensor(plan.slots[plan.fresh], dtype=torch.long, device=self.device)
+        host = torch.from_numpy(plan.slots[plan.fresh].astype("int32")).pin_memory()
+        slots = host.to(self.device, non_blocking=True)
         for table in self.cache.states.values():
-            table.index_fill_(0, slots, 0)
+            K.fill_rows(table, slots, 0.0)
+        self._fresh_slots_host = host          # pinned memory must outlive its copy
+
+    @property
+    def max_positions(self) -> Optional[int]:
+        """The most positions a request may reach (config.json's max_position_embeddings), or None."""
+        return self.spec.max_positions
+
+    def new_request_ids(self):
+        """The counter that every scheduler over this engine draws its request ids from, so that two
+        schedulers alive at once never give two requests the same name in the one cache."""
+        return self._request_ids
 
     @property
     def recorded_passes(self) -> int:

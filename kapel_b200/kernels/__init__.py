@@ -79,6 +79,13 @@ def check_async_errors() -> None:
         raise KernelError("a wait inside a kernel gave up after its time limit: " + "; ".join(bad))
 
 
+def wait_probe(limit_clocks: int = 2_000_000) -> None:
+    """Launches one small block whose bounded wait (the products' own) runs out after
+    `limit_clocks` because nothing ever arrives at its barrier. For testing that the flag reaches
+    `check_async_errors` and that the device goes on working afterwards."""
+    _check(library().kb_wait_probe(ctypes.c_longlong(int(limit_clocks)), _stream()))
+
+
 def launch_count() -> int:
     """Kernels launched (or recorded under a graph capture) by this library so far."""
     return int(library().kb_launch_count())
@@ -127,6 +134,52 @@ def _f(x: float) -> ctypes.c_float:
     return ctypes.c_float(float(x))
 
 
+# With KAPEL_B200_POISON=1 every buffer a kernel is about to write (outputs, scratch, split-K partial
+# sums) is first filled with NaN, so that a kernel which reads what nobody wrote, or leaves part
+# of its output unwritten, shows in the logits instead of passing on whatever the allocator left
+# there. Kapel's debugging switch of the same kind is `poison_buffers` (crates/kapel-cuda/src/device.rs:1019).
+POISON = _os.environ.get("KAPEL_B200_POISON", "0") == "1"
+
+
+def set_poison(on: bool) -> None:
+    global POISON
+    POISON = bool(on)
+
+
+_fail_allocation_in = 0
+
+
+def fail_allocation_in(calls: int) -> None:
+    """Failure injection on the host, for tests: the `calls`-th buffer asked for from now on is
+    refused with torch's out-of-memory error, as if the device had no room (0 turns it off)."""
+    global _fail_allocation_in
+    _fail_allocation_in = int(calls)
+
+
+def _fresh(shape, dtype, device) -> torch.Tensor:
+    """A new buffer for a kernel to write; NaN all over in the poisoning mode."""
+    global _fail_allocation_in
+    if _fail_allocation_in > 0:
+        _fail_allocation_in -= 1
+        if _fail_allocation_in == 0:
+            raise torch.OutOfMemoryError(f"injected: no room for a buffer of shape {tuple(shape)}")
+    t = torch.empty(tuple(shape), dtype=dtype, device=device)
+    if POISON and dtype in _CODES and t.numel():
+        _check(library().kb_poison(_ptr(t), _CODES[dtype], ctypes.c_longlong(t.numel()), _stream()))
+    return t
+
+
+def fill_rows(table: torch.Tensor, rows: torch.Tensor, value: float = 0.0) -> None:
+    """table[rows[i]] = value for a float32 table [n, ...] and int32 row numbers on the device."""
+    _need(table, "fill_rows table", torch.float32)
+    _need(rows, "fill_rows rows", torch.int32)
+    if table.dim() < 1 or table.shape[0] == 0 or rows.numel() == 0:
+        return
+    width = table.numel() // table.shape[0]
+    _check(library().kb_fill_rows_f32(_ptr(table), _ptr(rows), int(rows.numel()), ctypes.c_longlong(width), int(table.shape[0]),
+                                      _f(value), _stream()))
+
+
 class SplitSum:
     """A product that is still a stack of split-K partial sums: `partials` is float32
     [splits, rows, cols] and the value is their sum over the first dimension. The kernels that
@@ -165,7 +218,7 @@ def finish(x, dtype: torch.dtype) -> torch.Tensor:
     """A SplitSum added up into a tensor of `dtype`; a tensor as it is (cast if need be)."""
     if isinstance(x, SplitSum):
         _need(x.partials, "finish partials", torch.float32)
-        out = torch.empty(x.shape, dtype=dtype, device=x.device)
+        out = _fresh(x.shape, dtype, x.device)
         _check(library().kb_splitk_reduce(_ptr(out), _dt(out, "finish output"), _ptr(x.partials),
                                           ctypes.c_longlong(out.numel()), x.splits, _stream()))
         return out
@@ -180,7 +233,7 @@ def embed(table: torch.Tensor, ids: torch.Tensor, scale: float, out: Optional[to
     vocab, width = table.shape
     rows = ids.numel()
     if out is None:
-        out = torch.empty((rows, width), dtype=torch.float32, device=table.device)
+        out = _fresh((rows, width), torch.float32, table.device)
     _need(out, "embed out", torch.float32, (rows, width))
     _check(library().kb_embed(_ptr(out), _ptr(table), _dt(table, "embed table"), _ptr(ids), rows, width, vocab, _f(scale), _stream()))
     return out
@@ -190,7 +243,7 @@ def rope_table(positions: torch.Tensor, rotary: int, theta: float) -> torch.Tens
     """[rows, rotary/2, 2] float32 of (cos, sin); angles in float64 on the device."""
     _need(positions, "rope positions", torch.int32)
     rows = positions.numel()
-    out = torch.empty((rows, rotary // 2, 2), dtype=torch.float32, device=positions.device)
+    out = _fresh((rows, rotary // 2, 2), torch.float32, positions.device)
     _check(library().kb_rope_table(_ptr(out), _ptr(positions), rows, int(rotary), ctypes.c_double(float(theta)), _stream()))
     return out
 
@@ -207,7 +260,7 @@ def rope_append(qkv, cos_sin, lines, k_table, v_table, hq: int, hkv: int, d: int
     out_dtype = out_dtype or (src.dtype if not isinstance(qkv, SplitSum) else k_table.dtype)
     if rotary:
         _need(cos_sin, "rope_append cos_sin", torch.float32, (rows, rotary // 2, 2))
-    q = torch.empty((rows, hq, d), dtype=out_dtype, device=src.device)
+    q = _fresh((rows, hq, d), out_dtype, src.device)
     table_lines, page_size = 0, 0
     if write_kv:
         _need(lines, "rope_append lines", torch.int32, (rows,))
@@ -235,7 +288,7 @@ def glu(x, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Te
     rows, two_n = x.shape
     n = two_n // 2
     out_dtype = out_dtype or (src.dtype if not isinstance(x, SplitSum) else torch.bfloat16)
-    out = torch.empty((rows, n), dtype=out_dtype, device=src.device)
+    out = _fresh((rows, n), out_dtype, src.device)
     _check(library().kb_glu(_ptr(out), _dt(out, "glu output"), _ptr(src), in_dt, splits, ctypes.c_longlong(stride),
                             ctypes.c_longlong(rows), n, ACT_CODES[activation], _stream()))
     return out
@@ -243,7 +296,7 @@ def glu(x, activation: str, out_dtype: Optional[torch.dtype] = None) -> torch.Te
 
 def cast(x: torch.Tensor, dtype: torch.dtype) -> torch.Tensor:
     _need(x, "cast input")
-    out = torch.empty(x.shape, dtype=dtype, device=x.device)
+    out = _fresh(x.shape, dtype, x.device)
     _check(library().kb_cast(_ptr(out), _dt(out, "cast output"), _ptr(x), _dt(x, "cast input"), ctypes.c_longlong(x.numel()), _stream()))
     return out
 
@@ -252,7 +305,7 @@ def gather_rows(x: torch.Tensor, rows: torch.Tensor) -> torch.Tensor:
     _need(x, "gather_rows input", torch.float32)
     _need(rows, "gather_rows rows", torch.int32)
     n, width = rows.numel(), x.shape[1]
-    out = torch.empty((n, width), dtype=torch.float32, device=x.device)
+    out = _fresh((n, width), torch.float32, x.device)
     _check(library().kb_gather_rows_f32(_ptr(out), _ptr(x), _ptr(rows), n, width, x.shape[0], _stream()))
     return out
 
@@ -261,7 +314,7 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, offset: float, ou
     _need(x, "rmsnorm input")
     rows, width = x.shape
     _need(weight, "rmsnorm weight", shape=(width,))
-    y = torch.empty((rows, width), dtype=out_dtype, device=x.device)
+    y = _fresh((rows, width), out_dtype, x.device)
     _check(
         library().kb_rmsnorm(_ptr(y), _dt(y, "rmsnorm output"), _ptr(x), _dt(x, "rmsnorm input"), _ptr(weight),
                              _dt(weight, "rmsnorm weight"), rows, width, _f(eps), _f(offset), _stream())
@@ -286,7 +339,7 @@ def add_rmsnorm(residual, branch, post, nxt, out_dtype):
     if len({w.dtype for w in ws}) > 1:
         raise KernelError("add_rmsnorm: the two norms' weights differ in dtype; call the norms one by one")
     w_dt = _dt(ws[0], "add_rmsnorm weight") if ws else F32
-    h = torch.empty((rows, width), dtype=out_dtype, device=residual.device) if w_next is not None else None
+    h = _fresh((rows, width), out_dtype, residual.device) if w_next is not None else None
     _check(
         library().kb_add_rmsnorm(_ptr(residual), _ptr(src), b_dt, splits, ctypes.c_longlong(stride), _ptr(w_post), _f(eps_post),
                                  _f(off_post), _ptr(w_next), _f(eps_next), _f(off_next), _ptr(h), _CODES[out_dtype], w_dt,
@@ -312,7 +365,7 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
     epi, cap = (1, softcap) if softcap is not None else (0, 0.0)
     lib = library()
     if a.dtype == torch.float32:
-        out = torch.empty((m, n), dtype=torch.float32, device=a.device)
+        out = _fresh((m, n), torch.float32, a.device)
         _check(lib.kb_gemm_f32(_ptr(out), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
         if out_dtype is not None and out_dtype != torch.float32:
             out = cast(out, out_dtype)
@@ -321,11 +374,11 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
     if 0 < m <= 64 and GEMM_SMALL == "skinny":
         splits = int(lib.kb_gemm_skinny_splits(n, k))
         if splits == 1:
-            out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+            out = _fresh((m, n), out_dtype, a.device)
             _check(lib.kb_gemm_skinny(_ptr(out), _dt(out, "gemm output"), None, _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
             return out
         if softcap is None:
-            partials = torch.empty((splits, m, n), dtype=torch.float32, device=a.device)
+            partials = _fresh((splits, m, n), torch.float32, a.device)
             _check(lib.kb_gemm_skinny(None, 0, _ptr(partials), _ptr(a), _ptr(w), m, n, k, 0, _f(0.0), _stream()))
             split_sum = SplitSum(partials)
             return split_sum if keep_split else finish(split_sum, out_dtype)
@@ -333,16 +386,16 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
     if keep_split and softcap is None and 0 < m <= 16:
         splits = int(lib.kb_gemm_bf16_row16_splits(n, k))
         if splits > 1:
-            partials = torch.empty((splits, m, n), dtype=torch.float32, device=a.device)
+            partials = _fresh((splits, m, n), torch.float32, a.device)
             _check(lib.kb_gemm_bf16_partial(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
             return SplitSum(partials)
-    out = torch.empty((m, n), dtype=out_dtype, device=a.device)
+    out = _fresh((m, n), out_dtype, a.device)
     if m > 64 and GEMM_LARGE in _TCGEN05_KERNELS:
         _check(lib.kb_gemm_tcgen05(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap),
                                    _TCGEN05_KERNELS[GEMM_LARGE], _stream()))
         return out
     need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
-    scratch = torch.empty((need,), dtype=torch.float32, device=a.device) if need else None
+    scratch = _fresh((need,), torch.float32, a.device) if need else None
     _check(lib.kb_gemm_bf16(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _ptr(scratch), _stream()))
     return out
 
@@ -367,7 +420,7 @@ def gemm_glu_fused(a: torch.Tensor, w: torch.Tensor, act: str) -> Optional[torch
     n2, k2 = w.shape
     if k != k2 or n2 % 2:
         raise KernelError(f"gemm_glu: input [{m}, {k}] against stacked weight [{n2}, {k2}]")
-    out = torch.empty((m, n2 // 2), dtype=torch.bfloat16, device=a.device)
+    out = _fresh((m, n2 // 2), torch.bfloat16, a.device)
     if few:
         _check(library().kb_gemm_skinny_glu(_ptr(out), _ptr(a), _ptr(w), m, n2 // 2, k, ACT_CODES[act], _stream()))
         return out
@@ -399,10 +452,10 @@ def paged_attention_rows(q, k_table, v_table, block_table, row_entry, row_count,
     _need(block_table, "attention block table", torch.int32)
     _need(row_entry, "attention row_entry", torch.int32, (rows,))
     _need(row_count, "attention row_count", torch.int32, (rows,))
-    out = torch.empty_like(q)
+    out = _fresh(q.shape, q.dtype, q.device)
     lib = library()
     need = lib.kb_paged_attention_scratch_floats(rows, hq, d, int(slots))
-    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    scratch = _fresh((need,), torch.float32, q.device) if need else None
     _check(
         lib.kb_paged_attention_rows(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _dt(q, "attention q"), _ptr(block_table),
                                     _ptr(row_entry), _ptr(row_count), rows, hq, hkv, d, int(page_size), int(block_table.shape[1]),
@@ -451,10 +504,10 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
         _need(t, "attention tiles", torch.int32, (n_tiles,))
     _need(block_table, "attention block table", torch.int32)
     _need(row_count, "attention row_count", torch.int32, (rows,))
-    out = torch.empty_like(q)
+    out = _fresh(q.shape, q.dtype, q.device)
     lib = library()
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
-    scratch = torch.empty((need,), dtype=torch.float32, device=q.device) if need else None
+    scratch = _fresh((need,), torch.float32, q.device) if need else None
     if not decode and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
         _check(
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
@@ -483,7 +536,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
     if temperature is not None:
         _need(temperature, "sample temperature", torch.float32, (rows,))
         _need(uniform, "sample uniform", torch.float32, (rows,))
-    out = torch.empty((rows,), dtype=torch.int32, device=logits.device)
+    out = _fresh((rows,), torch.int32, logits.device)
     _check(library().kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _stream()))
     return out
 

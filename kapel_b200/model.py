@@ -30,7 +30,13 @@ _KV_NAMES = {"f32": "float32", "bf16": "bfloat16", "float32": "float32", "bfloat
 class Model:
     def __init__(self, name, device: str = "cuda", dtype: Optional[str] = None, quantize: Optional[str] = None,
                  kv_cache: Optional[str] = None, revision: str = "main", max_tokens_cached: int = 65536,
-                 max_sequences: int = 256, _engine: Optional[Engine] = None):
+                 max_sequences: int = 256, pages: Optional[int] = None, max_pass_tokens: int = 2048, strict: bool = False,
+                 _engine: Optional[Engine] = None):
+        """`pages` sizes every layer group's page pool (else `max_tokens_cached` / 16 pages);
+        `max_pass_tokens` is the most tokens one pass of `generate` holds (the portions a prompt is
+        cut into); `strict` makes a tensor of the file that the model does not name an error."""
+        self.max_pass_tokens = int(max_pass_tokens)
+        self.max_sequences = int(max_sequences)
         if quantize is not None:
             raise KapelError("quantized weights are not built in this engine")
         if not str(device).startswith("cuda"):
@@ -49,17 +55,24 @@ class Model:
                 torch.cuda.set_device(index)
             self.folder = Path(name)
             try:
-                self.engine = Engine.from_dir(self.folder, dtype=self.dtype, max_tokens=max_tokens_cached, max_sequences=max_sequences)
+                self.engine = Engine.from_dir(self.folder, dtype=self.dtype, max_tokens=max_tokens_cached, max_sequences=max_sequences,
+                                              pages=pages, strict=strict)
             except (ValueError, OSError) as e:
                 raise KapelError(str(e)) from e
         self._defaults = self._read_generation_config()
         self._tokenizer = None
 
     @classmethod
-    def random(cls, config, seed: int = 0, dtype: str = "bf16", max_tokens_cached: int = 65536, max_sequences: int = 256) -> "Model":
-        """A model of `config` (config.json's dict or a typed configuration) with random weights."""
-        engine = Engine.random(config, seed=seed, dtype=dtype, max_tokens=max_tokens_cached, max_sequences=max_sequences)
-        return cls(None, dtype=dtype, _engine=engine)
+    def random(cls, config, seed: int = 0, dtype: str = "bf16", max_tokens_cached: int = 65536, max_sequences: int = 256,
+               pages: Optional[int] = None, max_pass_tokens: int = 2048) -> "Model":
+        """A model of `config` (config.json's dict, a typed configuration, the path of a config.json
+        or the name of a preset) with random weights made on the device from `seed`."""
+        if isinstance(config, (str, Path)):
+            from .config import read_config_file
+
+            config = read_config_file(config)
+        engine = Engine.random(config, seed=seed, dtype=dtype, max_tokens=max_tokens_cached, max_sequences=max_sequences, pages=pages)
+        return cls(None, dtype=dtype, max_sequences=max_sequences, max_pass_tokens=max_pass_tokens, _engine=engine)
 
     # ------------------------------------------------------------------ defaults
     def _read_generation_config(self):
@@ -132,7 +145,8 @@ class Model:
         return self.detokenize(tokens, skip_special_tokens=True) if as_text else tokens
 
     def _run_one(self, request: Request) -> Iterator[int]:
-        sched = Scheduler(self.engine, EngineOptions(max_sequences=1))
+        sched = Scheduler(self.engine, EngineOptions(max_pass_tokens=self.max_pass_tokens, max_sequences=1))
+        self.last_scheduler = sched
         rid = sched.add(request)
         try:
             while sched.has_work():
@@ -172,6 +186,8 @@ class Model:
 
     def scheduler(self, **options) -> Scheduler:
         """A scheduler of one's own over this model: `add`, `cancel`, `step`, `stats`."""
+        options.setdefault("max_pass_tokens", self.max_pass_tokens)
+        options.setdefault("max_sequences", self.max_sequences)
         return Scheduler(self.engine, EngineOptions(**options))
 
     def step(self, entries):

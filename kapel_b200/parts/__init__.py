@@ -1,6 +1,6 @@
 """Layer parts: mixers, feed-forwards, norms, position encodings, blocks, and the two ends."""
 from .attention import Attention
-from .base import BuildContext, LayerCache, Part, linear, matrix_for
+from .base import BuildContext, LayerCache, Part, linear, matrix_for, matrix_named, require_product_widths, stack_rows
 from .block import PreNormBlock, SandwichBlock
 from .embedding import Embedding, VocabHead
 from .feed_forward import GatedMLP

@@ -12,7 +12,7 @@ import torch
 
 from .. import kernels as K
 from ..cache import CacheNeeds, PagedKV
-from .base import Part, linear, matrix_for
+from .base import Part, linear, matrix_named, require_product_widths, stack_rows
 from .registry import build_part
 
 
@@ -31,21 +31,14 @@ class Attention(Part):
             raise ValueError(f"attention: {spec.num_heads} heads over {spec.num_kv_heads} kv heads")
         if spec.head_dim % 16:
             raise ValueError(f"attention: head_dim {spec.head_dim} must be a multiple of 16 for the kernels")
+        require_product_widths(ctx, "attention", hidden_size=spec.hidden,
+                               **{"num_attention_heads x head_dim": spec.num_heads * spec.head_dim})
         self.position = build_part("position", spec.position, ctx)
 
     def load(self, tensors):
         w = self.spec.weights
-        parts = [tensors[w["q"]], tensors[w["k"]], tensors[w["v"]]]
-        if len({p.dtype for p in parts}) != 1:
-            raise ValueError("attention: q, k and v weights differ in dtype and cannot be stacked")
-        rows = sum(p.shape[0] for p in parts)
-        stacked = torch.empty((rows, self.spec.hidden), dtype=parts[0].dtype, device=parts[0].device)
-        at = 0
-        for p in parts:
-            stacked[at : at + p.shape[0]].copy_(p)
-            at += p.shape[0]
-        self.w_qkv = matrix_for(self.ctx, stacked)
-        self.w_o = matrix_for(self.ctx, tensors[w["o"]])
+        self.w_qkv = stack_rows(self.ctx, tensors, [w["q"], w["k"], w["v"]], "attention")
+        self.w_o = matrix_named(self.ctx, tensors, w["o"])
 
     def cache_needs(self) -> CacheNeeds:
         s = self.spec

@@ -4,7 +4,12 @@ Every part class has:
 
     expected_tensors(spec) -> {tensor name: shape}      (a static method; no device needed)
     __init__(spec, ctx)                                 (ctx: BuildContext)
-    load(tensors)                                       (tensors: {name: device tensor})
+    load(tensors)                                       (tensors: a mapping name -> device tensor; it
+                                                         may read a tensor only when asked, and may
+                                                         offer `copy_into(name, dest)`, `shape(name)`
+                                                         and `dtype(name)` as `weights.WeightSource`
+                                                         does; `stack_rows` and `matrix_named` below
+                                                         use those where they exist)
 
 and, by category:
 
@@ -23,6 +28,9 @@ and, by category:
                       h: this block's first norm already applied to x, or None;
                       next_norm: the norm that the next consumer applies to x first, or None;
                       h_next: next_norm(x) if the block computed it on the way, else None.
+                  cache_needs() -> CacheNeeds: what the layer keeps between steps (its mixer's)
+                  first_norm() -> the norm the block applies to x first, or None: the block
+                      before it may apply it on the way (`next_norm` above)
     embedding     forward(ids) -> float32 [rows, hidden]
     head          forward(x_rows) -> float32 logits [n, vocab]
 
@@ -31,7 +39,7 @@ names its spec gives.
 """
 from __future__ import annotations
 
-from dataclasses import dataclass
+from dataclasses import dataclass, field
 from typing import Dict, Optional
 
 import torch
@@ -45,6 +53,9 @@ class BuildContext:
     dtype: torch.dtype
     device: torch.device
     page_size: int = 16
+    # weights already prepared for the products, by tensor name: a table that two parts read (a
+    # tied embedding and head) is on the device once
+    prepared: Dict[str, torch.Tensor] = field(default_factory=dict)
 
     @property
     def is_f32(self) -> bool:
@@ -92,9 +103,62 @@ class Part:
 def matrix_for(ctx: BuildContext, t: torch.Tensor) -> torch.Tensor:
     """A weight as the products take it: kept as stored (bfloat16, or float32 if the file has
     it in 32-bit); widened to float32 on the 32-bit path."""
+    if t.device != ctx.device:
+        t = t.to(ctx.device)
     if ctx.is_f32 and t.dtype != torch.float32:
         return t.to(torch.float32)
     return t.contiguous()
+
+
+def matrix_named(ctx: BuildContext, tensors, name: str) -> torch.Tensor:
+    """`matrix_for` of the tensor `name`, made once a model: parts that read the same name share it."""
+    if name not in ctx.prepared:
+        ctx.prepared[name] = matrix_for(ctx, tensors[name])
+    return ctx.prepared[name]
+
+
+def stack_rows(ctx: BuildContext, tensors, names, what: str = "weights") -> torch.Tensor:
+    """The matrices `names` (each [rows_i, width]) one below the other in one device tensor, as the
+    products take it. Where `tensors` can copy a tensor into a destination (`copy_into`), each
+    goes from where it lies (a file's mapping) straight into its rows of the one allocation, so
+    the device never holds the parts beside the whole."""
+    if hasattr(tensors, "copy_into") and hasattr(tensors, "shape") and hasattr(tensors, "dtype"):
+        shapes = [tuple(tensors.shape(n)) for n in names]
+        dtypes = {tensors.dtype(n) for n in names}
+        parts = None
+    else:
+        parts = [tensors[n] for n in names]
+        shapes = [tuple(p.shape) for p in parts]
+        dtypes = {p.dtype for p in parts}
+    if len(dtypes) != 1:
+        raise ValueError(f"{what}: {', '.join(names)} differ in dtype and cannot be stacked")
+    if any(len(s) != 2 or s[1] != shapes[0][1] for s in shapes):
+        raise ValueError(f"{what}: {', '.join(names)} have shapes {shapes} and cannot be stacked")
+    kept = dtypes.pop()
+    dtype = torch.float32 if (ctx.is_f32 and kept.is_floating_point) else kept
+    stacked = torch.empty((sum(s[0] for s in shapes), shapes[0][1]), dtype=dtype, device=ctx.device)
+    at = 0
+    for i, (name, shape) in enumerate(zip(names, shapes)):
+        dest = stacked[at : at + shape[0]]
+        if parts is None:
+            tensors.copy_into(name, dest)
+        else:
+            dest.copy_(parts[i])
+            parts[i] = None
+        at += shape[0]
+    return stacked
+
+
+def require_product_widths(ctx: BuildContext, what: str, **widths) -> None:
+    """Refuses, when a part is built, inner widths that the bfloat16 products cannot take (their
+    rows are read 16 bytes at a time: a multiple of 8 elements), naming the configuration's key.
+    The 32-bit path takes any width."""
+    if ctx.is_f32:
+        return
+    bad = {k: v for k, v in widths.items() if v % 8}
+    if bad:
+        listed = ", ".join(f"{k} = {v}" for k, v in bad.items())
+        raise ValueError(f"{what}: {listed} must be a multiple of 8 for the bfloat16 kernels (the float32 path takes any width)")
 
 
 def linear(ctx: BuildContext, x: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None,

@@ -42,6 +42,15 @@ class SandwichBlock(Part):
     def graph_safe(self) -> bool:
         return all(p.graph_safe for p in (self.mixer, self.ffn, *self.norms.values()))
 
+    def cache_needs(self):
+        """What this layer keeps between steps: its mixer's pages and state."""
+        return self.mixer.cache_needs()
+
+    def first_norm(self):
+        """The norm this block applies to the residual first; the block before it may apply it on
+        the way and hand the result in as `h`."""
+        return self.norms["pre_mixer"]
+
     def load(self, tensors):
         self.mixer.load(tensors)
         self.ffn.load(tensors)

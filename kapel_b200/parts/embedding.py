@@ -10,7 +10,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import Part, linear, matrix_for
+from .base import Part, linear, matrix_named
 
 
 class Embedding(Part):
@@ -21,7 +21,7 @@ class Embedding(Part):
         return {}          # the table's shape is the model's [vocab, hidden]; ModelParts adds it
 
     def load(self, tensors):
-        self.table = matrix_for(self.ctx, tensors[self.spec.weight])
+        self.table = matrix_named(self.ctx, tensors, self.spec.weight)
         scale = float(self.spec.scale)
         if self.spec.round_scale and self.ctx.dtype == torch.bfloat16:
             scale = float(torch.tensor(scale, dtype=torch.float32).to(torch.bfloat16).float())
@@ -37,7 +37,7 @@ class VocabHead(Part):
     graph_safe = True
 
     def load(self, tensors):
-        self.table = matrix_for(self.ctx, tensors[self.spec.weight])
+        self.table = matrix_named(self.ctx, tensors, self.spec.weight)
 
     def forward(self, h):
         return linear(self.ctx, h, self.table, out_dtype=torch.float32, softcap=self.spec.softcap)

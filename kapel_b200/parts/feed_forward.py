@@ -5,7 +5,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels as K
-from .base import Part, linear, matrix_for
+from .base import Part, linear, matrix_named, require_product_widths, stack_rows
 
 
 class GatedMLP(Part):
@@ -24,17 +24,12 @@ class GatedMLP(Part):
         super().__init__(spec, ctx)
         if spec.activation not in K.ACT_CODES:
             raise ValueError(f"gated_mlp: activation {spec.activation!r} is not built")
+        require_product_widths(ctx, "gated_mlp", hidden_size=spec.hidden, intermediate_size=spec.intermediate)
 
     def load(self, tensors):
         w = self.spec.weights
-        gate, up = tensors[w["gate"]], tensors[w["up"]]
-        if gate.dtype != up.dtype:
-            raise ValueError("gated_mlp: gate and up weights differ in dtype and cannot be stacked")
-        stacked = torch.empty((2 * self.spec.intermediate, self.spec.hidden), dtype=gate.dtype, device=gate.device)
-        stacked[: self.spec.intermediate].copy_(gate)
-        stacked[self.spec.intermediate :].copy_(up)
-        self.w_gate_up = matrix_for(self.ctx, stacked)
-        self.w_down = matrix_for(self.ctx, tensors[w["down"]])
+        self.w_gate_up = stack_rows(self.ctx, tensors, [w["gate"], w["up"]], "gated_mlp")
+        self.w_down = matrix_named(self.ctx, tensors, w["down"])
 
     def forward(self, h):
         # many rows of bfloat16: the gated unit is the epilogue of the gate|up product

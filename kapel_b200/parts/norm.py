@@ -15,6 +15,8 @@ class RMSNorm(Part):
 
     def load(self, tensors):
         w = tensors[self.spec.weight]
+        if w.device != self.ctx.device:
+            w = w.to(self.ctx.device)
         self.weight = w.float() if self.ctx.is_f32 else w.contiguous()
 
     def forward(self, x, out_dtype=None):

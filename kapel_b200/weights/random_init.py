@@ -10,7 +10,7 @@ from __future__ import annotations
 
 import json
 from pathlib import Path
-from typing import Dict
+from typing import Dict, Mapping
 
 import torch
 
@@ -39,6 +39,52 @@ def random_tensor(name: str, shape, std: float, seed: int, device="cpu", dtype=t
     return t.to(dtype)
 
 
+class RandomSource(Mapping):
+    """The random tensors of a configuration by name, each made when it is asked for (on `device`),
+    so that a model of any size can be built without its parts lying about twice. The interface is
+    `weights.WeightSource`'s."""
+
+    def __init__(self, config, seed: int, device="cpu", dtype=torch.bfloat16):
+        from ..parts import expected_tensors
+
+        self.config, self.seed, self.device, self._dtype = config, seed, device, dtype
+        self._shapes = {n: tuple(s) for n, s in expected_tensors(config.to_spec()).items()}
+        self.unexpected = []
+
+    def __iter__(self):
+        return iter(self._shapes)
+
+    def __len__(self):
+        return len(self._shapes)
+
+    def __contains__(self, name):
+        return name in self._shapes
+
+    def __getitem__(self, name):
+        shape = self._shapes[name]
+        return random_tensor(name, shape, self.config.init_std(name, shape), self.seed, self.device, self._dtype)
+
+    def shape(self, name):
+        return self._shapes[name]
+
+    def dtype(self, name):
+        return self._dtype
+
+    def shapes(self):
+        return dict(self._shapes)
+
+    def check(self, expected, strict: bool = False):
+        from .loader import check_names
+
+        return check_names(expected, self._shapes, "random weights", strict)
+
+    def copy_into(self, name, dest) -> None:
+        dest.copy_(self[name])
+
+    def close(self) -> None:
+        pass
+
+
 def random_tensors(config, seed: int, device="cpu", dtype=torch.bfloat16) -> Dict[str, torch.Tensor]:
     from ..parts import expected_tensors
 
@@ -49,11 +95,14 @@ def random_tensors(config, seed: int, device="cpu", dtype=torch.bfloat16) -> Dic
     }
 
 
-def write_random_model(folder, config, seed: int, dtype=torch.bfloat16) -> Path:
-    """Writes config.json and model.safetensors for `config` with weights from `seed`."""
+def write_random_model(folder, config, seed: int, dtype=torch.bfloat16, device="cpu") -> Path:
+    """Writes config.json and model.safetensors for `config` with weights from `seed`. `device` is
+    where the values are drawn before they are written: a CUDA device makes a folder of several GB
+    in seconds (its generator gives other values than the CPU's for the same seed; the folder, not
+    the seed, is then what its readers share)."""
     folder = Path(folder)
     folder.mkdir(parents=True, exist_ok=True)
     (folder / "config.json").write_text(json.dumps(config.to_json(), indent=2))
-    write_safetensors(folder / "model.safetensors", random_tensors(config, seed, "cpu", dtype),
+    write_safetensors(folder / "model.safetensors", random_tensors(config, seed, device, dtype),
                       metadata={"format": "pt", "seed": seed})
     return folder

@@ -143,4 +143,4 @@ def write_safetensors(path, tensors: Dict[str, torch.Tensor], metadata=None) -> 
             if t.numel() == 0:
                 continue
             raw = t.view(torch.uint8) if t.dtype != torch.bool else t.to(torch.uint8)
-            f.write(raw.reshape(-1).numpy().tobytes())
+            f.write(memoryview(raw.reshape(-1).numpy()))

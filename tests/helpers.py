@@ -39,13 +39,13 @@ TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
 TOL = {"float32": 2e-5, "bfloat16": 4e-2}
 
 
-def make_model_dir(raw_config: dict, seed: int, folder=None, scale_up: float = 1.0) -> Path:
+def make_model_dir(raw_config: dict, seed: int, folder=None, scale_up: float = 1.0, device="cpu") -> Path:
     """config.json and model.safetensors with seeded random weights, in a temporary folder."""
     from kapel_b200.config import config_from_json
     from kapel_b200.weights import write_random_model
 
     folder = Path(folder or tempfile.mkdtemp(prefix="kapel_b200_model_"))
-    write_random_model(folder, config_from_json(raw_config), seed)
+    write_random_model(folder, config_from_json(raw_config), seed, device=device)
     return folder
 
 

@@ -6,8 +6,15 @@ here (no Rust toolchain, no network for its dependencies), so this file rests on
 alone; `tests/golden/` holds outputs of this file, not of Kapel.
 
 It shares no code with `kapel_b200`: it reads config.json and model.safetensors with its own
-few lines, and uses torch on the CPU only as an array library. Everything is computed in the
-dtype given (`torch.float64` by default, as kapel-ref computes; `torch.float32` on request).
+few lines, and uses torch only as an array library. Everything is computed in the dtype given
+(`torch.float64` by default, as kapel-ref computes; `torch.float32` on request).
+
+For the sizes of the real models there is a second way through the same functions:
+`forward_streamed` reads one layer's weights at a time from the file (so memory is one layer)
+and uses `attention_blocked`, the same attention written as matrix products over a block of
+query rows at a time; both run wherever torch puts their arrays (a GPU's 64-bit arithmetic
+makes 4,000 tokens through 26 layers a matter of seconds). `attention_blocked` is proved equal
+to the loop of `attention` on the tiny configurations in tests/test_plain.py.
 """
 from __future__ import annotations
 
@@ -171,6 +178,38 @@ def attention(q, k, v, scale, softcap, window):
     return out
 
 
+def attention_blocked(q, k, v, scale, softcap, window, block=256):
+    """`attention` again, the same formulas in the same order (scale, soft cap, mask, softmax over
+    the visible keys, weighted sum; the same citations), for a block of query rows at a time as
+    matrix products, so that thousands of positions take seconds, not hours.
+
+    q: [T, Hq, D]; k, v: [T, Hkv, D]. Returns [T, Hq, D].
+    """
+    t, hq, d = q.shape
+    hkv = k.shape[1]
+    group = hq // hkv
+    out = torch.empty_like(q)
+    for r0 in range(0, t, block):
+        r1 = min(t, r0 + block)
+        j0 = max(0, r0 + 1 - window) if window is not None else 0       # the first key the block's first row sees
+        qb = q[r0:r1].permute(1, 0, 2)                                                   # [Hq, rows, D]
+        kb = k[j0:r1].permute(1, 2, 0).repeat_interleave(group, dim=0)                   # [Hq, D, keys]: head h reads kv head h // group
+        vb = v[j0:r1].permute(1, 0, 2).repeat_interleave(group, dim=0)                   # [Hq, keys, D]
+        s = scale * (qb @ kb)
+        if softcap is not None:
+            s = softcap * torch.tanh(s / softcap)
+        rows = torch.arange(r0, r1, device=q.device)[:, None]
+        cols = torch.arange(j0, r1, device=q.device)[None, :]
+        visible = cols <= rows                                            # j < c, the row's own position included
+        if window is not None:
+            visible = visible & (rows - cols < window)                    # c - 1 - j < window
+        s = s.masked_fill(~visible[None], float("-inf"))
+        wgt = torch.exp(s - s.max(dim=-1, keepdim=True).values)
+        wgt = wgt / wgt.sum(dim=-1, keepdim=True)
+        out[r0:r1] = (wgt @ vb).permute(1, 0, 2)
+    return out
+
+
 def gelu_tanh(x):
     """x/2 * (1 + tanh(sqrt(2/pi) * (x + 0.044715 x^3))) (crates/kapel-ops/src/elementwise.rs:33-35)."""
     return 0.5 * x * (1.0 + torch.tanh(math.sqrt(2.0 / math.pi) * (x + 0.044715 * x * x * x)))
@@ -181,7 +220,7 @@ def geglu_ffn(h, w_gate, w_up, w_down):
     return (gelu_tanh(h @ w_gate.T) * (h @ w_up.T)) @ w_down.T
 
 
-def attention_mixer(h, positions, w, prefix, cfg, window):
+def attention_mixer(h, positions, w, prefix, cfg, window, attention_fn=None):
     """q/k/v products, RoPE on q and k, attention, output product
     (crates/kapel-models/src/model.rs:1506-1517,1541-1590,1633-1637)."""
     hq, hkv, d = cfg["num_attention_heads"], cfg.get("num_key_value_heads") or cfg["num_attention_heads"], head_dim_of(cfg)
@@ -192,16 +231,16 @@ def attention_mixer(h, positions, w, prefix, cfg, window):
     theta = cfg.get("rope_theta", 10000.0)
     q = rope(q, positions, theta)
     k = rope(k, positions, theta)
-    y = attention(q, k, v, score_scale(cfg), cfg.get("attn_logit_softcapping"), window)
+    y = (attention_fn or attention)(q, k, v, score_scale(cfg), cfg.get("attn_logit_softcapping"), window)
     return y.reshape(t, hq * d) @ w[f"{prefix}.self_attn.o_proj.weight"].T
 
 
-def sandwich_block(x, positions, w, prefix, cfg, window):
+def sandwich_block(x, positions, w, prefix, cfg, window, attention_fn=None):
     """h=norm_in(x); a=attn(h); a=norm_post_attn(a); x=x+a; h=norm_pre_ffn(x); m=mlp(h);
     m=norm_post_ffn(m); x=x+m (crates/kapel-models/src/model.rs:1401-1460)."""
     eps = cfg.get("rms_norm_eps", 1e-6)
     h = rms_norm(x, w[f"{prefix}.input_layernorm.weight"], eps)
-    a = attention_mixer(h, positions, w, prefix, cfg, window)
+    a = attention_mixer(h, positions, w, prefix, cfg, window, attention_fn)
     a = rms_norm(a, w[f"{prefix}.post_attention_layernorm.weight"], eps)
     x = x + a
     h = rms_norm(x, w[f"{prefix}.pre_feedforward_layernorm.weight"], eps)
@@ -250,6 +289,76 @@ def load(folder, dtype=torch.float64):
     """(config dict, weights dict) of a model folder."""
     folder = Path(folder)
     return read_config(folder), read_safetensors(folder / "model.safetensors", dtype)
+
+
+class TensorFile:
+    """One safetensors file read a tensor at a time (the format as `read_safetensors` takes it):
+    what `forward_streamed` needs so that only one layer's weights are held at once."""
+
+    def __init__(self, path):
+        self.raw = np.memmap(path, dtype=np.uint8, mode="r")
+        (n,) = struct.unpack("<Q", self.raw[:8].tobytes())
+        self.header = json.loads(self.raw[8 : 8 + n].tobytes())
+        self.base = 8 + n
+
+    def names(self):
+        return [n for n in self.header if n != "__metadata__"]
+
+    def tensor(self, name, dtype=torch.float64, device="cpu"):
+        meta = self.header[name]
+        a, b = meta["data_offsets"]
+        buf = self.raw[self.base + a : self.base + b]
+        kind = meta["dtype"]
+        if kind == "BF16":                       # the 16 bits are the upper half of a float32
+            bits = torch.from_numpy(np.array(buf.view(np.uint16)).astype(np.int32)).to(device)
+            t = (bits << 16).view(torch.float32)
+        elif kind == "F32":
+            t = torch.from_numpy(np.array(buf.view(np.float32))).to(device)
+        elif kind == "F16":
+            t = torch.from_numpy(np.array(buf.view(np.float16))).to(device)
+        elif kind == "F64":
+            t = torch.from_numpy(np.array(buf.view(np.float64))).to(device)
+        else:
+            raise ValueError(f"{name}: dtype {kind} not handled by the plain reader")
+        return t.to(dtype).reshape(meta["shape"])
+
+
+def forward_streamed(folder, sequences, dtype=torch.float64, device="cpu", block=256):
+    """Logits at chosen positions of several whole sequences of one model folder, with one layer's
+    weights in memory at a time and the blocked attention: `forward` for the real sizes.
+
+    `sequences` is a list of (ids, wanted positions, embed_scale or None); the result a list of
+    float64 CPU tensors [wanted, V], one a sequence. The same functions as `forward` run, layer by
+    layer over every sequence, so what is computed is the same; only the order of reading differs.
+    """
+    folder = Path(folder)
+    cfg = read_config(folder)
+    file = TensorFile(folder / "model.safetensors")
+    table = file.tensor("model.embed_tokens.weight", dtype, device)
+    xs, positions = [], []
+    for ids, _, scale in sequences:
+        ids_t = torch.tensor(list(ids), dtype=torch.long, device=device)
+        xs.append(embed(table, ids_t, math.sqrt(cfg["hidden_size"]) if scale is None else scale))
+        positions.append(torch.arange(len(ids), device=device))
+    windows = layer_windows(cfg)
+
+    def blocked(q, k, v, scale, softcap, window):
+        return attention_blocked(q, k, v, scale, softcap, window, block)
+
+    for i in range(cfg["num_hidden_layers"]):
+        prefix = f"model.layers.{i}"
+        w = {n: file.tensor(n, dtype, device) for n in file.names() if n.startswith(prefix + ".")}
+        for s in range(len(xs)):
+            xs[s] = sandwich_block(xs[s], positions[s], w, prefix, cfg, windows[i], blocked)
+        del w
+    head = {"model.embed_tokens.weight": table, "model.norm.weight": file.tensor("model.norm.weight", dtype, device)}
+    if "lm_head.weight" in file.header and not cfg.get("tie_word_embeddings", True):
+        head["lm_head.weight"] = file.tensor("lm_head.weight", dtype, device)
+    out = []
+    for x, (_, want, _) in zip(xs, sequences):
+        rows = x[torch.tensor(list(want), dtype=torch.long, device=device)]
+        out.append(logits_head(rows, head, cfg).to(torch.float64).cpu())
+    return out
 
 
 # ----------------------------------------------------------------------------------------

@@ -181,6 +181,7 @@ def test_a_recorded_pass_s_staging_buffer_is_the_same_from_both_plans():
     for plan in plans:
         static = StaticBatch.__new__(StaticBatch)
         static.rows, static.width, static.turn = rows, width, 0
+        static.in_flight = [False, False]                        # no copy has read either buffer yet
         total = 6 * rows + n_groups * (rows + rows * width)
         static.hosts = [torch.full((total,), 12345, dtype=torch.int32) for _ in range(2)]
         assert static.fill_host(plan) == 0

@@ -78,6 +78,43 @@ def test_temperature_same_seed_same_tokens_and_chunked_prefill(folders):
     assert model.generate(prompts[2], max_tokens=5, temperature=0.8, top_k=1, seed=3) == model.generate(prompts[2], max_tokens=5)
 
 
+@pytest.mark.parametrize("route", ["device", "host"])
+def test_sampled_tokens_are_the_plain_samplers_over_the_plain_logits(folders, route):
+    """Tiny B's workload in 32-bit: prompts of 1, 50 and 90 in portions of 32 beside decoded tokens,
+    40 tokens each at temperature 0.8 with seed 7 (request i draws with seed 7 + i). Every token the
+    engine gives is the one the plain sampler draws, with the same uniform number, from the plain
+    logits of the sequence so far; a difference is allowed only where the plain running total of
+    probabilities passes the uniform number by less than 1e-5. `device`: the draw is made where the
+    logits are (32-bit softmax); `host`: a min_p too small to remove anything sends it through the
+    host sampler (64-bit)."""
+    import kapel_b200
+
+    raw, _ = TINY["B"]
+    rng = np.random.default_rng(22)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (1, 50, 90)]
+    model = kapel_b200.Model(str(folders["B"]), dtype="f32", max_tokens_cached=512, max_sequences=8)
+    extra = {} if route == "device" else {"min_p": 1e-30}
+    got = model.generate_batch(prompts, max_tokens=40, temperature=0.8, seed=7, max_pass_tokens=32, **extra)
+    near = 0
+    for i, (prompt, tokens) in enumerate(zip(prompts, got)):
+        assert len(tokens) == 40
+        logits = plain_logits(folders["B"], prompt + tokens, embed_scale=embed_scale_for(raw, "float32"))
+        draws = P.PlainRng(7 + i)
+        for t, token in enumerate(tokens):
+            u = draws.uniform()
+            row = [float(x) for x in logits[len(prompt) - 1 + t]]
+            want = P.plain_choose(row, 0.8, u)
+            if token != want:
+                scaled = np.asarray(row) / 0.8
+                prob = np.exp(scaled - scaled.max())
+                running = np.cumsum(prob / prob.sum())
+                lo, hi = min(token, want), max(token, want)
+                assert hi == lo + 1 and abs(running[lo] - u) < 1e-5, \
+                    f"request {i}, token {t}: engine {token}, plain {want}, u {u}, running total {running[lo]}"
+                near += 1
+    assert near <= 2, f"{near} draws fell on a boundary: too many for chance"
+
+
 def test_scheduler_with_few_pages_suspends_and_still_gives_each_its_tokens(folders):
     import kapel_b200
     from kapel_b200.engine.scheduler import Request
@@ -217,3 +254,29 @@ def test_command_line(folders):
     assert "tokens/s" in r.stderr
     r = subprocess.run(cmd[:5] + ["--quantize", "int8", "--tokens", "1"], capture_output=True, text=True, cwd=str(ROOT), timeout=600)
     assert r.returncode == 1 and "quantized" in r.stderr
+
+
+def test_command_line_with_random_weights_and_engine_options(folders, tmp_path):
+    """`run --random CONFIG --seed-weights S --prompt-len N --pages --max-pass-tokens --max-sequences`:
+    no folder, weights made on the device; the same tokens as the Python entry point gives for the
+    same configuration, seeds and prompt; the prompt runs in portions of --max-pass-tokens."""
+    import kapel_b200
+
+    raw, _ = TINY["B"]
+    config = tmp_path / "config.json"
+    config.write_text(json.dumps(raw))
+    cmd = [sys.executable, "-m", "kapel_b200", "run", "--random", str(config), "--seed-weights", "3", "--prompt-len", "21", "--seed", "5",
+           "--pages", "6", "--max-pass-tokens", "8", "--max-sequences", "2", "--max-tokens", "6", "--greedy", "--dtype", "f32", "--stats"]
+    r = subprocess.run(cmd, capture_output=True, text=True, cwd=str(ROOT), timeout=600)
+    assert r.returncode == 0, r.stderr
+    got = [int(t) for t in r.stdout.strip().splitlines()[-1].split(",")]
+    prompt = [int(t) for t in np.random.default_rng(5).integers(0, raw["vocab_size"], size=21)]
+    model = kapel_b200.Model.random(str(config), seed=3, dtype="f32", pages=6, max_sequences=2, max_pass_tokens=8)
+    assert model.engine.cache.total_pages() == [6, 6]
+    assert got == model.generate(prompt, max_tokens=6)
+    assert "prompt 21 tokens" in r.stderr and "passes 8 " in r.stderr          # 3 portions of at most 8, then 5 more tokens
+    r = subprocess.run(cmd[:4] + ["--tokens", "1"], capture_output=True, text=True, cwd=str(ROOT), timeout=600)
+    assert r.returncode == 2 and "either MODEL or --random" in r.stderr
+    r = subprocess.run([sys.executable, "-m", "kapel_b200", "run", "--random", "no-such-size", "--tokens", "1"],
+                       capture_output=True, text=True, cwd=str(ROOT), timeout=600)
+    assert r.returncode == 1 and "presets" in r.stderr

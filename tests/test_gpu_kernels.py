@@ -253,15 +253,16 @@ def test_glu(dtype, act):
 
 
 # ------------------------------------------------------------------------------------------
-def paged_reference(q, k_table, v_table, block_table, row_entry, row_count, page, window, scale, cap):
-    """Row by row in 64-bit, as crates/kapel-ref/src/paged.rs:28-92."""
+def paged_reference(q, k_table, v_table, block_table, row_entry, row_count, page, window, scale, cap, only=None):
+    """Row by row in 64-bit, as crates/kapel-ref/src/paged.rs:28-92. With `only`, just those rows
+    (the others stay zero): for histories of thousands of keys, where a sample of rows is checked."""
     rows, hq, d = q.shape
     hkv = k_table.shape[1]                      # tables are [pages, kv heads, page, d]
     group = hq // hkv
     kt = k_table.double().permute(0, 2, 1, 3).reshape(-1, hkv, d)        # [lines, kv heads, d]
     vt = v_table.double().permute(0, 2, 1, 3).reshape(-1, hkv, d)
     out = torch.zeros(rows, hq, d, dtype=torch.float64)
-    for r in range(rows):
+    for r in (range(rows) if only is None else only):
         e, c = int(row_entry[r]), int(row_count[r])
         first = max(0, c - window) if window else 0
         if c <= first:
@@ -504,6 +505,50 @@ def test_paged_attention_mma_far_key_and_window_edge(decode):
         want = paged_reference(q, kt2, vt2, bt, re, rc, page, win, 1.0, None)
         assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
         assert (abs(float(got[0, 0].mean()) - 5.0) < 0.1) == seen
+
+
+@pytest.mark.parametrize("hq,hkv,d,scalar", [(8, 4, 256, 256), (32, 16, 128, 144)])
+@pytest.mark.parametrize("window", [4096, None])
+def test_paged_attention_at_the_sizes_and_histories_that_are_timed(hq, hkv, d, scalar, window):
+    """The decode kernel and the tcgen05 prompt kernel at the head counts and head sizes of Gemma 2
+    2B (8 over 4 of 256) and 27B (32 over 16 of 128), with the window of 4,096 and without, over
+    histories of 4,097, 4,100 and 6,144 positions, cut into key slots as the engine's planners cut
+    them. A sample of rows (each request's first and last, and those around the window's first move)
+    against the row-by-row reference."""
+    from kapel_b200.engine.batch import decode_split, prompt_split, sm_count
+
+    scale, cap = 1.0 / math.sqrt(scalar), 50.0
+    sms = sm_count(torch.device("cuda"))
+    # decoding: one token of each of three requests
+    lengths = [4100, 6144, 4097]
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, [1, 1, 1], seed=d + hq)
+    q = q * 4.0                                            # scores of a few units: the soft cap bends them
+    split, slots = decode_split(len(lengths) * hkv, max(lengths), sms, window, True)
+    from kapel_b200.engine.batch import cut_tiles
+
+    tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(np.arange(3, dtype=np.int32), np.ones(3, np.int32), 1))
+    got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, 16, window, scale, cap, hq // hkv, split, slots, True).cpu().double()
+    K().check_async_errors()
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
+    assert rel_err(got.numpy(), want.numpy()) < 1.5e-2, f"decode, split {split} x {slots}"
+    # a prompt portion of 200 tokens behind 3,950 (it crosses position 4,096) beside a whole prompt of 2,048
+    lengths, q_lens = [4150, 2048], [200, 2048]
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=d + hq + 1)
+    q = q * 4.0
+    per_tile = max(1, K().attention_mma_rows(False) // (hq // hkv))
+    q_len = np.asarray(q_lens, np.int32)
+    q_start = np.asarray([0, 200], np.int32)
+    arrays = cut_tiles(q_start, q_len, per_tile)
+    firsts = rc.numpy()[arrays[1]]
+    kernel = K().attention_prompt_kernel(hq, hkv, d, 16, cap)
+    assert kernel == "tcgen05"
+    split, slots = prompt_split(firsts, firsts + arrays[2] - 1, hkv, sms, window, int(q_len.sum()), hq, d, kernel)
+    tiles = tuple(dev(torch.from_numpy(a)) for a in arrays)
+    got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, 16, window, scale, cap, 0, split, slots).cpu().double()
+    K().check_async_errors()
+    sample = [0, 1, 144, 145, 146, 147, 199, 200, 201, 263, 264, 200 + 1023, 200 + 2047]     # rows 145/146 see 4,096/4,097 positions
+    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap, only=sample)
+    assert rel_err(got[sample].numpy(), want[sample].numpy()) < 1.5e-2, f"prompt, split {split} x {slots}"
 
 
 # ------------------------------------------------------------------------------------------

@@ -82,3 +82,32 @@ def test_golden_outputs_are_still_what_this_file_computes():
         got = logits[-1][rec["columns"]]
         assert np.abs(got - np.array(rec["last_row"])).max() < 1e-9, name
         assert int(np.argmax(logits[-1])) == rec["argmax"]
+
+
+def test_blocked_attention_equals_the_loop():
+    """`attention_blocked` (matrix products over blocks of rows) against the loop of `attention`:
+    groups of heads, a window's edge inside and across blocks, a soft cap, blocks that do not divide
+    the length."""
+    g = torch.Generator().manual_seed(1)
+    for t, hq, hkv, d, window, cap, block in ((37, 4, 2, 8, None, 50.0, 16), (50, 6, 1, 16, 24, 20.0, 7),
+                                              (33, 3, 3, 4, 5, None, 64), (20, 2, 1, 8, 1, 30.0, 3)):
+        q, k, v = (torch.randn(t, h, d, generator=g, dtype=torch.float64) * 3 for h in (hq, hkv, hkv))
+        want = P.attention(q, k, v, 0.25, cap, window)
+        got = P.attention_blocked(q, k, v, 0.25, cap, window, block)
+        assert (got - want).abs().max() < 1e-12, (t, hq, hkv, d, window, cap, block)
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_streamed_forward_equals_the_whole_forward(name):
+    """`forward_streamed` (a layer's weights at a time, blocked attention, logits at chosen places,
+    several sequences in one pass over the file) against `forward` on the tiny configurations."""
+    raw, seed = TINY[name]
+    folder = make_model_dir(raw, seed)
+    cfg, w = P.load(folder, torch.float64)
+    rng = np.random.default_rng(4)
+    a = [int(t) for t in rng.integers(0, raw["vocab_size"], size=70)]
+    b = [int(t) for t in rng.integers(0, raw["vocab_size"], size=9)]
+    want_a, want_b = [0, 15, 16, 17, 69], [8]
+    got = P.forward_streamed(folder, [(a, want_a, None), (b, want_b, 9.8125)], block=13)
+    assert rel_err(got[0].numpy(), P.forward(cfg, w, a).numpy()[want_a]) < 1e-12
+    assert rel_err(got[1].numpy(), P.forward(cfg, w, b, embed_scale=9.8125).numpy()[want_b]) < 1e-12

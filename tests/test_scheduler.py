@@ -319,3 +319,73 @@ def test_a_reserve_keeps_a_share_of_the_pool_free_at_admission():
     rid = sched.add(Request(prompt=ps[0], sampling=greedy, max_tokens=3))
     out, finishes = run(sched)
     assert out[rid] == expected(ps[0], 3)
+
+
+class LimitedEngine(FakeEngine):
+    """The stand-in with a limit on positions, refusing what passes it as the step function does."""
+
+    def __init__(self, limit, **kw):
+        super().__init__(**kw)
+        self.max_positions = limit
+
+    def step(self, entries):
+        for e in entries:
+            if self.cache.length(e.id) + len(e.tokens) > self.max_positions:
+                raise ValueError(f"request {e.id!r} would pass {self.max_positions} positions")
+        return super().step(entries)
+
+
+def test_a_request_that_reaches_the_position_limit_ends_alone_with_length():
+    """One request reaches max_position_embeddings while another decodes beside it: the first ends
+    with "length" after the last token it can be given, the second goes on and finishes normally,
+    and the step function's own refusal is never met."""
+    eng = LimitedEngine(40, pages=32)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=16))
+    long_prompt, short_prompt = [3] * 30, [4, 5, 6]
+    a = sched.add(Request(long_prompt, max_tokens=100))
+    b = sched.add(Request(short_prompt, max_tokens=25))
+    out, fin = run(sched)
+    # positions 0..39 can be fed: the prompt's 30 and 10 generated tokens; the 11th token is the last given
+    assert fin[a] == ("length", None) and out[a] == expected(long_prompt, 11)
+    assert fin[b] == ("length", None) and out[b] == expected(short_prompt, 25)
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+    with pytest.raises(ValueError, match="longer than the 40 positions"):
+        sched.add(Request([1] * 41, max_tokens=1))
+    c = sched.add(Request([1] * 40, max_tokens=5))          # exactly the limit: one token, then "length"
+    out, fin = run(sched)
+    assert out[c] == expected([1] * 40, 1) and fin[c][0] == "length"
+
+
+def test_a_staged_pass_is_not_taken_beyond_the_position_limit():
+    class Both(StagingEngine):
+        max_positions = 24
+
+    eng = Both(pages=32)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=16))
+    a = sched.add(Request([2] * 10, max_tokens=100))
+    out, fin = run(sched)
+    assert out[a] == expected([2] * 10, 15) and fin[a][0] == "length"
+    assert eng.cache.free_pages() == eng.cache.total_pages() and eng.ran_staged > 5
+
+
+def test_two_schedulers_over_one_engine_never_share_a_request_id():
+    """A stream that is not exhausted beside another call: both schedulers name sequences in the
+    one cache, so their ids come from one counter, and ending one request leaves the other's pages."""
+    eng = FakeEngine(pages=32)
+    s1, s2 = Scheduler(eng), Scheduler(eng)
+    p1, p2 = [1, 2, 3, 4], [9, 8, 7]
+    a = s1.add(Request(p1, max_tokens=6))
+    b = s2.add(Request(p2, max_tokens=6))
+    assert a != b
+    out = {a: [], b: []}
+    for _ in range(3):                                       # both are live at once
+        for s in (s1, s2):
+            for ev in s.step():
+                out[ev.id].append(ev.token)
+    s1.cancel(a)                                             # one ends early; the other's pages stay
+    eng.cache.check()
+    while s2.has_work():
+        for ev in s2.step():
+            out[ev.id].append(ev.token)
+    assert out[b] == expected(p2, 6) and out[a] == expected(p1, 3)
+    assert eng.cache.free_pages() == eng.cache.total_pages()

@@ -121,3 +121,65 @@ def test_random_weights_depend_on_name_and_seed_only():
     assert a["model.embed_tokens.weight"].dtype == torch.bfloat16
     assert abs(float(a["model.embed_tokens.weight"].float().std()) - 0.02) < 0.002
     assert abs(float(torch.cat([a[n].float() for n in a if n.endswith("norm.weight")]).std()) - 0.1) < 0.02
+
+
+def test_a_tensor_the_model_does_not_name_is_no_error_unless_strict(tmp_path):
+    """Only the names the model reads are required (crates/kapel-models/src/model.rs:294-311 keeps
+    every tensor of a checkpoint and asks for those it uses): an extra tensor is remembered, and an
+    error only on request."""
+    from kapel_b200.weights import open_weights
+
+    folder = make_model_dir(TINY_A, 0, tmp_path / "m")
+    expected = expected_tensors(config_from_json(TINY_A).to_spec())
+    f = SafetensorsFile(folder / "model.safetensors")
+    tensors = {n: f.tensor(n).clone() for n in f.names()}
+    tensors["vision_tower.patch.weight"] = torch.zeros(3, 5)
+    write_safetensors(folder / "model.safetensors", tensors)
+    loaded = load_tensors(folder, expected, "cpu")
+    assert sorted(loaded) == sorted(expected)
+    source = open_weights(folder, "cpu")
+    assert source.check(expected) == ["vision_tower.patch.weight"] and source.unexpected == ["vision_tower.patch.weight"]
+    with pytest.raises(WeightsError) as info:
+        source.check(expected, strict=True)
+    assert info.value.unexpected == ["vision_tower.patch.weight"] and not info.value.missing and not info.value.wrong_shape
+    with pytest.raises(WeightsError):
+        load_tensors(folder, expected, "cpu", strict=True)
+
+
+def test_stacked_weights_are_copied_straight_into_their_rows(tmp_path):
+    """`stack_rows` over a source that reads on demand equals the parts one below the other, in the
+    kept dtype on the bfloat16 path and widened on the 32-bit path; `copy_into` refuses a wrong shape."""
+    from kapel_b200.parts import BuildContext, stack_rows
+    from kapel_b200.weights import open_weights
+
+    folder = make_model_dir(TINY_B, 1, tmp_path / "m")
+    source = open_weights(folder, "cpu")
+    names = [f"model.layers.1.self_attn.{r}_proj.weight" for r in "qkv"]
+    want = torch.cat([source.host(n) for n in names])
+    for dtype in (torch.bfloat16, torch.float32):
+        ctx = BuildContext(dtype=dtype, device=torch.device("cpu"))
+        got = stack_rows(ctx, source, names)
+        assert got.dtype == dtype and torch.equal(got.float(), want.float())
+        assert torch.equal(stack_rows(ctx, {n: source[n] for n in names}, names), got)     # a plain dict of tensors too
+    with pytest.raises(WeightsError):
+        source.copy_into(names[0], torch.empty(3, 3))
+    with pytest.raises(ValueError, match="cannot be stacked"):
+        stack_rows(ctx, source, [names[0], "model.norm.weight"])
+
+
+def test_widths_the_bfloat16_kernels_cannot_take_are_refused_when_the_parts_are_built():
+    """hidden_size, heads x head_dim and intermediate_size are inner widths of bfloat16 products, read
+    16 bytes at a time: a width that is no multiple of 8 is refused when the model is put together,
+    with the key's name, not at the first step; the 32-bit path takes it."""
+    from kapel_b200.parts import BuildContext, build_part
+
+    raw = dict(TINY_A, hidden_size=68, intermediate_size=132)
+    spec = config_from_json(raw).to_spec()
+    bf16 = BuildContext(dtype=torch.bfloat16, device=torch.device("cpu"))
+    with pytest.raises(ValueError, match=r"hidden_size = 68.*multiple of 8"):
+        build_part("block", spec.layers[0], bf16)
+    raw = dict(TINY_A, intermediate_size=132)
+    with pytest.raises(ValueError, match=r"gated_mlp: intermediate_size = 132"):
+        build_part("block", config_from_json(raw).to_spec().layers[0], bf16)
+    f32 = BuildContext(dtype=torch.float32, device=torch.device("cpu"))
+    build_part("block", spec.layers[0], f32)

@@ -66,6 +66,45 @@ def test_two_calls_in_a_row_match_the_allocating_entry_point():
         assert torch.equal(out, want), "same kernels, same split of K: the same bits as kb_gemm_bf16"
 
 
+def test_a_product_that_fills_the_built_in_scratch_to_its_end():
+    """An accepted product whose partial sums end within a few percent of the array's last value
+    (found by asking the library how much each size needs): a bound off by one in the entry point,
+    or a split that writes past its share at the far end, would show as a refusal or as other bits
+    than kb_gemm_bf16 gives with scratch of the exact size the library asks for."""
+    from kapel_b200 import kernels as K
+
+    lib = ctypes.CDLL(K.library_path())
+    lib.kb_last_error.restype = ctypes.c_char_p
+    lib.kb_gemm_bf16_scratch_floats.restype = ctypes.c_longlong
+    best = None
+    for m, k in ((64, 1024), (64, 2048), (64, 512), (48, 1024), (16, 2048), (16, 4096)):
+        for n in range(65536, 1024, -8):
+            need = lib.kb_gemm_bf16_scratch_floats(m, n, k)
+            if 0 < need <= MAX_FLOATS and (best is None or need > best[0]):
+                best = (need, m, n, k)
+    assert best is not None and best[0] >= 0.97 * MAX_FLOATS, f"no size found that fills the array: {best}"
+    need, m, n, k = best
+    g = torch.Generator().manual_seed(1)
+    a = torch.randn(m, k, generator=g).bfloat16().cuda()
+    w = (torch.randn(n, k, generator=g) * 0.05).bfloat16().cuda()
+    out = torch.full((m, n), float("nan"), dtype=torch.float32, device="cuda")
+    for _ in range(2):                                     # two calls in a row over the same, nearly full array
+        code, msg = _call(lib, out, a, w)
+        assert code == 0, msg
+    scratch = torch.empty((need,), dtype=torch.float32, device="cuda")
+    want = torch.empty_like(out)
+    code = lib.kb_gemm_bf16(
+        ctypes.c_void_p(want.data_ptr()), 0, ctypes.c_void_p(a.data_ptr()), ctypes.c_void_p(w.data_ptr()), m, n, k, 0,
+        ctypes.c_float(0.0), ctypes.c_void_p(scratch.data_ptr()), ctypes.c_void_p(torch.cuda.current_stream().cuda_stream),
+    )
+    assert code == 0, lib.kb_last_error().decode()
+    torch.cuda.synchronize()
+    assert torch.isfinite(out).all() and torch.equal(out, want)
+    ref = a.double().cpu() @ w.double().cpu().T
+    assert float((out.double().cpu() - ref).abs().max() / ref.abs().max()) < 2e-5
+    print(f"[{m}, {k}] x [{n}, {k}]: {need} of {MAX_FLOATS} scratch values")
+
+
 def test_sizes_beyond_the_built_in_scratch_are_refused():
     from kapel_b200 import kernels as K
 
