@@ -35,8 +35,10 @@ TINY_B = dict(
 )
 TINY = {"A": (TINY_A, 0), "B": (TINY_B, 1)}
 
-# Tolerances: the largest difference of logits over the largest logit of the plain result.
-TOL = {"float32": 2e-5, "bfloat16": 4e-2}
+# Tolerances: the largest difference of logits over the largest logit of the plain result. In
+# 32-bit the reference's own bar (2e-5; these tests see about 1e-6). In bfloat16 the tiny models,
+# whose logits are a few tenths, see up to 1.2e-2 in the worst cut; the bound leaves a quarter above that.
+TOL = {"float32": 2e-5, "bfloat16": 1.5e-2}
 
 
 def make_model_dir(raw_config: dict, seed: int, folder=None, scale_up: float = 1.0, device="cpu") -> Path:

@@ -139,8 +139,8 @@ def rope(x, positions, theta):
     x: [T, heads, D]; positions: [T] integers.
     """
     d = x.shape[-1]
-    w = rope_frequencies(theta, d)
-    angle = positions.to(torch.float64)[:, None] * w[None, :]          # [T, D/2]
+    w = rope_frequencies(theta, d).to(x.device)
+    angle = positions.to(device=x.device, dtype=torch.float64)[:, None] * w[None, :]          # [T, D/2]
     cos = torch.cos(angle).to(x.dtype)[:, None, :]
     sin = torch.sin(angle).to(x.dtype)[:, None, :]
     a, b = x[..., : d // 2], x[..., d // 2 :]
