@@ -28,7 +28,8 @@ PRESETS = ROOT / "kapel_b200" / "config" / "presets"
 # name -> (preset, layers built); the ids say "<built>-of-<the model's>"
 SIZES = {"2b-26-of-26-layers": ("gemma2-2b", 26), "9b-6-of-42-layers": ("gemma2-9b", 6), "27b-4-of-46-layers": ("gemma2-27b", 4)}
 LENGTH_A, LENGTH_B = 4300, 300
-TOL_BF16_DEEP = {"2b-26-of-26-layers": 3e-2, "9b-6-of-42-layers": 2e-2, "27b-4-of-46-layers": 2e-2}
+# bfloat16 bounds at about twice what each size shows (1.0e-2 through 26 layers, 2.6e-3 through 6 and 4)
+TOL_BF16_DEEP = {"2b-26-of-26-layers": 2e-2, "9b-6-of-42-layers": 6e-3, "27b-4-of-46-layers": 6e-3}
 
 
 def _traces(a, b):
