@@ -39,10 +39,11 @@
 // add up as they are. Without a soft cap, with a larger cap, or with a head size other than 64, 128
 // or 256 the mma.sync kernel runs instead.
 //
-// Six warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
-// every MMA; warps 2-5 are the softmax and the epilogue. Every wait on an mbarrier gives up after
-// about a second, raises a flag that `kb_attention_tc_error` reports, and the block still meets at
-// its final barrier, frees its TMEM and returns.
+// Ten warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
+// every MMA; warps 2-5 are the softmax (and put Q into TMEM); warps 6-9 read O out when a segment is
+// complete, so that the softmax of the next segment's first steps runs meanwhile. Every wait on an
+// mbarrier gives up after about a second, raises a flag that `kb_attention_tc_error` reports, and
+// the block still meets at its final barrier, frees its TMEM and returns.
 #include "common.cuh"
 #include "tensor_map.cuh"
 
@@ -50,7 +51,7 @@ namespace kb {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 192;
+constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 320;
 constexpr int AT_SEG_WORDS = 8;       // a segment's record: tile, kv head, first step, end step, slot, slots, partial base, item
 
 __device__ int g_attention_tc_error = 0;
@@ -182,7 +183,9 @@ template <int HD> struct AtCfg {
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
     static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
     static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // 3 HD / 2 + 128 rounded up to a power of two
-    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 512 /* barriers */;
+    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 384 /* barriers */ + 3 * 128 * 4 /* row sums */;
+    static_assert((2 * SLOTS + 11) * 8 + 8 <= 384, "the barriers outgrew their room");
+    static_assert(SMEM <= 232448, "more shared memory than a block can have");
 };
 
 // What a block needs to know of one segment of its work: steps s0 .. s1 - 1 (key tiles of 64) of the
@@ -224,6 +227,10 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     uint64_t* merge_known = merge_written + 1;                   // [1] whether this block arrived last at the item is known
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_known + 1);
     int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);     // the merge: whether this block wrote an item's last partial sums
+    // [3][128] sum p of each row, by segment (softmax -> epilogue). Three suffice: the softmax can finish a
+    // segment only when the product two steps back is issued, and the first product of a segment waits
+    // until the epilogue of the segment before has read its sums.
+    float* l_rows = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 384);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int group = p.hq / p.hkv;
@@ -388,8 +395,8 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 }
             }
         }
-    } else {
-        // ---------------------------------------------------------------- softmax and epilogue, one row a thread
+    } else if (warp < 6) {
+        // ---------------------------------------------------------------- softmax, one row a thread
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // the row of the tile, and the TMEM lane
         const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
@@ -416,7 +423,6 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
         AtSeg sg = at_segment(p, seg_begin, group);
         put_q(sg);
         int it = 0;
-        uint32_t merges = 0;                                     // segments of this block that went through the merge so far
         for (int g = seg_begin; g < seg_end && !failed; ++g) {
             const int nth = g - seg_begin;
             const bool own = r < sg.rows_valid;
@@ -454,6 +460,9 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + h * 16), pr);
                 }
                 l += la + lb;
+                // The row's sum goes to the epilogue warps with the segment's last P: what they wait for
+                // (O complete) comes after the product that waits for this arrival.
+                if (kt == sg.s1 - 1) l_rows[(nth % 3) * AT_ROWS + r] = l;
                 asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
                 at_fence_before();
                 __syncwarp();
@@ -461,14 +470,25 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             }
             if (failed) break;
             // Every score product of this segment is complete (its last S was read above), so Q may be
-            // replaced: the next segment's goes in now and its first scores run under this epilogue.
-            const AtSeg cur = sg;
+            // replaced: the next segment's goes in now and its first scores run under this segment's epilogue.
             if (g + 1 < seg_end) {
                 sg = at_segment(p, g + 1, group);
                 put_q(sg);
             }
+        }
+    } else {
+        // ---------------------------------------------------------------- epilogue, one row a thread
+        const int quarter = warp & 3;
+        const int r = quarter * 32 + lane;
+        const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
+        uint32_t merges = 0;                                     // segments of this block that went through the merge so far
+        for (int g = seg_begin; g < seg_end && !failed; ++g) {
+            const int nth = g - seg_begin;
+            const AtSeg cur = at_segment(p, g, group);
+            const bool own = r < cur.rows_valid;
             if (!__all_sync(0xffffffffu, at_mbar_wait(o_full, (uint32_t)nth & 1u))) { failed = true; break; }
             at_fence_after();
+            const float l = l_rows[(nth % 3) * AT_ROWS + r];
             const int row = cur.row0 + r / group, head = cur.kvh * group + r % group;
             if (cur.slot < 0) {                                  // the whole item was this segment: finish the rows
                 const float inv = l > 0.f ? 1.f / l : 0.f;
@@ -492,21 +512,33 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 __syncwarp();
                 if (lane == 0) at_mbar_arrive(o_empty);
             } else {
-                // Partial sums (reference 0, so the merge is a plain sum): column c of row r at c * 128 + r,
-                // a warp's 32 rows side by side. The segment that arrives last at the item's counter adds
-                // the slots up in their order, whichever it is, and finishes the rows.
+                // Partial sums (reference 0, so the merge is a plain sum): four columns of a row as one
+                // 16-byte value, a warp's 32 rows side by side: columns 4 q .. 4 q + 3 of row r at
+                // (q * 128 + r) * 4, sum p of row r at HD * 128 + r. The segment that arrives last at the
+                // item's counter adds the slots up in their order, whichever it is (its own slot from
+                // TMEM, where it still lies, the others from memory), and finishes the rows.
                 float* mine = p.partial + (size_t)(cur.pbase + cur.slot) * (HD + 1) * AT_ROWS;
                 for (int c0 = 0; c0 < HD; c0 += 32) {
                     uint32_t o[32];
                     at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
                     asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                    float4* dst4 = reinterpret_cast<float4*>(mine) + (size_t)(c0 / 4) * AT_ROWS + r;
 #pragma unroll
-                    for (int j = 0; j < 32; ++j) mine[(size_t)(c0 + j) * AT_ROWS + r] = __uint_as_float(o[j]);
+                    for (int j = 0; j < 8; ++j)
+                        dst4[(size_t)j * AT_ROWS] = make_float4(__uint_as_float(o[4 * j]), __uint_as_float(o[4 * j + 1]),
+                                                                __uint_as_float(o[4 * j + 2]), __uint_as_float(o[4 * j + 3]));
                 }
                 mine[(size_t)HD * AT_ROWS + r] = l;
-                at_fence_before();
-                __syncwarp();
-                if (lane == 0) at_mbar_arrive(o_empty);          // O is read out: the next segment's products may start
+                // A block's last segment keeps O for the merge, if the merge falls to it (the head of an item
+                // that was cut runs last in its block and is usually the last to arrive). Any other segment
+                // gives O up now, so that the products of the segment behind it may start, and would read
+                // its own slot back from memory like the others: the same values, the same sum.
+                const bool keep = g == seg_end - 1;
+                if (!keep) {
+                    at_fence_before();
+                    __syncwarp();
+                    if (lane == 0) at_mbar_arrive(o_empty);
+                }
                 // The four warps meet twice on barriers with bounded waits: when all their partial sums are
                 // written, and when the first of them has counted this segment in at the item's counter.
                 __threadfence();
@@ -524,29 +556,51 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                 if (is_last) {
                     __threadfence();
                     const float* base = p.partial + (size_t)cur.pbase * (HD + 1) * AT_ROWS;
+                    constexpr size_t SLOT_FLOATS = (size_t)(HD + 1) * AT_ROWS;
                     float total = 0.f;
-                    for (int z = 0; z < cur.slots; ++z) total += __ldcg(base + ((size_t)z * (HD + 1) + HD) * AT_ROWS + r);
+                    for (int z = 0; z < cur.slots; ++z) total += z == cur.slot ? l : __ldcg(base + z * SLOT_FLOATS + (size_t)HD * AT_ROWS + r);
                     const float inv = total > 0.f ? 1.f / total : 0.f;
                     bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
-                    for (int c0 = 0; c0 < HD; c0 += 8) {
-                        float acc[8];
+                    for (int c0 = 0; c0 < HD; c0 += 32) {
+                        uint32_t o[32];
+                        if (keep) at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
+                        float acc[32];
 #pragma unroll
-                        for (int j = 0; j < 8; ++j) acc[j] = 0.f;
+                        for (int j = 0; j < 32; ++j) acc[j] = 0.f;
+                        if (keep) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
                         for (int z = 0; z < cur.slots; ++z) {
-                            const float* src = base + ((size_t)z * (HD + 1) + c0) * AT_ROWS + r;
+                            if (z == cur.slot && keep) {
 #pragma unroll
-                            for (int j = 0; j < 8; ++j) acc[j] += __ldcg(src + (size_t)j * AT_ROWS);
+                                for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(o[j]);
+                            } else {
+                                const float4* src = reinterpret_cast<const float4*>(base + z * SLOT_FLOATS) + (size_t)(c0 / 4) * AT_ROWS + r;
+                                float4 t[8];
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) t[j] = __ldcg(src + (size_t)j * AT_ROWS);
+#pragma unroll
+                                for (int j = 0; j < 8; ++j) {
+                                    acc[4 * j] += t[j].x; acc[4 * j + 1] += t[j].y; acc[4 * j + 2] += t[j].z; acc[4 * j + 3] += t[j].w;
+                                }
+                            }
                         }
                         if (own) {
-                            uint4 v;
-                            v.x = at_pack(acc[0] * inv, acc[1] * inv);
-                            v.y = at_pack(acc[2] * inv, acc[3] * inv);
-                            v.z = at_pack(acc[4] * inv, acc[5] * inv);
-                            v.w = at_pack(acc[6] * inv, acc[7] * inv);
-                            *reinterpret_cast<uint4*>(dst + c0) = v;
+#pragma unroll
+                            for (int j = 0; j < 32; j += 8) {
+                                uint4 v;
+                                v.x = at_pack(acc[j] * inv, acc[j + 1] * inv);
+                                v.y = at_pack(acc[j + 2] * inv, acc[j + 3] * inv);
+                                v.z = at_pack(acc[j + 4] * inv, acc[j + 5] * inv);
+                                v.w = at_pack(acc[j + 6] * inv, acc[j + 7] * inv);
+                                *reinterpret_cast<uint4*>(dst + c0 + j) = v;
+                            }
                         }
                     }
                     if (r == 0) p.counters[cur.item] = 0;            // as the next launch expects to find it
+                }
+                if (keep) {
+                    at_fence_before();
+                    __syncwarp();
+                    if (lane == 0) at_mbar_arrive(o_empty);
                 }
                 // last_flag is written again only behind the next merge's first barrier, which every warp
                 // reaches after it has read the flag here.

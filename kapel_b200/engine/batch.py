@@ -121,7 +121,7 @@ class PromptBalance:
 
 
 def balance_prompt_tiles(tile_row0, tile_nq, row_count, kv_heads: int, window: Optional[int], blocks: int,
-                         min_steps: int = 4, item_cost: int = 2) -> PromptBalance:
+                         min_steps: int = 4, item_cost: float = 2.0, snap: int = 2) -> PromptBalance:
     """Shares the prompt kernel's work out evenly. An item is a (tile, kv head) pair and the keys
     its rows see, walked in steps of 64 keys from the 64-key boundary at or below its first visible
     key; a late tile of a long prompt has many times the steps of an early one. All steps of all
@@ -130,8 +130,10 @@ def balance_prompt_tiles(tile_row0, tile_nq, row_count, kv_heads: int, window: O
     queries go into tensor memory, its result comes out); a share is a list of segments (steps s0
     .. s1 - 1 of an item). An item that falls into one share whole is finished there (slot -1);
     one that is cut leaves one slot of partial sums a segment, which the kernel merges itself.
-    Fewer blocks are used when the work is small: as many as there are items, or one for every
-    `min_steps` steps if that is more. Every step of every item lies in exactly one segment."""
+    A cut that falls within `snap` steps of an item's end is moved there: cutting an item costs a
+    merge, more than the few steps it evens out. Fewer blocks are used when the work is small: as
+    many as there are items, or one for every `min_steps` steps if that is more. Every step of
+    every item lies in exactly one segment."""
     row0 = np.asarray(tile_row0, np.int64)
     nq = np.asarray(tile_nq, np.int64)
     counts = np.asarray(row_count, np.int64)
@@ -148,14 +150,25 @@ def balance_prompt_tiles(tile_row0, tile_nq, row_count, kv_heads: int, window: O
     item_steps = steps[item_tile]
     n_items = item_tile.size
     total = int(item_steps.sum())
+    import os
+    blocks = int(os.environ.get("KAPEL_B200_TC_BLOCKS", blocks))
     blocks = max(1, min(int(blocks), max(min(n_items, total), total // max(1, min_steps))))
     starts = np.concatenate(([0], np.cumsum(item_steps)))              # [items + 1]
     # the cuts are made where the cost (steps + item_cost an item) is equal, then moved to the step they fall on
-    cost_starts = np.concatenate(([0], np.cumsum(item_steps + item_cost)))
-    cost_bounds = (np.arange(blocks + 1, dtype=np.int64) * int(cost_starts[-1])) // blocks
-    at = np.minimum(np.searchsorted(cost_starts, cost_bounds, side="right") - 1, n_items - 1)
-    bounds = starts[at] + np.clip(cost_bounds - cost_starts[at] - item_cost, 0, item_steps[at])
+    import os
+    item_cost = float(os.environ.get("KAPEL_B200_TC_ITEM_COST", item_cost))
+    snap = int(os.environ.get("KAPEL_B200_TC_SNAP", snap))
+    blocks = int(os.environ.get("KAPEL_B200_TC_BLOCKS", blocks))
+    cost_starts = np.concatenate(([0.0], np.cumsum(item_steps + item_cost)))
+    cost_bounds = np.arange(blocks + 1, dtype=np.float64) * (cost_starts[-1] / blocks)
+    at = np.clip(np.searchsorted(cost_starts, cost_bounds, side="right") - 1, 0, n_items - 1)
+    bounds = starts[at] + np.clip(np.rint(cost_bounds - cost_starts[at] - item_cost).astype(np.int64), 0, item_steps[at])
     bounds[-1] = total
+    if snap > 0:
+        right = np.minimum(np.searchsorted(starts, bounds, side="left"), n_items)
+        nearest = np.where(np.abs(starts[right] - bounds) <= np.abs(bounds - starts[np.maximum(right - 1, 0)]), starts[right],
+                           starts[np.maximum(right - 1, 0)])
+        bounds = np.where(np.abs(nearest - bounds) <= snap, nearest, bounds)
     bounds = np.unique(bounds)                                          # a share that came out empty is dropped
     blocks = bounds.size - 1
     cuts = np.unique(np.concatenate((starts, bounds)))

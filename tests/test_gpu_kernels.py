@@ -462,7 +462,7 @@ def test_paged_attention_tcgen05_shared_out_among_any_number_of_blocks(hq, hkv, 
         assert rel_err(got.double().numpy(), want.numpy()) < 1.5e-2, f"{balance.blocks} blocks, {balance.partial_slots} partial slots"
         outs.append(got)
     assert torch.equal(outs[0], outs[1])
-    if blocks in (3, 7):
+    if blocks in (3, 7) and window is None:
         assert balance.partial_slots > 0                   # some item was cut: the merge ran
 
 

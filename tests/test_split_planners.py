@@ -120,10 +120,10 @@ def test_balanced_shares_hold_every_step_of_every_item_once(window):
                     assert s[4] + s[2] not in used
                     used.add(s[4] + s[2])
         assert used == set(range(b.partial_slots))
-        # segments of a block are consecutive in the list, and the shares are even: no block's cost
-        # (steps plus two an item it touches) is more than the mean plus the heaviest single step count
+        # segments of a block are consecutive in the list, and the shares are even: no block's cost (steps
+        # plus two an item it touches) is far above the mean (a cut may move two steps to an item's end)
         cost = np.add.reduceat(b.segments[:, 3] - b.segments[:, 2] + 2, b.cta_first[:-1])
-        assert cost.max() <= cost.mean() + 4
+        assert cost.max() <= cost.mean() + 8
 
 
 def test_balanced_shares_refuse_a_tile_that_has_seen_nothing():
