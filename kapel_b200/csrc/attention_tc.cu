@@ -1,49 +1,35 @@
 // Paged attention for prompt portions on the fifth-generation tensor cores (bfloat16, soft cap).
 //
-// The work is cut into items: a tile of 128 rows — (token, query head) pairs of one kv head, the same
-// tiles as the mma.sync kernel — and the keys it sees, walked 64 at a time ("steps"). A late tile of
-// a long prompt has many times the steps of an early one, so items are not handed to blocks whole:
-// the host lays all steps of all items in a row and gives every block an equal share of it (at most
-// one block a multiprocessor), as a list of segments: steps s0 .. s1 - 1 of an item. A block runs
-// its segments one after the other through the same pipeline. An item that lies within one segment
-// is finished by it; the segments of an item that was cut each leave partial sums (sum p v, sum p),
-// and the one that arrives last at the item's counter adds them up, in the order of the cut, and
-// finishes the rows: no second kernel, no spinning, the same bits whoever is last.
-//
-// A step:
+// One block takes a tile of 128 rows — (token, query head) pairs of one kv head, the same tiles as
+// the mma.sync kernel — and walks its keys 64 at a time:
 //   S = Q K^T      tcgen05.mma with Q [128 x d] as the A operand from tensor memory (TMEM), where
-//                  it is put once a segment (read from shared memory, Q would cost every product 4 KB),
-//                  the key tile [64 x d] K-major in shared memory (128-byte swizzle), S [128 x 64]
+//                  it is put once (read from shared memory, Q would cost every product 4 KB), the
+//                  key tile [64 x d] K-major in shared memory (128-byte swizzle), S [128 x 64]
 //                  float32 in TMEM;
 //   P = exp(cap tanh(S scale / cap)), masked, read from TMEM and written back over S as bfloat16
 //                  by four warps, one row a thread;
 //   O += P V       tcgen05.mma with P as the A operand straight from TMEM and the value tile
-//                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM for the segment.
+//                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM throughout.
 // TMEM columns: O (d), two S buffers (64 each; P lies over the first 32 columns of its S), Q (d / 2).
-// One thread issues every MMA and they run in the order issued, so the scores of step it + 2 land on
-// their buffer only after the product that read step it's P from it. Between two segments the next
-// Q goes into TMEM as soon as the last scores of the segment before are complete, and its first
-// scores run while the softmax warps read O out; the first P V product of a segment waits for that.
+// One thread issues every MMA and they run in the order issued, so the scores of tile kt + 2 land on
+// their buffer only after the product that read tile kt's P from it.
 // Keys and values arrive by TMA in two rings of slots, one for key tiles and one for value tiles,
-// each slot freed by the tcgen05.commit of the product that read it; the rings run on through the
-// segments. A product costs the tensor cores about 90 cycles whatever its width up to 128 columns, so
-// the scores take all 64 keys in one product a 16-element step: the key tile is laid out [chunk of 64
-// elements][64 keys], boxes of 16 keys x 64 elements, one a (page, chunk). The values, whose products
-// step through the keys 16 at a time, come as one three-dimensional copy a page: [page][chunk][16
-// keys]. S and P are double-buffered so the exponentials of one step run under the products of its
-// neighbours.
+// each slot freed by the tcgen05.commit of the product that read it. A product costs the tensor
+// cores about 50 cycles beyond its arithmetic, so the scores take all 64 keys in one product a
+// 16-element step: the key tile is laid out [chunk of 64 elements][64 keys], boxes of 16 keys x 64
+// elements, one a (page, chunk). The values, whose products step through the keys 16 at a time,
+// come as one three-dimensional copy a page: [page][chunk][16 keys]. S and P are double-buffered so
+// the exponentials of one tile run under the products of its neighbours.
 //
 // The soft cap bounds every score by +-cap, so exp(s) itself is safe in float32 and bfloat16 for
 // cap <= 64 (e^64 times 2^17 keys < 3e38, e^-64 > 1e-38): the softmax uses the fixed reference 0
-// instead of a running maximum, O never has to be rescaled, and partial sums of different segments
-// add up as they are. Without a soft cap, with a larger cap, or with a head size other than 64, 128
-// or 256 the mma.sync kernel runs instead.
+// instead of a running maximum, and O never has to be rescaled. Without a soft cap, with a larger
+// cap, or with a head size other than 64, 128 or 256 the mma.sync kernel runs instead.
 //
-// Ten warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
-// every MMA; warps 2-5 are the softmax (and put Q into TMEM); warps 6-9 read O out when a segment is
-// complete, so that the softmax of the next segment's first steps runs meanwhile. Every wait on an
-// mbarrier gives up after about a second, raises a flag that `kb_attention_tc_error` reports, and
-// the block still meets at its final barrier, frees its TMEM and returns.
+// Six warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
+// every MMA; warps 2-5 are the softmax and the epilogue. Every wait on an mbarrier gives up after
+// about a second, raises a flag that `kb_attention_tc_error` reports, and the block still meets at
+// its final barrier, frees its TMEM and returns.
 #include "common.cuh"
 #include "tensor_map.cuh"
 
@@ -51,8 +37,7 @@ namespace kb {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 320;
-constexpr int AT_SEG_WORDS = 8;       // a segment's record: tile, kv head, first step, end step, slot, slots, partial base, item
+constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 192;
 
 __device__ int g_attention_tc_error = 0;
 
@@ -63,13 +48,10 @@ struct AttTcParams {
     const int* tile_entry;     // [tiles]
     const int* tile_row0;      // [tiles] first row (token) of the tile in the batch
     const int* tile_nq;        // [tiles] tokens in the tile
-    const int* segments;       // [n_segments, AT_SEG_WORDS]
-    const int* cta_first;      // [blocks + 1]: block b runs segments cta_first[b] .. cta_first[b + 1] - 1
     bf16* out;                 // [rows, hq, d]
-    float* partial;            // [partial slots, d + 1, 128]: column c of row r at (c * 128 + r); column d is sum p
-    int* counters;             // [items]: segments of an item that have written their partial sums; zero between launches
+    float* partial;            // [rows, hq, slots, d + 2] when slots > 1: (sum p v, reference 0, sum p)
     int rows, hq, hkv, d, page_size, table_width, n_pages;
-    int window;
+    int window, split, slots;
     float scale, cap;
 };
 
@@ -183,30 +165,8 @@ template <int HD> struct AtCfg {
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
     static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
     static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // 3 HD / 2 + 128 rounded up to a power of two
-    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 384 /* barriers */ + 3 * 128 * 4 /* row sums */;
-    static_assert((2 * SLOTS + 11) * 8 + 8 <= 384, "the barriers outgrew their room");
-    static_assert(SMEM <= 232448, "more shared memory than a block can have");
+    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 256 /* barriers */;
 };
-
-// What a block needs to know of one segment of its work: steps s0 .. s1 - 1 (key tiles of 64) of the
-// item (tile, kv head), whose keys are [klo, khi) and whose first key tile starts at k_begin.
-struct AtSeg {
-    int tile, kvh, s0, s1, slot, pbase, item, slots;
-    int row0, nq, entry, rows_valid, c_first, klo, khi, k_begin, n_steps;
-};
-__device__ __forceinline__ AtSeg at_segment(const AttTcParams& p, int g, int group) {
-    const int* w = p.segments + (size_t)g * AT_SEG_WORDS;
-    AtSeg s;
-    s.tile = w[0]; s.kvh = w[1]; s.s0 = w[2]; s.s1 = w[3]; s.slot = w[4]; s.slots = w[5]; s.pbase = w[6]; s.item = w[7];
-    s.row0 = p.tile_row0[s.tile]; s.nq = p.tile_nq[s.tile]; s.entry = p.tile_entry[s.tile];
-    s.rows_valid = s.nq * group;
-    s.c_first = p.row_count[s.row0];
-    s.klo = (p.window > 0 && s.c_first > p.window) ? s.c_first - p.window : 0;
-    s.khi = s.c_first > 0 ? s.c_first + s.nq - 1 : 0;
-    s.k_begin = s.klo / AT_KEYS * AT_KEYS;
-    s.n_steps = (s.khi - s.k_begin + AT_KEYS - 1) / AT_KEYS;
-    return s;
-}
 
 template <int HD>
 __global__ void __launch_bounds__(AT_THREADS, 1)
@@ -220,35 +180,41 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete
     uint64_t* s_full = empty + NS;                               // [2] S complete (MMA -> softmax)
     uint64_t* p_full = s_full + 2;                               // [2] P written (softmax -> MMA), four warps arrive
-    uint64_t* o_full = p_full + 2;                               // [1] O of a segment complete (MMA -> softmax)
-    uint64_t* o_empty = o_full + 1;                              // [1] O read out (softmax -> MMA), four warps arrive
-    uint64_t* q_full = o_empty + 1;                              // [1] Q of a segment in TMEM (softmax -> MMA), four warps arrive
-    uint64_t* merge_written = q_full + 1;                        // [1] the four warps' partial sums are in memory
-    uint64_t* merge_known = merge_written + 1;                   // [1] whether this block arrived last at the item is known
-    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(merge_known + 1);
-    int* last_flag = reinterpret_cast<int*>(tmem_slot + 1);     // the merge: whether this block wrote an item's last partial sums
-    // [3][128] sum p of each row, by segment (softmax -> epilogue). Three suffice: the softmax can finish a
-    // segment only when the product two steps back is issued, and the first product of a segment waits
-    // until the epilogue of the segment before has read its sums.
-    float* l_rows = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 384);
+    uint64_t* o_full = p_full + 2;                               // [1] O complete
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    const int kvh = blockIdx.x, slot = blockIdx.y;
+    // Later tiles of a prompt see more keys: they start first, all their heads and slots together.
+    const int tile = gridDim.z - 1 - blockIdx.z;
     const int group = p.hq / p.hkv;
-    const int seg_begin = p.cta_first[blockIdx.x], seg_end = p.cta_first[blockIdx.x + 1];
-    if (seg_begin >= seg_end) {                                  // nothing for this block: before anything is allocated
+    const int row0 = p.tile_row0[tile], nq = p.tile_nq[tile];
+    const int entry = p.tile_entry[tile];
+    const int rows_valid = nq * group;
+    const int c_first = p.row_count[row0];
+    int klo = (p.window > 0 && c_first > p.window) ? c_first - p.window : 0;
+    int khi = c_first > 0 ? c_first + nq - 1 : 0;                // a padding row sees nothing
+    if (p.split > 0) {
+        klo = max(klo, slot * p.split);
+        khi = min(khi, (slot + 1) * p.split);
+    }
+    const int d = HD;
+    if (klo >= khi) {                                            // nothing for this block: before anything is allocated
         dependent_wait();
+        if (p.slots == 1 && c_first <= 0)
+            for (int i = tid; i < rows_valid * d; i += AT_THREADS) {
+                const int r = i / d, c = i % d;
+                p.out[((size_t)(row0 + r / group) * p.hq + kvh * group + r % group) * d + c] = __float2bfloat16_rn(0.f);
+            }
         return;
     }
-    constexpr int d = HD;
+    const int k_begin = klo / AT_KEYS * AT_KEYS;
+    const int n_tiles = (khi - k_begin + AT_KEYS - 1) / AT_KEYS;
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 1); at_mbar_init(empty + s, 1); }
         for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 4); }
         at_mbar_init(o_full, 1);
-        at_mbar_init(o_empty, 4);
-        at_mbar_init(q_full, 4);
-        at_mbar_init(merge_written, 4);
-        at_mbar_init(merge_known, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     if (warp == 1) {
@@ -260,74 +226,85 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     at_fence_after();
     const uint32_t tmem = *tmem_slot;
     dependent_wait();                                       // the queries and the newest keys are the kernel before's
+    // Q into TMEM as the A operand of the score products: row r in lane r, two elements a column.
+    if (warp >= 2) {
+        const int r = (warp & 3) * 32 + lane;
+        const bf16* src = p.q + ((size_t)(row0 + (r < rows_valid ? r / group : 0)) * p.hq + kvh * group + (r < rows_valid ? r % group : 0)) * d;
+        for (int c0 = 0; c0 < HD; c0 += 64) {
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    // The MMA warp must see Q in place; the copying warp need not, and asks for keys meanwhile.
+    at_fence_before();
+    if (warp >= 1) asm volatile("bar.sync 1, 160;" ::: "memory");
+    at_fence_after();
     bool failed = false;
 
     if (warp == 0) {
         // ---------------------------------------------------------------- pages and boxes
-        // The keys of the block's step `it` (counted through all its segments) go to key slot
-        // it % KS, its values to value slot KS + it % VS. The pages of eight steps are looked up at
-        // once, lane 4 t + sub for keys 16 sub .. of the batch's step t, and one batch ahead of their
-        // use. A group without a page (before the window, past the end) is cleared instead when it
-        // holds values: 0 * garbage could be NaN.
+        // The keys of tile kt go to key slot kt % KS, its values to value slot KS + kt % VS. The pages
+        // of eight tiles are looked up at once, lane 4 t + sub for keys 16 sub .. of the batch's tile
+        // t, and one batch ahead of their use. A group without a page (before the window, past the
+        // end) is cleared instead when it holds values: 0 * garbage could be NaN.
+        auto lookup = [&](int kt_first) -> int {
+            const int kt = kt_first + (lane >> 2);
+            const int j = k_begin + kt * AT_KEYS + (lane & 3) * 16;
+            int page = -1;
+            if (kt < n_tiles && j < khi && j + 16 > klo) {
+                const int lp = max(j, klo) / p.page_size;
+                if (lp < p.table_width) page = p.block_table[(size_t)entry * p.table_width + lp];
+                if (page >= p.n_pages) page = -1;
+            }
+            return page;
+        };
+        int pages_now = 0, pages_next = lookup(0);
         constexpr uint32_t PAGE_BYTES = NBOX * 2048u;                                // a page's keys (or values) of one kv head
-        int it = 0;
-        for (int g = seg_begin; g < seg_end && !failed; ++g) {
-            const AtSeg sg = at_segment(p, g, group);
-            auto lookup = [&](int kt_first) -> int {
-                const int kt = kt_first + (lane >> 2);
-                const int j = sg.k_begin + kt * AT_KEYS + (lane & 3) * 16;
-                int page = -1;
-                if (kt < sg.s1 && j < sg.khi && j + 16 > sg.klo) {
-                    const int lp = max(j, sg.klo) / p.page_size;
-                    if (lp < p.table_width) page = p.block_table[(size_t)sg.entry * p.table_width + lp];
-                    if (page >= p.n_pages) page = -1;
-                }
-                return page;
-            };
-            int pages_now = 0, pages_next = lookup(sg.s0);
-            for (int kt = sg.s0; kt < sg.s1 && !failed; ++kt, ++it) {
-                const int local = kt - sg.s0;
-                if ((local & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
-                const int j0 = sg.k_begin + kt * AT_KEYS;
-                const int page = __shfl_sync(0xffffffffu, pages_now, (local & 7) * 4 + (lane & 3));
-                const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
-                const int live = __popc(have);
-                for (int half = 0; half < 2; ++half) {               // keys, then values
-                    const int s = half == 0 ? it % KS : KS + it % VS;
-                    const int round = half == 0 ? it / KS : it / VS;
-                    bool ok = true;
-                    if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
-                    if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
-                    unsigned char* dst = ring + s * C::SLOT_BYTES;
-                    if (half == 1 && live < 4) {
-                        for (int sub = 0; sub < 4; ++sub) {
-                            if (have & (1u << sub)) continue;
-                            uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_BYTES);
-                            for (int e = lane; e < (int)(PAGE_BYTES / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
-                        }
-                        at_fence_async_smem();
-                        __syncwarp();
+        for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+            if ((kt & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
+            const int j0 = k_begin + kt * AT_KEYS;
+            const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
+            const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
+            const int live = __popc(have);
+            for (int half = 0; half < 2; ++half) {               // keys, then values
+                const int s = half == 0 ? kt % KS : KS + kt % VS;
+                const int round = half == 0 ? kt / KS : kt / VS;
+                bool ok = true;
+                if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
+                if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
+                unsigned char* dst = ring + s * C::SLOT_BYTES;
+                if (half == 1 && live < 4) {
+                    for (int sub = 0; sub < 4; ++sub) {
+                        if (have & (1u << sub)) continue;
+                        uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_BYTES);
+                        for (int e = lane; e < (int)(PAGE_BYTES / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
                     }
-                    if (lane == 0) {
-                        if (live > 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_BYTES);
-                        else at_mbar_arrive(full + s);           // no copy will arrive on its behalf
-                    }
+                    at_fence_async_smem();
                     __syncwarp();
-                    if (half == 0) {
-                        // keys: a box of 16 keys x 64 elements a lane, chunk by chunk [chunk][page][16 keys], so that
-                        // the tile's eight-key groups are 1 KB apart and one product takes all 64 keys
-                        const int sub = (lane / NBOX) & 3, bx = lane % NBOX;
-                        const int pg = __shfl_sync(0xffffffffu, page, sub);
-                        if (lane < 4 * NBOX && pg >= 0) {
-                            const int j = j0 + sub * 16;
-                            const int row = (pg * p.hkv + sg.kvh) * p.page_size + j % p.page_size;
-                            at_tma_box(at_saddr(dst) + (uint32_t)(bx * 4 + sub) * 2048u, &map_k, bx * 64, row, full + s);
-                        }
-                    } else if (lane < 4 && page >= 0) {              // values: one copy a page, [page][chunk][16 keys]
-                        const int j = j0 + lane * 16;
-                        const int row = (page * p.hkv + sg.kvh) * p.page_size + j % p.page_size;
-                        at_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_BYTES, &map_v, row, full + s);
+                }
+                if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_BYTES);
+                __syncwarp();
+                if (half == 0) {
+                    // keys: a box of 16 keys x 64 elements a lane, chunk by chunk [chunk][page][16 keys], so that
+                    // the tile's eight-key groups are 1 KB apart and one product takes all 64 keys
+                    const int sub = (lane / NBOX) & 3, bx = lane % NBOX;
+                    const int pg = __shfl_sync(0xffffffffu, page, sub);
+                    if (lane < 4 * NBOX && pg >= 0) {
+                        const int j = j0 + sub * 16;
+                        const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
+                        at_tma_box(at_saddr(dst) + (uint32_t)(bx * 4 + sub) * 2048u, &map_k, bx * 64, row, full + s);
                     }
+                } else if (lane < 4 && page >= 0) {              // values: one copy a page, [page][chunk][16 keys]
+                    const int j = j0 + lane * 16;
+                    const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                    at_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_BYTES, &map_v, row, full + s);
                 }
             }
         }
@@ -338,12 +315,12 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
             constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
             const uint32_t ring_addr = at_saddr(ring);
-            auto issue_s = [&](int it) -> bool {                 // S[it & 1] = Q K(step it)^T
-                const int s = it % KS;
-                if (!at_mbar_wait(full + s, (uint32_t)(it / KS) & 1u)) return false;
+            auto issue_s = [&](int kt) -> bool {                 // S[kt & 1] = Q K(kt)^T
+                const int s = kt % KS;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) return false;
                 at_fence_after();
                 const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (it & 1) * AT_KEYS);
+                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (kt & 1) * AT_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
                     const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
@@ -353,151 +330,94 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                         at_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);                            // the key slot is free when S is complete
-                at_commit(s_full + (it & 1));
+                at_commit(s_full + (kt & 1));
                 return true;
             };
-            int it = 0;
-            // The scores of a segment's first step need its Q in place; those of the step after the one
-            // whose P V product is due are issued before that product, so the softmax never waits for them.
-            if (!at_mbar_wait(q_full, 0u)) failed = true;
-            if (!failed) { at_fence_after(); if (!issue_s(0)) failed = true; }
-            for (int g = seg_begin; g < seg_end && !failed; ++g) {
-                const int* w = p.segments + (size_t)g * AT_SEG_WORDS;
-                const int n = w[3] - w[2];
-                const int nth = g - seg_begin;                   // this block's nth segment
-                for (int local = 0; local < n && !failed; ++local, ++it) {
-                    const int b = it & 1;
-                    const bool last = local == n - 1;
-                    if (!last && !issue_s(it + 1)) { failed = true; break; }
-                    const int s = KS + it % VS;
-                    if (!at_mbar_wait(full + s, (uint32_t)(it / VS) & 1u)) { failed = true; break; }
-                    if (!at_mbar_wait(p_full + b, (uint32_t)(it >> 1) & 1u)) { failed = true; break; }
-                    // the first product of a segment overwrites O: the segment before must have been read out
-                    if (local == 0 && nth > 0 && !at_mbar_wait(o_empty, (uint32_t)(nth - 1) & 1u)) { failed = true; break; }
-                    at_fence_after();
-                    const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                    const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
+            if (!issue_s(0)) failed = true;
+            for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+                const int b = kt & 1;
+                if (kt + 1 < n_tiles && !issue_s(kt + 1)) { failed = true; break; }
+                const int s = KS + kt % VS;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / VS) & 1u)) { failed = true; break; }
+                if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
+                at_fence_after();
+                const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
+                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
 #pragma unroll
-                    for (int kk = 0; kk < 4; ++kk) {
-                        // keys 16 kk ..: page kk of the tile, its two eight-key groups 1 KB apart, chunks 2 KB apart
-                        const uint64_t bdesc = at_desc(v_addr + (uint32_t)kk * PAGE_BYTES, 2048, 1024);
-                        at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (local | kk) != 0 ? 1u : 0u);
-                    }
-                    at_commit(empty + s);
-                    if (last) {
-                        at_commit(o_full);
-                        if (g + 1 < seg_end) {                   // the next segment's first scores, once its Q is in place
-                            if (!at_mbar_wait(q_full, (uint32_t)(nth + 1) & 1u)) { failed = true; break; }
-                            at_fence_after();
-                            if (!issue_s(it + 1)) { failed = true; break; }
-                        }
-                    }
+                for (int kk = 0; kk < 4; ++kk) {
+                    // keys 16 kk ..: page kk of the tile, its two eight-key groups 1 KB apart, chunks 2 KB apart
+                    const uint64_t bdesc = at_desc(v_addr + (uint32_t)kk * PAGE_BYTES, 2048, 1024);
+                    at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
                 }
+                at_commit(empty + s);
             }
+            if (!failed) at_commit(o_full);
         }
-    } else if (warp < 6) {
-        // ---------------------------------------------------------------- softmax, one row a thread
+    } else {
+        // ---------------------------------------------------------------- softmax and epilogue, one row a thread
         const int quarter = warp & 3;
         const int r = quarter * 32 + lane;                       // the row of the tile, and the TMEM lane
+        const bool own = r < rows_valid;
+        const int cnt = own ? c_first + r / group : 0;
+        const int fst = (own && p.window > 0 && cnt > p.window) ? cnt - p.window : 0;
+        const int lo = max(fst, klo), hi = min(cnt, khi);        // this row sees keys [lo, hi) of this block's
+        const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
         const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
         const float c1 = p.scale / p.cap, c2 = p.cap * 1.4426950408889634f;
-        // Q into TMEM as the A operand of the score products: row r in lane r, two elements a column.
-        auto put_q = [&](const AtSeg& sg) {
-            const bool own = r < sg.rows_valid;
-            const bf16* src = p.q + ((size_t)(sg.row0 + (own ? r / group : 0)) * p.hq + sg.kvh * group + (own ? r % group : 0)) * d;
-            for (int c0 = 0; c0 < HD; c0 += 64) {
-                uint32_t w[32];
+        float l = 0.f;
+        for (int kt = 0; kt < n_tiles; ++kt) {
+            const int b = kt & 1;
+            const int j0 = k_begin + kt * AT_KEYS;
+            if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
+            at_fence_after();
+            uint32_t s0[32], s1[32], pr[16];
+            const bool edge = j0 < lo_max || j0 + AT_KEYS > hi_min;      // the same for the whole warp
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS), s0);
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + 32), s1);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float la = 0.f, lb = 0.f;                            // two chains of additions
 #pragma unroll
-                for (int j = 0; j < 8; ++j) {
-                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                    if (own) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
-                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            for (int h = 0; h < 2; ++h) {
+#pragma unroll
+                for (int j = 0; j < 32; j += 2) {
+                    float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
+                    float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
+                    if (edge) {
+                        const int jj = j0 + h * 32 + j;
+                        if (jj < lo || jj >= hi) p0 = 0.f;
+                        if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
+                    }
+                    la += p0;
+                    lb += p1;
+                    pr[j >> 1] = at_pack(p0, p1);
                 }
-                at_st32(lanes + (uint32_t)(C::COL_Q + c0 / 2), w);
+                at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + h * 16), pr);
             }
+            l += la + lb;
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             at_fence_before();
             __syncwarp();
-            if (lane == 0) at_mbar_arrive(q_full);
-        };
-        AtSeg sg = at_segment(p, seg_begin, group);
-        put_q(sg);
-        int it = 0;
-        for (int g = seg_begin; g < seg_end && !failed; ++g) {
-            const int nth = g - seg_begin;
-            const bool own = r < sg.rows_valid;
-            const int cnt = own ? sg.c_first + r / group : 0;
-            const int fst = (own && p.window > 0 && cnt > p.window) ? cnt - p.window : 0;
-            const int lo = max(fst, sg.klo), hi = min(cnt, sg.khi);  // this row sees keys [lo, hi)
-            const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
-            float l = 0.f;
-            for (int kt = sg.s0; kt < sg.s1; ++kt, ++it) {
-                const int b = it & 1;
-                const int j0 = sg.k_begin + kt * AT_KEYS;
-                if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(it >> 1) & 1u))) { failed = true; break; }
-                at_fence_after();
-                uint32_t s0[32], s1[32], pr[16];
-                const bool edge = j0 < lo_max || j0 + AT_KEYS > hi_min;      // the same for the whole warp
-                at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS), s0);
-                at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + 32), s1);
-                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                float la = 0.f, lb = 0.f;                            // two chains of additions
-#pragma unroll
-                for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                    for (int j = 0; j < 32; j += 2) {
-                        float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
-                        float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
-                        if (edge) {
-                            const int jj = j0 + h * 32 + j;
-                            if (jj < lo || jj >= hi) p0 = 0.f;
-                            if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
-                        }
-                        la += p0;
-                        lb += p1;
-                        pr[j >> 1] = at_pack(p0, p1);
-                    }
-                    at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + h * 16), pr);
-                }
-                l += la + lb;
-                // The row's sum goes to the epilogue warps with the segment's last P: what they wait for
-                // (O complete) comes after the product that waits for this arrival.
-                if (kt == sg.s1 - 1) l_rows[(nth % 3) * AT_ROWS + r] = l;
-                asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
-                at_fence_before();
-                __syncwarp();
-                if (lane == 0) at_mbar_arrive(p_full + b);
-            }
-            if (failed) break;
-            // Every score product of this segment is complete (its last S was read above), so Q may be
-            // replaced: the next segment's goes in now and its first scores run under this segment's epilogue.
-            if (g + 1 < seg_end) {
-                sg = at_segment(p, g + 1, group);
-                put_q(sg);
-            }
+            if (lane == 0) at_mbar_arrive(p_full + b);
         }
-    } else {
-        // ---------------------------------------------------------------- epilogue, one row a thread
-        const int quarter = warp & 3;
-        const int r = quarter * 32 + lane;
-        const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
-        uint32_t merges = 0;                                     // segments of this block that went through the merge so far
-        for (int g = seg_begin; g < seg_end && !failed; ++g) {
-            const int nth = g - seg_begin;
-            const AtSeg cur = at_segment(p, g, group);
-            const bool own = r < cur.rows_valid;
-            if (!__all_sync(0xffffffffu, at_mbar_wait(o_full, (uint32_t)nth & 1u))) { failed = true; break; }
+        if (!failed && !__all_sync(0xffffffffu, at_mbar_wait(o_full, 0u))) failed = true;
+        if (!failed) {
             at_fence_after();
-            const float l = l_rows[(nth % 3) * AT_ROWS + r];
-            const int row = cur.row0 + r / group, head = cur.kvh * group + r % group;
-            if (cur.slot < 0) {                                  // the whole item was this segment: finish the rows
-                const float inv = l > 0.f ? 1.f / l : 0.f;
-                bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t o[32];
-                    at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    if (!own) continue;
+            // With several slots, a row whose keys all lie in one slot is finished by that slot's block.
+            const int z0 = p.slots > 1 ? fst / p.split : 0;
+            const int z1 = p.slots > 1 ? min(p.slots - 1, (max(cnt, 1) - 1) / p.split) : 0;
+            const bool direct = z0 == z1;
+            const bool writes = own && (!direct || slot == z0);
+            const int row = row0 + r / group, head = kvh * group + r % group;
+            const float inv = l > 0.f ? 1.f / l : 0.f;
+            bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
+            float* pdst = p.partial ? p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2) : nullptr;
+            for (int c0 = 0; c0 < HD; c0 += 32) {
+                uint32_t o[32];
+                __syncwarp();
+                at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!writes) continue;
+                if (direct) {
 #pragma unroll
                     for (int j = 0; j < 32; j += 8) {
                         uint4 v;
@@ -507,104 +427,13 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                         v.w = at_pack(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
                         *reinterpret_cast<uint4*>(dst + c0 + j) = v;
                     }
-                }
-                at_fence_before();
-                __syncwarp();
-                if (lane == 0) at_mbar_arrive(o_empty);
-            } else {
-                // Partial sums (reference 0, so the merge is a plain sum): four columns of a row as one
-                // 16-byte value, a warp's 32 rows side by side: columns 4 q .. 4 q + 3 of row r at
-                // (q * 128 + r) * 4, sum p of row r at HD * 128 + r. The segment that arrives last at the
-                // item's counter adds the slots up in their order, whichever it is (its own slot from
-                // TMEM, where it still lies, the others from memory), and finishes the rows.
-                float* mine = p.partial + (size_t)(cur.pbase + cur.slot) * (HD + 1) * AT_ROWS;
-                for (int c0 = 0; c0 < HD; c0 += 32) {
-                    uint32_t o[32];
-                    at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
-                    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                    float4* dst4 = reinterpret_cast<float4*>(mine) + (size_t)(c0 / 4) * AT_ROWS + r;
+                } else {
 #pragma unroll
-                    for (int j = 0; j < 8; ++j)
-                        dst4[(size_t)j * AT_ROWS] = make_float4(__uint_as_float(o[4 * j]), __uint_as_float(o[4 * j + 1]),
-                                                                __uint_as_float(o[4 * j + 2]), __uint_as_float(o[4 * j + 3]));
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2*>(pdst + c0 + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
                 }
-                mine[(size_t)HD * AT_ROWS + r] = l;
-                // A block's last segment keeps O for the merge, if the merge falls to it (the head of an item
-                // that was cut runs last in its block and is usually the last to arrive). Any other segment
-                // gives O up now, so that the products of the segment behind it may start, and would read
-                // its own slot back from memory like the others: the same values, the same sum.
-                const bool keep = g == seg_end - 1;
-                if (!keep) {
-                    at_fence_before();
-                    __syncwarp();
-                    if (lane == 0) at_mbar_arrive(o_empty);
-                }
-                // The four warps meet twice on barriers with bounded waits: when all their partial sums are
-                // written, and when the first of them has counted this segment in at the item's counter.
-                __threadfence();
-                __syncwarp();
-                if (lane == 0) at_mbar_arrive(merge_written);
-                if (r == 0) {
-                    const bool ok = at_mbar_wait(merge_written, merges & 1u);
-                    *last_flag = !ok ? -1 : (atomicAdd(p.counters + cur.item, 1) == cur.slots - 1 ? 1 : 0);
-                    at_mbar_arrive(merge_known);
-                }
-                if (!__all_sync(0xffffffffu, at_mbar_wait(merge_known, merges & 1u))) { failed = true; break; }
-                ++merges;
-                const int is_last = *reinterpret_cast<volatile int*>(last_flag);
-                if (is_last < 0) { failed = true; break; }
-                if (is_last) {
-                    __threadfence();
-                    const float* base = p.partial + (size_t)cur.pbase * (HD + 1) * AT_ROWS;
-                    constexpr size_t SLOT_FLOATS = (size_t)(HD + 1) * AT_ROWS;
-                    float total = 0.f;
-                    for (int z = 0; z < cur.slots; ++z) total += z == cur.slot ? l : __ldcg(base + z * SLOT_FLOATS + (size_t)HD * AT_ROWS + r);
-                    const float inv = total > 0.f ? 1.f / total : 0.f;
-                    bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
-                    for (int c0 = 0; c0 < HD; c0 += 32) {
-                        uint32_t o[32];
-                        if (keep) at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
-                        float acc[32];
-#pragma unroll
-                        for (int j = 0; j < 32; ++j) acc[j] = 0.f;
-                        if (keep) asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
-                        for (int z = 0; z < cur.slots; ++z) {
-                            if (z == cur.slot && keep) {
-#pragma unroll
-                                for (int j = 0; j < 32; ++j) acc[j] += __uint_as_float(o[j]);
-                            } else {
-                                const float4* src = reinterpret_cast<const float4*>(base + z * SLOT_FLOATS) + (size_t)(c0 / 4) * AT_ROWS + r;
-                                float4 t[8];
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) t[j] = __ldcg(src + (size_t)j * AT_ROWS);
-#pragma unroll
-                                for (int j = 0; j < 8; ++j) {
-                                    acc[4 * j] += t[j].x; acc[4 * j + 1] += t[j].y; acc[4 * j + 2] += t[j].z; acc[4 * j + 3] += t[j].w;
-                                }
-                            }
-                        }
-                        if (own) {
-#pragma unroll
-                            for (int j = 0; j < 32; j += 8) {
-                                uint4 v;
-                                v.x = at_pack(acc[j] * inv, acc[j + 1] * inv);
-                                v.y = at_pack(acc[j + 2] * inv, acc[j + 3] * inv);
-                                v.z = at_pack(acc[j + 4] * inv, acc[j + 5] * inv);
-                                v.w = at_pack(acc[j + 6] * inv, acc[j + 7] * inv);
-                                *reinterpret_cast<uint4*>(dst + c0 + j) = v;
-                            }
-                        }
-                    }
-                    if (r == 0) p.counters[cur.item] = 0;            // as the next launch expects to find it
-                }
-                if (keep) {
-                    at_fence_before();
-                    __syncwarp();
-                    if (lane == 0) at_mbar_arrive(o_empty);
-                }
-                // last_flag is written again only behind the next merge's first barrier, which every warp
-                // reaches after it has read the flag here.
             }
+            if (writes && !direct) { pdst[d] = 0.f; pdst[d + 1] = l; }
         }
     }
     if (failed) atomicExch(&g_attention_tc_error, 1);
@@ -617,7 +446,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 }
 
 template <int HD>
-static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_table, int blocks, cudaStream_t s) {
+static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_table, int tiles, cudaStream_t s) {
     using C = AtCfg<HD>;
     static bool attr_set = false;
     if (!attr_set) {
@@ -629,7 +458,8 @@ static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_ta
     CUtensorMap map_k, map_v;
     if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
     if (int e = encode_map_bf16_chunks(&map_v, v_table, rows, p.d, 16)) return e;
-    launch_dependent_if(false, attention_tc_kernel<HD>, dim3(blocks), dim3(AT_THREADS), (size_t)C::SMEM, s, p, map_k, map_v);
+    dim3 grid(p.hkv, p.slots, tiles);
+    launch_dependent_if(false, attention_tc_kernel<HD>, grid, dim3(AT_THREADS), (size_t)C::SMEM, s, p, map_k, map_v);
     return check_launch("attention_tc");
 }
 
@@ -652,42 +482,29 @@ extern "C" int kb_attention_tc_takes(int hq, int hkv, int d, int page_size, floa
            hq % hkv == 0 && hq / hkv <= AT_ROWS;
 }
 
-// Keys a step holds, and words a segment's record has: what the host's planner must agree with.
-extern "C" int kb_attention_tc_step_keys() { return AT_KEYS; }
-extern "C" int kb_attention_tc_segment_words() { return AT_SEG_WORDS; }
-
-// Floats of partial sums for `slots` segments of items that were cut, at head size d.
-extern "C" long long kb_attention_tc_partial_floats(int slots, int d) { return (long long)slots * (d + 1) * AT_ROWS; }
-
-// Prompt portions. `segments` [n_segments, 8] (tile, kv head, first step, end step, slot or -1, slots of
-// the item, the item's first partial slot, item) and `cta_first` [blocks + 1] are on the device, made
-// by the host's planner (`engine/batch.py balance_prompt_tiles`): block b runs segments cta_first[b]
-// .. cta_first[b + 1] - 1 in order. `partial` holds kb_attention_tc_partial_floats(partial_slots, d)
-// floats and `counters` one zero an item; the kernel leaves the counters zero again.
+// Prompt portions; arguments as kb_attention_mma's with decode = 0. With slots > 1, `scratch` holds
+// [rows, hq, slots, d + 2] floats and the caller merges it (kb_attention_mma_combine).
 extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, const void* v_table, const int* block_table,
                                const int* row_count, const int* tile_entry, const int* tile_row0, const int* tile_nq, int tiles,
-                               const int* segments, const int* cta_first, int n_segments, int blocks, float* partial,
-                               int partial_slots, int* counters, int items, int rows, int hq, int hkv, int d, int page_size,
-                               int table_width, int n_pages, int window, float scale, float cap, void* stream) {
+                               int rows, int hq, int hkv, int d, int page_size, int table_width, int n_pages, int window,
+                               int split, int slots, float scale, float cap, float* scratch, void* stream) {
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0, "attention_tc: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
     KB_REQUIRE(kb_attention_tc_takes(hq, hkv, d, page_size, cap), "attention_tc: head_dim %d, %d heads over %d, pages of %d, cap %g are not taken",
                d, hq, hkv, page_size, cap);
     KB_REQUIRE(table_width > 0 && n_pages > 0 && window >= 0, "attention_tc: table width %d, pages %d, window %d", table_width, n_pages, window);
-    if (rows == 0 || tiles == 0) return 0;
-    KB_REQUIRE(blocks >= 1 && blocks <= 65535 && n_segments >= blocks, "attention_tc: %d segments for %d blocks (every block has one at least)",
-               n_segments, blocks);
-    KB_REQUIRE(segments != nullptr && cta_first != nullptr, "attention_tc: no list of segments");
-    KB_REQUIRE(partial_slots >= 0 && items >= 1 && counters != nullptr, "attention_tc: %d partial slots, %d items", partial_slots, items);
-    KB_REQUIRE(partial_slots == 0 || partial != nullptr, "attention_tc: %d partial slots need scratch memory", partial_slots);
+    KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AT_KEYS == 0 && slots >= 1 && slots <= 65535),
+               "attention_tc: split %d (a multiple of %d) with %d slots", split, AT_KEYS, slots);
+    KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_tc: %d slots need scratch memory", slots);
+    KB_REQUIRE(tiles <= 65535 && hkv <= 65535, "attention_tc: %d tiles, %d kv heads is too many for one launch", tiles, hkv);
     KB_REQUIRE((((uintptr_t)q | (uintptr_t)out | (uintptr_t)k_table | (uintptr_t)v_table) & 15) == 0, "attention_tc: operands must be 16-byte aligned");
+    if (rows == 0 || tiles == 0) return 0;
     AttTcParams p;
     p.q = (const bf16*)q; p.block_table = block_table; p.row_count = row_count; p.tile_entry = tile_entry;
-    p.tile_row0 = tile_row0; p.tile_nq = tile_nq; p.segments = segments; p.cta_first = cta_first; p.out = (bf16*)out;
-    p.partial = partial; p.counters = counters;
+    p.tile_row0 = tile_row0; p.tile_nq = tile_nq; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
     p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width; p.n_pages = n_pages;
-    p.window = window; p.scale = scale; p.cap = cap;
+    p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
     cudaStream_t s = (cudaStream_t)stream;
-    if (d == 64) return launch_tc<64>(p, k_table, v_table, blocks, s);
-    if (d == 128) return launch_tc<128>(p, k_table, v_table, blocks, s);
-    return launch_tc<256>(p, k_table, v_table, blocks, s);
+    if (d == 64) return launch_tc<64>(p, k_table, v_table, tiles, s);
+    if (d == 128) return launch_tc<128>(p, k_table, v_table, tiles, s);
+    return launch_tc<256>(p, k_table, v_table, tiles, s);
 }

@@ -57,9 +57,10 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
 
 
 # What a block costs beyond its 64-key steps, what the merge of partial sums costs beyond its traffic
-# (both in steps), and microseconds a step, for the mma.sync prompt kernel; from sweeps of the split at
-# Gemma 2 2B head sizes. (The tcgen05 prompt kernel is not cut this way: `balance_prompt_tiles`.)
-PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5)}
+# (both in steps), and microseconds a step, by prompt kernel; from sweeps of the split at Gemma 2 2B
+# head sizes. The tcgen05 kernel's steps are short, so its fixed costs weigh more and it is cut into
+# slots only when a few tiles face a long history.
+PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5), "tcgen05": (8.0, 15.0, 1.34)}
 
 
 def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, window: Optional[int], rows: int, hq: int, d: int,
@@ -99,97 +100,6 @@ def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, windo
         if best is None or cost < best[0]:
             best = (cost, split, slots)
     return (best[1], best[2]) if best else (0, 1)
-
-
-STEP_KEYS = 64           # keys a step of the tcgen05 prompt kernel walks
-SEG_WORDS = 8            # tile, kv head, first step, end step, slot (-1: the whole item), slots, partial base, item
-
-
-class PromptBalance:
-    """How the tcgen05 prompt kernel's work is shared out among its blocks (`balance_prompt_tiles`)."""
-
-    __slots__ = ("segments", "cta_first", "blocks", "items", "partial_slots", "steps", "device")
-
-    def __init__(self, segments, cta_first, items, partial_slots, steps):
-        self.segments = segments            # int32 [n, SEG_WORDS]
-        self.cta_first = cta_first          # int32 [blocks + 1]
-        self.blocks = int(cta_first.size - 1)
-        self.items = int(items)
-        self.partial_slots = int(partial_slots)
-        self.steps = int(steps)
-        self.device = None                  # (segments, cta_first, counters) on the device, once uploaded
-
-
-def balance_prompt_tiles(tile_row0, tile_nq, row_count, kv_heads: int, window: Optional[int], blocks: int,
-                         min_steps: int = 4, item_cost: float = 2.0, snap: int = 2) -> PromptBalance:
-    """Shares the prompt kernel's work out evenly. An item is a (tile, kv head) pair and the keys
-    its rows see, walked in steps of 64 keys from the 64-key boundary at or below its first visible
-    key; a late tile of a long prompt has many times the steps of an early one. All steps of all
-    items are laid in a row (heaviest tiles first, the kv heads of a tile side by side) and cut
-    into `blocks` shares of equal cost, an item counting `item_cost` steps beyond its own (its
-    queries go into tensor memory, its result comes out); a share is a list of segments (steps s0
-    .. s1 - 1 of an item). An item that falls into one share whole is finished there (slot -1);
-    one that is cut leaves one slot of partial sums a segment, which the kernel merges itself.
-    A cut that falls within `snap` steps of an item's end is moved there: cutting an item costs a
-    merge, more than the few steps it evens out. Fewer blocks are used when the work is small: as
-    many as there are items, or one for every `min_steps` steps if that is more. Every step of
-    every item lies in exactly one segment."""
-    row0 = np.asarray(tile_row0, np.int64)
-    nq = np.asarray(tile_nq, np.int64)
-    counts = np.asarray(row_count, np.int64)
-    first = counts[row0]                                  # positions the tile's first row has seen
-    if (first <= 0).any():
-        raise ValueError("a prompt tile's first row has seen nothing: rows of a prompt portion see themselves at least")
-    klo = np.maximum(0, first - window) if window else np.zeros_like(first)
-    khi = first + nq - 1
-    steps = -(-(khi - klo // STEP_KEYS * STEP_KEYS) // STEP_KEYS)
-    order = np.argsort(-steps, kind="stable")
-    n_tiles = row0.size
-    item_tile = np.repeat(order, kv_heads)                # items in the order they are laid out
-    item_head = np.tile(np.arange(kv_heads), n_tiles)
-    item_steps = steps[item_tile]
-    n_items = item_tile.size
-    total = int(item_steps.sum())
-    import os
-    blocks = int(os.environ.get("KAPEL_B200_TC_BLOCKS", blocks))
-    blocks = max(1, min(int(blocks), max(min(n_items, total), total // max(1, min_steps))))
-    starts = np.concatenate(([0], np.cumsum(item_steps)))              # [items + 1]
-    # the cuts are made where the cost (steps + item_cost an item) is equal, then moved to the step they fall on
-    import os
-    item_cost = float(os.environ.get("KAPEL_B200_TC_ITEM_COST", item_cost))
-    snap = int(os.environ.get("KAPEL_B200_TC_SNAP", snap))
-    blocks = int(os.environ.get("KAPEL_B200_TC_BLOCKS", blocks))
-    cost_starts = np.concatenate(([0.0], np.cumsum(item_steps + item_cost)))
-    cost_bounds = np.arange(blocks + 1, dtype=np.float64) * (cost_starts[-1] / blocks)
-    at = np.clip(np.searchsorted(cost_starts, cost_bounds, side="right") - 1, 0, n_items - 1)
-    bounds = starts[at] + np.clip(np.rint(cost_bounds - cost_starts[at] - item_cost).astype(np.int64), 0, item_steps[at])
-    bounds[-1] = total
-    if snap > 0:
-        right = np.minimum(np.searchsorted(starts, bounds, side="left"), n_items)
-        nearest = np.where(np.abs(starts[right] - bounds) <= np.abs(bounds - starts[np.maximum(right - 1, 0)]), starts[right],
-                           starts[np.maximum(right - 1, 0)])
-        bounds = np.where(np.abs(nearest - bounds) <= snap, nearest, bounds)
-    bounds = np.unique(bounds)                                          # a share that came out empty is dropped
-    blocks = bounds.size - 1
-    cuts = np.unique(np.concatenate((starts, bounds)))
-    seg_lo, seg_hi = cuts[:-1], cuts[1:]
-    seg_item = np.searchsorted(starts, seg_lo, side="right") - 1
-    seg_block = np.searchsorted(bounds, seg_lo, side="right") - 1
-    per_item = np.bincount(seg_item, minlength=n_items)
-    first_seg = np.concatenate(([0], np.cumsum(per_item)))[:-1]
-    cut_items = per_item > 1
-    base = np.concatenate(([0], np.cumsum(np.where(cut_items, per_item, 0))))[:-1]
-    seg = np.empty((seg_lo.size, SEG_WORDS), np.int32)
-    seg[:, 0] = item_tile[seg_item]
-    seg[:, 1] = item_head[seg_item]
-    seg[:, 2] = seg_lo - starts[seg_item]
-    seg[:, 3] = seg_hi - starts[seg_item]
-    seg[:, 4] = np.where(cut_items[seg_item], np.arange(seg_lo.size) - first_seg[seg_item], -1)
-    seg[:, 5] = per_item[seg_item]
-    seg[:, 6] = base[seg_item]
-    seg[:, 7] = seg_item
-    cta_first = np.searchsorted(seg_block, np.arange(blocks + 1), side="left").astype(np.int32)
-    return PromptBalance(seg, cta_first, n_items, int(np.where(cut_items, per_item, 0).sum()), total)
 
 
 _SMS = {}
@@ -258,13 +168,12 @@ class StepBatch:
     def attention_tiles(self, heads_per_kv: int, kv_heads: int, window: Optional[int] = None, head_dim: int = 256,
                         prompt_kernel: str = "mma"):
         """How the tensor-core attention kernel cuts this step: (decode, (tile_entry, tile_row0,
-        tile_nq) on the device, split, slots, relative, balance). `decode` is the most rows (tokens x
-        query heads of a kv head) of any request when that is at most 16, which selects the decode
-        kernel, else 0. The keys are split across blocks when the tiles alone are too few to fill
-        the GPU. `relative` says whether the slots are counted from each row's first visible key
-        (every request brings one token) or from key 0. For prompt portions under the tcgen05
-        kernel (`prompt_kernel`), `balance` is the `PromptBalance` that shares its steps out among
-        the blocks, and split and slots are not used."""
+        tile_nq) on the device, split, slots). `decode` is the most rows (tokens x query heads of a
+        kv head) of any request when that is at most 16, which selects the decode kernel, else 0.
+        The keys are split across blocks when the tiles alone are too few to fill the GPU;
+        `prompt_kernel` names the kernel whose costs decide that for prompt portions. A fifth
+        value says whether the slots are counted from each row's first visible key (every
+        request brings one token) or from key 0."""
         key = ("tiles", heads_per_kv, kv_heads, window, head_dim, prompt_kernel)
         if key not in self.memo:
             from .. import kernels as K
@@ -280,18 +189,14 @@ class StepBatch:
             tiles = (dev[:n], dev[n : 2 * n], dev[2 * n :])
             longest = int(plan.row_count.max())
             relative = bool(decode) and int(plan.q_len.max()) == 1
-            balance = None
             if decode:
                 split, slots = decode_split(n * kv_heads, longest, sm_count(self.ids.device), window, relative)
-            elif prompt_kernel == "tcgen05":
-                split, slots = 0, 1
-                balance = balance_prompt_tiles(arrays[1], arrays[2], plan.row_count, kv_heads, window, sm_count(self.ids.device))
             else:
                 firsts = plan.row_count[arrays[1]]
                 split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,
                                             plan.rows, heads_per_kv * kv_heads, head_dim, prompt_kernel)
-            self.memo[key] = (decode, tiles, split, slots, relative, balance, host)
-        return self.memo[key][:6]
+            self.memo[key] = (decode, tiles, split, slots, relative, host)
+        return self.memo[key][:5]
 
     def attention_slots(self, window: Optional[int]) -> int:
         """Chunk slots the row-wise attention kernel needs for a layer with this window."""

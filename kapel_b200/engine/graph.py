@@ -71,7 +71,7 @@ class StaticBatch:
         if (kv_heads, window) not in self._mma:
             self._mma[(kv_heads, window)] = decode_split(self.rows * kv_heads, self._longest, sm_count(self._device), window, True)
         split, slots = self._mma[(kv_heads, window)]
-        return heads_per_kv, self._tiles, split, slots, True, None  # one token a row: heads_per_kv rows a tile, slots from its window's start
+        return heads_per_kv, self._tiles, split, slots, True  # one token a row: heads_per_kv rows a tile, slots from its window's start
 
     def fill(self, plan, ids) -> None:
         """Writes a plan of at most `rows` single-token entries into the buffers; the rest are

@@ -107,7 +107,7 @@ def main(argv=None) -> int:
         return host_bench(args)
 
     from . import kernels as K
-    from .engine.batch import balance_prompt_tiles, cut_tiles, decode_split, prompt_split, sm_count
+    from .engine.batch import cut_tiles, decode_split, prompt_split, sm_count
 
     dev = torch.device("cuda", torch.cuda.current_device())
     K.library()
@@ -219,18 +219,12 @@ def main(argv=None) -> int:
         per_tile = max(1, K.attention_mma_rows(False) // (Hq // Hkv))
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
         firsts = tiles[1].cpu().numpy() + 1
-        kernel = K.attention_prompt_kernel(Hq, Hkv, D, page, cap)
-        balance, split, slots = None, 0, 1
-        if kernel == "tcgen05":
-            balance = balance_prompt_tiles(tiles[1].cpu().numpy(), tiles[2].cpu().numpy(), rc.cpu().numpy(), Hkv, window, sm_count(dev))
-            how = f"{balance.blocks} blocks, {balance.partial_slots} partial slots"
-        else:
-            split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D, kernel)
-            how = f"split={split}x{slots}"
+        split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D,
+                                    K.attention_prompt_kernel(Hq, Hkv, D, page, cap))
         pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
-                                                   0, split, slots, False, balance), max(3, args.iters // 4))
-        report(f"{name} [{t} tokens] {how}", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
+                                                   0, split, slots), max(3, args.iters // 4))
+        report(f"{name} [{t} tokens] split={split}x{slots}", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
 
     if args.prompt <= ctx:
         prompt_case(None)

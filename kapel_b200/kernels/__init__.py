@@ -56,8 +56,7 @@ def library():
                 path = ensure_built()
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
-                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats",
-                             "kb_attention_tc_partial_floats"):
+                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -482,32 +481,16 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
     return "mma"
 
 
-def _upload_balance(balance, device):
-    """The planner's arrays on the device (one copy), and one zeroed counter an item; kept on the plan."""
-    if balance.device is None:
-        import numpy as np
-
-        host = torch.from_numpy(np.concatenate([balance.segments.reshape(-1), balance.cta_first]).astype(np.int32)).pin_memory()
-        dev = host.to(device, non_blocking=True)
-        n = balance.segments.size
-        balance.device = {"segments": dev[:n], "cta_first": dev[n:], "counters": torch.zeros(balance.items, dtype=torch.int32, device=device),
-                          "host": host, "partial": {}}
-    return balance.device
-
-
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
-                        relative: bool = False, balance=None) -> torch.Tensor:
+                        relative: bool = False) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
     one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
     (tokens x query heads of a kv head) any tile holds, at most 16. `split` > 0 cuts the keys at
     absolute multiples of it over `slots` blocks (slots >= ceil(longest count / split)). With
     `relative` (decode mode, every tile one token) the multiples are counted from each row's first
-    visible key, so a windowed row needs ceil(window / split) slots however long its history.
-    Prompt portions that the tcgen05 kernel takes are shared out among its blocks by `balance`
-    (`engine.batch.balance_prompt_tiles`; made here from the tiles, with a copy back to the host,
-    when none is given) and `split` and `slots` play no part."""
+    visible key, so a windowed row needs ceil(window / split) slots however long its history."""
     rows, hq, d = q.shape
     _need(q, "attention q", torch.bfloat16)
     _need(k_table, "attention k table", torch.bfloat16)
@@ -523,30 +506,19 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
     _need(row_count, "attention row_count", torch.int32, (rows,))
     out = _fresh(q.shape, q.dtype, q.device)
     lib = library()
-    if not decode and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
-        if n_tiles == 0 or rows == 0:
-            return out
-        if balance is None:
-            from ..engine.batch import balance_prompt_tiles, sm_count
-
-            balance = balance_prompt_tiles(tile_row0.cpu().numpy(), tile_nq.cpu().numpy(), row_count.cpu().numpy(), hkv, window,
-                                           sm_count(q.device))
-        dev = _upload_balance(balance, q.device)
-        partial = None
-        if balance.partial_slots:
-            if d not in dev["partial"]:
-                dev["partial"][d] = _fresh((int(lib.kb_attention_tc_partial_floats(balance.partial_slots, d)),), torch.float32, q.device)
-            partial = dev["partial"][d]
-        _check(
-            lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
-                                _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, _ptr(dev["segments"]), _ptr(dev["cta_first"]),
-                                int(balance.segments.shape[0]), int(balance.blocks), _ptr(partial), int(balance.partial_slots),
-                                _ptr(dev["counters"]), int(balance.items), rows, hq, hkv, d, int(page_size),
-                                int(block_table.shape[1]), int(n_pages), int(window or 0), _f(scale), _f(softcap or 0.0), _stream())
-        )
-        return out
     need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
     scratch = _fresh((need,), torch.float32, q.device) if need else None
+    if not decode and attention_prompt_kernel(hq, hkv, d, page_size, softcap) == "tcgen05":
+        _check(
+            lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
+                                _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
+                                int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
+                                _f(softcap or 0.0), _ptr(scratch), _stream())
+        )
+        if slots > 1:
+            _check(lib.kb_attention_mma_combine(_ptr(out), _ptr(row_count), _ptr(scratch), rows, hq, d, int(window or 0), int(split),
+                                                int(slots), _stream()))
+        return out
     _check(
         lib.kb_attention_mma(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                              _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),

@@ -56,12 +56,12 @@ class Attention(Part):
         )
         heads_per_kv = s.num_heads // s.num_kv_heads
         if K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
-            decode, tiles, split, slots, relative, balance = batch.attention_tiles(
+            decode, tiles, split, slots, relative = batch.attention_tiles(
                 heads_per_kv, s.num_kv_heads, s.window, s.head_dim,
                 K.attention_prompt_kernel(s.num_heads, s.num_kv_heads, s.head_dim, self.ctx.page_size, s.softcap))
             y = K.paged_attention_mma(
                 q, k_table, v_table, group.block_table, batch.row_count, tiles,
-                self.ctx.page_size, s.window, s.scale, s.softcap, decode, split, slots, relative, balance,
+                self.ctx.page_size, s.window, s.scale, s.softcap, decode, split, slots, relative,
             )
         else:                   # the 32-bit path, and sizes the tensor-core kernel does not take
             y = K.paged_attention_rows(

@@ -434,38 +434,6 @@ def test_paged_attention_mma_prompt_mode(kernel, hq, hkv, d, window, cap, split)
     assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
 
 
-@pytest.mark.parametrize("hq,hkv,d", [(16, 1, 64), (8, 4, 128), (8, 4, 256), (2, 2, 128)])
-@pytest.mark.parametrize("window", [None, 300])
-@pytest.mark.parametrize("blocks", [1, 3, 7, 23, 148])
-def test_paged_attention_tcgen05_shared_out_among_any_number_of_blocks(hq, hkv, d, window, blocks):
-    """The tcgen05 prompt kernel with its steps shared out among 1, a few and many blocks: one block
-    runs every item one after the other (Q replaced in tensor memory, O read out and started again,
-    the rings running on); with a few, items are cut in the middle and their partial sums merged by
-    whichever segment arrives last; the result is the reference's, and the same bits however many
-    blocks share the work in the same cuts (run twice: the merge adds the slots in their order)."""
-    from kapel_b200.engine.batch import balance_prompt_tiles, cut_tiles
-
-    lengths, q_lens = [1, 37, 300, 700, 1500], [1, 37, 130, 33, 400]
-    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d + 7)
-    scale, cap = 1.0 / math.sqrt(d * 1.5), 30.0
-    per_tile = max(1, K().attention_mma_rows(False) // (hq // hkv))
-    q_len = np.asarray(q_lens, np.int32)
-    q_start = np.concatenate(([0], np.cumsum(q_len)[:-1])).astype(np.int32)
-    arrays = cut_tiles(q_start, q_len, per_tile)
-    tiles = tuple(dev(torch.from_numpy(a)) for a in arrays)
-    want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
-    outs = []
-    for _ in range(2):
-        balance = balance_prompt_tiles(arrays[1], arrays[2], rc.numpy(), hkv, window, blocks, min_steps=1)
-        got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, 16, window, scale, cap, 0, 0, 1, False, balance).cpu()
-        K().check_async_errors()
-        assert rel_err(got.double().numpy(), want.numpy()) < 1.5e-2, f"{balance.blocks} blocks, {balance.partial_slots} partial slots"
-        outs.append(got)
-    assert torch.equal(outs[0], outs[1])
-    if blocks in (3, 7) and window is None:
-        assert balance.partial_slots > 0                   # some item was cut: the merge ran
-
-
 @pytest.mark.parametrize("d", [64, 128, 256])
 def test_paged_attention_tcgen05_far_key_and_window_edge(d):
     """One key among hundreds carries the weight: seen at the far end and at the window's first
@@ -572,17 +540,15 @@ def test_paged_attention_at_the_sizes_and_histories_that_are_timed(hq, hkv, d, s
     q_start = np.asarray([0, 200], np.int32)
     arrays = cut_tiles(q_start, q_len, per_tile)
     firsts = rc.numpy()[arrays[1]]
-    assert K().attention_prompt_kernel(hq, hkv, d, 16, cap) == "tcgen05"
-    from kapel_b200.engine.batch import balance_prompt_tiles
-
-    balance = balance_prompt_tiles(arrays[1], arrays[2], rc.numpy(), hkv, window, sms)
-    split, slots = balance.blocks, balance.partial_slots
+    kernel = K().attention_prompt_kernel(hq, hkv, d, 16, cap)
+    assert kernel == "tcgen05"
+    split, slots = prompt_split(firsts, firsts + arrays[2] - 1, hkv, sms, window, int(q_len.sum()), hq, d, kernel)
     tiles = tuple(dev(torch.from_numpy(a)) for a in arrays)
-    got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, 16, window, scale, cap, 0, 0, 1, False, balance).cpu().double()
+    got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, 16, window, scale, cap, 0, split, slots).cpu().double()
     K().check_async_errors()
     sample = [0, 1, 144, 145, 146, 147, 199, 200, 201, 263, 264, 200 + 1023, 200 + 2047]     # rows 145/146 see 4,096/4,097 positions
     want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap, only=sample)
-    assert rel_err(got[sample].numpy(), want[sample].numpy()) < 1.5e-2, f"prompt, {split} blocks, {slots} partial slots"
+    assert rel_err(got[sample].numpy(), want[sample].numpy()) < 1.5e-2, f"prompt, split {split} x {slots}"
 
 
 # ------------------------------------------------------------------------------------------

@@ -24,7 +24,7 @@ def lib():
     lib.kb_rope_table.argtypes = [vp, vp, i32, i32, f64, vp]
     lib.kb_rope_append.argtypes = [vp, i32, i32, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i32, vp]
     lib.kb_glu.argtypes = [vp, i32, vp, i32, i32, i64, i64, i32, i32, vp]
-    lib.kb_attention_tc.argtypes = [vp] * 9 + [i32, vp, vp, i32, i32, vp, i32, vp] + [i32] * 9 + [f32, f32, vp]
+    lib.kb_attention_tc.argtypes = [vp] * 9 + [i32] * 11 + [f32, f32, vp, vp]
     lib.kb_attention_tc_takes.argtypes = [i32, i32, i32, i32, f32]
     return lib
 
@@ -72,15 +72,7 @@ def test_tcgen05_attention_says_what_it_takes(lib):
     assert takes(8, 4, 128, 16, 0.0) == 0                    # the fixed softmax reference needs a soft cap
     assert takes(8, 4, 128, 16, 100.0) == 0                  # ... of at most 64
     assert takes(8, 3, 128, 16, 50.0) == 0                   # heads must divide into kv heads
-    def call(d=128, segments=A, n_segments=4, blocks=2, partial=None, partial_slots=0, counters=A, items=2):
-        # out .. tile_nq, tiles, segments, cta_first, n_segments, blocks, partial, partial_slots, counters, items,
-        # rows, hq, hkv, d, page_size, table_width, n_pages, window, scale, cap, stream
-        return lib.kb_attention_tc(*([A] * 9), 1, segments, A, n_segments, blocks, partial, partial_slots, counters, items,
-                                   64, 8, 4, d, 16, 8, 8, 0, 0.1, 50.0, None)
-
-    refused(lib, call(d=96), "attention_tc", "head_dim 96", "are not taken")
-    refused(lib, call(n_segments=1, blocks=2), "attention_tc", "1 segments for 2 blocks")
-    refused(lib, call(segments=None), "no list of segments")
-    refused(lib, call(partial_slots=3), "3 partial slots need scratch memory")
-    refused(lib, call(counters=None), "2 items")
-    assert lib.kb_attention_tc_step_keys() == 64 and lib.kb_attention_tc_segment_words() == 8
+    args = [A] * 9 + [1, 64, 8, 4, 96, 16, 8, 8, 0, 0, 1]
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "head_dim 96", "are not taken")
+    args = [A] * 9 + [1, 64, 8, 4, 128, 16, 8, 8, 0, 96, 2]
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "split 96")

@@ -32,7 +32,7 @@ def test_decode_split_prefers_one_slot_when_the_pairs_fill_the_gpu():
     assert slots > 8 and split * slots >= 8192
 
 
-@pytest.mark.parametrize("kernel", ["mma"])
+@pytest.mark.parametrize("kernel", ["mma", "tcgen05"])
 @pytest.mark.parametrize("window", [None, 300, 4096])
 def test_prompt_split_covers_every_visible_key(kernel, window):
     rng = np.random.default_rng(4)
@@ -76,58 +76,3 @@ def test_chunks_touched_counts_absolute_chunks():
     assert _chunks_touched(counts, 100, 64) == 2                            # keys 900..999 touch chunks 14 and 15
     assert _chunks_touched(np.array([1025], np.int32), 100, 64) == 3        # keys 925..1024 touch chunks 14, 15 and 16
     assert _chunks_touched(np.zeros(3, np.int32), None, 64) == 1
-
-
-@pytest.mark.parametrize("window", [None, 300, 4096])
-def test_balanced_shares_hold_every_step_of_every_item_once(window):
-    """`balance_prompt_tiles`: whatever the tiles, the kv heads and the number of blocks, every step of
-    every (tile, kv head) item lies in exactly one segment; the segments of an item are in order,
-    numbered as slots when the item was cut and -1 when it was not; partial slots of different items
-    do not overlap; every block has work; the shares' costs differ by little."""
-    from kapel_b200.engine.batch import STEP_KEYS, balance_prompt_tiles
-
-    rng = np.random.default_rng(6)
-    for trial in range(200):
-        tiles = int(rng.integers(1, 60))
-        nq = rng.integers(1, 65, size=tiles)
-        first = rng.integers(1, 20000, size=tiles)                 # positions each tile's first row has seen
-        row0 = np.concatenate(([0], np.cumsum(nq)[:-1]))
-        counts = np.concatenate([np.arange(f, f + n) for f, n in zip(first, nq)])
-        hkv = int(rng.integers(1, 17))
-        blocks = int(rng.choice([1, 3, 7, 148, 2000]))
-        b = balance_prompt_tiles(row0, nq, counts, hkv, window, blocks)
-        klo = np.maximum(0, first - window) if window else np.zeros_like(first)
-        steps = -(-(first + nq - 1 - klo // STEP_KEYS * STEP_KEYS) // STEP_KEYS)
-        assert b.items == tiles * hkv and b.steps == int(steps.sum()) * hkv and 1 <= b.blocks <= blocks
-        assert b.cta_first[0] == 0 and b.cta_first[-1] == b.segments.shape[0] and (np.diff(b.cta_first) >= 1).all()
-        by_item, used = {}, set()
-        for tile, head, s0, s1, slot, slots, base, item in b.segments.tolist():
-            assert 0 <= tile < tiles and 0 <= head < hkv and 0 <= s0 < s1 <= steps[tile]
-            by_item.setdefault(item, []).append((s0, s1, slot, slots, base, tile, head))
-        assert sorted(by_item) == list(range(b.items))
-        seen_pairs = set()
-        for item, segs in by_item.items():
-            tile, head = segs[0][5], segs[0][6]
-            assert all(s[5] == tile and s[6] == head for s in segs) and (tile, head) not in seen_pairs
-            seen_pairs.add((tile, head))
-            assert segs[0][0] == 0 and segs[-1][1] == steps[tile] and all(a[1] == c[0] for a, c in zip(segs, segs[1:]))
-            assert all(s[3] == len(segs) for s in segs)
-            if len(segs) == 1:
-                assert segs[0][2] == -1
-            else:
-                assert [s[2] for s in segs] == list(range(len(segs)))
-                for s in segs:
-                    assert s[4] + s[2] not in used
-                    used.add(s[4] + s[2])
-        assert used == set(range(b.partial_slots))
-        # segments of a block are consecutive in the list, and the shares are even: no block's cost (steps
-        # plus two an item it touches) is far above the mean (a cut may move two steps to an item's end)
-        cost = np.add.reduceat(b.segments[:, 3] - b.segments[:, 2] + 2, b.cta_first[:-1])
-        assert cost.max() <= cost.mean() + 8
-
-
-def test_balanced_shares_refuse_a_tile_that_has_seen_nothing():
-    from kapel_b200.engine.batch import balance_prompt_tiles
-
-    with pytest.raises(ValueError, match="seen nothing"):
-        balance_prompt_tiles([0], [2], [0, 1], 2, None, 148)
