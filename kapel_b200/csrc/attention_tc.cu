@@ -11,8 +11,11 @@
 //   O += P V       tcgen05.mma with P as the A operand straight from TMEM and the value tile
 //                  [64 x d] as an MN-major B operand; O [128 x d] float32 stays in TMEM throughout.
 // TMEM columns: O (d), two S buffers (64 each; P lies over the first 32 columns of its S), Q (d / 2).
-// One thread issues every MMA and they run in the order issued, so the scores of tile kt + 2 land on
-// their buffer only after the product that read tile kt's P from it.
+// Issuing a tcgen05.mma keeps its thread busy for 50 to 100 cycles whatever the product's size (one
+// thread issuing 128 x 64 x 16 products gets a third of the tensor cores' rate, two threads issuing
+// side by side get two thirds), so the score products and the P V products have a thread each, in
+// warps of their own. The scores of tile kt + 2 may land on their buffer only when the product that
+// read tile kt's P from it is complete: that product's commit tells the score thread.
 // Keys and values arrive by TMA in two rings of slots, one for key tiles and one for value tiles,
 // each slot freed by the tcgen05.commit of the product that read it. A product costs the tensor
 // cores about 50 cycles beyond its arithmetic, so the scores take all 64 keys in one product a
@@ -26,10 +29,13 @@
 // instead of a running maximum, and O never has to be rescaled. Without a soft cap, with a larger
 // cap, or with a head size other than 64, 128 or 256 the mma.sync kernel runs instead.
 //
-// Six warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
-// every MMA; warps 2-5 are the softmax and the epilogue. Every wait on an mbarrier gives up after
-// about a second, raises a flag that `kb_attention_tc_error` reports, and the block still meets at
-// its final barrier, frees its TMEM and returns.
+// Eleven warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
+// the score products; warps 2-9 are the softmax and the epilogue, two warps to each quarter of the
+// rows (a warp reads the 32 TMEM lanes of its number modulo 4), one for the first 32 keys of a tile
+// and one for the last (two special-function operations an element keep a lone warp waiting); one
+// lane of warp 10 issues the P V products. Every wait on an mbarrier gives up after about a second,
+// raises a flag that `kb_attention_tc_error` reports, and the block still meets at its final
+// barrier, frees its TMEM and returns.
 #include "common.cuh"
 #include "tensor_map.cuh"
 
@@ -37,7 +43,8 @@ namespace kb {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 192;
+constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 352;
+constexpr int AT_WARP_PV = 10;          // the warp that issues the P V products (warp 1 issues the scores)
 
 __device__ int g_attention_tc_error = 0;
 
@@ -165,7 +172,9 @@ template <int HD> struct AtCfg {
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
     static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
     static constexpr int TMEM_COLS = HD == 64 ? 256 : 512;      // 3 HD / 2 + 128 rounded up to a power of two
-    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 256 /* barriers */;
+    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 320 /* barriers */ + 512 /* row sums */;
+    static_assert((2 * SLOTS + 7) * 8 + 8 <= 320, "the barriers outgrew their room");
+    static_assert(SMEM <= 232448, "more shared memory than a block can have");
 };
 
 template <int HD>
@@ -178,10 +187,12 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     unsigned char* ring = smem;
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] a slot's boxes have landed
     uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete
-    uint64_t* s_full = empty + NS;                               // [2] S complete (MMA -> softmax)
-    uint64_t* p_full = s_full + 2;                               // [2] P written (softmax -> MMA), four warps arrive
-    uint64_t* o_full = p_full + 2;                               // [1] O complete
+    uint64_t* s_full = empty + NS;                               // [2] S complete (score products -> softmax)
+    uint64_t* p_full = s_full + 2;                               // [2] P written (softmax -> P V products), eight warps arrive
+    uint64_t* s_free = p_full + 2;                               // [2] the product that read P is complete: S may be written again
+    uint64_t* o_full = s_free + 2;                               // [1] O complete
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    float* l_half = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 320);   // [128] sum p over the last 32 keys of every tile, by row
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     const int kvh = blockIdx.x, slot = blockIdx.y;
@@ -213,7 +224,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 1); at_mbar_init(empty + s, 1); }
-        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 4); }
+        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 8); at_mbar_init(s_free + b, 1); }
         at_mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -226,25 +237,39 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     at_fence_after();
     const uint32_t tmem = *tmem_slot;
     dependent_wait();                                       // the queries and the newest keys are the kernel before's
-    // Q into TMEM as the A operand of the score products: row r in lane r, two elements a column.
-    if (warp >= 2) {
+    // Q into TMEM as the A operand of the score products: row r in lane r, two elements a column. The
+    // two warps of a quarter of the rows take half of the head each.
+    if (warp >= 2 && warp < 10) {
         const int r = (warp & 3) * 32 + lane;
+        const int half = (warp - 2) >> 2;                        // 0: the head's first half, 1: its second
         const bf16* src = p.q + ((size_t)(row0 + (r < rows_valid ? r / group : 0)) * p.hq + kvh * group + (r < rows_valid ? r % group : 0)) * d;
-        for (int c0 = 0; c0 < HD; c0 += 64) {
+        if (HD >= 128) {
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 64) {
+                uint32_t w[32];
+#pragma unroll
+                for (int j = 0; j < 8; ++j) {
+                    uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                    if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
+                    w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                }
+                at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
+            }
+        } else if (half == 0) {                                  // 64 elements: one store, by the quarter's first warp
             uint32_t w[32];
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
-                if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
+                if (r < rows_valid) v = *reinterpret_cast<const uint4*>(src + j * 8);
                 w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
             }
-            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
+            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)C::COL_Q, w);
         }
         asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
     }
-    // The MMA warp must see Q in place; the copying warp need not, and asks for keys meanwhile.
+    // The score warp must see Q in place (the softmax warps and it meet here); the copying warp and
+    // the P V warp need not, and go ahead.
     at_fence_before();
-    if (warp >= 1) asm volatile("bar.sync 1, 160;" ::: "memory");
+    if (warp >= 1 && warp < 10) asm volatile("bar.sync 1, 288;" ::: "memory");
     at_fence_after();
     bool failed = false;
 
@@ -309,18 +334,18 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             }
         }
     } else if (warp == 1) {
-        // ---------------------------------------------------------------- every MMA, from one lane
+        // ---------------------------------------------------------------- the score products, from one lane
         if (lane == 0) {
             constexpr uint32_t IDESC_S = at_idesc(AT_ROWS, AT_KEYS, false);
-            constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
-            constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
             const uint32_t ring_addr = at_saddr(ring);
-            auto issue_s = [&](int kt) -> bool {                 // S[kt & 1] = Q K(kt)^T
-                const int s = kt % KS;
-                if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) return false;
+            for (int kt = 0; kt < n_tiles; ++kt) {               // S[kt & 1] = Q K(kt)^T
+                const int s = kt % KS, b = kt & 1;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) { failed = true; break; }
+                // the buffer still holds tile kt - 2's P until the product that reads it is complete
+                if (kt >= 2 && !at_mbar_wait(s_free + b, (uint32_t)((kt - 2) >> 1) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + (kt & 1) * AT_KEYS);
+                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
                     const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
@@ -330,13 +355,17 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                         at_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);                            // the key slot is free when S is complete
-                at_commit(s_full + (kt & 1));
-                return true;
-            };
-            if (!issue_s(0)) failed = true;
-            for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+                at_commit(s_full + b);
+            }
+        }
+    } else if (warp == AT_WARP_PV) {
+        // ---------------------------------------------------------------- the P V products, from one lane
+        if (lane == 0) {
+            constexpr uint32_t PAGE_BYTES = NBOX * 2048u;
+            constexpr uint32_t IDESC_O = at_idesc(AT_ROWS, HD, true);
+            const uint32_t ring_addr = at_saddr(ring);
+            for (int kt = 0; kt < n_tiles; ++kt) {
                 const int b = kt & 1;
-                if (kt + 1 < n_tiles && !issue_s(kt + 1)) { failed = true; break; }
                 const int s = KS + kt % VS;
                 if (!at_mbar_wait(full + s, (uint32_t)(kt / VS) & 1u)) { failed = true; break; }
                 if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
@@ -350,12 +379,14 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     at_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
                 }
                 at_commit(empty + s);
+                at_commit(s_free + b);                           // P has been read: the scores of tile kt + 2 may land
             }
             if (!failed) at_commit(o_full);
         }
     } else {
-        // ---------------------------------------------------------------- softmax and epilogue, one row a thread
+        // ---------------------------------------------------------------- softmax and epilogue, half a row a thread
         const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;                        // 0: keys 0-31 of a tile (and the head's first half), 1: the rest
         const int r = quarter * 32 + lane;                       // the row of the tile, and the TMEM lane
         const bool own = r < rows_valid;
         const int cnt = own ? c_first + r / group : 0;
@@ -367,38 +398,53 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
         float l = 0.f;
         for (int kt = 0; kt < n_tiles; ++kt) {
             const int b = kt & 1;
-            const int j0 = k_begin + kt * AT_KEYS;
+            const int j0 = k_begin + kt * AT_KEYS + half * 32;   // this warp's 32 keys of the tile
             if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
             at_fence_after();
-            uint32_t s0[32], s1[32], pr[16];
-            const bool edge = j0 < lo_max || j0 + AT_KEYS > hi_min;      // the same for the whole warp
-            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS), s0);
-            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + 32), s1);
+            uint32_t sv[32], pr[16];
+            const bool edge = j0 < lo_max || j0 + 32 > hi_min;   // the same for the whole warp
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 32), sv);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            // P lies over the first 32 columns of its S: the second warp's scores sit in columns that
+            // nobody overwrites, but the first warp's P covers columns 0-15 and the second's 16-31, which
+            // hold the first warp's scores 0-31: both warps have their scores in registers before either
+            // stores (the two meet on a named barrier of their own, one a quarter).
             float la = 0.f, lb = 0.f;                            // two chains of additions
 #pragma unroll
-            for (int h = 0; h < 2; ++h) {
-#pragma unroll
-                for (int j = 0; j < 32; j += 2) {
-                    float p0 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j] : s1[j]) * c1));
-                    float p1 = at_exp2(c2 * at_tanh(__uint_as_float(h == 0 ? s0[j + 1] : s1[j + 1]) * c1));
-                    if (edge) {
-                        const int jj = j0 + h * 32 + j;
-                        if (jj < lo || jj >= hi) p0 = 0.f;
-                        if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
-                    }
-                    la += p0;
-                    lb += p1;
-                    pr[j >> 1] = at_pack(p0, p1);
+            for (int j = 0; j < 32; j += 2) {
+                float p0 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j]) * c1));
+                float p1 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
+                if (edge) {
+                    const int jj = j0 + j;
+                    if (jj < lo || jj >= hi) p0 = 0.f;
+                    if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
                 }
-                at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + h * 16), pr);
+                la += p0;
+                lb += p1;
+                pr[j >> 1] = at_pack(p0, p1);
             }
             l += la + lb;
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");      // the quarter's two warps have read their scores
+            at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 16), pr);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             at_fence_before();
             __syncwarp();
             if (lane == 0) at_mbar_arrive(p_full + b);
         }
+        // The row's sum: the second warp's share goes to the first through shared memory, and the
+        // reciprocal of the whole comes back the same way. Both warps of a quarter pass these barriers
+        // whatever happened above.
+        if (half == 1) l_half[r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        float inv = 0.f;
+        if (half == 0) {
+            l += l_half[r];
+            inv = l > 0.f ? 1.f / l : 0.f;
+        }
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        if (half == 0) l_half[r] = inv;
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        if (half == 1) inv = l_half[r];
         if (!failed && !__all_sync(0xffffffffu, at_mbar_wait(o_full, 0u))) failed = true;
         if (!failed) {
             at_fence_after();
@@ -408,10 +454,10 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             const bool direct = z0 == z1;
             const bool writes = own && (!direct || slot == z0);
             const int row = row0 + r / group, head = kvh * group + r % group;
-            const float inv = l > 0.f ? 1.f / l : 0.f;
             bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
             float* pdst = p.partial ? p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2) : nullptr;
-            for (int c0 = 0; c0 < HD; c0 += 32) {
+            // the quarter's first warp reads out the head's first half, the second its second half
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
                 uint32_t o[32];
                 __syncwarp();
                 at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
@@ -433,7 +479,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                         *reinterpret_cast<float2*>(pdst + c0 + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
                 }
             }
-            if (writes && !direct) { pdst[d] = 0.f; pdst[d + 1] = l; }
+            if (writes && !direct && half == 0) { pdst[d] = 0.f; pdst[d + 1] = l; }
         }
     }
     if (failed) atomicExch(&g_attention_tc_error, 1);
