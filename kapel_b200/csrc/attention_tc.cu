@@ -29,8 +29,8 @@
 // instead of a running maximum, and O never has to be rescaled. Without a soft cap, with a larger
 // cap, or with a head size other than 64, 128 or 256 the mma.sync kernel runs instead.
 //
-// Eleven warps: warp 0 finds pages and asks TMA for boxes; warp 1 allocates TMEM and one lane issues
-// the score products; warps 2-9 are the softmax and the epilogue, two warps to each quarter of the
+// Thirteen warps: warps 0, 12 and 11 find pages and ask TMA for the boxes of keys (half a tile each)
+// and of values; warp 1 allocates TMEM and one lane issues the score products; warps 2-9 are the softmax and the epilogue, two warps to each quarter of the
 // rows (a warp reads the 32 TMEM lanes of its number modulo 4), one for the first 32 keys of a tile
 // and one for the last (two special-function operations an element keep a lone warp waiting); one
 // lane of warp 10 issues the P V products. Every wait on an mbarrier gives up after about a second,
@@ -43,8 +43,10 @@ namespace kb {
 
 typedef __nv_bfloat16 bf16;
 
-constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 352;
+constexpr int AT_ROWS = 128, AT_KEYS = 64, AT_THREADS = 416;
 constexpr int AT_WARP_PV = 10;          // the warp that issues the P V products (warp 1 issues the scores)
+constexpr int AT_WARP_V = 11;           // the warp that asks for the values (warp 0 asks for the keys)
+constexpr int AT_WARP_K2 = 12;          // the single-block kernel's second warp for keys: warp 0 asks for keys 0-31 of a tile, it for 32-63
 
 __device__ int g_attention_tc_error = 0;
 
@@ -223,7 +225,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     const int n_tiles = (khi - k_begin + AT_KEYS - 1) / AT_KEYS;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 1); at_mbar_init(empty + s, 1); }
+        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, s < KS ? 2 : 1); at_mbar_init(empty + s, 1); }   // two warps bring a key tile
         for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 8); at_mbar_init(s_free + b, 1); }
         at_mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
@@ -273,8 +275,13 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     at_fence_after();
     bool failed = false;
 
-    if (warp == 0) {
+    if (warp == 0 || warp == AT_WARP_V || warp == AT_WARP_K2) {
         // ---------------------------------------------------------------- pages and boxes
+        // Asking TMA for a box keeps the asking warp busy for more than a hundred clocks (a tile's 16
+        // boxes of keys from one warp took as long as the tile's arithmetic), so three warps ask: one
+        // for the values, two for the keys, half a tile each.
+        const int half = warp == AT_WARP_V ? 1 : 0;              // keys, or values
+        const int key_half = warp == AT_WARP_K2 ? 1 : 0;         // keys 0-31 of a tile (pages 0, 1 of its four), or 32-63
         // The keys of tile kt go to key slot kt % KS, its values to value slot KS + kt % VS. The pages
         // of eight tiles are looked up at once, lane 4 t + sub for keys 16 sub .. of the batch's tile
         // t, and one batch ahead of their use. A group without a page (before the window, past the
@@ -298,7 +305,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
             const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
             const int live = __popc(have);
-            for (int half = 0; half < 2; ++half) {               // keys, then values
+            {
                 const int s = half == 0 ? kt % KS : KS + kt % VS;
                 const int round = half == 0 ? kt / KS : kt / VS;
                 bool ok = true;
@@ -314,14 +321,17 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
                     at_fence_async_smem();
                     __syncwarp();
                 }
-                if (lane == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_BYTES);
+                if (lane == 0) {
+                    const uint32_t mine = half == 1 ? have : (have >> (2 * key_half)) & 3u;      // the page groups this warp brings
+                    at_mbar_expect_tx(full + s, (uint32_t)__popc(mine) * PAGE_BYTES);
+                }
                 __syncwarp();
                 if (half == 0) {
                     // keys: a box of 16 keys x 64 elements a lane, chunk by chunk [chunk][page][16 keys], so that
                     // the tile's eight-key groups are 1 KB apart and one product takes all 64 keys
-                    const int sub = (lane / NBOX) & 3, bx = lane % NBOX;
+                    const int sub = 2 * key_half + ((lane / NBOX) & 1), bx = lane % NBOX;
                     const int pg = __shfl_sync(0xffffffffu, page, sub);
-                    if (lane < 4 * NBOX && pg >= 0) {
+                    if (lane < 2 * NBOX && pg >= 0) {
                         const int j = j0 + sub * 16;
                         const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
                         at_tma_box(at_saddr(dst) + (uint32_t)(bx * 4 + sub) * 2048u, &map_k, bx * 64, row, full + s);
@@ -383,7 +393,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
             }
             if (!failed) at_commit(o_full);
         }
-    } else {
+    } else if (warp >= 2 && warp < 10) {
         // ---------------------------------------------------------------- softmax and epilogue, half a row a thread
         const int quarter = warp & 3;
         const int half = (warp - 2) >> 2;                        // 0: keys 0-31 of a tile (and the head's first half), 1: the rest
@@ -491,6 +501,412 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
     }
 }
 
+// ---------------------------------------------------------------------------------------
+// The same attention by pairs of blocks (a cluster of two, on the two multiprocessors of a pair),
+// for head sizes 128 and 256. A multiprocessor takes in about 35 bytes a clock from L2, and a step of
+// the kernel above needs 64 KB of keys and values for 128 rows: 2,500 clocks a step whatever the
+// tensor cores could do. Here tcgen05.mma.cta_group::2 works on 256 rows, the 128 of each block in
+// its own TMEM, against one tile of keys and values of which each block holds half: the first block
+// keys 0-31 of a step and the first half of the head's elements of the values, the second keys 32-63
+// and the second half (the B operand of a cta_group::2 product is split along its N between the two
+// blocks). A block takes in half as much a step and row.
+//   * a tile is up to 256 rows: the first block takes rows 0-127, the second rows 128-255;
+//   * both blocks' TMA copies complete on the first block's "full" barrier (two arrivals: the first
+//     block's, with the bytes expected from both, and the second block's, when it has cleared what
+//     it had no page for);
+//   * the first block's warps 1 and 10 issue the products for both; tcgen05.commit with a two-block
+//     mask frees the key and value slots and hands over S and O in both blocks;
+//   * the softmax warps of both blocks arrive on the first block's "P written" barrier;
+//   * the blocks meet at a cluster barrier after their Q is in TMEM and before TMEM is freed, so
+//     neither signals a block that is not there yet or has left.
+constexpr uint32_t AT_PEER_MASK = 0xFEFFFFFFu;                 // clears the bit that tells the two blocks' shared windows apart
+
+__device__ __forceinline__ void atp_tma_box(uint32_t dst, const CUtensorMap* map, int x, int y, uint32_t bar_addr) {
+    asm volatile("cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_addr), "r"(x), "r"(y) : "memory");
+}
+__device__ __forceinline__ void atp_tma_page(uint32_t dst, const CUtensorMap* map, int row, int chunk, uint32_t bar_addr) {
+    const int zero = 0;
+    asm volatile("cp.async.bulk.tensor.3d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4, %5}], [%2];"
+                 ::"r"(dst), "l"(map), "r"(bar_addr), "r"(zero), "r"(row), "r"(chunk) : "memory");
+}
+__device__ __forceinline__ void atp_commit_both(uint64_t* bar) {
+    const uint16_t mask = 3;
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+                 ::"r"(at_saddr(bar)), "h"(mask) : "memory");
+}
+__device__ __forceinline__ void atp_commit_here(uint64_t* bar) {
+    asm volatile("tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(at_saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void atp_arrive_on_first(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(at_saddr(bar)) : "memory");
+}
+// The same without the release: for a signal that only says "my tcgen05.st has completed" (the store was
+// waited for and fenced with tcgen05.fence::before_thread_sync), which needs no ordering of ordinary
+// memory. A release at cluster scope costs the arriving thread more than a thousand clocks.
+__device__ __forceinline__ void atp_arrive_on_first_relaxed(uint64_t* bar) {
+    asm volatile(
+        "{\n\t.reg .b32 ra;\n\tmapa.shared::cluster.u32 ra, %0, 0;\n\t"
+        "mbarrier.arrive.relaxed.cluster.shared::cluster.b64 _, [ra];\n\t}"
+        ::"r"(at_saddr(bar)) : "memory");
+}
+__device__ __forceinline__ void atp_cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void atp_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], [%1], %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "r"(a_tmem), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
+
+constexpr int ATP_ROWS = 256;                                   // rows a tile of the pair kernel
+
+template <int HD> struct AtpCfg {
+    static constexpr int NBOX = HD / 64;                        // chunks of 64 elements along the head
+    static constexpr int SLOT_BYTES = AT_KEYS * HD;             // a block's half of a key tile, or of a value tile
+    static constexpr int K_SLOTS = HD == 256 ? 5 : 6;
+    static constexpr int V_SLOTS = HD == 256 ? 6 : 8;
+    static constexpr int SLOTS = K_SLOTS + V_SLOTS;
+    static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
+    static constexpr int TMEM_COLS = 512;
+    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 320 /* barriers */ + 512 /* row sums */;
+    static_assert((2 * SLOTS + 7) * 8 + 8 <= 320, "the barriers outgrew their room");
+    static_assert(SMEM <= 232448, "more shared memory than a block can have");
+};
+
+template <int HD>
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AT_THREADS, 1)
+attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
+    using C = AtpCfg<HD>;
+    constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS;
+    constexpr uint32_t PAGE_FULL = NBOX * 2048u;                 // a page's keys (or values) of one kv head, both blocks' halves
+    constexpr uint32_t PAGE_HALF = PAGE_FULL / 2;                // a block's half of a page of values
+    extern __shared__ unsigned char at_smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
+    unsigned char* ring = smem;
+    uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] the first block's: both halves of a slot have landed
+    uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete (in both blocks)
+    uint64_t* s_full = empty + NS;                               // [2] S complete (in both blocks)
+    uint64_t* p_full = s_full + 2;                               // [2] the first block's: P written by the 16 softmax warps of both
+    uint64_t* s_free = p_full + 2;                               // [2] the first block's: the product that read P is complete
+    uint64_t* o_full = s_free + 2;                               // [1] O complete (in both blocks)
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
+    float* l_half = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 320);
+
+    const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
+    uint32_t rank;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(rank));
+    const int kvh = blockIdx.x >> 1, slot = blockIdx.y;
+    const int tile = gridDim.z - 1 - blockIdx.z;                 // later tiles of a prompt see more keys: they start first
+    const int group = p.hq / p.hkv;
+    const int row0 = p.tile_row0[tile], nq = p.tile_nq[tile];
+    const int entry = p.tile_entry[tile];
+    const int rows_all = nq * group;                             // rows of the tile, of which this block has 128 from rank * 128
+    const int c_first = p.row_count[row0];
+    int klo = (p.window > 0 && c_first > p.window) ? c_first - p.window : 0;
+    int khi = c_first > 0 ? c_first + nq - 1 : 0;                // a padding row sees nothing
+    if (p.split > 0) {
+        klo = max(klo, slot * p.split);
+        khi = min(khi, (slot + 1) * p.split);
+    }
+    constexpr int d = HD;
+    if (klo >= khi) {                                            // nothing for this pair (the same in both blocks): before anything is allocated
+        dependent_wait();
+        if (p.slots == 1 && c_first <= 0)
+            for (int i = tid; i < AT_ROWS * d; i += AT_THREADS) {
+                const int R = (int)rank * AT_ROWS + i / d, c = i % d;
+                if (R < rows_all) p.out[((size_t)(row0 + R / group) * p.hq + kvh * group + R % group) * d + c] = __float2bfloat16_rn(0.f);
+            }
+        return;
+    }
+    const int k_begin = klo / AT_KEYS * AT_KEYS;
+    const int n_tiles = (khi - k_begin + AT_KEYS - 1) / AT_KEYS;
+
+    if (tid == 0) {
+        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 2); at_mbar_init(empty + s, 1); }
+        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 16); at_mbar_init(s_free + b, 1); }
+        at_mbar_init(o_full, 1);
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    if (warp == 1) {
+        asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(at_saddr(tmem_slot)), "r"(C::TMEM_COLS) : "memory");
+        asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+    }
+    at_fence_before();
+    __syncthreads();
+    at_fence_after();
+    const uint32_t tmem = *tmem_slot;
+    dependent_wait();                                       // the queries and the newest keys are the kernel before's
+    // Q into TMEM as the A operand of the score products: this block's row r in lane r, two elements a
+    // column. The two warps of a quarter of the rows take half of the head each.
+    if (warp >= 2 && warp < 10) {
+        const int r = (warp & 3) * 32 + lane;
+        const int R = (int)rank * AT_ROWS + r;
+        const int half = (warp - 2) >> 2;
+        const bool own = R < rows_all;
+        const bf16* src = p.q + ((size_t)(row0 + (own ? R / group : 0)) * p.hq + kvh * group + (own ? R % group : 0)) * d;
+        for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 64) {
+            uint32_t w[32];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) {
+                uint4 v = make_uint4(0u, 0u, 0u, 0u);
+                if (own) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
+                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+            }
+            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
+        }
+        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+    }
+    // Both blocks' Q in place and both blocks' barriers made, before anything is signalled across.
+    at_fence_before();
+    __syncthreads();
+    atp_cluster_sync();
+    at_fence_after();
+    bool failed = false;
+
+    if (warp == 0 || warp == AT_WARP_V) {
+        // ---------------------------------------------------------------- pages and boxes, this block's halves
+        // Asking TMA for a box keeps the asking warp busy for more than a hundred clocks, so the keys
+        // and the values have a warp each.
+        const int half = warp == 0 ? 0 : 1;                      // keys, or values
+        // Keys: the first block brings keys 0-31 of a step (pages 0 and 1 of its four), the second keys
+        // 32-63, laid out [chunk][32 keys]: eight-key groups 1 KB apart. Values: every page's 16 keys,
+        // this block's half of the head's chunks, [page][chunk][16 keys]. A group without a page
+        // (before the window, past the end) is cleared instead when it holds values.
+        auto lookup = [&](int kt_first) -> int {
+            const int kt = kt_first + (lane >> 2);
+            const int j = k_begin + kt * AT_KEYS + (lane & 3) * 16;
+            int page = -1;
+            if (kt < n_tiles && j < khi && j + 16 > klo) {
+                const int lp = max(j, klo) / p.page_size;
+                if (lp < p.table_width) page = p.block_table[(size_t)entry * p.table_width + lp];
+                if (page >= p.n_pages) page = -1;
+            }
+            return page;
+        };
+        int pages_now = 0, pages_next = lookup(0);
+        for (int kt = 0; kt < n_tiles && !failed; ++kt) {
+            if ((kt & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
+            const int j0 = k_begin + kt * AT_KEYS;
+            const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
+            const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
+            const int live = __popc(have);
+            {
+                const int s = half == 0 ? kt % KS : KS + kt % VS;
+                const int round = half == 0 ? kt / KS : kt / VS;
+                bool ok = true;
+                if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
+                if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
+                unsigned char* dst = ring + s * C::SLOT_BYTES;
+                const uint32_t bar = at_saddr(full + s) & AT_PEER_MASK;          // the first block's barrier
+                if (half == 1 && live < 4) {
+                    for (int sub = 0; sub < 4; ++sub) {
+                        if (have & (1u << sub)) continue;
+                        uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_HALF);
+                        for (int e = lane; e < (int)(PAGE_HALF / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
+                    }
+                    at_fence_async_smem();
+                    __syncwarp();
+                }
+                if (lane == 0) {
+                    // one arrival a block: the first block's carries the bytes both will bring
+                    // (with a release only when this block cleared something the first block's products will read)
+                    if (rank == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_FULL);
+                    else if (half == 1 && live < 4) atp_arrive_on_first(full + s);
+                    else atp_arrive_on_first_relaxed(full + s);
+                }
+                __syncwarp();
+                if (half == 0) {
+                    // this block's two pages of keys: a box of 16 keys x 64 elements a lane, [chunk][page][16 keys]
+                    const int sub_local = (lane / NBOX) & 1, bx = lane % NBOX;
+                    const int sub = (int)rank * 2 + sub_local;
+                    const int pg = __shfl_sync(0xffffffffu, page, sub);
+                    if (lane < 2 * NBOX && pg >= 0) {
+                        const int j = j0 + sub * 16;
+                        const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
+                        atp_tma_box(at_saddr(dst) + (uint32_t)(bx * 2 + sub_local) * 2048u, &map_k, bx * 64, row, bar);
+                    }
+                } else if (lane < 4 && page >= 0) {              // values: one copy a page, this block's chunks
+                    const int j = j0 + lane * 16;
+                    const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                    atp_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_HALF, &map_v, row, (int)rank * (NBOX / 2), bar);
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------------------------------------------------------- the score products of both blocks, from one lane of the first
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t IDESC_S = at_idesc(ATP_ROWS, AT_KEYS, false);
+            const uint32_t ring_addr = at_saddr(ring);
+            for (int kt = 0; kt < n_tiles; ++kt) {               // S[kt & 1] = Q K(kt)^T
+                const int s = kt % KS, b = kt & 1;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) { failed = true; break; }
+                if (kt >= 2 && !at_mbar_wait(s_free + b, (uint32_t)((kt - 2) >> 1) & 1u)) { failed = true; break; }
+                at_fence_after();
+                const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
+                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);
+#pragma unroll
+                for (int bx = 0; bx < NBOX; ++bx) {
+                    const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
+                    const uint64_t bdesc = at_desc(k_addr + bx * (AT_KEYS / 2 * 128), 16, 1024);   // this chunk's 32 keys a block
+#pragma unroll
+                    for (int kk = 0; kk < 4; ++kk)
+                        atp_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                }
+                atp_commit_both(empty + s);                      // the key slot is free in both blocks when S is complete
+                atp_commit_both(s_full + b);
+            }
+        }
+    } else if (warp == AT_WARP_PV) {
+        // ---------------------------------------------------------------- the P V products of both blocks
+        if (lane == 0 && rank == 0) {
+            constexpr uint32_t IDESC_O = at_idesc(ATP_ROWS, HD, true);
+            const uint32_t ring_addr = at_saddr(ring);
+            for (int kt = 0; kt < n_tiles; ++kt) {
+                const int b = kt & 1;
+                const int s = KS + kt % VS;
+                if (!at_mbar_wait(full + s, (uint32_t)(kt / VS) & 1u)) { failed = true; break; }
+                if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
+                at_fence_after();
+                const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
+                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
+#pragma unroll
+                for (int kk = 0; kk < 4; ++kk) {
+                    // keys 16 kk ..: page kk, its two eight-key groups 1 KB apart, this block's chunks 2 KB apart
+                    const uint64_t bdesc = at_desc(v_addr + (uint32_t)kk * PAGE_HALF, 2048, 1024);
+                    atp_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
+                }
+                atp_commit_both(empty + s);
+                atp_commit_here(s_free + b);                     // P has been read: the scores of tile kt + 2 may land
+            }
+            if (!failed) atp_commit_both(o_full);
+        }
+    } else if (warp >= 2 && warp < 10) {
+        // ---------------------------------------------------------------- softmax and epilogue, half a row a thread
+        const int quarter = warp & 3;
+        const int half = (warp - 2) >> 2;
+        const int r = quarter * 32 + lane;                       // the TMEM lane
+        const int R = (int)rank * AT_ROWS + r;                   // the row of the tile
+        const bool own = R < rows_all;
+        const int cnt = own ? c_first + R / group : 0;
+        const int fst = (own && p.window > 0 && cnt > p.window) ? cnt - p.window : 0;
+        const int lo = max(fst, klo), hi = min(cnt, khi);
+        const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
+        const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
+        const float c1 = p.scale / p.cap, c2 = p.cap * 1.4426950408889634f;
+        float l = 0.f;
+        for (int kt = 0; kt < n_tiles; ++kt) {
+            const int b = kt & 1;
+            const int j0 = k_begin + kt * AT_KEYS + half * 32;
+            if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
+            at_fence_after();
+            uint32_t sv[32], pr[16];
+            const bool edge = j0 < lo_max || j0 + 32 > hi_min;
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 32), sv);
+            asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+            float la = 0.f, lb = 0.f;
+#pragma unroll
+            for (int j = 0; j < 32; j += 2) {
+                float p0 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j]) * c1));
+                float p1 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
+                if (edge) {
+                    const int jj = j0 + j;
+                    if (jj < lo || jj >= hi) p0 = 0.f;
+                    if (jj + 1 < lo || jj + 1 >= hi) p1 = 0.f;
+                }
+                la += p0;
+                lb += p1;
+                pr[j >> 1] = at_pack(p0, p1);
+            }
+            l += la + lb;
+            asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");      // the quarter's two warps have read their scores
+            at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 16), pr);
+            asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+            at_fence_before();
+            __syncwarp();
+            if (lane == 0) {
+                if (rank == 0) at_mbar_arrive(p_full + b);       // the first block's own barrier
+                else atp_arrive_on_first_relaxed(p_full + b);
+            }
+        }
+        if (half == 1) l_half[r] = l;
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        float inv = 0.f;
+        if (half == 0) {
+            l += l_half[r];
+            inv = l > 0.f ? 1.f / l : 0.f;
+        }
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        if (half == 0) l_half[r] = inv;
+        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
+        if (half == 1) inv = l_half[r];
+        if (!failed && !__all_sync(0xffffffffu, at_mbar_wait(o_full, 0u))) failed = true;
+        if (!failed) {
+            at_fence_after();
+            const int z0 = p.slots > 1 ? fst / p.split : 0;
+            const int z1 = p.slots > 1 ? min(p.slots - 1, (max(cnt, 1) - 1) / p.split) : 0;
+            const bool direct = z0 == z1;
+            const bool writes = own && (!direct || slot == z0);
+            const int row = row0 + R / group, head = kvh * group + R % group;
+            bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
+            float* pdst = p.partial ? p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2) : nullptr;
+            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+                uint32_t o[32];
+                __syncwarp();
+                at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
+                asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+                if (!writes) continue;
+                if (direct) {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 8) {
+                        uint4 v;
+                        v.x = at_pack(__uint_as_float(o[j]) * inv, __uint_as_float(o[j + 1]) * inv);
+                        v.y = at_pack(__uint_as_float(o[j + 2]) * inv, __uint_as_float(o[j + 3]) * inv);
+                        v.z = at_pack(__uint_as_float(o[j + 4]) * inv, __uint_as_float(o[j + 5]) * inv);
+                        v.w = at_pack(__uint_as_float(o[j + 6]) * inv, __uint_as_float(o[j + 7]) * inv);
+                        *reinterpret_cast<uint4*>(dst + c0 + j) = v;
+                    }
+                } else {
+#pragma unroll
+                    for (int j = 0; j < 32; j += 2)
+                        *reinterpret_cast<float2*>(pdst + c0 + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
+                }
+            }
+            if (writes && !direct && half == 0) { pdst[d] = 0.f; pdst[d + 1] = l; }
+        }
+    }
+    if (failed) atomicExch(&g_attention_tc_error, 1);
+    at_fence_before();
+    __syncthreads();
+    atp_cluster_sync();
+    if (warp == 1) {
+        at_fence_after();
+        asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(C::TMEM_COLS) : "memory");
+    }
+}
+
+template <int HD>
+static int launch_tc_pair(const AttTcParams& p, const void* k_table, const void* v_table, int tiles, cudaStream_t s) {
+    using C = AtpCfg<HD>;
+    static bool attr_set = false;
+    if (!attr_set) {
+        const cudaError_t e = cudaFuncSetAttribute(attention_tc_pair_kernel<HD>, cudaFuncAttributeMaxDynamicSharedMemorySize, C::SMEM);
+        if (e != cudaSuccess) return fail("attention_tc: cannot have %d bytes of shared memory: %s", C::SMEM, cudaGetErrorString(e));
+        attr_set = true;
+    }
+    const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
+    CUtensorMap map_k, map_v;
+    if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
+    if (int e = encode_map_bf16_chunks(&map_v, v_table, rows, p.d, 16, p.d / 128)) return e;
+    dim3 grid(2 * p.hkv, p.slots, tiles);
+    launch_dependent_if(false, attention_tc_pair_kernel<HD>, grid, dim3(AT_THREADS), (size_t)C::SMEM, s, p, map_k, map_v);
+    return check_launch("attention_tc (pairs)");
+}
+
 template <int HD>
 static int launch_tc(const AttTcParams& p, const void* k_table, const void* v_table, int tiles, cudaStream_t s) {
     using C = AtCfg<HD>;
@@ -528,12 +944,17 @@ extern "C" int kb_attention_tc_takes(int hq, int hkv, int d, int page_size, floa
            hq % hkv == 0 && hq / hkv <= AT_ROWS;
 }
 
-// Prompt portions; arguments as kb_attention_mma's with decode = 0. With slots > 1, `scratch` holds
-// [rows, hq, slots, d + 2] floats and the caller merges it (kb_attention_mma_combine).
+// Rows (token, query head of one kv head) a tile holds: 256 where pairs of blocks run it (head sizes
+// 128 and 256 with `pairs`), else 128.
+extern "C" int kb_attention_tc_rows(int d, int pairs) { return (pairs && (d == 128 || d == 256)) ? ATP_ROWS : AT_ROWS; }
+
+// Prompt portions; arguments as kb_attention_mma's with decode = 0, tiles of kb_attention_tc_rows(d,
+// pairs) rows. With slots > 1, `scratch` holds [rows, hq, slots, d + 2] floats and the caller merges it
+// (kb_attention_mma_combine). `pairs` 1: head sizes 128 and 256 run on pairs of blocks.
 extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, const void* v_table, const int* block_table,
                                const int* row_count, const int* tile_entry, const int* tile_row0, const int* tile_nq, int tiles,
                                int rows, int hq, int hkv, int d, int page_size, int table_width, int n_pages, int window,
-                               int split, int slots, float scale, float cap, float* scratch, void* stream) {
+                               int split, int slots, float scale, float cap, float* scratch, int pairs, void* stream) {
     KB_REQUIRE(rows >= 0 && tiles >= 0 && hq > 0 && hkv > 0, "attention_tc: rows %d, tiles %d, heads %d over %d", rows, tiles, hq, hkv);
     KB_REQUIRE(kb_attention_tc_takes(hq, hkv, d, page_size, cap), "attention_tc: head_dim %d, %d heads over %d, pages of %d, cap %g are not taken",
                d, hq, hkv, page_size, cap);
@@ -551,6 +972,7 @@ extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, co
     p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 64) return launch_tc<64>(p, k_table, v_table, tiles, s);
-    if (d == 128) return launch_tc<128>(p, k_table, v_table, tiles, s);
-    return launch_tc<256>(p, k_table, v_table, tiles, s);
+    if (pairs == 0) return d == 128 ? launch_tc<128>(p, k_table, v_table, tiles, s) : launch_tc<256>(p, k_table, v_table, tiles, s);
+    KB_REQUIRE(2 * hkv <= 65535, "attention_tc: %d kv heads is too many for one launch of pairs", hkv);
+    return d == 128 ? launch_tc_pair<128>(p, k_table, v_table, tiles, s) : launch_tc_pair<256>(p, k_table, v_table, tiles, s);
 }

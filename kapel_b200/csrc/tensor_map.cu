@@ -21,13 +21,16 @@ static int find_encoder() {
     return 0;
 }
 
-int encode_map_bf16_chunks(CUtensorMap* map, const void* base, unsigned long long rows, unsigned cols, unsigned box_rows) {
+int encode_map_bf16_chunks(CUtensorMap* map, const void* base, unsigned long long rows, unsigned cols, unsigned box_rows,
+                           unsigned box_chunks) {
     if (int e = find_encoder()) return e;
     if (((uintptr_t)base & 15) != 0 || cols % 64 != 0 || cols == 0)
         return fail("tensor map: base %p must be a multiple of 16 and %u columns a multiple of 64", base, cols);
     const cuuint64_t dims[3] = {64u, (cuuint64_t)rows, (cuuint64_t)(cols / 64)};
     const cuuint64_t strides[2] = {(cuuint64_t)cols * 2, 128u};
-    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)(cols / 64)};
+    if (box_chunks == 0) box_chunks = cols / 64;
+    if (box_chunks > cols / 64) return fail("tensor map: %u chunks a box of a matrix that has %u", box_chunks, cols / 64);
+    const cuuint32_t box[3] = {64u, (cuuint32_t)box_rows, (cuuint32_t)box_chunks};
     const cuuint32_t elem[3] = {1, 1, 1};
     const CUresult r = g_encode(map, CU_TENSOR_MAP_DATA_TYPE_BFLOAT16, 3, const_cast<void*>(base), dims, strides, box, elem,
                                 CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B,

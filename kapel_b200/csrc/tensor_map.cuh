@@ -14,6 +14,8 @@ int encode_map_bf16(CUtensorMap* map, const void* base, unsigned long long rows,
 // rows, chunks of 64 columns. A box of box_rows rows lands in shared memory chunk by chunk:
 // [cols / 64][box_rows][128 bytes] under the 128-byte swizzle, one copy for rows of any width.
 // Coordinates are (0, row, 0).
-int encode_map_bf16_chunks(CUtensorMap* map, const void* base, unsigned long long rows, unsigned cols, unsigned box_rows);
+// `box_chunks` (0: all of them) chunks a box; the third coordinate is then the first chunk wanted.
+int encode_map_bf16_chunks(CUtensorMap* map, const void* base, unsigned long long rows, unsigned cols, unsigned box_rows,
+                           unsigned box_chunks = 0);
 
 }  // namespace kb

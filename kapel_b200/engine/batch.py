@@ -181,7 +181,7 @@ class StepBatch:
             plan = self.plan
             most = int(plan.q_len.max()) * heads_per_kv
             decode = most if most <= K.attention_mma_rows(True) else 0      # rows a tile in decode mode, else 0
-            per_tile = max(1, K.attention_mma_rows(bool(decode)) // heads_per_kv)
+            per_tile = max(1, K.attention_tile_rows(bool(decode), prompt_kernel, head_dim) // heads_per_kv)
             arrays = cut_tiles(plan.q_start, plan.q_len, per_tile)
             n = arrays[0].size
             host = torch.from_numpy(np.concatenate(arrays)).pin_memory() if self.ids.is_cuda else torch.from_numpy(np.concatenate(arrays))

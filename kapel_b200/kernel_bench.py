@@ -216,7 +216,7 @@ def main(argv=None) -> int:
         t = args.prompt
         q = torch.randn(t, Hq, D, device=dev).to(bf)
         rc = torch.arange(1, t + 1, dtype=torch.int32, device=dev)
-        per_tile = max(1, K.attention_mma_rows(False) // (Hq // Hkv))
+        per_tile = max(1, K.attention_tile_rows(False, K.attention_prompt_kernel(Hq, Hkv, D, page, cap), D) // (Hq // Hkv))
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
         firsts = tiles[1].cpu().numpy() + 1
         split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D,

@@ -36,6 +36,11 @@ GEMM_SMALL = _os.environ.get("KAPEL_B200_GEMM_SMALL", "skinny")
 # tcgen05.mma, scores and probabilities in tensor memory) or "mma" (the mma.sync flash kernel, which
 # also takes what the first does not: no soft cap, other head sizes).
 ATTENTION_PROMPT = _os.environ.get("KAPEL_B200_ATTENTION_PROMPT", "tcgen05")
+# Whether the tcgen05 prompt attention runs on pairs of blocks (tcgen05.mma.cta_group::2, 256 rows to one
+# tile of keys and values) at the head sizes that have such a kernel (128 and 256), or on single blocks.
+# Single blocks by default: the two measure the same at head size 256 (both are bound by their softmax
+# warps) and the pairs are slower at 128.
+ATTENTION_PAIRS = _os.environ.get("KAPEL_B200_ATTENTION_PAIRS", "0") == "1"
 # Whether the kernels of a decode step are launched as programmatic dependents of one another, so
 # that a kernel sets up (and asks for its first weights) while the one before it finishes.
 PDL = _os.environ.get("KAPEL_B200_PDL", "1") == "1"
@@ -469,6 +474,14 @@ def attention_mma_rows(decode: bool) -> int:
     return int(library().kb_attention_mma_rows(int(bool(decode))))
 
 
+def attention_tile_rows(decode: bool, prompt_kernel: str = "mma", d: int = 0) -> int:
+    """Rows a tile holds for the kernel that will run: the decode kernel's, the mma.sync prompt
+    kernel's, or the tcgen05 prompt kernel's (twice as many where pairs of blocks run it)."""
+    if not decode and prompt_kernel == "tcgen05":
+        return int(library().kb_attention_tc_rows(int(d), int(ATTENTION_PAIRS)))
+    return attention_mma_rows(decode)
+
+
 def attention_mma_takes(dtype, d: int, heads_per_kv: int) -> bool:
     """Whether the tensor-core kernel takes these sizes (else the row-wise kernel does)."""
     return dtype == torch.bfloat16 and d % 16 == 0 and d <= 256 and heads_per_kv <= 16
@@ -513,7 +526,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                                 _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
                                 int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                                _f(softcap or 0.0), _ptr(scratch), _stream())
+                                _f(softcap or 0.0), _ptr(scratch), int(ATTENTION_PAIRS), _stream())
         )
         if slots > 1:
             _check(lib.kb_attention_mma_combine(_ptr(out), _ptr(row_count), _ptr(scratch), rows, hq, d, int(window or 0), int(split),

@@ -395,7 +395,8 @@ def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split, 
     from kapel_b200.engine.batch import cut_tiles
 
     hq, hkv = q.shape[1], kt.shape[1]
-    per_tile = max(1, K().attention_mma_rows(decode) // (hq // hkv))
+    kernel = "mma" if decode else K().attention_prompt_kernel(hq, hkv, q.shape[2], page, cap)
+    per_tile = max(1, K().attention_tile_rows(decode, kernel, q.shape[2]) // (hq // hkv))
     q_len = np.asarray(q_lens, np.int32)
     q_start = np.concatenate(([0], np.cumsum(q_len)[:-1])).astype(np.int32)
     tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(q_start, q_len, per_tile))
@@ -411,24 +412,27 @@ def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split, 
 @pytest.mark.parametrize("hq,hkv,d", [(4, 2, 16), (6, 1, 32), (3, 3, 48), (16, 1, 64), (8, 4, 128), (8, 4, 256), (5, 1, 80)])
 @pytest.mark.parametrize("window,cap", [(None, None), (24, 20.0), (300, 50.0)])
 @pytest.mark.parametrize("split", [0, 64, 256])
-@pytest.mark.parametrize("kernel", ["tcgen05", "mma"])
+@pytest.mark.parametrize("kernel", ["tcgen05", "tcgen05_single", "mma"])
 def test_paged_attention_mma_prompt_mode(kernel, hq, hkv, d, window, cap, split):
-    """Prompt portions: the tcgen05 kernel where it applies (head sizes 64, 128, 256 with a soft
-    cap) and the mma.sync kernel everywhere."""
+    """Prompt portions: the tcgen05 kernels where they apply (head sizes 64, 128, 256 with a soft
+    cap; pairs of blocks at 128 and 256, and single blocks at all three) and the mma.sync kernel
+    everywhere."""
     import kapel_b200.kernels as KK
 
     takes = d in (64, 128, 256) and cap is not None
-    if kernel == "tcgen05" and not takes:
+    if kernel.startswith("tcgen05") and not takes:
         pytest.skip("the mma.sync kernel runs these sizes under either setting")
+    if kernel == "tcgen05_single" and d == 64:
+        pytest.skip("head size 64 runs on single blocks under either setting")
     lengths, q_lens = [1, 37, 300, 700], [1, 37, 130, 33]
     q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d)
     scale = 1.0 / math.sqrt(d * 1.5)
-    old = KK.ATTENTION_PROMPT
-    KK.ATTENTION_PROMPT = kernel
+    old = KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS
+    KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS = kernel.split("_")[0], kernel != "tcgen05_single"
     try:
         got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, False, split).double()
     finally:
-        KK.ATTENTION_PROMPT = old
+        KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS = old
     K().check_async_errors()
     want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
     assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
@@ -535,7 +539,7 @@ def test_paged_attention_at_the_sizes_and_histories_that_are_timed(hq, hkv, d, s
     lengths, q_lens = [4150, 2048], [200, 2048]
     q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=d + hq + 1)
     q = q * 4.0
-    per_tile = max(1, K().attention_mma_rows(False) // (hq // hkv))
+    per_tile = max(1, K().attention_tile_rows(False, "tcgen05", d) // (hq // hkv))
     q_len = np.asarray(q_lens, np.int32)
     q_start = np.asarray([0, 200], np.int32)
     arrays = cut_tiles(q_start, q_len, per_tile)

@@ -24,7 +24,7 @@ def lib():
     lib.kb_rope_table.argtypes = [vp, vp, i32, i32, f64, vp]
     lib.kb_rope_append.argtypes = [vp, i32, i32, i64, vp, vp, vp, vp, vp, i32, i32, i32, i32, i32, i32, i32, i64, i32, vp]
     lib.kb_glu.argtypes = [vp, i32, vp, i32, i32, i64, i64, i32, i32, vp]
-    lib.kb_attention_tc.argtypes = [vp] * 9 + [i32] * 11 + [f32, f32, vp, vp]
+    lib.kb_attention_tc.argtypes = [vp] * 9 + [i32] * 11 + [f32, f32, vp, i32, vp]
     lib.kb_attention_tc_takes.argtypes = [i32, i32, i32, i32, f32]
     return lib
 
@@ -73,6 +73,8 @@ def test_tcgen05_attention_says_what_it_takes(lib):
     assert takes(8, 4, 128, 16, 100.0) == 0                  # ... of at most 64
     assert takes(8, 3, 128, 16, 50.0) == 0                   # heads must divide into kv heads
     args = [A] * 9 + [1, 64, 8, 4, 96, 16, 8, 8, 0, 0, 1]
-    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "head_dim 96", "are not taken")
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, 1, None), "attention_tc", "head_dim 96", "are not taken")
     args = [A] * 9 + [1, 64, 8, 4, 128, 16, 8, 8, 0, 96, 2]
-    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, None), "attention_tc", "split 96")
+    refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, 1, None), "attention_tc", "split 96")
+    assert lib.kb_attention_tc_rows(256, 1) == 256 and lib.kb_attention_tc_rows(128, 1) == 256
+    assert lib.kb_attention_tc_rows(64, 1) == 128 and lib.kb_attention_tc_rows(256, 0) == 128
