@@ -157,6 +157,20 @@ __device__ __forceinline__ float at_exp2(float x) {
     asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
     return y;
 }
+// 2^x on the FMA and integer pipes, for |x| < 126: x = n + f with n the nearest integer (the magic
+// constant's addition rounds it into the low bits), 2^f by a polynomial on [-1/2, 1/2] (relative error
+// below 6e-5, far below bfloat16's 4e-3), 2^n added to the exponent. The special-function unit makes 16
+// results a clock a multiprocessor and the softmax needs two an element (tanh and exp): half of the
+// exponentials are computed this way so that both pipes work.
+__device__ __forceinline__ float at_exp2_poly(float x) {
+    const float t = x + 12582912.f;                              // 1.5 * 2^23: the integer part lands in the mantissa
+    const float f = x - (t - 12582912.f);
+    float p = fmaf(f, 0.0096181291f, 0.0555041087f);
+    p = fmaf(p, f, 0.2402265070f);
+    p = fmaf(p, f, 0.6931471806f);
+    p = fmaf(p, f, 1.0f);
+    return __int_as_float(__float_as_int(p) + (__float_as_int(t) << 23));
+}
 __device__ __forceinline__ uint32_t at_pack(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
@@ -423,7 +437,7 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
                 float p0 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j]) * c1));
-                float p1 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
+                float p1 = at_exp2_poly(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
                 if (edge) {
                     const int jj = j0 + j;
                     if (jj < lo || jj >= hi) p0 = 0.f;
@@ -510,7 +524,8 @@ attention_tc_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map
 // keys 0-31 of a step and the first half of the head's elements of the values, the second keys 32-63
 // and the second half (the B operand of a cta_group::2 product is split along its N between the two
 // blocks). A block takes in half as much a step and row.
-//   * a tile is up to 256 rows: the first block takes rows 0-127, the second rows 128-255;
+//   * a tile is up to 256 rows: the first block takes rows 0-127, the second rows 128-255; each keeps its Q
+//     in shared memory (the A operand of the score products) and four S buffers in TMEM;
 //   * both blocks' TMA copies complete on the first block's "full" barrier (two arrivals: the first
 //     block's, with the bytes expected from both, and the second block's, when it has cleared what
 //     it had no page for);
@@ -544,6 +559,12 @@ __device__ __forceinline__ void atp_arrive_on_first(uint64_t* bar) {
         "mbarrier.arrive.release.cluster.shared::cluster.b64 _, [ra];\n\t}"
         ::"r"(at_saddr(bar)) : "memory");
 }
+__device__ __forceinline__ void atp_mma_ss(uint32_t d_tmem, uint64_t adesc, uint64_t bdesc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\tsetp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}"
+        ::"r"(d_tmem), "l"(adesc), "l"(bdesc), "r"(idesc), "r"(accumulate) : "memory");
+}
 // The same without the release: for a signal that only says "my tcgen05.st has completed" (the store was
 // waited for and fenced with tcgen05.fence::before_thread_sync), which needs no ordering of ordinary
 // memory. A release at cluster scope costs the arriving thread more than a thousand clocks.
@@ -564,22 +585,32 @@ __device__ __forceinline__ void atp_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 }
 
 constexpr int ATP_ROWS = 256;                                   // rows a tile of the pair kernel
+// Twenty warps: the single-block kernel's roles in warps 0-11, and a second group of eight softmax warps
+// (12-19). The first group takes the even tiles, the second the odd ones: while one group waits for its
+// scores, its TMEM loads and stores or its partner warp, the other keeps the special-function unit busy.
+constexpr int ATP_THREADS = 640;
 
 template <int HD> struct AtpCfg {
     static constexpr int NBOX = HD / 64;                        // chunks of 64 elements along the head
     static constexpr int SLOT_BYTES = AT_KEYS * HD;             // a block's half of a key tile, or of a value tile
-    static constexpr int K_SLOTS = HD == 256 ? 5 : 6;
-    static constexpr int V_SLOTS = HD == 256 ? 6 : 8;
+    static constexpr int K_SLOTS = HD == 256 ? 4 : 6;
+    static constexpr int V_SLOTS = HD == 256 ? 5 : 8;
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
-    static constexpr int COL_O = 0, COL_S = HD, COL_Q = HD + 2 * AT_KEYS;
+    // Q lies in shared memory here (a block has room: its slots are half the single kernel's), which
+    // leaves TMEM for four S buffers: the chain scores -> softmax -> P V -> "S may be written again"
+    // is then four tiles long instead of two, and the score products no longer wait for it.
+    static constexpr int S_BUFS = 4;
+    static constexpr int Q_BYTES = AT_ROWS * HD * 2;
+    static constexpr int COL_O = 0, COL_S = HD;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int SMEM = SLOTS * SLOT_BYTES + 1024 /* alignment */ + 320 /* barriers */ + 512 /* row sums */;
-    static_assert((2 * SLOTS + 7) * 8 + 8 <= 320, "the barriers outgrew their room");
+    static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024 /* alignment */ + 384 /* barriers */ + 2048 /* row sums */;
+    static_assert(HD + S_BUFS * AT_KEYS <= TMEM_COLS, "O and the S buffers outgrew TMEM");
+    static_assert((2 * SLOTS + 3 * S_BUFS + 1) * 8 + 8 <= 384, "the barriers outgrew their room");
     static_assert(SMEM <= 232448, "more shared memory than a block can have");
 };
 
 template <int HD>
-__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(AT_THREADS, 1)
+__global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ATP_THREADS, 1)
 attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     using C = AtpCfg<HD>;
     constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS;
@@ -587,15 +618,17 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
     constexpr uint32_t PAGE_HALF = PAGE_FULL / 2;                // a block's half of a page of values
     extern __shared__ unsigned char at_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
-    unsigned char* ring = smem;
+    constexpr int SB = C::S_BUFS;
+    unsigned char* q_smem = smem;                                // [chunk][128 rows][128 bytes], 128-byte swizzle
+    unsigned char* ring = smem + C::Q_BYTES;
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] the first block's: both halves of a slot have landed
     uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete (in both blocks)
-    uint64_t* s_full = empty + NS;                               // [2] S complete (in both blocks)
-    uint64_t* p_full = s_full + 2;                               // [2] the first block's: P written by the 16 softmax warps of both
-    uint64_t* s_free = p_full + 2;                               // [2] the first block's: the product that read P is complete
-    uint64_t* o_full = s_free + 2;                               // [1] O complete (in both blocks)
+    uint64_t* s_full = empty + NS;                               // [SB] S complete (in both blocks)
+    uint64_t* p_full = s_full + SB;                              // [SB] the first block's: P written by 16 softmax warps, 8 of each block
+    uint64_t* s_free = p_full + SB;                              // [SB] the first block's: the product that read P is complete
+    uint64_t* o_full = s_free + SB;                              // [1] O complete (in both blocks)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
-    float* l_half = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 320);
+    float* l_part = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 384);   // [4][128] sum p by row: a share from each softmax warp of a quarter
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t rank;
@@ -617,7 +650,7 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
     if (klo >= khi) {                                            // nothing for this pair (the same in both blocks): before anything is allocated
         dependent_wait();
         if (p.slots == 1 && c_first <= 0)
-            for (int i = tid; i < AT_ROWS * d; i += AT_THREADS) {
+            for (int i = tid; i < AT_ROWS * d; i += ATP_THREADS) {
                 const int R = (int)rank * AT_ROWS + i / d, c = i % d;
                 if (R < rows_all) p.out[((size_t)(row0 + R / group) * p.hq + kvh * group + R % group) * d + c] = __float2bfloat16_rn(0.f);
             }
@@ -628,7 +661,7 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
 
     if (tid == 0) {
         for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 2); at_mbar_init(empty + s, 1); }
-        for (int b = 0; b < 2; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 16); at_mbar_init(s_free + b, 1); }
+        for (int b = 0; b < SB; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 16); at_mbar_init(s_free + b, 1); }
         at_mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -641,8 +674,9 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
     at_fence_after();
     const uint32_t tmem = *tmem_slot;
     dependent_wait();                                       // the queries and the newest keys are the kernel before's
-    // Q into TMEM as the A operand of the score products: this block's row r in lane r, two elements a
-    // column. The two warps of a quarter of the rows take half of the head each.
+    // Q into shared memory as the A operand of the score products, K-major under the 128-byte swizzle:
+    // chunk c (64 elements) of row r at c * 16 KB + r * 128, its 16-byte pieces exchanged by r mod 8.
+    // The two warps of a quarter of the rows (of the first softmax group) take half of the head each.
     if (warp >= 2 && warp < 10) {
         const int r = (warp & 3) * 32 + lane;
         const int R = (int)rank * AT_ROWS + r;
@@ -650,16 +684,15 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
         const bool own = R < rows_all;
         const bf16* src = p.q + ((size_t)(row0 + (own ? R / group : 0)) * p.hq + kvh * group + (own ? R % group : 0)) * d;
         for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 64) {
-            uint32_t w[32];
+            unsigned char* dst = q_smem + (size_t)(c0 / 64) * (AT_ROWS * 128) + (size_t)r * 128;
 #pragma unroll
             for (int j = 0; j < 8; ++j) {
                 uint4 v = make_uint4(0u, 0u, 0u, 0u);
                 if (own) v = *reinterpret_cast<const uint4*>(src + c0 + j * 8);
-                w[4 * j] = v.x; w[4 * j + 1] = v.y; w[4 * j + 2] = v.z; w[4 * j + 3] = v.w;
+                *reinterpret_cast<uint4*>(dst + ((j ^ (r & 7)) << 4)) = v;
             }
-            at_st32(tmem + ((uint32_t)((warp & 3) * 32) << 16) + (uint32_t)(C::COL_Q + c0 / 2), w);
         }
-        asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
+        at_fence_async_smem();
     }
     // Both blocks' Q in place and both blocks' barriers made, before anything is signalled across.
     at_fence_before();
@@ -742,20 +775,22 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
         if (lane == 0 && rank == 0) {
             constexpr uint32_t IDESC_S = at_idesc(ATP_ROWS, AT_KEYS, false);
             const uint32_t ring_addr = at_saddr(ring);
-            for (int kt = 0; kt < n_tiles; ++kt) {               // S[kt & 1] = Q K(kt)^T
-                const int s = kt % KS, b = kt & 1;
+            const uint32_t q_addr = at_saddr(q_smem);
+            for (int kt = 0; kt < n_tiles; ++kt) {               // S[kt % SB] = Q K(kt)^T
+                const int s = kt % KS, b = kt % SB;
                 if (!at_mbar_wait(full + s, (uint32_t)(kt / KS) & 1u)) { failed = true; break; }
-                if (kt >= 2 && !at_mbar_wait(s_free + b, (uint32_t)((kt - 2) >> 1) & 1u)) { failed = true; break; }
+                // the buffer still holds tile kt - SB's P until the product that reads it is complete
+                if (kt >= SB && !at_mbar_wait(s_free + b, (uint32_t)(kt / SB - 1) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
                 const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
-                    const uint32_t a_tmem = tmem + (uint32_t)(C::COL_Q + bx * 32);          // 64 elements of Q: 32 columns
+                    const uint64_t adesc = at_desc(q_addr + bx * (AT_ROWS * 128), 16, 1024);        // 64 elements of the 128 rows
                     const uint64_t bdesc = at_desc(k_addr + bx * (AT_KEYS / 2 * 128), 16, 1024);   // this chunk's 32 keys a block
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
-                        atp_mma_ts(d_tmem, a_tmem + (uint32_t)(kk * 8), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
+                        atp_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
                 }
                 atp_commit_both(empty + s);                      // the key slot is free in both blocks when S is complete
                 atp_commit_both(s_full + b);
@@ -767,10 +802,10 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
             constexpr uint32_t IDESC_O = at_idesc(ATP_ROWS, HD, true);
             const uint32_t ring_addr = at_saddr(ring);
             for (int kt = 0; kt < n_tiles; ++kt) {
-                const int b = kt & 1;
+                const int b = kt % SB;
                 const int s = KS + kt % VS;
                 if (!at_mbar_wait(full + s, (uint32_t)(kt / VS) & 1u)) { failed = true; break; }
-                if (!at_mbar_wait(p_full + b, (uint32_t)(kt >> 1) & 1u)) { failed = true; break; }
+                if (!at_mbar_wait(p_full + b, (uint32_t)(kt / SB) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
                 const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
@@ -785,10 +820,12 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
             }
             if (!failed) atp_commit_both(o_full);
         }
-    } else if (warp >= 2 && warp < 10) {
+    } else if ((warp >= 2 && warp < 10) || warp >= 12) {
         // ---------------------------------------------------------------- softmax and epilogue, half a row a thread
         const int quarter = warp & 3;
-        const int half = (warp - 2) >> 2;
+        const int grp = warp >= 12 ? 1 : 0;                      // even tiles, or odd tiles
+        const int half = ((warp >= 12 ? warp - 12 : warp - 2) >> 2);    // keys 0-31 of a tile, or 32-63
+        const int share = grp * 2 + half;                        // which of the quarter's four warps this is
         const int r = quarter * 32 + lane;                       // the TMEM lane
         const int R = (int)rank * AT_ROWS + r;                   // the row of the tile
         const bool own = R < rows_all;
@@ -798,11 +835,12 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
         const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
         const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
         const float c1 = p.scale / p.cap, c2 = p.cap * 1.4426950408889634f;
+        const int pair_bar = 2 + grp * 4 + quarter;              // the named barrier of this warp and its partner
         float l = 0.f;
-        for (int kt = 0; kt < n_tiles; ++kt) {
-            const int b = kt & 1;
+        for (int kt = grp; kt < n_tiles; kt += 2) {
+            const int b = kt % SB;
             const int j0 = k_begin + kt * AT_KEYS + half * 32;
-            if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt >> 1) & 1u))) { failed = true; break; }
+            if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt / SB) & 1u))) { failed = true; break; }
             at_fence_after();
             uint32_t sv[32], pr[16];
             const bool edge = j0 < lo_max || j0 + 32 > hi_min;
@@ -812,7 +850,7 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
 #pragma unroll
             for (int j = 0; j < 32; j += 2) {
                 float p0 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j]) * c1));
-                float p1 = at_exp2(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
+                float p1 = at_exp2_poly(c2 * at_tanh(__uint_as_float(sv[j + 1]) * c1));
                 if (edge) {
                     const int jj = j0 + j;
                     if (jj < lo || jj >= hi) p0 = 0.f;
@@ -823,7 +861,7 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                 pr[j >> 1] = at_pack(p0, p1);
             }
             l += la + lb;
-            asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");      // the quarter's two warps have read their scores
+            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");          // the two warps have read their scores
             at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 16), pr);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             at_fence_before();
@@ -833,17 +871,12 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                 else atp_arrive_on_first_relaxed(p_full + b);
             }
         }
-        if (half == 1) l_half[r] = l;
-        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
-        float inv = 0.f;
-        if (half == 0) {
-            l += l_half[r];
-            inv = l > 0.f ? 1.f / l : 0.f;
-        }
-        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
-        if (half == 0) l_half[r] = inv;
-        asm volatile("bar.sync %0, 64;" ::"r"(2 + quarter) : "memory");
-        if (half == 1) inv = l_half[r];
+        // The row's sum: the quarter's four warps leave their shares in shared memory; all sixteen
+        // softmax warps pass this barrier whatever happened above.
+        l_part[share * AT_ROWS + r] = l;
+        asm volatile("bar.sync 10, 512;" ::: "memory");
+        l = l_part[r] + l_part[AT_ROWS + r] + l_part[2 * AT_ROWS + r] + l_part[3 * AT_ROWS + r];
+        const float inv = l > 0.f ? 1.f / l : 0.f;
         if (!failed && !__all_sync(0xffffffffu, at_mbar_wait(o_full, 0u))) failed = true;
         if (!failed) {
             at_fence_after();
@@ -854,7 +887,8 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
             const int row = row0 + R / group, head = kvh * group + R % group;
             bf16* dst = p.out + ((size_t)row * p.hq + head) * d;
             float* pdst = p.partial ? p.partial + (((size_t)row * p.hq + head) * p.slots + slot) * (d + 2) : nullptr;
-            for (int c0 = half * (HD / 2); c0 < (half + 1) * (HD / 2); c0 += 32) {
+            // each of the quarter's four warps reads out a quarter of the head
+            for (int c0 = share * (HD / 4); c0 < (share + 1) * (HD / 4); c0 += 32) {
                 uint32_t o[32];
                 __syncwarp();
                 at_ld32(lanes + (uint32_t)(C::COL_O + c0), o);
@@ -876,7 +910,7 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                         *reinterpret_cast<float2*>(pdst + c0 + j) = make_float2(__uint_as_float(o[j]), __uint_as_float(o[j + 1]));
                 }
             }
-            if (writes && !direct && half == 0) { pdst[d] = 0.f; pdst[d + 1] = l; }
+            if (writes && !direct && share == 0) { pdst[d] = 0.f; pdst[d + 1] = l; }
         }
     }
     if (failed) atomicExch(&g_attention_tc_error, 1);
@@ -903,7 +937,7 @@ static int launch_tc_pair(const AttTcParams& p, const void* k_table, const void*
     if (int e = encode_map_bf16(&map_k, k_table, rows, p.d, p.d, 16)) return e;
     if (int e = encode_map_bf16_chunks(&map_v, v_table, rows, p.d, 16, p.d / 128)) return e;
     dim3 grid(2 * p.hkv, p.slots, tiles);
-    launch_dependent_if(false, attention_tc_pair_kernel<HD>, grid, dim3(AT_THREADS), (size_t)C::SMEM, s, p, map_k, map_v);
+    launch_dependent_if(false, attention_tc_pair_kernel<HD>, grid, dim3(ATP_THREADS), (size_t)C::SMEM, s, p, map_k, map_v);
     return check_launch("attention_tc (pairs)");
 }
 
