@@ -167,12 +167,17 @@ class DecodeGraphs:
             return None
         return plan, key, self.graphs[key][1].fill_host(plan)
 
-    def run_prepared(self, prepared, ids) -> torch.Tensor:
-        """The staged pass with its token ids: one copy, one replay."""
+    def run_prepared(self, prepared, ids=None, ids_device=None) -> torch.Tensor:
+        """The staged pass with its token ids: one copy, one replay. The ids come from the host
+        (`ids`) or are already on the device (`ids_device`, int32, one a row in the staged order:
+        what the sampling kernel of the pass before wrote), in which case nothing waits for them."""
         plan, key, which = prepared
         graph, static, out = self.graphs[key]
-        static.set_ids(which, ids, plan.rows)
+        if ids_device is None:
+            static.set_ids(which, ids, plan.rows)
         static.upload(which)
+        if ids_device is not None:
+            static.ids[: plan.rows].copy_(ids_device[: plan.rows], non_blocking=True)
         graph.replay()
         self.replays += 1
         self.passes += 1

@@ -46,6 +46,10 @@ class EngineOptions:
     max_pass_tokens: int = 2048
     max_sequences: int = 256
     reserve: float = 0.0
+    # Decoding passes are enqueued one ahead of the host where the tokens can be chosen on the device:
+    # the pass after this one is fed the chosen tokens from device memory and starts before the host
+    # has read them (this engine's own; Kapel reads every token back before it launches the next pass).
+    run_ahead: bool = True
 
 
 @dataclass
@@ -119,6 +123,10 @@ class Scheduler:
         self.passes = 0
         self.staged = None            # (request ids, engine handle) of a decode pass staged ahead of its tokens
         self.staged_passes = 0        # passes that ran from a staged plan
+        self.ahead = None             # (request ids, logits) of a pass already enqueued whose tokens are not chosen yet
+        self.ahead_passes = 0         # passes that were enqueued before the host had the tokens they feed
+        self._token_host = None       # pinned memory the chosen tokens are copied to, and the event behind the copy
+        self._token_event = None
 
     # ------------------------------------------------------------------ requests
     def add(self, request: Request) -> int:
@@ -240,6 +248,10 @@ class Scheduler:
         """One pass of the model: a token of every decoding request and portions of prompts.
         Returns the tokens it gave and the requests that ended; nothing when there is no work."""
         events = self._admit()
+        ahead, self.ahead = self.ahead, None
+        if ahead is not None:
+            # This pass is already on its way (enqueued while the host still read the tokens before).
+            return self._after_launch(events, *ahead)
         staged, self.staged = self.staged, None
         if staged is not None:
             # The pass staged while the last one ran is this pass if nothing changed since: the same
@@ -298,14 +310,51 @@ class Scheduler:
             logits = self.engine.step_prepared(handle, [self.entries[r].sequence[-1] for r in rids])
             self.staged_passes += 1
             self.passes += 1
-            pass_ = [(r, 1) for r in rids]
-            self._stage_next(pass_, rids)
-            tokens = self._choose(logits, rids)
         except Exception as e:                      # the pass failed: every running request ends
             return self._fail_pass(events, e)
-        return self._give(events, rids, tokens)
+        return self._after_launch(events, rids, logits)
+
+    def _after_launch(self, events, rids, logits) -> List[Event]:
+        """A pass of one token for each of `rids` has been enqueued and `logits` (a row a request, in
+        that order) will hold its result. Stages the pass after it; chooses the tokens; and, where
+        they can be chosen on the device, enqueues the staged pass with the tokens fed from device
+        memory before the host waits for them. A request that ended or was cancelled since the pass
+        was enqueued has a row nobody reads."""
+        try:
+            rows = [i for i, r in enumerate(rids) if r in self.entries and self.entries[r].running]
+            producing = [rids[i] for i in rows]
+            whole = len(producing) == len(rids)
+            if whole:
+                self._stage_next([(r, 1) for r in rids], producing)
+            tokens = None
+            if whole and self.staged is not None and self.options.run_ahead and hasattr(self.engine, "step_prepared"):
+                chosen = self._choose_on_device(logits, producing, rows)
+                if chosen is not None:
+                    import torch
+
+                    if self._token_host is None or self._token_host.numel() < chosen.numel():
+                        self._token_host = torch.empty((max(256, chosen.numel()),), dtype=torch.int32).pin_memory()
+                        self._token_event = torch.cuda.Event()
+                    self._token_host[: chosen.numel()].copy_(chosen, non_blocking=True)
+                    self._token_event.record()
+                    next_rids, handle = self.staged
+                    self.staged = None
+                    ahead_logits = self.engine.step_prepared(handle, ids_device=chosen)     # enqueued behind the copy
+                    self.staged_passes += 1
+                    self.ahead_passes += 1
+                    self.passes += 1
+                    self.ahead = (next_rids, ahead_logits)
+                    self._token_event.synchronize()                                         # the pass just enqueued runs meanwhile
+                    host = self._token_host[: chosen.numel()].tolist()
+                    tokens = [host[i] for i in rows]
+            if tokens is None:
+                tokens = self._choose(logits, producing, rows)
+        except Exception as e:                      # the pass failed: every running request ends
+            return self._fail_pass(events, e)
+        return self._give(events, producing, tokens)
 
     def _fail_pass(self, events, e) -> List[Event]:
+        self.ahead = None                           # a pass on its way is left to finish; nobody reads its rows
         staged, self.staged = self.staged, None
         if staged is not None:
             self._discard(staged[1])
@@ -336,9 +385,13 @@ class Scheduler:
         try:
             logits = self.engine.step(entries)
             self.passes += 1
-            self._stage_next(pass_, producing)
-            tokens = self._choose(logits, producing)
         except Exception as e:                      # the pass failed: every running request ends
+            return self._fail_pass(events, e)
+        if len(producing) == len(pass_):
+            return self._after_launch(events, producing, logits)        # every request of the pass gets a token: a row each, in order
+        try:
+            tokens = self._choose(logits, producing)
+        except Exception as e:
             return self._fail_pass(events, e)
         return self._give(events, producing, tokens)
 
@@ -358,24 +411,45 @@ class Scheduler:
         return None
 
     # ------------------------------------------------------------------ choosing tokens
-    def _choose(self, logits, producing: List[int]) -> List[int]:
+    def _choose_on_device(self, logits, producing: List[int], rows: List[int]):
+        """The chosen tokens as an int32 device tensor, a token a row of `logits` (rows outside `rows`
+        belong to nobody and get the largest logit), enqueued and not waited for; None where the
+        choice needs the host (filters, penalties) or the logits are not on a device."""
+        if not producing or not getattr(logits, "is_cuda", False):
+            return None
+        entries = [self.entries[rid] for rid in producing]
+        if not all(e.request.sampling.on_device() for e in entries):
+            return None
+        import torch
+
+        from .. import kernels as K
+
+        if all(e.request.sampling.is_greedy() for e in entries):
+            return K.sample(logits)
+        n = int(logits.shape[0])
+        temps, us = [0.0] * n, [0.0] * n
+        for i, e in zip(rows, entries):
+            temps[i] = max(0.0, e.request.sampling.temperature)
+            us[i] = e.sampler.uniform() if temps[i] > 0 else 0.0
+        host = torch.tensor([temps, us], dtype=torch.float32).pin_memory()
+        dev = host.to(logits.device, non_blocking=True)
+        self._sample_inputs = host                  # pinned memory must outlive its copy
+        return K.sample(logits, dev[0], dev[1])
+
+    def _choose(self, logits, producing: List[int], rows: Optional[List[int]] = None) -> List[int]:
         """One token per producing request: on the device when only the logits decide (greedy
         without penalties, or a plain temperature; engine.rs:584-597), else on the host in
-        64-bit with the request's own sampler (engine.rs:599-616)."""
+        64-bit with the request's own sampler (engine.rs:599-616). `rows` names each request's
+        row of `logits` (by default row i is request i's)."""
         if not producing:
             return []
+        rows = list(range(len(producing))) if rows is None else rows
+        chosen = self._choose_on_device(logits, producing, rows)
+        if chosen is not None:
+            host = chosen.cpu().tolist()
+            return [host[i] for i in rows]
         entries = [self.entries[rid] for rid in producing]
-        if getattr(logits, "is_cuda", False) and all(e.request.sampling.on_device() for e in entries):
-            import torch
-
-            from .. import kernels as K
-
-            if all(e.request.sampling.is_greedy() for e in entries):
-                return K.sample(logits).cpu().tolist()
-            temps = [max(0.0, e.request.sampling.temperature) for e in entries]
-            us = [e.sampler.uniform() if t > 0 else 0.0 for e, t in zip(entries, temps)]
-            host = torch.tensor([temps, us], dtype=torch.float32).pin_memory()
-            dev = host.to(logits.device, non_blocking=True)
-            return K.sample(logits, dev[0], dev[1]).cpu().tolist()
-        rows = logits.detach().cpu().numpy() if hasattr(logits, "detach") else np.asarray(logits)
-        return choose_many([e.sampler for e in entries], rows, [e.sequence for e in entries], [e.prompt_len for e in entries])
+        table = logits.detach().cpu().numpy() if hasattr(logits, "detach") else np.asarray(logits)
+        if len(rows) != table.shape[0] or rows != list(range(table.shape[0])):
+            table = table[rows]
+        return choose_many([e.sampler for e in entries], table, [e.sequence for e in entries], [e.prompt_len for e in entries])

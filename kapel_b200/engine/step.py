@@ -231,18 +231,24 @@ class Engine:
             self.cache.abort(plan)
         return prepared
 
-    def step_prepared(self, prepared, ids) -> torch.Tensor:
+    def step_prepared(self, prepared, ids=None, ids_device=None) -> torch.Tensor:
         """Runs a staged pass with its token ids (one a sequence, in the staged order); logits as
-        `step` returns them, every row wanted."""
+        `step` returns them, every row wanted. The ids are a list on the host, or `ids_device`: an
+        int32 tensor on the device that a kernel enqueued earlier fills (the tokens the pass before
+        chose), so that the pass can be enqueued before the host has seen them."""
         plan = prepared[0]
         vocab = self.spec.vocab_size
         try:
-            if len(ids) != plan.rows:
-                raise ValueError(f"{len(ids)} tokens for a staged pass of {plan.rows}")
-            for t in ids:
-                if not 0 <= int(t) < vocab:
-                    raise ValueError(f"token {t} is outside the vocabulary (0..{vocab - 1})")
-            logits = self.graphs.run_prepared(prepared, ids)
+            if ids_device is not None:
+                if ids_device.dtype != torch.int32 or ids_device.numel() < plan.rows or ids_device.device != self.device:
+                    raise ValueError(f"device ids {tuple(ids_device.shape)} {ids_device.dtype} for a staged pass of {plan.rows}")
+            else:
+                if len(ids) != plan.rows:
+                    raise ValueError(f"{len(ids)} tokens for a staged pass of {plan.rows}")
+                for t in ids:
+                    if not 0 <= int(t) < vocab:
+                        raise ValueError(f"token {t} is outside the vocabulary (0..{vocab - 1})")
+            logits = self.graphs.run_prepared(prepared, ids, ids_device)
         except Exception:
             self.cache.abort(plan)
             raise

@@ -182,6 +182,54 @@ def test_passes_staged_ahead_give_the_same_tokens_and_hold_no_page_afterwards(fo
     assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
 
 
+@pytest.mark.parametrize("temperature", [0.0, 0.8])
+def test_passes_enqueued_ahead_of_the_host_give_the_same_tokens(folders, temperature):
+    """Where the tokens are chosen on the device, the pass after is fed them from device memory and
+    enqueued before the host has read them. The tokens are those of a scheduler that waits for every
+    token first; a request that meets its end-of-sequence token while the pass after it is already
+    on its way ends there (the row that pass computed for it is dropped), one that is cancelled and
+    one that joins late change the running set in mid-flight, and no page is lost."""
+    import kapel_b200
+    from kapel_b200.engine.scheduler import Request
+    from kapel_b200.sampling import Sampling
+
+    raw, _ = TINY["B"]
+    rng = np.random.default_rng(31)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (20, 31, 9, 14)]
+    model = kapel_b200.Model(str(folders["B"]), dtype="f32", max_tokens_cached=1024, max_sequences=8)
+
+    def run(run_ahead, eos):
+        sched = model.scheduler(max_pass_tokens=64, run_ahead=run_ahead)
+        def request(i, **kw):
+            return Request(prompts[i], sampling=Sampling(temperature=temperature, seed=5 + i), max_tokens=40, **kw)
+        ids = [sched.add(request(0)), sched.add(request(1, eos_ids=eos)), sched.add(request(2))]
+        out = {r: [] for r in ids}
+        passes = 0
+        while sched.has_work():
+            passes += 1
+            if passes == 12:
+                ids.append(sched.add(request(3)))
+                out[ids[-1]] = []
+            if passes == 25:
+                sched.cancel(ids[2])
+            for ev in sched.step():
+                assert ev.finish != "error", ev.error
+                if ev.token is not None:
+                    out[ev.id].append(ev.token)
+            model.engine.cache.check()
+        assert model.engine.cache.free_pages() == model.engine.cache.total_pages()
+        return [out[r] for r in ids], sched
+
+    plain, waited = run(False, [])
+    assert waited.ahead_passes == 0 and waited.staged_passes > 10
+    eos = [plain[1][17]]
+    want, _ = run(False, eos)
+    got, sched = run(True, eos)
+    assert got == want
+    assert len(got[1]) == want[1].index(eos[0]) + 1 < 40 and len(got[0]) == 40 and len(got[3]) == 40 and 0 < len(got[2]) < 40
+    assert sched.ahead_passes > 10, "decode passes were enqueued ahead of the host"
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(folders, dtype):
     """A one-token prompt, then every token one by one up to the model's limit: first tokens of a
