@@ -585,26 +585,26 @@ __device__ __forceinline__ void atp_mma_ts(uint32_t d_tmem, uint32_t a_tmem, uin
 }
 
 constexpr int ATP_ROWS = 256;                                   // rows a tile of the pair kernel
-// Twenty warps: the single-block kernel's roles in warps 0-11, and a second group of eight softmax warps
-// (12-19). The first group takes the even tiles, the second the odd ones: while one group waits for its
-// scores, its TMEM loads and stores or its partner warp, the other keeps the special-function unit busy.
-constexpr int ATP_THREADS = 640;
+// Twenty-one warps: the single-block kernel's roles in warps 0-12, and eight more softmax warps (13-20):
+// the four warps of a quarter of the rows take 32 keys of a step each.
+constexpr int ATP_THREADS = 672;
+
+constexpr int ATP_KEYS = 128;                                   // keys a step of the pair kernel: one product takes them all
 
 template <int HD> struct AtpCfg {
     static constexpr int NBOX = HD / 64;                        // chunks of 64 elements along the head
-    static constexpr int SLOT_BYTES = AT_KEYS * HD;             // a block's half of a key tile, or of a value tile
-    static constexpr int K_SLOTS = HD == 256 ? 4 : 6;
-    static constexpr int V_SLOTS = HD == 256 ? 5 : 8;
+    static constexpr int SLOT_BYTES = ATP_KEYS * HD;            // a block's half of a key tile (64 keys), or of a value tile (half the head)
+    static constexpr int K_SLOTS = HD == 256 ? 2 : 4;
+    static constexpr int V_SLOTS = HD == 256 ? 3 : 4;          // a value slot is held until its P V product is complete, longer than a key slot
     static constexpr int SLOTS = K_SLOTS + V_SLOTS;
-    // Q lies in shared memory here (a block has room: its slots are half the single kernel's), which
-    // leaves TMEM for four S buffers: the chain scores -> softmax -> P V -> "S may be written again"
-    // is then four tiles long instead of two, and the score products no longer wait for it.
-    static constexpr int S_BUFS = 4;
+    // Q lies in shared memory here (the A operand of the score products), which leaves TMEM for O and
+    // S buffers of 128 keys: a score product of 128 keys costs the tensor cores what one of 64 does.
+    static constexpr int S_BUFS = (512 - HD) / ATP_KEYS;        // 2 at head size 256, 3 at 128
     static constexpr int Q_BYTES = AT_ROWS * HD * 2;
     static constexpr int COL_O = 0, COL_S = HD;
     static constexpr int TMEM_COLS = 512;
-    static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024 /* alignment */ + 384 /* barriers */ + 2048 /* row sums */;
-    static_assert(HD + S_BUFS * AT_KEYS <= TMEM_COLS, "O and the S buffers outgrew TMEM");
+    static constexpr int SMEM = Q_BYTES + SLOTS * SLOT_BYTES + 1024 /* alignment */ + 384 /* barriers */;
+    static_assert(HD + S_BUFS * ATP_KEYS <= TMEM_COLS, "O and the S buffers outgrew TMEM");
     static_assert((2 * SLOTS + 3 * S_BUFS + 1) * 8 + 8 <= 384, "the barriers outgrew their room");
     static_assert(SMEM <= 232448, "more shared memory than a block can have");
 };
@@ -613,22 +613,23 @@ template <int HD>
 __global__ void __cluster_dims__(2, 1, 1) __launch_bounds__(ATP_THREADS, 1)
 attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMap map_k, const __grid_constant__ CUtensorMap map_v) {
     using C = AtpCfg<HD>;
-    constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS;
+    constexpr int NBOX = C::NBOX, NS = C::SLOTS, KS = C::K_SLOTS, VS = C::V_SLOTS, SB = C::S_BUFS;
     constexpr uint32_t PAGE_FULL = NBOX * 2048u;                 // a page's keys (or values) of one kv head, both blocks' halves
     constexpr uint32_t PAGE_HALF = PAGE_FULL / 2;                // a block's half of a page of values
     extern __shared__ unsigned char at_smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)at_smem_raw + 1023) & ~(uintptr_t)1023);
-    constexpr int SB = C::S_BUFS;
     unsigned char* q_smem = smem;                                // [chunk][128 rows][128 bytes], 128-byte swizzle
     unsigned char* ring = smem + C::Q_BYTES;
     uint64_t* full = reinterpret_cast<uint64_t*>(ring + NS * C::SLOT_BYTES);    // [NS] the first block's: both halves of a slot have landed
     uint64_t* empty = full + NS;                                 // [NS] the product that read a slot is complete (in both blocks)
     uint64_t* s_full = empty + NS;                               // [SB] S complete (in both blocks)
-    uint64_t* p_full = s_full + SB;                              // [SB] the first block's: P written by 16 softmax warps, 8 of each block
+    uint64_t* p_full = s_full + SB;                              // [SB] the first block's: P written by the 32 softmax warps of both
     uint64_t* s_free = p_full + SB;                              // [SB] the first block's: the product that read P is complete
     uint64_t* o_full = s_free + SB;                              // [1] O complete (in both blocks)
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(o_full + 1);
-    float* l_part = reinterpret_cast<float*>(ring + NS * C::SLOT_BYTES + 384);   // [4][128] sum p by row: a share from each softmax warp of a quarter
+    // [4][128] sum p by row, a share from each softmax warp of a quarter: over the start of Q, which nothing
+    // reads any more when the softmax warps have seen the last scores complete
+    float* l_part = reinterpret_cast<float*>(q_smem);
 
     const int tid = threadIdx.x, warp = tid >> 5, lane = tid & 31;
     uint32_t rank;
@@ -656,12 +657,13 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
             }
         return;
     }
-    const int k_begin = klo / AT_KEYS * AT_KEYS;
-    const int n_tiles = (khi - k_begin + AT_KEYS - 1) / AT_KEYS;
+    const int k_begin = klo / ATP_KEYS * ATP_KEYS;
+    const int n_tiles = (khi - k_begin + ATP_KEYS - 1) / ATP_KEYS;
 
     if (tid == 0) {
-        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, 2); at_mbar_init(empty + s, 1); }
-        for (int b = 0; b < SB; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 16); at_mbar_init(s_free + b, 1); }
+        // a key slot is filled by two warps of each block, a value slot by one of each
+        for (int s = 0; s < NS; ++s) { at_mbar_init(full + s, s < KS ? 4 : 2); at_mbar_init(empty + s, 1); }
+        for (int b = 0; b < SB; ++b) { at_mbar_init(s_full + b, 1); at_mbar_init(p_full + b, 32); at_mbar_init(s_free + b, 1); }
         at_mbar_init(o_full, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
@@ -701,18 +703,20 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
     at_fence_after();
     bool failed = false;
 
-    if (warp == 0 || warp == AT_WARP_V) {
+    if (warp == 0 || warp == AT_WARP_V || warp == AT_WARP_K2) {
         // ---------------------------------------------------------------- pages and boxes, this block's halves
-        // Asking TMA for a box keeps the asking warp busy for more than a hundred clocks, so the keys
-        // and the values have a warp each.
-        const int half = warp == 0 ? 0 : 1;                      // keys, or values
-        // Keys: the first block brings keys 0-31 of a step (pages 0 and 1 of its four), the second keys
-        // 32-63, laid out [chunk][32 keys]: eight-key groups 1 KB apart. Values: every page's 16 keys,
-        // this block's half of the head's chunks, [page][chunk][16 keys]. A group without a page
-        // (before the window, past the end) is cleared instead when it holds values.
+        // A step is 128 keys: eight pages of 16. Keys: the first block brings keys 0-63 of a step (pages
+        // 0-3), the second keys 64-127, each with two warps (two pages a warp), laid out [chunk][64
+        // keys]: eight-key groups 1 KB apart. Values: every page's 16 keys, this block's half of the
+        // head's chunks, [page][chunk][16 keys], one warp. A group without a page (before the window,
+        // past the end) is cleared instead when it holds values. Asking TMA for a box keeps the asking
+        // warp busy for more than a hundred clocks: hence three warps.
+        const int half = warp == AT_WARP_V ? 1 : 0;              // keys, or values
+        const int key_half = warp == AT_WARP_K2 ? 1 : 0;         // of this block's four pages of keys: 0, 1 or 2, 3
+        // The pages of four steps are looked up at once, lane 8 t + sub for keys 16 sub .. of the batch's step t.
         auto lookup = [&](int kt_first) -> int {
-            const int kt = kt_first + (lane >> 2);
-            const int j = k_begin + kt * AT_KEYS + (lane & 3) * 16;
+            const int kt = kt_first + (lane >> 3);
+            const int j = k_begin + kt * ATP_KEYS + (lane & 7) * 16;
             int page = -1;
             if (kt < n_tiles && j < khi && j + 16 > klo) {
                 const int lp = max(j, klo) / p.page_size;
@@ -723,57 +727,57 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
         };
         int pages_now = 0, pages_next = lookup(0);
         for (int kt = 0; kt < n_tiles && !failed; ++kt) {
-            if ((kt & 7) == 0) { pages_now = pages_next; pages_next = lookup(kt + 8); }
-            const int j0 = k_begin + kt * AT_KEYS;
-            const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 7) * 4 + (lane & 3));
-            const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFu;       // bit sub: group sub has a page
+            if ((kt & 3) == 0) { pages_now = pages_next; pages_next = lookup(kt + 4); }
+            const int j0 = k_begin + kt * ATP_KEYS;
+            const int page = __shfl_sync(0xffffffffu, pages_now, (kt & 3) * 8 + (lane & 7));
+            const uint32_t have = __ballot_sync(0xffffffffu, page >= 0) & 0xFFu;      // bit sub: group sub has a page
             const int live = __popc(have);
-            {
-                const int s = half == 0 ? kt % KS : KS + kt % VS;
-                const int round = half == 0 ? kt / KS : kt / VS;
-                bool ok = true;
-                if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
-                if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
-                unsigned char* dst = ring + s * C::SLOT_BYTES;
-                const uint32_t bar = at_saddr(full + s) & AT_PEER_MASK;          // the first block's barrier
-                if (half == 1 && live < 4) {
-                    for (int sub = 0; sub < 4; ++sub) {
-                        if (have & (1u << sub)) continue;
-                        uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_HALF);
-                        for (int e = lane; e < (int)(PAGE_HALF / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
-                    }
-                    at_fence_async_smem();
-                    __syncwarp();
+            const int s = half == 0 ? kt % KS : KS + kt % VS;
+            const int round = half == 0 ? kt / KS : kt / VS;
+            bool ok = true;
+            if (lane == 0) ok = at_mbar_wait(empty + s, ((uint32_t)round & 1u) ^ 1u);
+            if (!__shfl_sync(0xffffffffu, ok ? 1 : 0, 0)) { failed = true; break; }
+            unsigned char* dst = ring + s * C::SLOT_BYTES;
+            const uint32_t bar = at_saddr(full + s) & AT_PEER_MASK;              // the first block's barrier
+            if (half == 1 && live < 8) {
+                for (int sub = 0; sub < 8; ++sub) {
+                    if (have & (1u << sub)) continue;
+                    uint4* z = reinterpret_cast<uint4*>(dst + sub * PAGE_HALF);
+                    for (int e = lane; e < (int)(PAGE_HALF / 16); e += 32) z[e] = make_uint4(0u, 0u, 0u, 0u);
                 }
-                if (lane == 0) {
-                    // one arrival a block: the first block's carries the bytes both will bring
-                    // (with a release only when this block cleared something the first block's products will read)
-                    if (rank == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_FULL);
-                    else if (half == 1 && live < 4) atp_arrive_on_first(full + s);
-                    else atp_arrive_on_first_relaxed(full + s);
-                }
+                at_fence_async_smem();
                 __syncwarp();
-                if (half == 0) {
-                    // this block's two pages of keys: a box of 16 keys x 64 elements a lane, [chunk][page][16 keys]
-                    const int sub_local = (lane / NBOX) & 1, bx = lane % NBOX;
-                    const int sub = (int)rank * 2 + sub_local;
-                    const int pg = __shfl_sync(0xffffffffu, page, sub);
-                    if (lane < 2 * NBOX && pg >= 0) {
-                        const int j = j0 + sub * 16;
-                        const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
-                        atp_tma_box(at_saddr(dst) + (uint32_t)(bx * 2 + sub_local) * 2048u, &map_k, bx * 64, row, bar);
-                    }
-                } else if (lane < 4 && page >= 0) {              // values: one copy a page, this block's chunks
-                    const int j = j0 + lane * 16;
-                    const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
-                    atp_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_HALF, &map_v, row, (int)rank * (NBOX / 2), bar);
+            }
+            if (lane == 0) {
+                // One arrival a warp. The first block's first key warp and its value warp carry the bytes that
+                // all will bring; the second block's arrive with a release only when they cleared something
+                // the first block's products will read.
+                if (rank == 0 && key_half == 0) at_mbar_expect_tx(full + s, (uint32_t)live * PAGE_FULL);
+                else if (rank == 0) at_mbar_arrive(full + s);
+                else if (half == 1 && live < 8) atp_arrive_on_first(full + s);
+                else atp_arrive_on_first_relaxed(full + s);
+            }
+            __syncwarp();
+            if (half == 0) {
+                // this warp's two pages of keys: a box of 16 keys x 64 elements a lane, [chunk][page][16 keys]
+                const int sub_local = 2 * key_half + ((lane / NBOX) & 1), bx = lane % NBOX;
+                const int sub = (int)rank * 4 + sub_local;
+                const int pg = __shfl_sync(0xffffffffu, page, sub);
+                if (lane < 2 * NBOX && pg >= 0) {
+                    const int j = j0 + sub * 16;
+                    const int row = (pg * p.hkv + kvh) * p.page_size + j % p.page_size;
+                    atp_tma_box(at_saddr(dst) + (uint32_t)(bx * 4 + sub_local) * 2048u, &map_k, bx * 64, row, bar);
                 }
+            } else if (lane < 8 && page >= 0) {                  // values: one copy a page, this block's chunks
+                const int j = j0 + lane * 16;
+                const int row = (page * p.hkv + kvh) * p.page_size + j % p.page_size;
+                atp_tma_page(at_saddr(dst) + (uint32_t)lane * PAGE_HALF, &map_v, row, (int)rank * (NBOX / 2), bar);
             }
         }
     } else if (warp == 1) {
         // ---------------------------------------------------------------- the score products of both blocks, from one lane of the first
         if (lane == 0 && rank == 0) {
-            constexpr uint32_t IDESC_S = at_idesc(ATP_ROWS, AT_KEYS, false);
+            constexpr uint32_t IDESC_S = at_idesc(ATP_ROWS, ATP_KEYS, false);
             const uint32_t ring_addr = at_saddr(ring);
             const uint32_t q_addr = at_saddr(q_smem);
             for (int kt = 0; kt < n_tiles; ++kt) {               // S[kt % SB] = Q K(kt)^T
@@ -783,11 +787,11 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                 if (kt >= SB && !at_mbar_wait(s_free + b, (uint32_t)(kt / SB - 1) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t k_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);
+                const uint32_t d_tmem = tmem + (uint32_t)(C::COL_S + b * ATP_KEYS);
 #pragma unroll
                 for (int bx = 0; bx < NBOX; ++bx) {
                     const uint64_t adesc = at_desc(q_addr + bx * (AT_ROWS * 128), 16, 1024);        // 64 elements of the 128 rows
-                    const uint64_t bdesc = at_desc(k_addr + bx * (AT_KEYS / 2 * 128), 16, 1024);   // this chunk's 32 keys a block
+                    const uint64_t bdesc = at_desc(k_addr + bx * (ATP_KEYS / 2 * 128), 16, 1024);  // this chunk's 64 keys a block
 #pragma unroll
                     for (int kk = 0; kk < 4; ++kk)
                         atp_mma_ss(d_tmem, adesc + (uint64_t)(kk * 2), bdesc + (uint64_t)(kk * 2), IDESC_S, (bx | kk) != 0 ? 1u : 0u);
@@ -808,24 +812,22 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                 if (!at_mbar_wait(p_full + b, (uint32_t)(kt / SB) & 1u)) { failed = true; break; }
                 at_fence_after();
                 const uint32_t v_addr = ring_addr + (uint32_t)s * C::SLOT_BYTES;
-                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * AT_KEYS);          // P lies over its S
+                const uint32_t a_tmem = tmem + (uint32_t)(C::COL_S + b * ATP_KEYS);         // P lies over the first half of its S
 #pragma unroll
-                for (int kk = 0; kk < 4; ++kk) {
+                for (int kk = 0; kk < ATP_KEYS / 16; ++kk) {
                     // keys 16 kk ..: page kk, its two eight-key groups 1 KB apart, this block's chunks 2 KB apart
                     const uint64_t bdesc = at_desc(v_addr + (uint32_t)kk * PAGE_HALF, 2048, 1024);
                     atp_mma_ts(tmem + C::COL_O, a_tmem + (uint32_t)(kk * 8), bdesc, IDESC_O, (kt | kk) != 0 ? 1u : 0u);
                 }
                 atp_commit_both(empty + s);
-                atp_commit_here(s_free + b);                     // P has been read: the scores of tile kt + 2 may land
+                atp_commit_here(s_free + b);                     // P has been read: the scores of tile kt + SB may land
             }
             if (!failed) atp_commit_both(o_full);
         }
-    } else if ((warp >= 2 && warp < 10) || warp >= 12) {
-        // ---------------------------------------------------------------- softmax and epilogue, half a row a thread
+    } else if ((warp >= 2 && warp < 10) || warp >= 13) {
+        // ---------------------------------------------------------------- softmax and epilogue: a row's 32 keys of a step a thread
         const int quarter = warp & 3;
-        const int grp = warp >= 12 ? 1 : 0;                      // even tiles, or odd tiles
-        const int half = ((warp >= 12 ? warp - 12 : warp - 2) >> 2);    // keys 0-31 of a tile, or 32-63
-        const int share = grp * 2 + half;                        // which of the quarter's four warps this is
+        const int share = warp >= 13 ? 2 + ((warp - 13) >> 2) : (warp - 2) >> 2;    // which of the quarter's four warps: keys 32 share .. of a step
         const int r = quarter * 32 + lane;                       // the TMEM lane
         const int R = (int)rank * AT_ROWS + r;                   // the row of the tile
         const bool own = R < rows_all;
@@ -835,16 +837,15 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
         const int lo_max = __reduce_max_sync(0xffffffffu, lo), hi_min = __reduce_min_sync(0xffffffffu, hi);
         const uint32_t lanes = tmem + ((uint32_t)(quarter * 32) << 16);
         const float c1 = p.scale / p.cap, c2 = p.cap * 1.4426950408889634f;
-        const int pair_bar = 2 + grp * 4 + quarter;              // the named barrier of this warp and its partner
         float l = 0.f;
-        for (int kt = grp; kt < n_tiles; kt += 2) {
+        for (int kt = 0; kt < n_tiles; ++kt) {
             const int b = kt % SB;
-            const int j0 = k_begin + kt * AT_KEYS + half * 32;
+            const int j0 = k_begin + kt * ATP_KEYS + share * 32;
             if (!__all_sync(0xffffffffu, at_mbar_wait(s_full + b, (uint32_t)(kt / SB) & 1u))) { failed = true; break; }
             at_fence_after();
             uint32_t sv[32], pr[16];
             const bool edge = j0 < lo_max || j0 + 32 > hi_min;
-            at_ld32(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 32), sv);
+            at_ld32(lanes + (uint32_t)(C::COL_S + b * ATP_KEYS + share * 32), sv);
             asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
             float la = 0.f, lb = 0.f;
 #pragma unroll
@@ -861,8 +862,10 @@ attention_tc_pair_kernel(const AttTcParams p, const __grid_constant__ CUtensorMa
                 pr[j >> 1] = at_pack(p0, p1);
             }
             l += la + lb;
-            asm volatile("bar.sync %0, 64;" ::"r"(pair_bar) : "memory");          // the two warps have read their scores
-            at_st16(lanes + (uint32_t)(C::COL_S + b * AT_KEYS + half * 16), pr);
+            // P (64 columns) lies over the scores of keys 0-63: the quarter's four warps have all read
+            // theirs before any of them stores
+            asm volatile("bar.sync %0, 128;" ::"r"(2 + quarter) : "memory");
+            at_st16(lanes + (uint32_t)(C::COL_S + b * ATP_KEYS + share * 16), pr);
             asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory");
             at_fence_before();
             __syncwarp();
@@ -978,13 +981,17 @@ extern "C" int kb_attention_tc_takes(int hq, int hkv, int d, int page_size, floa
            hq % hkv == 0 && hq / hkv <= AT_ROWS;
 }
 
-// Rows (token, query head of one kv head) a tile holds: 256 where pairs of blocks run it (head sizes
-// 128 and 256 with `pairs`), else 128.
-extern "C" int kb_attention_tc_rows(int d, int pairs) { return (pairs && (d == 128 || d == 256)) ? ATP_ROWS : AT_ROWS; }
+// Whether pairs of blocks run head size d. `pairs`: 0 never, 1 wherever such a kernel exists (128 and
+// 256), 2 where it measured faster than single blocks (256: 42 against 47 us for a prompt of 2,048 tokens
+// with 8 heads over 4; at 128 with 32 heads over 16 the pairs took 86 us, single blocks 79).
+static bool tc_pairs(int d, int pairs) { return pairs == 1 ? (d == 128 || d == 256) : (pairs == 2 && d == 256); }
+
+// Rows (token, query head of one kv head) a tile holds: 256 where pairs of blocks run it, else 128.
+extern "C" int kb_attention_tc_rows(int d, int pairs) { return tc_pairs(d, pairs) ? ATP_ROWS : AT_ROWS; }
 
 // Prompt portions; arguments as kb_attention_mma's with decode = 0, tiles of kb_attention_tc_rows(d,
 // pairs) rows. With slots > 1, `scratch` holds [rows, hq, slots, d + 2] floats and the caller merges it
-// (kb_attention_mma_combine). `pairs` 1: head sizes 128 and 256 run on pairs of blocks.
+// (kb_attention_mma_combine). `pairs` as kb_attention_tc_rows takes it.
 extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, const void* v_table, const int* block_table,
                                const int* row_count, const int* tile_entry, const int* tile_row0, const int* tile_nq, int tiles,
                                int rows, int hq, int hkv, int d, int page_size, int table_width, int n_pages, int window,
@@ -1006,7 +1013,7 @@ extern "C" int kb_attention_tc(void* out, const void* q, const void* k_table, co
     p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
     cudaStream_t s = (cudaStream_t)stream;
     if (d == 64) return launch_tc<64>(p, k_table, v_table, tiles, s);
-    if (pairs == 0) return d == 128 ? launch_tc<128>(p, k_table, v_table, tiles, s) : launch_tc<256>(p, k_table, v_table, tiles, s);
+    if (!tc_pairs(d, pairs)) return d == 128 ? launch_tc<128>(p, k_table, v_table, tiles, s) : launch_tc<256>(p, k_table, v_table, tiles, s);
     KB_REQUIRE(2 * hkv <= 65535, "attention_tc: %d kv heads is too many for one launch of pairs", hkv);
     return d == 128 ? launch_tc_pair<128>(p, k_table, v_table, tiles, s) : launch_tc_pair<256>(p, k_table, v_table, tiles, s);
 }

@@ -37,10 +37,9 @@ GEMM_SMALL = _os.environ.get("KAPEL_B200_GEMM_SMALL", "skinny")
 # also takes what the first does not: no soft cap, other head sizes).
 ATTENTION_PROMPT = _os.environ.get("KAPEL_B200_ATTENTION_PROMPT", "tcgen05")
 # Whether the tcgen05 prompt attention runs on pairs of blocks (tcgen05.mma.cta_group::2, 256 rows to one
-# tile of keys and values) at the head sizes that have such a kernel (128 and 256), or on single blocks.
-# Single blocks by default: the two measure the same at head size 256 (both are bound by their softmax
-# warps) and the pairs are slower at 128.
-ATTENTION_PAIRS = _os.environ.get("KAPEL_B200_ATTENTION_PAIRS", "0") == "1"
+# tile of 128 keys and values): 0 never, 1 at both head sizes that have such a kernel (128 and 256), 2 (the
+# default) where it measured faster than single blocks (256).
+ATTENTION_PAIRS = int(_os.environ.get("KAPEL_B200_ATTENTION_PAIRS", "2"))
 # Whether the kernels of a decode step are launched as programmatic dependents of one another, so
 # that a kernel sets up (and asks for its first weights) while the one before it finishes.
 PDL = _os.environ.get("KAPEL_B200_PDL", "1") == "1"

@@ -428,7 +428,7 @@ def test_paged_attention_mma_prompt_mode(kernel, hq, hkv, d, window, cap, split)
     q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, q_lens, seed=hq * 100 + d)
     scale = 1.0 / math.sqrt(d * 1.5)
     old = KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS
-    KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS = kernel.split("_")[0], kernel != "tcgen05_single"
+    KK.ATTENTION_PROMPT, KK.ATTENTION_PAIRS = kernel.split("_")[0], (0 if kernel == "tcgen05_single" else 1)
     try:
         got = run_mma(q, kt, vt, bt, rc, q_lens, 16, window, scale, cap, False, split).double()
     finally:

@@ -78,3 +78,4 @@ def test_tcgen05_attention_says_what_it_takes(lib):
     refused(lib, lib.kb_attention_tc(*args, 0.1, 50.0, None, 1, None), "attention_tc", "split 96")
     assert lib.kb_attention_tc_rows(256, 1) == 256 and lib.kb_attention_tc_rows(128, 1) == 256
     assert lib.kb_attention_tc_rows(64, 1) == 128 and lib.kb_attention_tc_rows(256, 0) == 128
+    assert lib.kb_attention_tc_rows(256, 2) == 256 and lib.kb_attention_tc_rows(128, 2) == 128
