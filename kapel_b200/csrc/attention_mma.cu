@@ -819,8 +819,25 @@ attention_mma_combine_kernel(const AttMmaParams p) {
     __syncthreads();
     for (int i = threadIdx.x * 2; i < p.d; i += blockDim.x * 2) {      // d and the stride are even
         float a0 = 0.f, a1 = 0.f;
-#pragma unroll 4
-        for (int z = 0; z < nz; ++z) {
+        int z = 0;
+        // Sixteen slots' values are asked for before the first is used: with the one key of history a
+        // block a multiprocessor at batch 1 there are dozens of slots, and one load after the other
+        // each waited out its own trip to L2. The sums run in slot order either way.
+        for (; z + 16 <= nz; z += 16) {
+            float2 v[16];
+#pragma unroll
+            for (int j = 0; j < 16; ++j) v[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
+#pragma unroll
+            for (int j = 0; j < 16; ++j) { a0 = fmaf(cw[z + j], v[j].x, a0); a1 = fmaf(cw[z + j], v[j].y, a1); }
+        }
+        for (; z + 4 <= nz; z += 4) {
+            float2 v[4];
+#pragma unroll
+            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
+#pragma unroll
+            for (int j = 0; j < 4; ++j) { a0 = fmaf(cw[z + j], v[j].x, a0); a1 = fmaf(cw[z + j], v[j].y, a1); }
+        }
+        for (; z < nz; ++z) {
             const float2 v = *reinterpret_cast<const float2*>(base + (size_t)z * stride + i);
             a0 = fmaf(cw[z], v.x, a0);
             a1 = fmaf(cw[z], v.y, a1);
