@@ -785,9 +785,9 @@ __global__ void __launch_bounds__(128)
 attention_mma_combine_kernel(const AttMmaParams p) {
     extern __shared__ float cw[];                           // [slots] weights
     const int row = blockIdx.x, head = blockIdx.y;
+    const int count = p.row_count[row];                     // copied in before the step began: read ahead of the wait
     dependent_wait();
     dependent_trigger();
-    const int count = p.row_count[row];
     bf16* o = p.out + ((size_t)row * p.hq + head) * p.d;
     if (count <= 0) {
         for (int i = threadIdx.x; i < p.d; i += blockDim.x) o[i] = __float2bfloat16_rn(0.f);
@@ -800,13 +800,39 @@ attention_mma_combine_kernel(const AttMmaParams p) {
     if (nz == 1 && p.direct) return;
     const int stride = p.d + 2;
     const float* base = p.partial + (((size_t)row * p.hq + head) * p.slots + z0) * stride;
+    // The first sixteen slots' values are asked for before the weights are known: they do not depend
+    // on them, and so the kernel is the count's trip to memory and one more, not four in a row. With
+    // one key of history a block at batch 1 there are dozens of slots; the rest follow sixteen at a
+    // time. The sums run in slot order either way.
+    const int i0 = threadIdx.x * 2;                         // d and the stride are even
+    const bool mine = i0 < p.d;
+    float2 v[16];
+#pragma unroll
+    for (int j = 0; j < 16; ++j)
+        v[j] = (mine && j < nz) ? *reinterpret_cast<const float2*>(base + (size_t)j * stride + i0) : make_float2(0.f, 0.f);
     if (threadIdx.x < 32) {
         const int lane = threadIdx.x;
         float mx = -INFINITY;
-        for (int z = lane; z < nz; z += 32) mx = fmaxf(mx, base[(size_t)z * stride + p.d]);
+        float2 ml[4];                                       // (maximum, sum) of this lane's slots: up to 128 in registers
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int z = lane + 32 * j;
+            ml[j] = z < nz ? *reinterpret_cast<const float2*>(base + (size_t)z * stride + p.d) : make_float2(-INFINITY, 0.f);
+            mx = fmaxf(mx, ml[j].x);
+        }
+        for (int z = lane + 128; z < nz; z += 32) mx = fmaxf(mx, base[(size_t)z * stride + p.d]);
         mx = warp_max(mx);
         float denom = 0.f;
-        for (int z = lane; z < nz; z += 32) {
+#pragma unroll
+        for (int j = 0; j < 4; ++j) {
+            const int z = lane + 32 * j;
+            if (z < nz) {
+                const float w = (ml[j].x == -INFINITY) ? 0.f : __expf(ml[j].x - mx);
+                cw[z] = w;
+                denom += w * ml[j].y;
+            }
+        }
+        for (int z = lane + 128; z < nz; z += 32) {
             const float m = base[(size_t)z * stride + p.d];
             const float w = (m == -INFINITY) ? 0.f : __expf(m - mx);
             cw[z] = w;
@@ -817,30 +843,33 @@ attention_mma_combine_kernel(const AttMmaParams p) {
         for (int z = lane; z < nz; z += 32) cw[z] *= inv;
     }
     __syncthreads();
-    for (int i = threadIdx.x * 2; i < p.d; i += blockDim.x * 2) {      // d and the stride are even
+    for (int i = i0; i < p.d; i += blockDim.x * 2) {
         float a0 = 0.f, a1 = 0.f;
         int z = 0;
-        // Sixteen slots' values are asked for before the first is used: with the one key of history a
-        // block a multiprocessor at batch 1 there are dozens of slots, and one load after the other
-        // each waited out its own trip to L2. The sums run in slot order either way.
+        if (i == i0) {
+#pragma unroll
+            for (int j = 0; j < 16; ++j)
+                if (j < nz) { a0 = fmaf(cw[j], v[j].x, a0); a1 = fmaf(cw[j], v[j].y, a1); }
+            z = min(nz, 16);
+        }
         for (; z + 16 <= nz; z += 16) {
-            float2 v[16];
+            float2 u[16];
 #pragma unroll
-            for (int j = 0; j < 16; ++j) v[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
+            for (int j = 0; j < 16; ++j) u[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
 #pragma unroll
-            for (int j = 0; j < 16; ++j) { a0 = fmaf(cw[z + j], v[j].x, a0); a1 = fmaf(cw[z + j], v[j].y, a1); }
+            for (int j = 0; j < 16; ++j) { a0 = fmaf(cw[z + j], u[j].x, a0); a1 = fmaf(cw[z + j], u[j].y, a1); }
         }
         for (; z + 4 <= nz; z += 4) {
-            float2 v[4];
+            float2 u[4];
 #pragma unroll
-            for (int j = 0; j < 4; ++j) v[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
+            for (int j = 0; j < 4; ++j) u[j] = *reinterpret_cast<const float2*>(base + (size_t)(z + j) * stride + i);
 #pragma unroll
-            for (int j = 0; j < 4; ++j) { a0 = fmaf(cw[z + j], v[j].x, a0); a1 = fmaf(cw[z + j], v[j].y, a1); }
+            for (int j = 0; j < 4; ++j) { a0 = fmaf(cw[z + j], u[j].x, a0); a1 = fmaf(cw[z + j], u[j].y, a1); }
         }
         for (; z < nz; ++z) {
-            const float2 v = *reinterpret_cast<const float2*>(base + (size_t)z * stride + i);
-            a0 = fmaf(cw[z], v.x, a0);
-            a1 = fmaf(cw[z], v.y, a1);
+            const float2 u = *reinterpret_cast<const float2*>(base + (size_t)z * stride + i);
+            a0 = fmaf(cw[z], u.x, a0);
+            a1 = fmaf(cw[z], u.y, a1);
         }
         *reinterpret_cast<uint32_t*>(o + i) = am_pack(a0, a1);
     }
