@@ -86,7 +86,13 @@ template <typename T> struct Src {
 #pragma unroll
             for (int j = 0; j < 8; ++j) v += t[j];
         }
-        for (; s < splits; ++s) v += Elem<T>::load(p + (size_t)s * stride + i);
+        if (s < splits) {                                   // the last few, asked for together as well
+            float t[8];
+#pragma unroll
+            for (int j = 0; j < 8; ++j) t[j] = s + j < splits ? Elem<T>::load(p + (size_t)(s + j) * stride + i) : 0.f;
+#pragma unroll
+            for (int j = 0; j < 8; ++j) v += t[j];          // adding zero for an absent slice changes nothing
+        }
         return v;
     }
 };

@@ -77,20 +77,23 @@ __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__
     } else {
         ia = rotary + 2 * (i - half_r); ib = ia + 1; rotate = false;
     }
+    if (h >= hq && !write_kv) return;
+    if (h >= hq + hkv) rotate = false;                      // a value
+    // Everything this thread reads is asked for before anything is looked at, the line of the cache
+    // included: one trip to memory, where a test of the line first made it two.
+    float a = qkv.at(src + ia), b = qkv.at(src + ib);
+    const float2 cs = rotate ? cos_sin[(size_t)r * half_r + i] : make_float2(1.f, 0.f);
+    const int line = h >= hq ? lines[r] : 0;
     T* dst;
     if (h < hq) {
         dst = q_out + ((size_t)r * hq + h) * d;
     } else {
-        if (!write_kv) return;
-        const int line = lines[r];
         if (line < 0 || line >= table_lines) return;
         const bool is_key = h < hq + hkv;
         const int kvh = is_key ? h - hq : h - hq - hkv;
         dst = (is_key ? k_table : v_table) + kv_row(line, kvh, hkv, page_size) * d;
-        if (!is_key) rotate = false;
     }
-    float a = qkv.at(src + ia), b = qkv.at(src + ib);      // read only by the threads that write
-    if (rotate) rope_rotate(a, b, cos_sin[(size_t)r * half_r + i]);
+    if (rotate) rope_rotate(a, b, cs);
     Elem<T>::store(dst + ia, a);
     Elem<T>::store(dst + ib, b);
 }

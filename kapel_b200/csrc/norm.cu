@@ -206,6 +206,18 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
     __shared__ float scratch[32];
     const size_t base = (size_t)blockIdx.x * width;
     const int chunks = width >> 2;
+    // The norms' weights are constants: they are read ahead of the wait on the kernel before, so that
+    // after it there is one trip to memory (the slices and the residual) and no second or third.
+    uint2 wp[CPT], wn[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        wp[c] = wn[c] = make_uint2(0u, 0u);
+        if (ci < chunks) {
+            if (w_post != nullptr) wp[c] = *reinterpret_cast<const uint2*>(w_post + ci * 4);
+            if (w_next != nullptr) wn[c] = *reinterpret_cast<const uint2*>(w_next + ci * 4);
+        }
+    }
     dependent_wait();
     dependent_trigger();                                    // a few blocks with little to read: the next kernel may set up
     float4 b[CPT], r[CPT];
@@ -217,6 +229,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         r[c] = b[c];
         if (ci < chunks) {
             const float* src = parts + base + ci * 4;
+            r[c] = *reinterpret_cast<const float4*>(residual + base + ci * 4);    // in flight beside the slices
             float4 v = *reinterpret_cast<const float4*>(src);
             int s = 1;
             for (; s + 8 <= splits; s += 8) {
@@ -226,12 +239,15 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
 #pragma unroll
                 for (int j = 0; j < 8; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
             }
-            for (; s < splits; ++s) {
-                const float4 t = *reinterpret_cast<const float4*>(src + (size_t)s * stride);
-                v.x += t.x; v.y += t.y; v.z += t.z; v.w += t.w;
+            if (s < splits) {                               // the last few together as well; an absent slice adds zero
+                float4 t[8];
+#pragma unroll
+                for (int j = 0; j < 8; ++j)
+                    t[j] = s + j < splits ? *reinterpret_cast<const float4*>(src + (size_t)(s + j) * stride) : make_float4(0.f, 0.f, 0.f, 0.f);
+#pragma unroll
+                for (int j = 0; j < 8; ++j) { v.x += t[j].x; v.y += t[j].y; v.z += t[j].z; v.w += t[j].w; }
             }
             b[c] = v;
-            r[c] = *reinterpret_cast<const float4*>(residual + base + ci * 4);
             ss += v.x * v.x + v.y * v.y + v.z * v.z + v.w * v.w;
         }
     }
@@ -246,7 +262,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         const int ci = threadIdx.x + c * blockDim.x;
         if (ci < chunks) {
             if (w_post != nullptr) {
-                const uint2 uw = *reinterpret_cast<const uint2*>(w_post + ci * 4);
+                const uint2 uw = wp[c];
                 const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.x));
                 const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.y));
                 r[c].x += b[c].x * inv * (off_post + w0.x);
@@ -267,7 +283,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
     for (int c = 0; c < CPT; ++c) {
         const int ci = threadIdx.x + c * blockDim.x;
         if (ci < chunks) {
-            const uint2 uw = *reinterpret_cast<const uint2*>(w_next + ci * 4);
+            const uint2 uw = wn[c];
             const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.x));
             const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&uw.y));
             uint2 uo;
