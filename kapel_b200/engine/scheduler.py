@@ -190,6 +190,8 @@ class Scheduler:
         events: List[Event] = []
         if not self.waiting:                                # nobody to admit: nothing to count
             return events
+        if len(self.running) >= self.options.max_sequences or self.cache.free_slots() <= 0:
+            return events                                   # no slot to admit into either
         n_groups = len(self.cache.groups)
         promised = [0] * n_groups
         for rid in self.running:
@@ -292,7 +294,11 @@ class Scheduler:
         go on unless it meets an end-of-sequence or stop token, take the next pass's pages and
         write its inputs now, so that only the token ids remain to be filled in."""
         prepare = getattr(self.engine, "prepare_decode", None)
-        if prepare is None or self.waiting or len(producing) != len(pass_) or [r for r, _ in pass_] != self.running:
+        if prepare is None or len(producing) != len(pass_) or [r for r, _ in pass_] != self.running:
+            return
+        # A waiting request joins the next pass only if it can be admitted: with every slot taken it
+        # cannot be until a request ends, and a pass staged for a request that then ends is handled.
+        if self.waiting and len(self.running) < self.options.max_sequences and self.cache.free_slots() > 0:
             return
         for rid in producing:
             entry = self.entries[rid]

@@ -107,7 +107,17 @@ def _check(code: int) -> None:
         raise KernelError(library().kb_last_error().decode("utf-8", "replace"))
 
 
+# torch's current stream as a raw handle. The public route (torch.cuda.current_stream) builds a
+# Stream object and resolves the device each time, about 15 us a call, once a kernel: more host
+# time than everything else a launch does. torch's own C entry points give the same handle in
+# well under a microsecond; without them the public route stands.
+_RAW_STREAM = getattr(torch._C, "_cuda_getCurrentRawStream", None)
+_RAW_DEVICE = getattr(torch._C, "_cuda_getDevice", None)
+
+
 def _stream() -> ctypes.c_void_p:
+    if _RAW_STREAM is not None and _RAW_DEVICE is not None:
+        return ctypes.c_void_p(_RAW_STREAM(_RAW_DEVICE()))
     return ctypes.c_void_p(torch.cuda.current_stream().cuda_stream)
 
 

@@ -143,6 +143,31 @@ def test_a_staged_pass_runs_if_nothing_changed_and_gives_its_pages_back_if_somet
     assert eng.cache.free_pages() == eng.cache.total_pages()
 
 
+def test_passes_are_staged_while_a_waiting_request_has_no_slot_to_take():
+    """With every slot taken a waiting request cannot join until one ends, so the running ones' next
+    pass is staged all the same; when one ends the waiting request takes its slot and everybody's
+    tokens are what they would have been."""
+    rng = np.random.default_rng(11)
+    ps = prompts(rng, [5, 9, 7, 12])
+    lengths = [6, 14, 9, 8]
+    eng = StagingEngine(pages=64, max_sequences=2)
+    sched = Scheduler(eng, EngineOptions(max_pass_tokens=64, max_sequences=2))
+    rids = [sched.add(Request(p, max_tokens=n)) for p, n in zip(ps, lengths)]
+    staged_while_waiting = 0
+    out = {}
+    while sched.has_work():
+        waiting_before, staged_before = len(sched.waiting), eng.ran_staged
+        for ev in sched.step():
+            if ev.token is not None:
+                out.setdefault(ev.id, []).append(ev.token)
+        if waiting_before and eng.ran_staged > staged_before:
+            staged_while_waiting += 1
+    assert staged_while_waiting >= 5, staged_while_waiting
+    for rid, p, n in zip(rids, ps, lengths):
+        assert out[rid] == expected(p, n)
+    assert eng.cache.free_pages() == eng.cache.total_pages()
+
+
 def test_portions_under_a_token_budget_decodes_first():
     eng = FakeEngine(pages=32)
     sched = Scheduler(eng, EngineOptions(max_pass_tokens=7, max_sequences=8))
