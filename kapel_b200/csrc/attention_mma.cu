@@ -31,8 +31,12 @@
 //    kernel before them only where they first touch what it wrote.
 #include "common.cuh"
 #include "tensor_map.cuh"
+#include "timeline.cuh"
 
 namespace kb {
+
+KB_TIMELINE_ARRAY(attention)   // slots: kind 4 decoding attention (slots, window), kind 5 its merge
+
 
 typedef __nv_bfloat16 bf16;
 
@@ -556,7 +560,7 @@ constexpr int AD_STAGES = 3;
 template <int HD, int NB, bool FULL>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap map_k,
-                        const __grid_constant__ CUtensorMap map_v) {
+                        const __grid_constant__ CUtensorMap map_v KB_TL_PARAM) {
     extern __shared__ __align__(128) unsigned char am_smem[];
     const int d = p.d;
     const int ld = d + AM_PAD;
@@ -574,6 +578,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     uint64_t* bars = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + warp * AD_STAGES;
 
     const int kvh = blockIdx.y, slot = blockIdx.z;
+    KB_TL_ENTER(attention, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0, 4, p.slots, p.window);
     // Counts, tiles and block tables were copied in before the step began: they may be read ahead of
     // the wait on the kernel before this one, whose work the queries and the newest keys are.
     const AmTile x = am_tile_info(p, blockIdx.x, slot);
@@ -642,6 +647,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
         if (early[s]) load_tile(s, s);
     }
     dependent_wait();
+    KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     dependent_trigger();
     const int chunks = d / 8;
     for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
@@ -696,6 +702,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
 
     bool failed = false;
+    KB_TL_MARK(attention, 3, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);          // the loop over the keys begins
     for (int i = 0; warp + 4 * i < n_tiles; ++i) {
         const int tile = warp + 4 * i, stage = i % AD_STAGES;
         if (!am_mbar_wait(bars + stage, (uint32_t)(i / AD_STAGES) & 1u)) { failed = true; break; }
@@ -717,6 +724,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     }
     failed = __syncthreads_or(failed);
     if (failed) return;
+    KB_TL_MARK(attention, 4, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);          // and is done
 #pragma unroll
     for (int nb = 0; nb < NB; ++nb)
 #pragma unroll
@@ -775,6 +783,7 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
             if (c == 0) { dst[d] = mx; dst[d + 1] = l; }
         }
     }
+    KB_TL_LEAVE(attention, blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0, 0);
 }
 
 // out[row, head, :] = sum_z e^(m_z - M) acc_z / sum_z e^(m_z - M) l_z over the absolute slots the
@@ -782,11 +791,13 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
 // warp turns the slots' maxima and sums into weights, then every thread adds up its components
 // with independent loads.
 __global__ void __launch_bounds__(128)
-attention_mma_combine_kernel(const AttMmaParams p) {
+attention_mma_combine_kernel(const AttMmaParams p KB_TL_PARAM) {
     extern __shared__ float cw[];                           // [slots] weights
     const int row = blockIdx.x, head = blockIdx.y;
+    KB_TL_ENTER(attention, blockIdx.x == 0 && blockIdx.y == 0, 5, p.slots, p.window);
     const int count = p.row_count[row];                     // copied in before the step began: read ahead of the wait
     dependent_wait();
+    KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0);
     dependent_trigger();
     bf16* o = p.out + ((size_t)row * p.hq + head) * p.d;
     if (count <= 0) {
@@ -873,6 +884,7 @@ attention_mma_combine_kernel(const AttMmaParams p) {
         }
         *reinterpret_cast<uint32_t*>(o + i) = am_pack(a0, a1);
     }
+    KB_TL_LEAVE(attention, blockIdx.x == 0 && blockIdx.y == 0, 0);
 }
 
 
@@ -986,7 +998,7 @@ static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStr
     do {                                                                                                                       \
         if (smem > 48 * 1024)                                                                                                  \
             cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_dependent_if(p.rows <= DEPENDENT_ROWS, attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v);     \
+        launch_dependent_if(p.rows <= DEPENDENT_ROWS, attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v KB_TL_SLOT(attention, 4, q.slots, q.window));     \
     } while (0)
     if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true); else KB_DECODE(1, false); }
     else               { if (p.d == HD) KB_DECODE(2, true); else KB_DECODE(2, false); }
@@ -997,6 +1009,9 @@ static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStr
 }  // namespace kb
 
 using namespace kb;
+
+KB_TIMELINE_GETTER(attention)
+
 
 // Rows a tile may hold in each mode; the host cuts requests into tiles of rows / group tokens.
 extern "C" int kb_attention_mma_rows(int decode) { return decode ? 16 : AP_ROWS; }
@@ -1070,7 +1085,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
             if (int e2 = combine_smem(slots)) return e2;
             launch_dependent_if(false, attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
         } else {                                            // few (a decode step): a block each, for the latency
-            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p);
+            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p KB_TL_SLOT(attention, 5, p.slots, p.window));
         }
         return check_launch("attention_mma combine");
     }

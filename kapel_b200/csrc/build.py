@@ -28,6 +28,12 @@ HERE = Path(__file__).resolve().parent
 LIB_NAME = "libkapel_b200.so"
 ARCH_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a"]
 NVCC_FLAGS = ["-O3", "-std=c++17", "-lineinfo", "-Xcompiler", "-fPIC"]      # no fast-math: the 32-bit path is exact arithmetic
+# KAPEL_B200_TIMELINE=1: the library with time stamps compiled into the decoding kernels (timeline.cuh),
+# in a folder of its own beside the ordinary one. A measuring build: nothing else uses it.
+TIMELINE = os.environ.get("KAPEL_B200_TIMELINE") == "1"
+if TIMELINE:
+    NVCC_FLAGS = NVCC_FLAGS + ["-DKB_TIMELINE"]
+BUILD_FOLDER = "_build_timeline" if TIMELINE else "_build"
 
 
 def sources():
@@ -72,10 +78,10 @@ def build_dir() -> Path:
     env = os.environ.get("KAPEL_B200_BUILD_DIR")
     if env and _writable(Path(env)):
         return Path(env)
-    local = HERE / "_build"
+    local = HERE / BUILD_FOLDER
     if _writable(local):
         return local
-    fallback = Path(tempfile.gettempdir()) / f"kapel_b200-build-{os.getuid()}"
+    fallback = Path(tempfile.gettempdir()) / f"kapel_b200-{BUILD_FOLDER.strip('_')}-{os.getuid()}"
     if _writable(fallback):
         return fallback
     raise RuntimeError(f"kapel_b200: no folder to build in ({local} and {fallback} cannot be written)")
@@ -89,10 +95,10 @@ def _say(msg: str, verbose: bool) -> None:
 def ensure_built(verbose: bool = True, force: bool = False) -> Path:
     stamp = _stamp()
     # A library that an earlier call built anywhere it could is good if its stamp matches.
-    candidates = [HERE / "_build"]
+    candidates = [HERE / BUILD_FOLDER]
     if os.environ.get("KAPEL_B200_BUILD_DIR"):
         candidates.insert(0, Path(os.environ["KAPEL_B200_BUILD_DIR"]))
-    candidates.append(Path(tempfile.gettempdir()) / f"kapel_b200-build-{os.getuid()}")
+    candidates.append(Path(tempfile.gettempdir()) / f"kapel_b200-{BUILD_FOLDER.strip('_')}-{os.getuid()}")
     if not force:
         for d in candidates:
             lib, st = d / LIB_NAME, d / "stamp"
@@ -172,10 +178,10 @@ def _host_stamp() -> str:
 
 def ensure_host_built(verbose: bool = True, force: bool = False) -> Path:
     stamp = _host_stamp()
-    candidates = [HERE / "_build"]
+    candidates = [HERE / BUILD_FOLDER]
     if os.environ.get("KAPEL_B200_BUILD_DIR"):
         candidates.insert(0, Path(os.environ["KAPEL_B200_BUILD_DIR"]))
-    candidates.append(Path(tempfile.gettempdir()) / f"kapel_b200-build-{os.getuid()}")
+    candidates.append(Path(tempfile.gettempdir()) / f"kapel_b200-{BUILD_FOLDER.strip('_')}-{os.getuid()}")
     if not force:
         for d in candidates:
             lib, st = d / HOST_LIB_NAME, d / "stamp_host"

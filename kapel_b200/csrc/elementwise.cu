@@ -4,8 +4,12 @@
 // :1328 (here one kernel), rope_table :1092, rope_any :1545 and write_rows_any :1579 (here one
 // kernel), glu_any :2489, widen_16/narrow_16 :375,386.
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace kb {
+
+KB_TIMELINE_ARRAY(elementwise) // slots: kind 3 rotation and append (rows, slices)
+
 
 // ---------------------------------------------------------------------------------------
 // x[r, :] = table[ids[r], :] * scale, in 32-bit. An id outside the table gives a row of NaN.
@@ -58,12 +62,14 @@ template <typename TI, typename T>
 __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__ cos_sin,
                                    const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
                                    T* __restrict__ v_table, int rows, int hq, int hkv, int d, int rotary,
-                                   int write_kv, long long table_lines, int page_size) {
+                                   int write_kv, long long table_lines, int page_size KB_TL_PARAM) {
     const int half_d = d >> 1, half_r = rotary >> 1;
     const int heads = hq + 2 * hkv;
     const long long total = (long long)rows * heads * half_d;
     const long long idx = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    KB_TL_ENTER(elementwise, blockIdx.x == 0, 3, rows, qkv.splits);
     dependent_wait();
+    KB_TL_MARK(elementwise, 2, threadIdx.x == 0 && blockIdx.x == 0);
     dependent_trigger();
     if (idx >= total) return;
     const int i = (int)(idx % half_d);
@@ -96,6 +102,7 @@ __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__
     if (rotate) rope_rotate(a, b, cs);
     Elem<T>::store(dst + ia, a);
     Elem<T>::store(dst + ib, b);
+    KB_TL_LEAVE(elementwise, blockIdx.x == 0, 0);           // thread 0 of block 0 rotates a query: it never left early
 }
 
 // The same for bfloat16 in and out with the whole head rotated (rotary == d, d a multiple of 16):
@@ -275,6 +282,8 @@ extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int
     return check_launch("rope_table");
 }
 
+KB_TIMELINE_GETTER(elementwise)
+
 // qkv: `in_dt` (float32 or bfloat16), as `splits` slices `split_stride` elements apart that are
 // added up on the way in; q_out and the tables: `out_dt`.
 extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long split_stride, const float* cos_sin,
@@ -292,7 +301,7 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
 #define KB_ROPE(TI, T)                                                                                              \
     launch_dependent_if(rows <= DEPENDENT_ROWS, rope_append_kernel<TI, T>, dim3(blocks), dim3(256), 0, s, Src<TI>{(const TI*)qkv, splits, (size_t)split_stride}, \
                      (const float2*)cos_sin, lines, (T*)q_out, (T*)k_table, (T*)v_table, rows, hq, hkv, d, rotary, write_kv,       \
-                     table_lines, page_size > 0 ? page_size : 1)
+                     table_lines, page_size > 0 ? page_size : 1 KB_TL_SLOT(elementwise, 3, rows, splits))
     const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_table | (uintptr_t)v_table | (uintptr_t)cos_sin) & 15) == 0;
     if (in_dt == KB_DT_BF16 && out_dt == KB_DT_BF16 && splits == 1 && rotary == d && d % 16 == 0 && aligned) {
         const long long vec = (long long)rows * (hq + 2 * hkv) * (d / 16);

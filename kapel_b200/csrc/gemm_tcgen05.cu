@@ -27,8 +27,12 @@
 // barrier, frees its TMEM and returns.
 #include "common.cuh"
 #include "tensor_map.cuh"
+#include "timeline.cuh"
 
 namespace kb {
+
+KB_TIMELINE_ARRAY(gemm)        // slots: kind 0 the few-rows product [n, k], kind 1 the gated one
+
 
 typedef __nv_bfloat16 bf16;
 
@@ -473,7 +477,7 @@ template <int NP>
 __global__ void __launch_bounds__(TC_THREADS, 2)
 gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
                            void* __restrict__ c, int c_dt, float* __restrict__ partial, int m, int n, int k,
-                           int k_tiles_per_split, int epi, float cap) {
+                           int k_tiles_per_split, int epi, float cap KB_TL_PARAM) {
     constexpr int B_BYTES = NP * SK2_BK * 2;
     constexpr int STAGE = SK2_A_BYTES + (B_BYTES < 1024 ? 1024 : B_BYTES);        // stages stay 1024-byte aligned
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(SK2_BM >> 4) << 24);
@@ -492,6 +496,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     const int k_tiles_all = (k + SK2_BK - 1) / SK2_BK;
     const int kt0 = split * k_tiles_per_split;
     const int k_tiles = min(k_tiles_per_split, k_tiles_all - kt0);
+    KB_TL_ENTER(gemm, blockIdx.x == 0 && blockIdx.y == 0, 0, n, k);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < SK2_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
@@ -510,6 +515,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     dependent_wait();                                       // the activations are the kernel before's to finish
+    KB_TL_MARK(gemm, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0);
     if (threadIdx.x == 0) {
         for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt)
             tc_tma_load_2d(smem + kt * STAGE + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + kt);
@@ -537,6 +543,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
             for (int kt = 0; kt < k_tiles; ++kt) {
                 const int s = kt % SK2_STAGES;
                 if (!tc_mbar_wait(full + s, (uint32_t)(kt / SK2_STAGES) & 1u)) { failed = true; break; }
+                KB_TL_MARK(gemm, 3, kt == 0 && blockIdx.x == 0 && blockIdx.y == 0);          // the first tile has landed
                 tc_fence_after();
                 const uint32_t a_addr = tc_saddr(smem + s * STAGE);
                 const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + SK2_A_BYTES);
@@ -556,6 +563,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     } else {
         const int quarter = warp & 3;
         const bool complete = __all_sync(0xffffffffu, tc_mbar_wait(accum, 0u));
+        KB_TL_MARK(gemm, 4, warp == 2 && lane == 0 && blockIdx.x == 0 && blockIdx.y == 0);     // the sums are done
         dependent_trigger();
         if (!complete) {
             failed = true;
@@ -600,6 +608,7 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(COLS) : "memory");
     }
+    KB_TL_LEAVE(gemm, blockIdx.x == 0 && blockIdx.y == 0, 64);
 }
 
 // ---------------------------------------------------------------------------------------
@@ -621,7 +630,7 @@ template <int NP> struct SkGlu {
 template <int NP>
 __global__ void __launch_bounds__(TC_THREADS, 1)
 gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_constant__ CUtensorMap map_x,
-                       bf16* __restrict__ c, int m, int n, int k, int act) {
+                       bf16* __restrict__ c, int m, int n, int k, int act KB_TL_PARAM) {
     using G = SkGlu<NP>;
     constexpr int STAGES = G::STAGES, STAGE = G::STAGE;
     constexpr uint32_t IDESC = (1u << 4) | (1u << 7) | (1u << 10) | ((uint32_t)(NP >> 3) << 17) | ((uint32_t)(SK2_BM >> 4) << 24);
@@ -637,6 +646,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int n0 = blockIdx.x * SKG_ROWS;
     const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
+    KB_TL_ENTER(gemm, blockIdx.x == 0, 1, n, k);
 
     auto load_weights = [&](int kt) {
         const int s = kt % STAGES;
@@ -658,6 +668,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     dependent_wait();
+    KB_TL_MARK(gemm, 2, threadIdx.x == 0 && blockIdx.x == 0);
     if (threadIdx.x == 0)
         for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_rows(kt);
     tc_fence_before();
@@ -679,6 +690,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
             for (int kt = 0; kt < k_tiles; ++kt) {
                 const int s = kt % STAGES;
                 if (!tc_mbar_wait(full + s, (uint32_t)(kt / STAGES) & 1u)) { failed = true; break; }
+                KB_TL_MARK(gemm, 3, kt == 0 && blockIdx.x == 0);
                 tc_fence_after();
                 const uint32_t a_addr = tc_saddr(smem + s * STAGE);
                 const uint64_t adesc = tc_smem_desc(a_addr), bdesc = tc_smem_desc(a_addr + SK2_A_BYTES);
@@ -698,6 +710,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
     } else {
         const int quarter = warp & 3;                       // TMEM lanes 32 quarter ..: 0, 1 gates; 2, 3 ups
         const bool ok = __all_sync(0xffffffffu, tc_mbar_wait(accum, 0u));
+        KB_TL_MARK(gemm, 4, warp == 2 && lane == 0 && blockIdx.x == 0);
         dependent_trigger();
         if (!ok) failed = true;
         const int f = (quarter & 1) * 32 + lane;            // the output within the block's 64
@@ -752,6 +765,7 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         tc_fence_after();
         asm volatile("tcgen05.dealloc.cta_group::1.sync.aligned.b32 %0, %1;" ::"r"(tmem), "r"(COLS) : "memory");
     }
+    KB_TL_LEAVE(gemm, blockIdx.x == 0, 64);
 }
 
 template <int NP>
@@ -762,7 +776,7 @@ static int launch_skinny_glu(const CUtensorMap& map_w, const CUtensorMap& map_x,
         if (e != cudaSuccess) return fail("gemm_skinny_glu: cannot have %d bytes of shared memory: %s", SkGlu<NP>::SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    launch_dependent(gemm_skinny_glu_kernel<NP>, dim3((n + SKG_ROWS - 1) / SKG_ROWS), dim3(TC_THREADS), (size_t)SkGlu<NP>::SMEM, s, map_w, map_x, c, m, n, k, act);
+    launch_dependent(gemm_skinny_glu_kernel<NP>, dim3((n + SKG_ROWS - 1) / SKG_ROWS), dim3(TC_THREADS), (size_t)SkGlu<NP>::SMEM, s, map_w, map_x, c, m, n, k, act KB_TL_SLOT(gemm, 1, n, k));
     return check_launch("gemm_skinny_glu");
 }
 
@@ -804,7 +818,7 @@ static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
         attr_set = true;
     }
     dim3 grid((n + SK2_BM - 1) / SK2_BM, splits);
-    launch_dependent(gemm_skinny_tcgen05_kernel<NP>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map_w, map_x, c, c_dt, splits > 1 ? partial : (float*)nullptr, m, n, k, per, epi, cap);
+    launch_dependent(gemm_skinny_tcgen05_kernel<NP>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map_w, map_x, c, c_dt, splits > 1 ? partial : (float*)nullptr, m, n, k, per, epi, cap KB_TL_SLOT(gemm, 0, n, k));
     return check_launch("gemm_skinny_tcgen05");
 }
 
@@ -842,6 +856,8 @@ static int launch_pair(const CUtensorMap& map_a, const CUtensorMap& map_w, void*
 }  // namespace kb
 
 using namespace kb;
+
+KB_TIMELINE_GETTER(gemm)
 
 // 1 if a wait inside the tcgen05 product ever ran out (and clears the flag); synchronises the device.
 extern "C" int kb_tcgen05_error() {

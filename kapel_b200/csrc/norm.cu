@@ -6,8 +6,12 @@
 // read what the pass before wrote without a barrier beyond the reductions' own. The order of the
 // additions depends on the width and the block size only, never on the number of rows.
 #include "common.cuh"
+#include "timeline.cuh"
 
 namespace kb {
+
+KB_TIMELINE_ARRAY(norm)        // slots: kind 2 add-and-norm over split sums (slices, whether a next norm follows)
+
 
 template <typename TX, typename TW, typename TY>
 __global__ void rmsnorm_kernel(TY* __restrict__ y, const TX* __restrict__ x, const TW* __restrict__ w, int width,
@@ -202,8 +206,9 @@ template <int CPT>
 __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const float* __restrict__ parts, int splits, size_t stride,
                                           const __nv_bfloat16* __restrict__ w_post, float eps_post, float off_post,
                                           const __nv_bfloat16* __restrict__ w_next, float eps_next, float off_next,
-                                          __nv_bfloat16* __restrict__ h, int width) {
+                                          __nv_bfloat16* __restrict__ h, int width KB_TL_PARAM) {
     __shared__ float scratch[32];
+    KB_TL_ENTER(norm, blockIdx.x == 0, 2, splits, w_next != nullptr);
     const size_t base = (size_t)blockIdx.x * width;
     const int chunks = width >> 2;
     // The norms' weights are constants: they are read ahead of the wait on the kernel before, so that
@@ -219,6 +224,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         }
     }
     dependent_wait();
+    KB_TL_MARK(norm, 2, threadIdx.x == 0 && blockIdx.x == 0);
     dependent_trigger();                                    // a few blocks with little to read: the next kernel may set up
     float4 b[CPT], r[CPT];
     float ss = 0.f;
@@ -230,8 +236,8 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         if (ci < chunks) {
             const float* src = parts + base + ci * 4;
             r[c] = *reinterpret_cast<const float4*>(residual + base + ci * 4);    // in flight beside the slices
-            float4 v = *reinterpret_cast<const float4*>(src);
-            int s = 1;
+            float4 v = make_float4(0.f, 0.f, 0.f, 0.f);
+            int s = 0;
             for (; s + 8 <= splits; s += 8) {
                 float4 t[8];
 #pragma unroll
@@ -276,7 +282,10 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
             *reinterpret_cast<float4*>(residual + base + ci * 4) = r[c];
         }
     }
-    if (w_next == nullptr) return;
+    if (w_next == nullptr) {
+        KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
+        return;
+    }
     ss2 = block_sum(ss2, scratch);
     const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
 #pragma unroll
@@ -294,6 +303,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
             *reinterpret_cast<uint2*>(h + base + ci * 4) = uo;
         }
     }
+    KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
 }
 
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
@@ -302,6 +312,8 @@ static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ?
 
 using namespace kb;
 typedef __nv_bfloat16 bf16;
+
+KB_TIMELINE_GETTER(norm)
 
 // x: f32 or bf16; w: f32 or bf16; y: f32 or bf16.
 extern "C" int kb_rmsnorm(void* y, int y_dt, const void* x, int x_dt, const void* w, int w_dt, int rows, int width,
@@ -374,9 +386,9 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const bf16 *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
         const size_t stride = (size_t)split_stride;
         bf16* out = (bf16*)h;
-        if (cpt == 1) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else if (cpt == 2) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
-        else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
+        if (cpt == 1) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));
+        else if (cpt == 2) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));
+        else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));
         return check_launch("add_rmsnorm");
     }
     switch (code) {
