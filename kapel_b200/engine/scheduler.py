@@ -284,6 +284,27 @@ class Scheduler:
             return events
         return self._finish_pass(events, pass_)
 
+    def settle(self) -> List[Event]:
+        """Ends what runs ahead of the host: reads the pass that is already on its way (and gives its
+        tokens, as `step` would have), and gives back the pages of a pass that was staged. After it
+        the engine's cache holds every running request's tokens but the last, which is the one to
+        feed next; somebody who then steps the engine directly sees a consistent state."""
+        events: List[Event] = []
+        ahead, self.ahead = self.ahead, None
+        if ahead is not None:
+            rids, logits = ahead
+            try:
+                rows = [i for i, r in enumerate(rids) if r in self.entries and self.entries[r].running]
+                producing = [rids[i] for i in rows]
+                tokens = self._choose(logits, producing, rows)
+            except Exception as e:
+                return self._fail_pass(events, e)
+            events = self._give(events, producing, tokens)
+        staged, self.staged = self.staged, None
+        if staged is not None:
+            self._discard(staged[1])
+        return events
+
     def _discard(self, handle) -> None:
         discard = getattr(self.engine, "discard", None)
         if discard is not None:

@@ -230,6 +230,50 @@ def test_passes_enqueued_ahead_of_the_host_give_the_same_tokens(folders, tempera
     assert sched.ahead_passes > 10, "decode passes were enqueued ahead of the host"
 
 
+def test_settle_reads_the_pass_on_its_way_and_leaves_the_cache_one_token_behind(folders):
+    """After passes enqueued ahead of the host, `settle` gives the tokens of the pass on its way and
+    frees what was staged: every request's cache then holds all its tokens but the last, and stepping
+    the engine directly from there continues the sequence as the scheduler would have."""
+    import kapel_b200
+    from kapel_b200.engine import StepEntry
+    from kapel_b200.engine.scheduler import Request
+    from kapel_b200.sampling import Sampling
+
+    raw, _ = TINY["A"]
+    rng = np.random.default_rng(41)
+    prompts = [random_tokens(rng, n, raw["vocab_size"]) for n in (12, 27)]
+    model = kapel_b200.Model(str(folders["A"]), dtype="f32", max_tokens_cached=512, max_sequences=4)
+
+    def tokens_of(run_ahead, n):
+        sched = model.scheduler(max_pass_tokens=64, run_ahead=run_ahead)
+        ids = [sched.add(Request(p, sampling=Sampling(), max_tokens=60, ignore_eos=True)) for p in prompts]
+        for _ in range(n):
+            sched.step()
+        return sched, ids
+
+    want_sched, want_ids = tokens_of(False, 30)
+    want = [list(want_sched.entries[r].sequence) for r in want_ids]
+    for r in want_ids:
+        want_sched.cancel(r)
+    sched, ids = tokens_of(True, 14)
+    assert sched.ahead is not None and sched.ahead_passes > 5, "a pass is on its way"
+    given = sched.settle()
+    assert len(given) == 2 and sched.ahead is None and sched.staged is None
+    engine = model.engine
+    seqs = {r: list(sched.entries[r].sequence) for r in ids}
+    for r in ids:
+        assert engine.cache.length(r) == len(seqs[r]) - 1
+    while len(seqs[ids[0]]) < len(want[0]):
+        logits = engine.step([StepEntry(r, [seqs[r][-1]], [0]) for r in ids])
+        for r, row in zip(ids, logits.argmax(dim=-1).tolist()):
+            seqs[r].append(int(row))
+    assert [seqs[r] for r in ids] == want
+    for r in ids:
+        sched.cancel(r)
+    engine.cache.check()
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_long_decoding_and_first_tokens(folders, dtype):
     """A one-token prompt, then every token one by one up to the model's limit: first tokens of a
