@@ -511,6 +511,30 @@ def test_paged_attention_mma_far_key_and_window_edge(decode):
         assert (abs(float(got[0, 0].mean()) - 5.0) < 0.1) == seen
 
 
+@pytest.mark.parametrize("slots_wanted", [19, 150, 333])
+def test_decode_attention_over_many_key_slots_merges_them_all(slots_wanted):
+    """One request alone with a long history is cut into more key slots than the merge kernel keeps
+    in registers at once (16 values a thread, 128 maxima a warp): 19, 150 and 333 slots of 64 keys,
+    beside a short request that fills one slot. One key far back carries a value that stands out, so
+    a slot that the merge dropped or weighted wrongly shows."""
+    hq, hkv, d, page = 2, 1, 64, 16
+    lengths = [64 * slots_wanted - 7, 40]
+    q, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, [1, 1], seed=slots_wanted)
+    # the long request's key at position 70 (in its second slot) answers its query with a large score
+    line = int(bt[0, 70 // page]) * page + 70 % page
+    kt.view(-1, hkv, page, d)[line // page, 0, line % page] = (q[0, 0] * 3.0).to(kt.dtype)
+    vt.view(-1, hkv, page, d)[line // page, 0, line % page] = 5.0
+    from kapel_b200.engine.batch import cut_tiles
+
+    tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(np.arange(2, dtype=np.int32), np.ones(2, np.int32), 1))
+    got = K().paged_attention_mma(dev(q), dev(kt), dev(vt), dev(bt), dev(rc), tiles, page, None, 1.0 / 8, None, hq // hkv, 64,
+                                  slots_wanted, True).cpu().double()
+    K().check_async_errors()
+    want = paged_reference(q, kt, vt, bt, re, rc, page, None, 1.0 / 8, None)
+    assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+    assert float(want[0, 0].mean()) > 2.0, "the planted key decides the long request's first head"
+
+
 @pytest.mark.parametrize("hq,hkv,d,scalar", [(8, 4, 256, 256), (32, 16, 128, 144)])
 @pytest.mark.parametrize("window", [4096, None])
 def test_paged_attention_at_the_sizes_and_histories_that_are_timed(hq, hkv, d, scalar, window):
