@@ -57,10 +57,22 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
 
 
 # What a block costs beyond its 64-key steps, what the merge of partial sums costs beyond its traffic
-# (both in steps), and microseconds a step, by prompt kernel; from sweeps of the split at Gemma 2 2B
-# head sizes. The tcgen05 kernel's steps are short, so its fixed costs weigh more and it is cut into
-# slots only when a few tiles face a long history.
-PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5), "tcgen05": (8.0, 15.0, 1.34)}
+# (both in steps), microseconds a step, and how many multiprocessors a block takes, by prompt kernel;
+# from sweeps of the split at Gemma 2 2B head sizes with 2,048 tokens behind 4,096 to 129,024 (a block
+# that starts among running ones costs 20 to 27 us before its first and after its last step, twice
+# what it costs in a launch of its own). The tcgen05 kernels' steps are short, so their fixed costs
+# weigh more and they are cut into slots only when a few tiles face a long history; "tcgen05_pair" is
+# the kernel on pairs of blocks (a tile of 256 rows on two multiprocessors, half the time a step).
+PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5, 1), "tcgen05": (18.0, 15.0, 1.2, 1), "tcgen05_pair": (32.0, 18.0, 0.85, 2)}
+
+
+def prompt_costs_of(prompt_kernel: str, head_dim: int) -> str:
+    """The entry of PROMPT_KERNEL_COSTS for the kernel that will run prompt portions of this head size."""
+    from .. import kernels as K
+
+    if prompt_kernel == "tcgen05" and K.attention_tile_rows(False, prompt_kernel, head_dim) > 128:
+        return "tcgen05_pair"
+    return prompt_kernel
 
 
 def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, window: Optional[int], rows: int, hq: int, d: int,
@@ -70,7 +82,8 @@ def prompt_split(first_counts, last_counts, pairs_per_tile: int, sms: int, windo
     of `split` positions evens the blocks out at the price of partial sums that a second kernel
     merges. The choice minimises an estimate of the time: the longest block or the mean load of a
     multiprocessor, whichever is larger, plus the merge, all counted in 64-key steps."""
-    block_cost, merge_cost, step_us = PROMPT_KERNEL_COSTS[kernel]
+    block_cost, merge_cost, step_us, sms_a_block = PROMPT_KERNEL_COSTS[kernel]
+    sms = max(1, sms // sms_a_block)                     # blocks (or pairs of blocks) that run at once
     first = np.asarray(first_counts, np.int64)
     last = np.asarray(last_counts, np.int64)
     lo = np.maximum(0, first - window) if window else np.zeros_like(first)
@@ -179,6 +192,7 @@ class StepBatch:
             from .. import kernels as K
 
             plan = self.plan
+            costs_of = prompt_costs_of(prompt_kernel, head_dim)
             most = int(plan.q_len.max()) * heads_per_kv
             decode = most if most <= K.attention_mma_rows(True) else 0      # rows a tile in decode mode, else 0
             per_tile = max(1, K.attention_tile_rows(bool(decode), prompt_kernel, head_dim) // heads_per_kv)
@@ -194,7 +208,7 @@ class StepBatch:
             else:
                 firsts = plan.row_count[arrays[1]]
                 split, slots = prompt_split(firsts, firsts + arrays[2] - 1, kv_heads, sm_count(self.ids.device), window,
-                                            plan.rows, heads_per_kv * kv_heads, head_dim, prompt_kernel)
+                                            plan.rows, heads_per_kv * kv_heads, head_dim, costs_of)
             self.memo[key] = (decode, tiles, split, slots, relative, host)
         return self.memo[key][:5]
 

@@ -107,7 +107,7 @@ def main(argv=None) -> int:
         return host_bench(args)
 
     from . import kernels as K
-    from .engine.batch import cut_tiles, decode_split, prompt_split, sm_count
+    from .engine.batch import cut_tiles, decode_split, prompt_costs_of, prompt_split, sm_count
 
     dev = torch.device("cuda", torch.cuda.current_device())
     K.library()
@@ -220,15 +220,39 @@ def main(argv=None) -> int:
         tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
         firsts = tiles[1].cpu().numpy() + 1
         split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D,
-                                    K.attention_prompt_kernel(Hq, Hkv, D, page, cap))
+                                    prompt_costs_of(K.attention_prompt_kernel(Hq, Hkv, D, page, cap), D))
         pairs = sum(min(c, window) if window else c for c in range(1, t + 1))
         us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
                                                    0, split, slots), max(3, args.iters // 4))
         report(f"{name} [{t} tokens] split={split}x{slots}", us, t * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
 
+    def portion_case(window):
+        """The last `--prompt` tokens of a request of `--history` tokens: a portion of a long prompt,
+        every row of which sees the history before it."""
+        name = f"attention portion window={window}"
+        if not want(name):
+            return
+        t = min(args.prompt, ctx)
+        before = ctx - t
+        q = torch.randn(t, Hq, D, device=dev).to(bf)
+        rc = torch.arange(before + 1, ctx + 1, dtype=torch.int32, device=dev)
+        per_tile = max(1, K.attention_tile_rows(False, K.attention_prompt_kernel(Hq, Hkv, D, page, cap), D) // (Hq // Hkv))
+        tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.zeros(1, np.int32), np.asarray([t], np.int32), per_tile))
+        firsts = tiles[1].cpu().numpy() + before + 1
+        split, slots = prompt_split(firsts, firsts + tiles[2].cpu().numpy() - 1, Hkv, sm_count(dev), window, t, Hq, D,
+                                    prompt_costs_of(K.attention_prompt_kernel(Hq, Hkv, D, page, cap), D))
+        pairs = sum(min(c, window) if window else c for c in range(before + 1, ctx + 1))
+        seen = min(ctx, window + t) if window else ctx
+        us = _time(lambda i: K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
+                                                   0, split, slots), max(3, args.iters // 4))
+        report(f"{name} [{t} tokens behind {before}] split={split}x{slots}", us, seen * Hkv * D * 2 * 2 + 2 * t * Hq * D * 2, 4.0 * pairs * Hq * D)
+
     if args.prompt <= ctx:
         prompt_case(None)
         prompt_case(args.window)
+    if args.prompt < ctx:
+        portion_case(None)
+        portion_case(args.window)
 
     if want("rope_append"):
         for m, tag in ((B, "decode"), (args.prompt, "prompt")):
