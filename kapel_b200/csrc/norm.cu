@@ -258,6 +258,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         }
     }
     float inv = 1.f;
+    KB_TL_MARK(norm, 3, threadIdx.x == 0 && blockIdx.x == 0);          // the slices and the residual are here
     if (w_post != nullptr) {
         ss = block_sum(ss, scratch);
         inv = 1.f / sqrtf(ss / (float)width + eps_post);
@@ -287,6 +288,7 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
         return;
     }
     ss2 = block_sum(ss2, scratch);
+    KB_TL_MARK(norm, 4, threadIdx.x == 0 && blockIdx.x == 0);          // both sums are known
     const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
 #pragma unroll
     for (int c = 0; c < CPT; ++c) {

@@ -84,6 +84,8 @@ def main(argv=None) -> int:
                 marks.update({3: "block 0: first tile landed", 4: "block 0: sums done"})
             if kind == 4:
                 marks.update({3: "block 0: loop over keys begins", 4: "block 0: loop done"})
+            if kind == 2:
+                marks.update({3: "block 0: slices and residual loaded", 4: "block 0: both sums known"})
             events.extend((int(f[i]), f"{name}: {what}") for i, what in marks.items() if f[i])
     if not events:
         print("no kernel left a stamp", file=sys.stderr)

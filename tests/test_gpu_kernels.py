@@ -634,6 +634,36 @@ def test_split_sums_are_added_up_by_their_readers():
     assert rel_err(vt.cpu().double()[0, :, 9].numpy(), x[2, hq + hkv :].numpy()) < 1e-2
 
 
+@pytest.mark.parametrize("rows", [1, 8, 9, 64, 200])
+@pytest.mark.parametrize("width", [40, 520, 2304, 4608, 8200])
+@pytest.mark.parametrize("splits", [2, 8, 9, 16, 17, 35])
+def test_add_rmsnorm_over_split_sums_at_other_sizes(rows, width, splits):
+    """The residual sum with both norms over a stack of float32 partial sums: 2 to 35 slices (full
+    batches of eight in flight and what is left over), widths that leave a thread without a group of
+    four, with and without either norm; and a row's result does not depend on how many rows came
+    with it."""
+    g = torch.Generator().manual_seed(rows * 1000 + width + splits)
+    parts = (torch.randn(splits, rows, width, generator=g) * 0.7).float()
+    res = torch.randn(rows, width, generator=g).float() * 2
+    w1 = (torch.randn(width, generator=g) * 0.1).bfloat16()
+    w2 = (torch.randn(width, generator=g) * 0.1).bfloat16()
+    branch = parts.double().sum(0)
+    for post, nxt in [(True, True), (True, False), (False, True)]:
+        r = dev(res.clone())
+        h = K().add_rmsnorm(r, K().SplitSum(dev(parts)), (dev(w1), 1e-6, 1.0) if post else None, (dev(w2), 1e-5, 1.0) if nxt else None,
+                            torch.bfloat16)
+        b = P.rms_norm(branch, w1.double(), 1e-6) if post else branch
+        want_r = res.double() + b
+        assert rel_err(r.cpu().double().numpy(), want_r.numpy()) < 2e-6
+        if nxt:
+            assert rel_err(h.cpu().double().numpy(), P.rms_norm(want_r, w2.double(), 1e-5).numpy()) < 1e-2
+    if rows > 1:
+        r_all, r_one = dev(res.clone()), dev(res[:1].clone())
+        h_all = K().add_rmsnorm(r_all, K().SplitSum(dev(parts)), (dev(w1), 1e-6, 1.0), (dev(w2), 1e-5, 1.0), torch.bfloat16)
+        h_one = K().add_rmsnorm(r_one, K().SplitSum(dev(parts[:, :1].contiguous())), (dev(w1), 1e-6, 1.0), (dev(w2), 1e-5, 1.0), torch.bfloat16)
+        assert torch.equal(r_all[:1], r_one) and torch.equal(h_all[:1], h_one), "the same kernel and the same order of additions"
+
+
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 16])
 def test_gemm_bf16_rows_up_to_16_do_not_depend_on_the_batch(m):
     a, w = rnd(16, 2304, seed=38, dtype=torch.bfloat16), rnd(520, 2304, seed=39, dtype=torch.bfloat16)
