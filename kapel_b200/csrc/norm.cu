@@ -5,6 +5,7 @@
 // One block a row, any width. Each thread walks the same components in every pass, so a pass may
 // read what the pass before wrote without a barrier beyond the reductions' own. The order of the
 // additions depends on the width and the block size only, never on the number of rows.
+#include <algorithm>
 #include "common.cuh"
 #include "timeline.cuh"
 
@@ -308,6 +309,142 @@ __global__ void add_rmsnorm_splits_kernel(float* __restrict__ residual, const fl
     KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
 }
 
+// The same with the slices brought into shared memory by bulk copies (one a slice's row, all asked
+// for by one thread right after the wait) instead of loads by every thread. What the kernel before
+// has just written comes much sooner that way: loads by the threads of a block that was already
+// resident while that kernel ran took 2 to 3 us for sixteen slices however they were batched, the
+// copy engine brings them in 1.2 us (the whole kernel: 5.5 to 2.9 us over 16 slices; a decode step
+// at Gemma 2 2B sizes and batch 8: 2.38 to 2.26 ms).
+__device__ int g_norm_error = 0;
+__device__ __forceinline__ uint32_t nb_saddr(const void* p) { return (uint32_t)__cvta_generic_to_shared(p); }
+__device__ __forceinline__ bool nb_wait(uint64_t* bar, uint32_t parity) {
+    const uint32_t addr = nb_saddr(bar);
+    const long long start = clock64();
+    for (;;) {
+        uint32_t ok;
+        asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}"
+                     : "=r"(ok) : "r"(addr), "r"(parity) : "memory");
+        if (ok) return true;
+        if (clock64() - start > 2000000000ll) return false;
+    }
+}
+
+template <int CPT>
+__global__ void add_rmsnorm_splits_bulk_kernel(float* __restrict__ residual, const float* __restrict__ parts, int splits, size_t stride,
+                                               const __nv_bfloat16* __restrict__ w_post, float eps_post, float off_post,
+                                               const __nv_bfloat16* __restrict__ w_next, float eps_next, float off_next,
+                                               __nv_bfloat16* __restrict__ h, int width, int room KB_TL_PARAM) {
+    extern __shared__ __align__(128) unsigned char nb_smem[];
+    __shared__ float scratch[32];
+    __shared__ __align__(8) uint64_t landed;
+    float* rows = reinterpret_cast<float*>(nb_smem);        // [room][width]
+    KB_TL_ENTER(norm, blockIdx.x == 0, 2, splits, w_next != nullptr);
+    const size_t base = (size_t)blockIdx.x * width;
+    const int chunks = width >> 2;
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(nb_saddr(&landed)) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    uint2 wp[CPT], wn[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        wp[c] = wn[c] = make_uint2(0u, 0u);
+        if (ci < chunks) {
+            if (w_post != nullptr) wp[c] = *reinterpret_cast<const uint2*>(w_post + ci * 4);
+            if (w_next != nullptr) wn[c] = *reinterpret_cast<const uint2*>(w_next + ci * 4);
+        }
+    }
+    __syncthreads();
+    dependent_wait();
+    KB_TL_MARK(norm, 2, threadIdx.x == 0 && blockIdx.x == 0);
+    dependent_trigger();
+    const uint32_t row_bytes = (uint32_t)width * 4u;
+    float4 b[CPT], r[CPT];
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        b[c] = make_float4(0.f, 0.f, 0.f, 0.f);
+        r[c] = b[c];
+        if (ci < chunks) r[c] = *reinterpret_cast<const float4*>(residual + base + ci * 4);
+    }
+    // `room` slices fit the shared memory this launch has: all of them in one round as a rule, else
+    // round after round into the same rows (every thread has added a round up before the next lands on it).
+    bool ok = true;
+    for (int s0 = 0, round = 0; s0 < splits; s0 += room, ++round) {
+        const int n = min(room, splits - s0);
+        if (round > 0) __syncthreads();
+        if (threadIdx.x == 0) {
+            asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(nb_saddr(&landed)), "r"(row_bytes * (uint32_t)n) : "memory");
+            for (int s = 0; s < n; ++s)
+                asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                             ::"r"(nb_saddr(rows + (size_t)s * width)), "l"(parts + (size_t)(s0 + s) * stride + base), "r"(row_bytes), "r"(nb_saddr(&landed)) : "memory");
+        }
+        ok = nb_wait(&landed, (uint32_t)round & 1u) && ok;
+#pragma unroll
+        for (int c = 0; c < CPT; ++c) {
+            const int ci = threadIdx.x + c * blockDim.x;
+            if (ci < chunks) {
+                for (int s = 0; s < n; ++s) {               // in slice order
+                    const float4 t = *reinterpret_cast<const float4*>(rows + (size_t)s * width + ci * 4);
+                    b[c].x += t.x; b[c].y += t.y; b[c].z += t.z; b[c].w += t.w;
+                }
+            }
+        }
+    }
+    float ss = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) ss += b[c].x * b[c].x + b[c].y * b[c].y + b[c].z * b[c].z + b[c].w * b[c].w;
+    KB_TL_MARK(norm, 3, threadIdx.x == 0 && blockIdx.x == 0);
+    float inv = 1.f;
+    if (w_post != nullptr) {
+        ss = block_sum(ss, scratch);
+        inv = 1.f / sqrtf(ss / (float)width + eps_post);
+    }
+    float ss2 = 0.f;
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            if (w_post != nullptr) {
+                const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wp[c].x));
+                const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wp[c].y));
+                r[c].x += b[c].x * inv * (off_post + w0.x);
+                r[c].y += b[c].y * inv * (off_post + w0.y);
+                r[c].z += b[c].z * inv * (off_post + w1.x);
+                r[c].w += b[c].w * inv * (off_post + w1.y);
+            } else {
+                r[c].x += b[c].x; r[c].y += b[c].y; r[c].z += b[c].z; r[c].w += b[c].w;
+            }
+            ss2 += r[c].x * r[c].x + r[c].y * r[c].y + r[c].z * r[c].z + r[c].w * r[c].w;
+            *reinterpret_cast<float4*>(residual + base + ci * 4) = r[c];
+        }
+    }
+    if (!ok && threadIdx.x == 0) atomicExch(&g_norm_error, 1);
+    if (w_next == nullptr) {
+        KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
+        return;
+    }
+    ss2 = block_sum(ss2, scratch);
+    KB_TL_MARK(norm, 4, threadIdx.x == 0 && blockIdx.x == 0);
+    const float inv2 = 1.f / sqrtf(ss2 / (float)width + eps_next);
+#pragma unroll
+    for (int c = 0; c < CPT; ++c) {
+        const int ci = threadIdx.x + c * blockDim.x;
+        if (ci < chunks) {
+            const float2 w0 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wn[c].x));
+            const float2 w1 = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&wn[c].y));
+            uint2 uo;
+            __nv_bfloat162 o0 = __floats2bfloat162_rn(r[c].x * inv2 * (off_next + w0.x), r[c].y * inv2 * (off_next + w0.y));
+            __nv_bfloat162 o1 = __floats2bfloat162_rn(r[c].z * inv2 * (off_next + w1.x), r[c].w * inv2 * (off_next + w1.y));
+            uo.x = *reinterpret_cast<uint32_t*>(&o0);
+            uo.y = *reinterpret_cast<uint32_t*>(&o1);
+            *reinterpret_cast<uint2*>(h + base + ci * 4) = uo;
+        }
+    }
+    KB_TL_LEAVE(norm, blockIdx.x == 0, 0);
+}
+
 static int threads_for(int width) { return width >= 2048 ? 512 : (width >= 512 ? 256 : 128); }
 
 }  // namespace kb
@@ -316,6 +453,14 @@ using namespace kb;
 typedef __nv_bfloat16 bf16;
 
 KB_TIMELINE_GETTER(norm)
+
+// 1 if a wait inside a norm kernel ever ran out (and clears the flag); synchronises the device.
+extern "C" int kb_norm_error() {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_norm_error, sizeof(int)) != cudaSuccess) return -1;
+    if (flag) cudaMemcpyToSymbol(g_norm_error, &zero, sizeof(int));
+    return flag;
+}
 
 // x: f32 or bf16; w: f32 or bf16; y: f32 or bf16.
 extern "C" int kb_rmsnorm(void* y, int y_dt, const void* x, int x_dt, const void* w, int w_dt, int rows, int width,
@@ -388,6 +533,24 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         const bf16 *wp = (const bf16*)w_post, *wn = (const bf16*)w_next;
         const size_t stride = (size_t)split_stride;
         bf16* out = (bf16*)h;
+        // A decode step's rows: the slices come into shared memory by bulk copies (see the kernel). Up to 192 KB of
+        // it, so sixteen slices of 2,304 or eleven of 4,608 values land in one round.
+        const int room = (int)std::min<size_t>((size_t)splits, (size_t)(192 * 1024) / ((size_t)width * 4));
+        if (rows <= DEPENDENT_ROWS && splits > 1 && room >= 1) {
+            static bool attr_set = false;
+            if (!attr_set) {
+                const cudaError_t e = cudaFuncSetAttribute(add_rmsnorm_splits_bulk_kernel<1>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+                const cudaError_t e2 = cudaFuncSetAttribute(add_rmsnorm_splits_bulk_kernel<2>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+                const cudaError_t e4 = cudaFuncSetAttribute(add_rmsnorm_splits_bulk_kernel<4>, cudaFuncAttributeMaxDynamicSharedMemorySize, 192 * 1024);
+                if (e != cudaSuccess || e2 != cudaSuccess || e4 != cudaSuccess) return fail("add_rmsnorm: cannot have 192 KB of shared memory");
+                attr_set = true;
+            }
+            const size_t bytes = (size_t)room * width * 4;
+            if (cpt == 1) launch_dependent_if(true, add_rmsnorm_splits_bulk_kernel<1>, dim3(rows), dim3(tv), bytes, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width, room KB_TL_SLOT(norm, 2, splits, wn != nullptr));
+            else if (cpt == 2) launch_dependent_if(true, add_rmsnorm_splits_bulk_kernel<2>, dim3(rows), dim3(tv), bytes, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width, room KB_TL_SLOT(norm, 2, splits, wn != nullptr));
+            else launch_dependent_if(true, add_rmsnorm_splits_bulk_kernel<4>, dim3(rows), dim3(tv), bytes, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width, room KB_TL_SLOT(norm, 2, splits, wn != nullptr));
+            return check_launch("add_rmsnorm");
+        }
         if (cpt == 1) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<1>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));
         else if (cpt == 2) launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<2>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));
         else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_splits_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, splits, stride, wp, eps_post, off_post, wn, eps_next, off_next, out, width KB_TL_SLOT(norm, 2, splits, wn != nullptr));

