@@ -105,6 +105,93 @@ __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__
     KB_TL_LEAVE(elementwise, blockIdx.x == 0, 0);           // thread 0 of block 0 rotates a query: it never left early
 }
 
+// The same over float32 split sums for a decode step, with the slices brought into shared memory by
+// bulk copies instead of the threads' loads: what the product before has just written arrives much
+// sooner that way (see add_rmsnorm_splits_bulk_kernel). A block of 256 threads owns 256 pairs, which
+// are 256 / (d / 2) whole heads of one row: 512 consecutive values of each slice, one copy a slice.
+// The sums are added in slice order, as Src::at adds them.
+__device__ int g_rope_error = 0;
+template <typename T>
+__global__ void __launch_bounds__(256) rope_append_bulk_kernel(const float* __restrict__ parts, int splits, size_t stride,
+                                                               const float2* __restrict__ cos_sin, const int* __restrict__ lines,
+                                                               T* __restrict__ q_out, T* __restrict__ k_table, T* __restrict__ v_table,
+                                                               int rows, int hq, int hkv, int d, int rotary, int write_kv,
+                                                               long long table_lines, int page_size KB_TL_PARAM) {
+    extern __shared__ __align__(128) unsigned char rb_smem[];
+    __shared__ __align__(8) uint64_t landed;
+    float* vals = reinterpret_cast<float*>(rb_smem);        // [splits][512]
+    const int half_d = d >> 1, half_r = rotary >> 1;
+    const int heads = hq + 2 * hkv;
+    const int blocks_a_row = heads * half_d / 256;
+    const int r = blockIdx.x / blocks_a_row, seg = blockIdx.x % blocks_a_row;
+    const int heads_a_block = 256 / half_d;
+    const int h0 = seg * heads_a_block;
+    KB_TL_ENTER(elementwise, blockIdx.x == 0, 3, rows, splits);
+    const uint32_t bar = (uint32_t)__cvta_generic_to_shared(&landed);
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.init.shared::cta.b64 [%0], 1;" ::"r"(bar) : "memory");
+        asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+    }
+    const int h = h0 + (int)threadIdx.x / half_d, i = (int)threadIdx.x % half_d;
+    int ia, ib;
+    bool rotate;
+    if (i < half_r) {
+        ia = i; ib = i + half_r; rotate = true;
+    } else {
+        ia = rotary + 2 * (i - half_r); ib = ia + 1; rotate = false;
+    }
+    if (h >= hq + hkv) rotate = false;                      // a value
+    __syncthreads();
+    dependent_wait();
+    KB_TL_MARK(elementwise, 2, threadIdx.x == 0 && blockIdx.x == 0);
+    dependent_trigger();
+    if (threadIdx.x == 0) {
+        asm volatile("mbarrier.arrive.expect_tx.shared::cta.b64 _, [%0], %1;" ::"r"(bar), "r"(2048u * (uint32_t)splits) : "memory");
+        const float* src = parts + ((size_t)r * heads + h0) * d;
+        for (int s = 0; s < splits; ++s)
+            asm volatile("cp.async.bulk.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1], %2, [%3];"
+                         ::"r"((uint32_t)__cvta_generic_to_shared(vals + s * 512)), "l"(src + (size_t)s * stride), "r"(2048u), "r"(bar) : "memory");
+    }
+    // the angle and the cache line come by ordinary loads while the copies are on their way (in the
+    // first layer the table of angles is the work of the kernel just before: not ahead of the wait)
+    const float2 cs = rotate ? cos_sin[(size_t)r * half_r + i] : make_float2(1.f, 0.f);
+    const int line = h >= hq ? lines[r] : 0;
+    bool ok = false;
+    {
+        const long long start = clock64();
+        for (;;) {
+            uint32_t done;
+            asm volatile("{\n\t.reg .pred p;\n\tmbarrier.try_wait.parity.shared::cta.b64 p, [%1], %2;\n\tselp.u32 %0, 1, 0, p;\n\t}" : "=r"(done) : "r"(bar), "r"(0u) : "memory");
+            if (done) { ok = true; break; }
+            if (clock64() - start > 2000000000ll) break;    // about a second: a copy never landed
+        }
+    }
+    if (!ok) {
+        if (threadIdx.x == 0) atomicExch(&g_rope_error, 1);
+        return;
+    }
+    if (h >= hq && !write_kv) return;
+    const int local = (h - h0) * d;
+    float a = vals[local + ia], b = vals[local + ib];
+    for (int s = 1; s < splits; ++s) {
+        a += vals[s * 512 + local + ia];
+        b += vals[s * 512 + local + ib];
+    }
+    T* dst;
+    if (h < hq) {
+        dst = q_out + ((size_t)r * hq + h) * d;
+    } else {
+        if (line < 0 || line >= table_lines) return;
+        const bool is_key = h < hq + hkv;
+        const int kvh = is_key ? h - hq : h - hq - hkv;
+        dst = (is_key ? k_table : v_table) + kv_row(line, kvh, hkv, page_size) * d;
+    }
+    if (rotate) rope_rotate(a, b, cs);
+    Elem<T>::store(dst + ia, a);
+    Elem<T>::store(dst + ib, b);
+    KB_TL_LEAVE(elementwise, blockIdx.x == 0, 0);
+}
+
 // The same for bfloat16 in and out with the whole head rotated (rotary == d, d a multiple of 16):
 // one thread takes eight components of the first half and their eight partners of the second, with
 // 16-byte loads and stores.
@@ -284,6 +371,14 @@ extern "C" int kb_rope_table(float* cos_sin, const int* positions, int rows, int
 
 KB_TIMELINE_GETTER(elementwise)
 
+// 1 if a wait inside the rotation kernel ever ran out (and clears the flag); synchronises the device.
+extern "C" int kb_rope_error() {
+    int flag = 0, zero = 0;
+    if (cudaMemcpyFromSymbol(&flag, g_rope_error, sizeof(int)) != cudaSuccess) return -1;
+    if (flag) cudaMemcpyToSymbol(g_rope_error, &zero, sizeof(int));
+    return flag;
+}
+
 // qkv: `in_dt` (float32 or bfloat16), as `splits` slices `split_stride` elements apart that are
 // added up on the way in; q_out and the tables: `out_dt`.
 extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long split_stride, const float* cos_sin,
@@ -308,6 +403,19 @@ extern "C" int kb_rope_append(const void* qkv, int in_dt, int splits, long long 
         launch_dependent_if(rows <= DEPENDENT_ROWS, rope_append_bf16x8_kernel, dim3((unsigned)((vec + 255) / 256)), dim3(256), 0, s,
             (const bf16*)qkv, (const float2*)cos_sin, lines, (bf16*)q_out, (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d,
             write_kv, table_lines, page_size > 0 ? page_size : 1);
+    }
+    else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16 && splits > 1 && rows <= DEPENDENT_ROWS && d % 4 == 0 && 256 % (d / 2) == 0 &&
+             ((hq + 2 * hkv) * (d / 2)) % 256 == 0 && splits <= 32 && (split_stride % 4) == 0 && (((uintptr_t)qkv) & 15) == 0) {
+        // a decode step's split sums: the slices come into shared memory by bulk copies (2 KB a slice and block)
+        static bool attr_set = false;
+        if (!attr_set) {
+            if (cudaFuncSetAttribute(rope_append_bulk_kernel<bf16>, cudaFuncAttributeMaxDynamicSharedMemorySize, 32 * 2048) != cudaSuccess)
+                return fail("rope_append: cannot have 64 KB of shared memory");
+            attr_set = true;
+        }
+        launch_dependent_if(true, rope_append_bulk_kernel<bf16>, dim3(blocks), dim3(256), (size_t)splits * 2048, s, (const float*)qkv, splits,
+                            (size_t)split_stride, (const float2*)cos_sin, lines, (bf16*)q_out, (bf16*)k_table, (bf16*)v_table, rows, hq, hkv, d,
+                            rotary, write_kv, table_lines, page_size > 0 ? page_size : 1 KB_TL_SLOT(elementwise, 3, rows, splits));
     }
     else if (in_dt == KB_DT_F32 && out_dt == KB_DT_F32) KB_ROPE(float, float);
     else if (in_dt == KB_DT_F32 && out_dt == KB_DT_BF16) KB_ROPE(float, bf16);

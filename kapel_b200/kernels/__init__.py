@@ -79,6 +79,8 @@ def check_async_errors() -> None:
         bad.append("tcgen05 product (a TMA load or an MMA commit never arrived)")
     if lib.kb_attention_tc_error() != 0:
         bad.append("tcgen05 attention (a TMA load, an MMA commit or a softmax warp never arrived)")
+    if lib.kb_rope_error() != 0:
+        bad.append("rotate and append (a bulk copy of partial sums into shared memory never completed)")
     if lib.kb_norm_error() != 0:
         bad.append("add-and-norm (a bulk copy of partial sums into shared memory never completed)")
     if bad:

@@ -50,6 +50,54 @@ def test_rope_table():
         assert (got[..., 1] - torch.sin(angle)).abs().max() < 1e-6
 
 
+@pytest.mark.parametrize("hq,hkv,d,rotary", [(8, 4, 256, 256), (32, 16, 128, 128), (4, 2, 16, 16), (6, 1, 32, 16), (2, 1, 64, 32), (3, 3, 48, 48),
+                                            (5, 1, 64, 64)])
+@pytest.mark.parametrize("rows,splits", [(1, 2), (8, 9), (9, 24), (64, 5), (7, 30)])
+def test_rope_append_over_split_sums(hq, hkv, d, rotary, rows, splits):
+    """Rotation and append over a stack of float32 partial sums, as a decode step has them: the
+    sizes whose slices come in by bulk copies (a block's 256 pairs are whole heads of one row) and
+    the others, 2 to 30 slices, 1 to 64 rows, a rotary width below the head size; rows with no line
+    write nothing, and what nobody wrote stays as it was."""
+    g = torch.Generator().manual_seed(hq * 100 + d + rows + splits)
+    heads = hq + 2 * hkv
+    parts = (torch.randn(splits, rows, heads * d, generator=g) * 0.5).float()
+    page, pages = 16, 8
+    pos = torch.randint(0, 5000, (rows,), generator=g, dtype=torch.int32)
+    perm = torch.randperm(page * pages, generator=g)[:rows].to(torch.int32)
+    lines = perm.clone()
+    lines[rows // 2] = -1
+    kt = torch.full((pages, hkv, page, d), 7.0, dtype=torch.bfloat16)
+    vt = torch.full((pages, hkv, page, d), 7.0, dtype=torch.bfloat16)
+    kd, vd = dev(kt), dev(vt)
+    cs = K().rope_table(dev(pos), rotary, 10000.0)
+    q = K().rope_append(K().SplitSum(dev(parts)), cs, dev(lines), kd, vd, hq, hkv, d, rotary, out_dtype=torch.bfloat16).cpu().double()
+    K().check_async_errors()
+    x = parts.double().sum(0).reshape(rows, heads, d)
+
+    def rot(t):
+        return torch.cat([P.rope(t[..., :rotary], pos, 10000.0), t[..., rotary:]], dim=-1)
+
+    assert rel_err(q.numpy(), rot(x[:, :hq]).numpy()) < 1e-2
+    k_want, v_want = rot(x[:, hq : hq + hkv]), x[:, hq + hkv :]
+    kc = kd.cpu().double().permute(0, 2, 1, 3).reshape(page * pages, hkv, d)
+    vc = vd.cpu().double().permute(0, 2, 1, 3).reshape(page * pages, hkv, d)
+    written = set()
+    for r in range(rows):
+        l = int(lines[r])
+        if l < 0:
+            continue
+        written.add(l)
+        assert rel_err(kc[l].numpy(), k_want[r].numpy()) < 1e-2 and rel_err(vc[l].numpy(), v_want[r].numpy()) < 1e-2
+    for l in range(page * pages):
+        if l not in written:
+            assert (kc[l] == 7.0).all() and (vc[l] == 7.0).all(), f"line {l} was written by no row"
+    # the same bits as the slices added up first and rotated by the kernel that takes one input
+    whole = K().finish(K().SplitSum(dev(parts)), torch.float32)
+    kd2, vd2 = dev(kt), dev(vt)
+    q2 = K().rope_append(whole, cs, dev(lines), kd2, vd2, hq, hkv, d, rotary, out_dtype=torch.bfloat16).cpu().double()
+    assert torch.equal(q, q2) and torch.equal(kd.cpu(), kd2.cpu()) and torch.equal(vd.cpu(), vd2.cpu())
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 @pytest.mark.parametrize("hq,hkv,d,rotary", [(4, 2, 16, 16), (6, 1, 32, 32), (3, 3, 48, 48), (2, 1, 64, 32)])
 def test_rope_append(dtype, hq, hkv, d, rotary):
