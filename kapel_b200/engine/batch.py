@@ -140,7 +140,9 @@ class StepBatch:
     """Device views of a step. `memo` holds what parts share within the step (rotary tables)."""
 
     def __init__(self, plan: Plan, ids: Sequence[int], want_rows: Sequence[int], device, chunk: int,
-                 fixed_slots: Optional[int] = None):
+                 fixed_slots: Optional[int] = None, into: Optional[torch.Tensor] = None):
+        """`into`: a device buffer of a recorded pass of the same shape (the same number of values), to
+        be rewritten in place instead of a new one."""
         self.plan = plan
         self.rows = plan.rows
         self.entries = len(plan.entries)
@@ -164,7 +166,15 @@ class StepBatch:
             flat[at : at + p.size] = p
             at += p.size
         self.h2d_bytes = total * 4
-        dev = host.to(device, non_blocking=True)
+        if into is not None:
+            if into.numel() != host.numel():
+                raise ValueError(f"a recorded pass of {into.numel()} input values was offered a pass of {host.numel()}")
+            into.copy_(host, non_blocking=True)
+            dev = into
+        else:
+            dev = host.to(device, non_blocking=True)
+        self.dev = dev
+        self.sizes = sizes
         self._host = host                 # keeps the pinned buffer alive until the copy is done
         self._assign(dev, sizes, [g.block_table.shape for g in plan.groups])
 

@@ -97,9 +97,10 @@ class Engine:
         self.steps = 0
         self.last_h2d_bytes = 0
         self._request_ids = itertools.count()
-        from .graph import DecodeGraphs
+        from .graph import DecodeGraphs, PromptGraphs
 
         self.graphs = DecodeGraphs(self, max_sequences) if (graphs and self.model.graph_safe()) else None
+        self.prompt_graphs = PromptGraphs(self, self.graphs) if self.graphs is not None else None
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -178,8 +179,8 @@ class Engine:
         in the order of the entries and of each entry's `want`.
 
         The step is enqueued on the current stream and not waited for. The logits of a pass in
-        which every request brings one token may be a view of a recorded step's output buffer,
-        which the next such pass overwrites: read them (or enqueue what reads them, on the same
+        which every request brings one token, or of a pass whose shape was seen before, may be a
+        view of a recorded step's output buffer, which the next such pass overwrites: read them (or enqueue what reads them, on the same
         stream) before the next step, or clone them. A caller may enqueue step after step without
         synchronising; the inputs of recorded steps are staged so that this is safe, and the
         host is held back once it is two recorded steps ahead of the device."""
@@ -193,6 +194,9 @@ class Engine:
             # A pass of single tokens whose logits are all wanted goes through a recording.
             if self.graphs is not None and plan.rows == len(entries) and len(want_rows) == plan.rows:
                 logits = self.graphs.run(plan, ids)
+            # A pass with prompt portions whose shape was seen before goes through a recording too.
+            if logits is None and self.prompt_graphs is not None and self.graphs is not None:
+                logits = self.prompt_graphs.run(plan, ids, want_rows)
             if logits is None:
                 batch = StepBatch(plan, ids, want_rows, self.device, self.chunk)
                 self.last_h2d_bytes = batch.h2d_bytes
@@ -282,7 +286,7 @@ class Engine:
 
     @property
     def recorded_passes(self) -> int:
-        return self.graphs.replays if self.graphs is not None else 0
+        return (self.graphs.replays if self.graphs is not None else 0) + (self.prompt_graphs.replays if self.prompt_graphs is not None else 0)
 
     def end(self, seq_id) -> None:
         """The request is finished: everything it holds goes back."""
