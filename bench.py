@@ -238,8 +238,10 @@ class Bench:
             once()
         ms = min(self.timed(once, 1) for _ in range(3))
         flops = prefill_flops(self.cfg, self.layers, PREFILL_TOKENS)
+        pg = getattr(self.engine, "prompt_graphs", None)
         return {"value": PREFILL_TOKENS / ms * 1e3, "tokens": PREFILL_TOKENS, "ms": ms,
-                "frac": flops / (ms * 1e-3) / (self.pk["bf16_tflops"] * 1e12)}
+                "frac": flops / (ms * 1e-3) / (self.pk["bf16_tflops"] * 1e12),
+                "recorded": bool(pg is not None and pg.replays > 0)}      # the pass's shape was seen before: the engine replays its recording
 
     def decode_point(self, batch, check_logits=False):
         """dict: device ms a step, e2e ms a step, launches a step, h2d and d2h bytes a step, hbm fraction."""
