@@ -785,16 +785,18 @@ static int launch_skinny_glu(const CUtensorMap& map_w, const CUtensorMap& map_x,
         if (e != cudaSuccess) return fail("gemm_skinny_glu: cannot have %d bytes of shared memory: %s", SkGlu<NP>::SMEM, cudaGetErrorString(e));
         attr_set = true;
     }
-    launch_dependent(gemm_skinny_glu_kernel<NP>, dim3((n + SKG_ROWS - 1) / SKG_ROWS), dim3(TC_THREADS), (size_t)SkGlu<NP>::SMEM, s, map_w, map_x, c, m, n, k, act KB_TL_SLOT(gemm, 1, n, k));
+    launch_dependent_if(m <= DEPENDENT_ROWS, gemm_skinny_glu_kernel<NP>, dim3((n + SKG_ROWS - 1) / SKG_ROWS), dim3(TC_THREADS), (size_t)SkGlu<NP>::SMEM, s, map_w, map_x, c, m, n, k, act KB_TL_SLOT(gemm, 1, n, k));
     return check_launch("gemm_skinny_glu");
 }
 
-// (splits, k tiles a split) for a weight [n, k]: about two blocks a multiprocessor, a
-// split at least four k tiles long. Depends on n and k only.
-static void skinny_plan(int n, int k, int sms, int* splits, int* k_tiles_per_split) {
+// (splits, k tiles a split) for a weight [n, k]: about two blocks a multiprocessor (one beyond 64
+// rows), a split at least four k tiles long. Depends on n, k and on whether there are more than 64 rows.
+static void skinny_plan(int n, int k, int sms, int* splits, int* k_tiles_per_split, int m = 1) {
     const int n_tiles = (n + SK2_BM - 1) / SK2_BM;
     const int k_tiles = (k + SK2_BK - 1) / SK2_BK;
-    int s = (2 * sms + n_tiles / 2) / n_tiles;
+    // beyond 64 rows a block fills a multiprocessor's shared memory alone, and the partial sums
+    // (rows x columns x splits floats) begin to weigh beside the weights: half as many splits
+    int s = ((m <= 64 ? 2 : 1) * sms + n_tiles / 2) / n_tiles;
     const int max_splits = (k_tiles + 3) / 4;
     if (s > max_splits) s = max_splits;
     if (s < 1) s = 1;
@@ -827,7 +829,7 @@ static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
         attr_set = true;
     }
     dim3 grid((n + SK2_BM - 1) / SK2_BM, splits);
-    launch_dependent(gemm_skinny_tcgen05_kernel<NP>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map_w, map_x, c, c_dt, splits > 1 ? partial : (float*)nullptr, m, n, k, per, epi, cap KB_TL_SLOT(gemm, 0, n, k));
+    launch_dependent_if(m <= DEPENDENT_ROWS, gemm_skinny_tcgen05_kernel<NP>, grid, dim3(TC_THREADS), (size_t)SMEM, s, map_w, map_x, c, c_dt, splits > 1 ? partial : (float*)nullptr, m, n, k, per, epi, cap KB_TL_SLOT(gemm, 0, n, k));
     return check_launch("gemm_skinny_tcgen05");
 }
 
@@ -954,10 +956,16 @@ extern "C" int kb_gemm_skinny_glu(void* c, const void* a, const void* w, int m, 
     return launch_skinny_glu<64>(map_w, map_x, (bf16*)c, m, n, k, act, s);
 }
 
-// Partial sums the skinny kernel leaves for a weight [n, k] (1: it writes the result itself).
+// Partial sums the skinny kernel leaves for a weight [n, k] and up to 64 rows (1: it writes the result itself).
 extern "C" int kb_gemm_skinny_splits(int n, int k) {
     int splits, per;
     skinny_plan(n, k, skinny_sms(), &splits, &per);
+    return splits;
+}
+// The same for m rows (up to 256).
+extern "C" int kb_gemm_skinny_splits_for(int m, int n, int k) {
+    int splits, per;
+    skinny_plan(n, k, skinny_sms(), &splits, &per, m);
     return splits;
 }
 
@@ -965,21 +973,23 @@ extern "C" int kb_gemm_skinny_splits(int n, int k) {
 // its epilogue. With more: `partial` (f32 [splits, m, n]) gets the partial sums and c is not touched.
 extern "C" int kb_gemm_skinny(void* c, int c_dt, float* partial, const void* a, const void* w, int m, int n, int k,
                               int epilogue, float cap, void* stream) {
-    KB_REQUIRE(m > 0 && m <= 64 && n > 0 && k > 0, "gemm_skinny: m %d (1..64), n %d, k %d", m, n, k);
+    KB_REQUIRE(m > 0 && m <= 256 && n > 0 && k > 0, "gemm_skinny: m %d (1..256), n %d, k %d", m, n, k);
     KB_REQUIRE(k % 8 == 0, "gemm_skinny: k = %d must be a multiple of 8 (16-byte rows)", k);
     KB_REQUIRE(epilogue == 0 || (epilogue == 1 && cap > 0.f), "gemm_skinny: epilogue %d with cap %g", epilogue, cap);
     KB_REQUIRE(((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0, "gemm_skinny: operands must be 16-byte aligned");
     int splits, per;
-    skinny_plan(n, k, skinny_sms(), &splits, &per);
+    skinny_plan(n, k, skinny_sms(), &splits, &per, m);
     KB_REQUIRE(splits == 1 || partial != nullptr, "gemm_skinny: %d splits over K need room for partial sums", splits);
     KB_REQUIRE(splits > 1 || (c != nullptr && (c_dt == KB_DT_F32 || c_dt == KB_DT_BF16)), "gemm_skinny: no output");
     KB_REQUIRE(splits == 1 || epilogue == 0, "gemm_skinny: an epilogue cannot be applied to partial sums");
-    const int np = m <= 16 ? 16 : (m <= 32 ? 32 : 64);
+    const int np = m <= 16 ? 16 : (m <= 32 ? 32 : (m <= 64 ? 64 : (m <= 128 ? 128 : 256)));
     CUtensorMap map_w, map_x;
     if (int e = encode_map_bf16(&map_w, w, n, k, k, SK2_BM)) return e;
     if (int e = encode_map_bf16(&map_x, a, m, k, k, np)) return e;
     cudaStream_t s = (cudaStream_t)stream;
     if (np == 16) return launch_skinny<16>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
     if (np == 32) return launch_skinny<32>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
-    return launch_skinny<64>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
+    if (np == 64) return launch_skinny<64>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
+    if (np == 128) return launch_skinny<128>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
+    return launch_skinny<256>(map_w, map_x, c, c_dt, partial, m, n, k, splits, per, epilogue, cap, s);
 }

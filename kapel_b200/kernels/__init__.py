@@ -366,6 +366,24 @@ def add_rmsnorm(residual, branch, post, nxt, out_dtype):
     return h
 
 
+# Up to 64 rows, and up to SKINNY_ROWS where the kernels for many rows would have few tiles, a
+# product streams the weights once through many blocks that split K (the "few-rows" kernels, whose
+# MMA takes the rows as its N, up to 256). With one or two row tiles and a narrow weight the kernels
+# for many rows leave most multiprocessors idle: the way down of Gemma 2 2B at 128 rows took 50 us by
+# 9 blocks against 15 us, o 17 against 7; a wide weight has tiles enough (gate|up: 22 us either way).
+SKINNY_ROWS = int(_os.environ.get("KAPEL_B200_SKINNY_ROWS", "256"))
+SKINNY_TILES = 24          # tiles of 128 x 256 below which the few-rows kernel is taken beyond 64 rows
+
+
+def few_rows_product(m: int, n: int) -> bool:
+    """Whether a product of m rows by a weight of n rows goes to the few-rows kernels."""
+    if m <= 0:
+        return False
+    if m <= 64:
+        return True
+    return m <= SKINNY_ROWS and -(-m // 128) * -(-n // 256) <= SKINNY_TILES
+
+
 def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = None, softcap: Optional[float] = None,
          keep_split: bool = False):
     """a [m, k] . w [n, k]^T -> [m, n]; float32 x float32 in true 32-bit, bfloat16 x bfloat16 on
@@ -389,8 +407,8 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             out = cast(out, out_dtype)
         return out
     out_dtype = out_dtype or torch.bfloat16
-    if 0 < m <= 64 and GEMM_SMALL == "skinny":
-        splits = int(lib.kb_gemm_skinny_splits(n, k))
+    if few_rows_product(m, n) and GEMM_SMALL == "skinny":
+        splits = int(lib.kb_gemm_skinny_splits_for(m, n, k))
         if splits == 1:
             out = _fresh((m, n), out_dtype, a.device)
             _check(lib.kb_gemm_skinny(_ptr(out), _dt(out, "gemm output"), None, _ptr(a), _ptr(w), m, n, k, epi, _f(cap), _stream()))
