@@ -50,7 +50,7 @@ def test_products_refuse_rows_that_are_no_multiple_of_16_bytes_and_unknown_choic
     refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 128, 64, 36, 0, 0.0, 0, None), "gemm_tcgen05", "multiple of 8")
     refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 128, 64, 64, 0, 0.0, 5, None), "kernel choice 5")
     refused(lib, lib.kb_gemm_tcgen05(A, BF16, A, A, 0, 64, 64, 0, 0.0, 0, None), "m 0")
-    refused(lib, lib.kb_gemm_skinny(A, BF16, None, A, A, 65, 64, 64, 0, 0.0, None), "gemm_skinny", "m 65 (1..64)")
+    refused(lib, lib.kb_gemm_skinny(A, BF16, None, A, A, 257, 64, 64, 0, 0.0, None), "gemm_skinny", "m 257 (1..256)")
     refused(lib, lib.kb_gemm_skinny(A, BF16, None, A + 8, A, 8, 64, 64, 0, 0.0, None), "16-byte aligned")
     refused(lib, lib.kb_gemm_f32(A, A, A, 4, 64, 0, 0, 0.0, None), "gemm_f32", "k 0")
 
