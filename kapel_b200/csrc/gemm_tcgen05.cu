@@ -224,7 +224,9 @@ __device__ __forceinline__ void tc_epilogue(uint32_t lanes, int row, int n0, voi
 template <int TC_STAGES, int EPI>
 __global__ void __launch_bounds__(TC_THREADS, TC_STAGES == 2 ? 2 : 1)
 gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_constant__ CUtensorMap map_w,
-                    void* __restrict__ c, int c_dt, int m, int n, int k, float cap) {
+                    void* __restrict__ c, int c_dt, int m, int n, int k, float cap, int k_tiles_a_split) {
+    // k_tiles_a_split > 0: blockIdx.z takes that many k tiles from its multiple on and leaves its
+    // sums, float32, in slice blockIdx.z of c [splits, m, n] (few tiles and a long K: see kb_gemm_tcgen05_split)
     extern __shared__ unsigned char tc_smem_raw[];
     // 1024-byte alignment for the 128-byte swizzle
     unsigned char* smem = reinterpret_cast<unsigned char*>(((uintptr_t)tc_smem_raw + 1023) & ~(uintptr_t)1023);
@@ -235,7 +237,10 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int m0 = blockIdx.x * TC_BM, n0 = blockIdx.y * TC_BN;
-    const int k_tiles = (k + TC_BK - 1) / TC_BK;
+    const int k_tiles_all = (k + TC_BK - 1) / TC_BK;
+    const int kt0 = k_tiles_a_split > 0 ? (int)blockIdx.z * k_tiles_a_split : 0;
+    const int k_tiles = k_tiles_a_split > 0 ? min(k_tiles_a_split, k_tiles_all - kt0) : k_tiles_all;
+    if (k_tiles_a_split > 0) c = static_cast<float*>(c) + (size_t)blockIdx.z * m * n;
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < TC_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
@@ -260,8 +265,8 @@ gemm_tcgen05_kernel(const __grid_constant__ CUtensorMap map_a, const __grid_cons
                 if (kt >= TC_STAGES && !tc_mbar_wait(empty + s, (uint32_t)((kt / TC_STAGES) - 1) & 1u)) { failed = true; break; }
                 unsigned char* a_dst = smem + s * TC_STAGE_BYTES;
                 tc_mbar_expect_tx(full + s, TC_STAGE_BYTES);
-                tc_tma_load_2d(a_dst, &map_a, kt * TC_BK, m0, full + s);
-                tc_tma_load_2d(a_dst + TC_A_BYTES, &map_w, kt * TC_BK, n0, full + s);
+                tc_tma_load_2d(a_dst, &map_a, (kt0 + kt) * TC_BK, m0, full + s);
+                tc_tma_load_2d(a_dst + TC_A_BYTES, &map_w, (kt0 + kt) * TC_BK, n0, full + s);
             }
         }
     } else if (warp == 1) {
@@ -835,14 +840,14 @@ static int launch_skinny(const CUtensorMap& map_w, const CUtensorMap& map_x, voi
 
 template <int STAGES, int EPI>
 static int launch_single(const CUtensorMap& map_a, const CUtensorMap& map_w, void* c, int c_dt, int m, int n, int k, float cap,
-                         dim3 grid, cudaStream_t s) {
+                         dim3 grid, cudaStream_t s, int k_tiles_a_split = 0) {
     static bool attr_set = false;
     if (!attr_set) {
         const cudaError_t e = cudaFuncSetAttribute(gemm_tcgen05_kernel<STAGES, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, tc_smem_bytes(STAGES));
         if (e != cudaSuccess) return fail("gemm_tcgen05: cannot have %d bytes of shared memory: %s", tc_smem_bytes(STAGES), cudaGetErrorString(e));
         attr_set = true;
     }
-    launch_dependent_if(false, gemm_tcgen05_kernel<STAGES, EPI>, grid, dim3(TC_THREADS), (size_t)tc_smem_bytes(STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap);
+    launch_dependent_if(false, gemm_tcgen05_kernel<STAGES, EPI>, grid, dim3(TC_THREADS), (size_t)tc_smem_bytes(STAGES), s, map_a, map_w, c, c_dt, m, n, k, cap, k_tiles_a_split);
     return check_launch("gemm_tcgen05");
 }
 
@@ -921,6 +926,42 @@ extern "C" int kb_gemm_tcgen05(void* c, int c_dt, const void* a, const void* w, 
                     : launch_single<4, EPI_NONE>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s);
     return many ? launch_single<2, EPI_SOFTCAP>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s)
                 : launch_single<4, EPI_SOFTCAP>(map_a, map_w, c, c_dt, m, n, k, cap, grid, s);
+}
+
+// How many slices of K `kb_gemm_tcgen05_split` cuts a product of m rows into (1: it is not worth cutting).
+// A prompt portion of a few hundred rows by a narrow weight has a handful of 128 x 256 tiles, each
+// walking all of K on its own multiprocessor (the way down of Gemma 2 2B at 512 rows: 36 tiles, 50 us);
+// cut over K the tiles fill the GPU, at the price of float32 partial sums that the reader adds up.
+static void split_plan(int m, int n, int k, int* splits, int* per) {
+    const long long tiles = (long long)((m + TC_BM - 1) / TC_BM) * ((n + TC_BN - 1) / TC_BN);
+    const int k_tiles = (k + TC_BK - 1) / TC_BK;
+    int s = (int)(skinny_sms() / (tiles > 0 ? tiles : 1));
+    const int most = k_tiles / 8;                           // a slice is at least eight k tiles (512 of K) long
+    if (s > most) s = most;
+    if (s > 16) s = 16;
+    if (s < 1) s = 1;
+    *per = (k_tiles + s - 1) / s;
+    *splits = (k_tiles + *per - 1) / *per;
+}
+extern "C" int kb_gemm_tcgen05_splits(int m, int n, int k) {
+    int splits, per;
+    split_plan(m, n, k, &splits, &per);
+    return splits;
+}
+// a: bf16 [m,k]; w: bf16 [n,k]; partial: f32 [kb_gemm_tcgen05_splits(m, n, k), m, n], the slices' sums.
+extern "C" int kb_gemm_tcgen05_split(float* partial, const void* a, const void* w, int m, int n, int k, void* stream) {
+    KB_REQUIRE(m > 0 && n > 0 && k > 0, "gemm_tcgen05_split: m %d, n %d, k %d", m, n, k);
+    KB_REQUIRE(k % 8 == 0, "gemm_tcgen05_split: k = %d must be a multiple of 8 (16-byte rows)", k);
+    KB_REQUIRE(partial != nullptr && ((uintptr_t)a & 15) == 0 && ((uintptr_t)w & 15) == 0 && ((uintptr_t)partial & 15) == 0,
+               "gemm_tcgen05_split: operands must be there and 16-byte aligned");
+    int splits, per;
+    split_plan(m, n, k, &splits, &per);
+    CUtensorMap map_a, map_w;
+    if (int e = encode_map_bf16(&map_a, a, m, k, k, TC_BM)) return e;
+    if (int e = encode_map_bf16(&map_w, w, n, k, k, TC_BN)) return e;
+    dim3 grid((m + TC_BM - 1) / TC_BM, (n + TC_BN - 1) / TC_BN, splits);
+    KB_REQUIRE(grid.y <= 65535, "gemm_tcgen05_split: %d columns is too many for one launch", n);
+    return launch_single<4, EPI_NONE>(map_a, map_w, partial, KB_DT_F32, m, n, k, 0.f, grid, (cudaStream_t)stream, per);
 }
 
 // The gated unit in the product's epilogue: a bf16 [m,k]; w bf16 [2 n, k], gate rows then up rows;

@@ -522,8 +522,8 @@ extern "C" int kb_add_rmsnorm(float* residual, const void* branch, int branch_dt
         else launch_dependent_if(rows <= DEPENDENT_ROWS, add_rmsnorm_bf16x8_kernel<4>, dim3(rows), dim3(tv), 0, s, residual, b, wp, eps_post, off_post, wn, eps_next, off_next, out, width);
         return check_launch("add_rmsnorm");
     }
-    // float32 partial sums of few rows (a decode step): the kernel that keeps many slices in flight
-    if (branch_dt == KB_DT_F32 && w_dt == KB_DT_BF16 && h_dt == KB_DT_BF16 && rows <= 256 && width % 4 == 0 && width <= 4 * 4 * 1024 &&
+    // float32 partial sums of a product split over K (a decode step, or a prompt portion of a few hundred rows): a block a row
+    if (branch_dt == KB_DT_F32 && w_dt == KB_DT_BF16 && h_dt == KB_DT_BF16 && rows <= 65535 && width % 4 == 0 && width <= 4 * 4 * 1024 &&
         (split_stride % 4) == 0 && (((uintptr_t)residual | (uintptr_t)branch | (uintptr_t)h) & 15) == 0 &&
         (((uintptr_t)w_post | (uintptr_t)w_next) & 7) == 0) {
         const int chunks = width / 4;

@@ -425,6 +425,13 @@ def gemm(a: torch.Tensor, w: torch.Tensor, out_dtype: Optional[torch.dtype] = No
             partials = _fresh((splits, m, n), torch.float32, a.device)
             _check(lib.kb_gemm_bf16_partial(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
             return SplitSum(partials)
+    if keep_split and softcap is None and m > 64 and GEMM_LARGE == "tcgen05":
+        # a few hundred rows by a narrow weight: few tiles, each walking all of K; cut over K instead
+        splits = int(lib.kb_gemm_tcgen05_splits(m, n, k))
+        if splits > 1:
+            partials = _fresh((splits, m, n), torch.float32, a.device)
+            _check(lib.kb_gemm_tcgen05_split(_ptr(partials), _ptr(a), _ptr(w), m, n, k, _stream()))
+            return SplitSum(partials)
     out = _fresh((m, n), out_dtype, a.device)
     if m > 64 and GEMM_LARGE in _TCGEN05_KERNELS:
         _check(lib.kb_gemm_tcgen05(_ptr(out), _dt(out, "gemm output"), _ptr(a), _ptr(w), m, n, k, epi, _f(cap),

@@ -716,6 +716,30 @@ def test_add_rmsnorm_over_split_sums_at_other_sizes(rows, width, splits):
             assert rel_err(h_all[:1].cpu().double().numpy(), h_one.cpu().double().numpy()) < 1e-2
 
 
+@pytest.mark.parametrize("m", [65, 130, 300, 512, 1000])
+@pytest.mark.parametrize("n,k", [(2304, 9216), (2304, 2048), (4096, 2304), (72, 1000 * 8), (520, 4104)])
+def test_products_of_a_few_hundred_rows_split_over_k(m, n, k):
+    """A prompt portion's product by a narrow weight is cut over K (by the few-rows kernels up to 256
+    rows, by the many-rows kernel beyond) and comes back as partial sums when the caller can take
+    them; finished, they are the product, and the readers that add slices up themselves get the same."""
+    a, w = rnd(m, k, seed=m + n, dtype=torch.bfloat16), rnd(n, k, seed=m + k, dtype=torch.bfloat16, scale=0.05)
+    want = a.double() @ w.double().T
+    kept = K().gemm(dev(a), dev(w), keep_split=True)
+    K().check_async_errors()
+    got = K().finish(kept, torch.float32).cpu().double() if isinstance(kept, K().SplitSum) else kept.cpu().double()
+    assert rel_err(got.numpy(), want.numpy()) < (2e-5 if isinstance(kept, K().SplitSum) else 1e-2)
+    whole = K().gemm(dev(a), dev(w), out_dtype=torch.float32).cpu().double()
+    assert rel_err(whole.numpy(), want.numpy()) < 2e-5
+    if isinstance(kept, K().SplitSum) and n == 2304:
+        res = rnd(m, n, seed=3)
+        w1, w2 = rnd(n, seed=4, dtype=torch.bfloat16, scale=0.1), rnd(n, seed=5, dtype=torch.bfloat16, scale=0.1)
+        r = dev(res.clone())
+        h = K().add_rmsnorm(r, kept, (dev(w1), 1e-6, 1.0), (dev(w2), 1e-6, 1.0), torch.bfloat16)
+        want_r = res.double() + P.rms_norm(want, w1.double(), 1e-6)
+        assert rel_err(r.cpu().double().numpy(), want_r.numpy()) < 1e-5
+        assert rel_err(h.cpu().double().numpy(), P.rms_norm(want_r, w2.double(), 1e-6).numpy()) < 1e-2
+
+
 @pytest.mark.parametrize("m", [1, 7, 8, 9, 16])
 def test_gemm_bf16_rows_up_to_16_do_not_depend_on_the_batch(m):
     a, w = rnd(16, 2304, seed=38, dtype=torch.bfloat16), rnd(520, 2304, seed=39, dtype=torch.bfloat16)
