@@ -349,6 +349,36 @@ def test_recorded_prompt_passes_equal_eager_ones_bit_for_bit(folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_prompts_of_any_length_share_recordings_of_round_lengths(folders, dtype):
+    """A prompt alone in its pass is rounded up to a round number of rows, so that prompts of 66 to 96
+    tokens are one shape: the third such prompt is replayed from the recording the second made. The
+    rows added write nothing into the cache and are seen by nobody: every request's logits at its last
+    prompt token and over the tokens decoded after it are the plain implementation's, and the pages
+    are all given back."""
+    from kapel_b200.engine import Engine, StepEntry
+
+    raw, _ = TINY["B"]                                     # 256 positions
+    rng = np.random.default_rng(61)
+    lengths = [70, 96, 67, 91, 130, 150, 131]
+    engine = Engine.from_dir(folders["B"], dtype=dtype, max_tokens=1024, max_sequences=4)
+    for i, n in enumerate(lengths):
+        toks = random_tokens(rng, n + 6, raw["vocab_size"])
+        want = plain_logits(folders["B"], toks, embed_scale_for(raw, dtype))
+        name = f"q{i}"
+        got = [engine.step([StepEntry(name, toks[:n], [n - 1])]).float().cpu().numpy()[0]]
+        for t in range(n, n + 6):
+            got.append(engine.step([StepEntry(name, [toks[t]], [0])]).float().cpu().numpy()[0])
+        for j, row in enumerate(got):
+            ref = want[n - 1 + j]
+            assert np.abs(row - ref).max() / np.abs(ref).max() < TOL[dtype], (n, j)
+        engine.end(name)
+        engine.cache.check()
+    pg = engine.prompt_graphs
+    assert len(pg.recorded) == 2 and pg.replays == 5, (len(pg.recorded), pg.replays)      # 96 rows: 4 prompts, 3 replays; 160 rows: 3 prompts, 2 replays
+    assert engine.cache.free_pages() == engine.cache.total_pages()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_replay_program(folders, dtype):
     """bin/trace_run as a program: whole, then portions beside decoded tokens, pages used again."""
     raw, _ = TINY["A"]
