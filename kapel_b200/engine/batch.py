@@ -66,11 +66,11 @@ def decode_split(pairs: int, longest: int, sms: int, window: Optional[int] = Non
 PROMPT_KERNEL_COSTS = {"mma": (0.5, 1.0, 4.5, 1), "tcgen05": (18.0, 15.0, 1.2, 1), "tcgen05_pair": (32.0, 18.0, 0.85, 2)}
 
 
-def prompt_costs_of(prompt_kernel: str, head_dim: int) -> str:
+def prompt_costs_of(prompt_kernel: str, head_dim: int, pairs: Optional[int] = None) -> str:
     """The entry of PROMPT_KERNEL_COSTS for the kernel that will run prompt portions of this head size."""
     from .. import kernels as K
 
-    if prompt_kernel == "tcgen05" and K.attention_tile_rows(False, prompt_kernel, head_dim) > 128:
+    if prompt_kernel == "tcgen05" and K.attention_tile_rows(False, prompt_kernel, head_dim, pairs) > 128:
         return "tcgen05_pair"
     return prompt_kernel
 
@@ -202,10 +202,12 @@ class StepBatch:
             from .. import kernels as K
 
             plan = self.plan
-            costs_of = prompt_costs_of(prompt_kernel, head_dim)
+            pairs = K.prompt_pairs(plan.rows, int(plan.row_count.max()))
+            self.pairs = pairs                              # the attention part hands it to the kernel
+            costs_of = prompt_costs_of(prompt_kernel, head_dim, pairs)
             most = int(plan.q_len.max()) * heads_per_kv
             decode = most if most <= K.attention_mma_rows(True) else 0      # rows a tile in decode mode, else 0
-            per_tile = max(1, K.attention_tile_rows(bool(decode), prompt_kernel, head_dim) // heads_per_kv)
+            per_tile = max(1, K.attention_tile_rows(bool(decode), prompt_kernel, head_dim, pairs) // heads_per_kv)
             arrays = cut_tiles(plan.q_start, plan.q_len, per_tile)
             n = arrays[0].size
             host = torch.from_numpy(np.concatenate(arrays)).pin_memory() if self.ids.is_cuda else torch.from_numpy(np.concatenate(arrays))

@@ -512,11 +512,22 @@ def attention_mma_rows(decode: bool) -> int:
     return int(library().kb_attention_mma_rows(int(bool(decode))))
 
 
-def attention_tile_rows(decode: bool, prompt_kernel: str = "mma", d: int = 0) -> int:
+def prompt_pairs(rows: int, longest: int) -> int:
+    """The pairs setting for a pass of `rows` query rows whose longest request sees `longest` keys:
+    ATTENTION_PAIRS, except that a small pass runs on single blocks (setting 0) where pairs would be
+    the default only for head size 256: a pair's launch costs a few microseconds more than it saves
+    until there are some hundreds of keys to walk (128 tokens at Gemma 2 2B sizes: 13.4 us on single
+    blocks, 17.2 us on pairs; 2,048 tokens: 55 against 42)."""
+    if ATTENTION_PAIRS == 2 and rows < 768 and longest < 2048:
+        return 0
+    return ATTENTION_PAIRS
+
+
+def attention_tile_rows(decode: bool, prompt_kernel: str = "mma", d: int = 0, pairs: Optional[int] = None) -> int:
     """Rows a tile holds for the kernel that will run: the decode kernel's, the mma.sync prompt
     kernel's, or the tcgen05 prompt kernel's (twice as many where pairs of blocks run it)."""
     if not decode and prompt_kernel == "tcgen05":
-        return int(library().kb_attention_tc_rows(int(d), int(ATTENTION_PAIRS)))
+        return int(library().kb_attention_tc_rows(int(d), int(ATTENTION_PAIRS if pairs is None else pairs)))
     return attention_mma_rows(decode)
 
 
@@ -534,7 +545,7 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
 
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
-                        relative: bool = False) -> torch.Tensor:
+                        relative: bool = False, pairs: Optional[int] = None) -> torch.Tensor:
     """Attention over the paged cache on tensor cores (bfloat16). `tiles` = (tile_entry, tile_row0,
     tile_nq) int32 device tensors: each tile is up to `attention_mma_rows(decode) // group` tokens of
     one request at consecutive positions. `decode` is 0 for prompt portions, else the most rows
@@ -564,7 +575,7 @@ def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page
             lib.kb_attention_tc(_ptr(out), _ptr(q), _ptr(k_table), _ptr(v_table), _ptr(block_table), _ptr(row_count),
                                 _ptr(tile_entry), _ptr(tile_row0), _ptr(tile_nq), n_tiles, rows, hq, hkv, d, int(page_size),
                                 int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots), _f(scale),
-                                _f(softcap or 0.0), _ptr(scratch), int(ATTENTION_PAIRS), _stream())
+                                _f(softcap or 0.0), _ptr(scratch), int(ATTENTION_PAIRS if pairs is None else pairs), _stream())
         )
         if slots > 1:
             _check(lib.kb_attention_mma_combine(_ptr(out), _ptr(row_count), _ptr(scratch), rows, hq, d, int(window or 0), int(split),

@@ -62,6 +62,7 @@ class Attention(Part):
             y = K.paged_attention_mma(
                 q, k_table, v_table, group.block_table, batch.row_count, tiles,
                 self.ctx.page_size, s.window, s.scale, s.softcap, decode, split, slots, relative,
+                pairs=getattr(batch, "pairs", None),
             )
         else:                   # the 32-bit path, and sizes the tensor-core kernel does not take
             y = K.paged_attention_rows(
