@@ -127,11 +127,56 @@ sample_kernel(int* __restrict__ tokens, const float* __restrict__ logits, const 
 
 using namespace kb;
 
+// Greedy choice of a few rows over a large vocabulary, in two steps: SMP_PARTS blocks a row find the
+// first largest value of their share of the columns, then one block a row picks among those (one
+// block a row alone read a 1 MB row from one multiprocessor: 12 us at batch 8 against 4).
+constexpr int SMP_PARTS = 32;
+__global__ void __launch_bounds__(256) argmax_parts_kernel(int2* __restrict__ parts, const float* __restrict__ logits, int vocab) {
+    __shared__ Best sbest[32];
+    const int r = blockIdx.x, part = blockIdx.y;
+    const float* row = logits + (size_t)r * vocab;
+    const int per = (vocab + SMP_PARTS - 1) / SMP_PARTS;
+    const int begin = min(vocab, part * per), end = min(vocab, begin + per);
+    Best mine; mine.v = 0.f; mine.i = -1;
+    for (int i = begin + threadIdx.x; i < end; i += blockDim.x) {
+        const float v = row[i];
+        if (v != v) continue;
+        Best c; c.v = v; c.i = i;
+        mine = better(mine, c);
+    }
+    const Best top = block_best(mine, sbest);
+    if (threadIdx.x == 0) parts[(size_t)r * SMP_PARTS + part] = make_int2(__float_as_int(top.v), top.i);
+}
+__global__ void __launch_bounds__(32) argmax_pick_kernel(int* __restrict__ tokens, const int2* __restrict__ parts) {
+    const int2 e = parts[(size_t)blockIdx.x * SMP_PARTS + threadIdx.x];
+    Best x; x.v = __int_as_float(e.x); x.i = e.y;
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) {
+        Best y;
+        y.v = __shfl_xor_sync(0xffffffffu, x.v, o);
+        y.i = __shfl_xor_sync(0xffffffffu, x.i, o);
+        x = better(x, y);
+    }
+    if (threadIdx.x == 0) tokens[blockIdx.x] = x.i < 0 ? 0 : x.i;
+}
+
+// Floats of scratch memory the greedy choice of `rows` rows wants for its two steps (0: one step).
+extern "C" long long kb_sample_scratch_floats(int rows, int vocab) {
+    return (rows > 0 && rows * SMP_PARTS <= 4096 && vocab >= 65536) ? (long long)rows * SMP_PARTS * 2 : 0;
+}
+
 extern "C" int kb_sample(int* tokens, const float* logits, const float* temperature, const float* uniform, int rows,
-                         int vocab, void* stream) {
+                         int vocab, float* scratch, void* stream) {
     KB_REQUIRE(rows >= 0 && vocab > 0, "sample: rows %d, vocab %d", rows, vocab);
     KB_REQUIRE(temperature == nullptr || uniform != nullptr, "sample: a temperature needs uniform numbers");
     if (rows == 0) return 0;
+    if (temperature == nullptr && scratch != nullptr && kb_sample_scratch_floats(rows, vocab) > 0) {
+        int2* parts = reinterpret_cast<int2*>(scratch);
+        argmax_parts_kernel<<<dim3(rows, SMP_PARTS), 256, 0, (cudaStream_t)stream>>>(parts, logits, vocab);
+        if (int e = check_launch("sample")) return e;
+        argmax_pick_kernel<<<rows, 32, 0, (cudaStream_t)stream>>>(tokens, parts);
+        return check_launch("sample");
+    }
     sample_kernel<<<rows, SMP_THREADS, 0, (cudaStream_t)stream>>>(tokens, logits, temperature, uniform, vocab);
     return check_launch("sample");
 }

@@ -60,7 +60,7 @@ def library():
                 path = ensure_built()
                 lib = ctypes.CDLL(str(path))
                 lib.kb_last_error.restype = ctypes.c_char_p
-                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats"):
+                for name in ("kb_gemm_bf16_scratch_floats", "kb_paged_attention_scratch_floats", "kb_attention_mma_scratch_floats", "kb_sample_scratch_floats"):
                     getattr(lib, name).restype = ctypes.c_longlong
                 lib.kb_launch_count.restype = ctypes.c_ulonglong
                 lib.kb_set_pdl(1 if PDL else 0)
@@ -599,7 +599,10 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
         _need(temperature, "sample temperature", torch.float32, (rows,))
         _need(uniform, "sample uniform", torch.float32, (rows,))
     out = _fresh((rows,), torch.int32, logits.device)
-    _check(library().kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _stream()))
+    lib = library()
+    need = int(lib.kb_sample_scratch_floats(rows, vocab)) if temperature is None else 0
+    scratch = _fresh((need,), torch.float32, logits.device) if need else None
+    _check(lib.kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _ptr(scratch), _stream()))
     return out
 
 

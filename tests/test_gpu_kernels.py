@@ -410,6 +410,16 @@ def test_sample_greedy_rules():
     big[2, 255999] = 100.0
     got = K().sample(dev(big)).cpu().tolist()
     assert got == big.argmax(dim=1).tolist()
+    # the two-step choice of a large vocabulary: a tie across two blocks' shares (the first wins), a
+    # row of NaN but one value, a row of nothing but NaN, the largest in the last column
+    big = rnd(5, 256000, seed=22)
+    big[0, 9000] = big[0, 200000] = 50.0
+    big[1, :] = nan
+    big[1, 131072] = -7.0
+    big[2, :] = nan
+    big[3, 255999] = 60.0
+    got = K().sample(dev(big)).cpu().tolist()
+    assert got == [9000, 131072, 0, 255999, int(big[4].argmax())]
 
 
 def test_sample_temperature_follows_plain_rule_and_probabilities():
