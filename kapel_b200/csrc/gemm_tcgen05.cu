@@ -507,10 +507,15 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
         for (int s = 0; s < SK2_STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
         tc_mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        // The first stages are asked for at once, before the block meets: the copies are on their
-        // way while TMEM is allocated. This thread made the barriers, so it may use them already.
-        // The weights do not depend on the kernel before this one: they are asked for ahead of the wait.
-        for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt) {
+    }
+    __syncthreads();                                        // the barriers stand for every warp
+    // The first stages are asked for at once, while TMEM is allocated, each by another thread (the
+    // first lanes of the producer warp and of the four epilogue warps): a request keeps its thread
+    // for a few hundred clocks. The weights do not depend on the kernel before this one: they are
+    // asked for ahead of the wait.
+    const int asker = lane != 0 ? -1 : (warp == 0 ? 0 : (warp >= 2 ? warp - 1 : -1));
+    if (asker >= 0) {
+        for (int kt = asker; kt < k_tiles && kt < SK2_STAGES; kt += 5) {
             tc_mbar_expect_tx(full + kt, SK2_A_BYTES + B_BYTES);
             tc_tma_load_2d(smem + kt * STAGE, &map_w, (kt0 + kt) * SK2_BK, n0, full + kt);
         }
@@ -521,8 +526,8 @@ gemm_skinny_tcgen05_kernel(const __grid_constant__ CUtensorMap map_w, const __gr
     }
     dependent_wait();                                       // the activations are the kernel before's to finish
     KB_TL_MARK(gemm, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0);
-    if (threadIdx.x == 0) {
-        for (int kt = 0; kt < k_tiles && kt < SK2_STAGES; ++kt)
+    if (asker >= 0) {
+        for (int kt = asker; kt < k_tiles && kt < SK2_STAGES; kt += 5)
             tc_tma_load_2d(smem + kt * STAGE + SK2_A_BYTES, &map_x, (kt0 + kt) * SK2_BK, 0, full + kt);
     }
     tc_fence_before();
@@ -675,16 +680,23 @@ gemm_skinny_glu_kernel(const __grid_constant__ CUtensorMap map_w, const __grid_c
         for (int s = 0; s < STAGES; ++s) { tc_mbar_init(full + s, 1); tc_mbar_init(empty + s, 1); }
         tc_mbar_init(accum, 1);
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
-        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_weights(kt);      // on their way ahead of the wait
     }
+    __syncthreads();                                        // the barriers stand for every warp
+    // The first stages' tiles are asked for by five threads (the first lanes of the producer warp
+    // and of the four epilogue warps), two stages each: a request keeps its thread for a few hundred
+    // clocks, and twenty of them in a row by one thread made the block reach its wait 2 to 3 us
+    // after the kernel before had finished.
+    const int asker = lane != 0 ? -1 : (warp == 0 ? 0 : (warp >= 2 ? warp - 1 : -1));
+    if (asker >= 0)
+        for (int kt = asker; kt < k_tiles && kt < STAGES; kt += 5) load_weights(kt);     // on their way ahead of the wait
     if (warp == 1) {
         asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(tc_saddr(tmem_slot)), "r"(COLS) : "memory");
         asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");
     }
     dependent_wait();
     KB_TL_MARK(gemm, 2, threadIdx.x == 0 && blockIdx.x == 0);
-    if (threadIdx.x == 0)
-        for (int kt = 0; kt < k_tiles && kt < STAGES; ++kt) load_rows(kt);
+    if (asker >= 0)
+        for (int kt = asker; kt < k_tiles && kt < STAGES; kt += 5) load_rows(kt);
     tc_fence_before();
     __syncthreads();
     tc_fence_after();
