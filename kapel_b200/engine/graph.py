@@ -336,7 +336,8 @@ class PromptGraphs:
             return None
         self.passes += 1
         eng = self._engine()
-        rounded = len(plan.entries) == 1 and len(want_rows) <= 1
+        # (a part that keeps a state of its own a request would take the added rows for tokens: no rounding then)
+        rounded = len(plan.entries) == 1 and len(want_rows) <= 1 and not eng.cache.states
         if rounded:
             plan = self.padded(plan, self.round_rows(plan.rows), eng.cache.page_size)
             ids = list(ids) + [0] * (plan.rows - len(ids))
