@@ -85,7 +85,9 @@ class LayerCache:
 class Part:
     # True when `forward` only enqueues kernels whose arguments are device tensors of the batch:
     # such a part can be recorded into a CUDA graph. A part that reads the plan on the host (a
-    # loop over requests, say) leaves it False, and the engine then runs every step eagerly.
+    # loop over requests, say) leaves it False, and the engine then runs every step eagerly. A
+    # recorded step may hold rows that belong to no token (padding up to the recording's size):
+    # their cache line is -1, and a part must write nothing that lasts for them.
     graph_safe = False
 
     @staticmethod
