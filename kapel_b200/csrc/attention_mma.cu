@@ -59,7 +59,7 @@ struct AttMmaParams {
     int window, split, slots;
     int decode_bar_offset;     // bytes from the start of shared memory to the decode kernel's mbarriers
     int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
-    int relative;              // 1: slots are counted from the tile's first visible key (every tile is one token), else from key 0
+    int relative;              // 1: every request brings one token (tile t = row t = request t) and slots are counted from the row's first visible key, else from key 0
     float scale, cap;
 };
 
@@ -265,9 +265,16 @@ struct AmTile {
 __device__ __forceinline__ AmTile am_tile_info(const AttMmaParams& p, int tile, int slot) {
     AmTile x;
     x.group = p.hq / p.hkv;
-    x.entry = p.tile_entry[tile];
-    x.row0 = p.tile_row0[tile];
-    x.nq = p.tile_nq[tile];
+    if (p.relative) {
+        // every request brings one token: tile t is row t of request t, and the three lists need not
+        // be read (one trip to memory fewer before the row's count, its pages and its first keys)
+        x.entry = x.row0 = tile;
+        x.nq = 1;
+    } else {
+        x.entry = p.tile_entry[tile];
+        x.row0 = p.tile_row0[tile];
+        x.nq = p.tile_nq[tile];
+    }
     x.rows_valid = x.nq * x.group;
     x.c_first = p.row_count[x.row0];
     x.klo = (p.window > 0 && x.c_first > p.window) ? x.c_first - p.window : 0;
@@ -1144,6 +1151,7 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     KB_REQUIRE(!(decode && split == 0 && slots != 1), "attention_mma: decode mode without a split has one slot");
     KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_mma: %d slots need scratch memory", slots);
     KB_REQUIRE(relative == 0 || relative == 1, "attention_mma: relative %d (0 or 1: slots counted from each tile's first visible key, for tiles of one token)", relative);
+    KB_REQUIRE(!(decode && relative) || tiles == rows, "attention_mma: relative with %d tiles for %d rows (every request brings one token: tile t is row t of request t)", tiles, rows);
     KB_REQUIRE(hkv <= 65535, "attention_mma: %d kv heads is too many for one launch", hkv);
     if (rows == 0 || tiles == 0) return 0;
     AttMmaParams p;

@@ -266,6 +266,14 @@ def main(argv=None) -> int:
                 parts = K.SplitSum(torch.randn(9, m, (Hq + 2 * Hkv) * D, device=dev))
                 us = _time(lambda i: K.rope_append(parts, cs, lines, tables[0][0], tables[0][1], Hq, Hkv, D, D, out_dtype=bf), args.iters)
                 report(f"rope_append {tag} of partial sums [9x{m}]", us, m * (Hq + 2 * Hkv) * D * (4 * 9 + 2))
+    for name, sampled in (("sample greedy", False), ("sample draw", True)):
+        if want(name):
+            c = min(copies(B * V * 4), 16)
+            logits = [torch.randn(B, V, device=dev) for _ in range(c)]
+            temps = torch.full((B,), 0.8, device=dev) if sampled else None
+            us_ = torch.rand(B, device=dev) if sampled else None
+            us = _time(lambda i: K.sample(logits[i % c], temps, us_), args.iters)
+            report(f"{name} [{B}x{V}]", us, B * V * 4)
     return 0
 
 

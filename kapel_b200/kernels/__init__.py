@@ -600,7 +600,7 @@ def sample(logits: torch.Tensor, temperature: Optional[torch.Tensor] = None, uni
         _need(uniform, "sample uniform", torch.float32, (rows,))
     out = _fresh((rows,), torch.int32, logits.device)
     lib = library()
-    need = int(lib.kb_sample_scratch_floats(rows, vocab)) if temperature is None else 0
+    need = int(lib.kb_sample_scratch_floats(rows, vocab))
     scratch = _fresh((need,), torch.float32, logits.device) if need else None
     _check(lib.kb_sample(_ptr(out), _ptr(logits), _ptr(temperature), _ptr(uniform), rows, vocab, _ptr(scratch), _stream()))
     return out

@@ -448,6 +448,45 @@ def test_sample_temperature_follows_plain_rule_and_probabilities():
     assert got == [2, 0]
 
 
+def test_sample_draws_over_a_large_vocabulary_in_two_steps():
+    """A vocabulary of 65,536 and more is drawn from in two steps (shares of the columns, then one
+    share walked). The plain rule in 64-bit: the first index whose running total exceeds u x total.
+    32-bit sums of 256,000 terms differ from 64-bit ones in the seventh digit, so a draw may fall
+    on a neighbour where the target is that close to a token's edge: the chosen token's own
+    interval, widened by 4e-6 of the total, must hold the target. A peaked row (a few tokens carry
+    everything) must agree exactly but for such edges."""
+    vocab, n = 256000, 96
+    for scale, temp in ((1.0, 0.8), (12.0, 1.3)):
+        row = rnd(1, vocab, seed=31, scale=scale)[0]
+        row[5] = row[77777] = float("nan")
+        row[250000:] = -1e30                              # impossible tokens at the end
+        us = torch.rand(n, generator=torch.Generator().manual_seed(9))
+        us[0], us[1], us[2] = 0.0, 0.99999994, 0.5
+        got = K().sample(dev(row.repeat(n, 1)), dev(torch.full((n,), temp)), dev(us)).cpu().numpy()
+        x = row.double().numpy() / temp
+        ok = ~np.isnan(x)
+        p = np.where(ok, np.exp(x - x[ok].max()), 0.0)
+        c = np.cumsum(p)
+        total = c[-1]
+        want = np.searchsorted(c, us.double().numpy() * total, side="right")
+        exact = 0
+        for g, w, u in zip(got, want, us.double().numpy()):
+            assert 0 <= g < 250000 and p[g] > 0, f"token {g} cannot be drawn"
+            lo, hi = (c[g - 1] if g else 0.0), c[g]
+            assert lo - 4e-6 * total <= u * total <= hi + 4e-6 * total, f"u {u}: token {g} holds [{lo / total}, {hi / total}), the plain rule gives {w}"
+            exact += int(g == w)
+        if scale > 4:
+            assert exact >= n - 3, f"{n - exact} of {n} draws on a peaked row differ from the plain rule"
+    # a row whose target lies beyond every total gets the last possible token; greedy rows beside drawn ones
+    rows = rnd(3, vocab, seed=33)
+    rows[0, 200000:] = float("nan")
+    rows[1, 1000] = rows[1, 130000] = 40.0              # a tie across two shares: the first wins
+    rows[2, :] = -1e30
+    rows[2, 123] = 0.0                                    # all the probability in one token
+    got = K().sample(dev(rows), dev(torch.tensor([1.0, 0.0, 0.7])), dev(torch.tensor([1.0, 0.3, 0.9]))).cpu().tolist()
+    assert got == [199999, 1000, 123]
+
+
 # ------------------------------------------------------------------------------------------
 def run_mma(q, kt, vt, bt, rc, q_lens, page, window, scale, cap, decode, split, relative=False):
     from kapel_b200.engine.batch import cut_tiles
