@@ -61,6 +61,16 @@ struct AttMmaParams {
     int direct;                // 1: a row whose keys all lie in one slot was written to `out` by that slot's block
     int relative;              // 1: every request brings one token (tile t = row t = request t) and slots are counted from the row's first visible key, else from key 0
     float scale, cap;
+    // The decode kernel taking over the rotation and the cache's newest line (null: the queries come in `q`):
+    const float* qkv_parts;    // [qkv_splits][rows][(hq + 2 hkv) d] partial sums of the stacked q|k|v product
+    long long qkv_stride;      // floats from one slice to the next
+    int qkv_splits;
+    int stage_offset;          // bytes from the start of shared memory to where the slices land
+    const float2* cos_sin;     // [rows][d / 2] (cos, sin) of each row's position
+    const int* lines;          // [rows] the cache line of each row's token; negative: none
+    bf16* k_new;               // the key and value tables to write the newest line to; null: the layer reads another layer's cache
+    bf16* v_new;
+    long long table_lines;
 };
 
 __device__ __forceinline__ void am_cp_async16(void* smem, const void* gmem, bool valid) {
@@ -564,7 +574,17 @@ attention_mma_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap m
 constexpr int AD_WK = 16;             // keys a warp tile
 constexpr int AD_STAGES = 3;
 
-template <int HD, int NB, bool FULL>
+// FUSED (one token a request, the whole head rotated): the kernel takes the stacked q|k|v product's
+// partial sums instead of finished queries. Every block brings its kv head's query heads of its row in
+// by bulk copies (one a slice), adds the slices up in order, rotates and leaves them where the queries
+// lie otherwise. The one block of a (row, kv head) whose keys end with the row's own position also
+// brings the key's and the value's slices in (behind the queries, into the same place; the warp that
+// owns the slot's last tile asks and waits, at the end of its walk), writes them to the cache's line
+// for the steps to come, and puts them into its own copy of that tile, which TMA fetched before the
+// line was written. The sums, the rotation and the roundings are rope_append's, bit for bit.
+// (The queries' slices by the threads' own loads, all in flight at once, landed no sooner, 3.3 us
+// after the wait either way, and their registers slowed the walk.)
+template <int HD, int NB, bool FULL, bool FUSED>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap map_k,
                         const __grid_constant__ CUtensorMap map_v KB_TL_PARAM) {
@@ -602,12 +622,16 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     const int k_begin = klo / AD_WK * AD_WK;
     const int n_tiles = (khi - k_begin + AD_WK - 1) / AD_WK;
 
+    uint64_t* qbar = reinterpret_cast<uint64_t*>(am_smem + p.decode_bar_offset) + 4 * AD_STAGES;     // FUSED: the queries' slices have landed
+    uint64_t* kvbar = qbar + 1;                                                                       // FUSED: the key's and the value's
     if (lane == 0) {
 #pragma unroll
         for (int s = 0; s < AD_STAGES; ++s) am_mbar_init(bars + s, 1);
+        if (FUSED && warp == 0) { am_mbar_init(qbar, 1); am_mbar_init(kvbar, 1); }
         asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
     }
     __syncwarp();                                           // a warp's barriers are its own
+    if (FUSED) __syncthreads();                             // but the two of the slices are everyone's
     // A tile is 16 consecutive positions from a multiple of 16: with pages of a multiple of 16
     // positions it lies in one page, where the kv head's rows are consecutive. Lane i < nbox asks
     // TMA for box i of the keys, lane nbox + i for box i of the values. A tile whose page the
@@ -657,18 +681,69 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
     dependent_trigger();
     const int chunks = d / 8;
-    for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
-        const int r = i / chunks, ch = i % chunks;
-        const bool valid = r < rows_valid;
-        const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
-        am_cp_async16(sQ + r * ld + ch * 8, src, valid);
+    float* stg = reinterpret_cast<float*>(am_smem + p.stage_offset);       // FUSED: [slice][query heads of the kv head][d], then [slice][key, value][d]
+    const int heads_all = p.hq + 2 * p.hkv;
+    bool failed = false;
+    float2 cs_q = make_float2(1.f, 0.f);                    // FUSED: this thread's pairs all have component tid mod d/2 (128 is a multiple of d/2)
+    float2 cs_k[HD / 64];                                   // FUSED: the angles of the key's pairs lane, lane + 32, .. for the warp that owns the newest tile
+    if (FUSED) {
+        if (warp == 0) {
+            if (lane == 0) am_mbar_expect_tx(qbar, (uint32_t)(p.qkv_splits * group * d) * 4u);
+            __syncwarp();
+            for (int s = lane; s < p.qkv_splits; s += 32)   // a copy a lane: a request keeps its thread for a while
+                am_bulk_copy(stg + (size_t)s * group * d, p.qkv_parts + (size_t)s * p.qkv_stride + ((size_t)row0 * heads_all + kvh * group) * d,
+                             (uint32_t)(group * d) * 4u, qbar);
+        }
+        cs_q = p.cos_sin[(size_t)row0 * (d >> 1) + tid % (d >> 1)];        // on its way while the slices are
+    } else {
+        for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
+            const int r = i / chunks, ch = i % chunks;
+            const bool valid = r < rows_valid;
+            const bf16* src = p.q + ((size_t)(row0 + (valid ? r / group : 0)) * p.hq + kvh * group + (valid ? r % group : 0)) * d + ch * 8;
+            am_cp_async16(sQ + r * ld + ch * 8, src, valid);
+        }
+        am_commit();
     }
-    am_commit();
 #pragma unroll
     for (int s = 0; s < AD_STAGES; ++s)
         if (!early[s] && warp + 4 * s < n_tiles) load_tile(s, s);
-    am_wait<0>();                                           // this thread's part of Q has landed
+    // FUSED: which tile of this block's holds the row's own position, if any does and the layer writes its cache
+    int t_new = -1, line_new = -1;
+    if (FUSED) {
+        const int half_d = d >> 1;
+        const int newest = x.c_first - 1;
+        if (p.k_new != nullptr && newest >= klo && newest < khi) {
+            line_new = p.lines[row0];
+            if (line_new >= 0 && line_new < p.table_lines) t_new = (newest - k_begin) / AD_WK;
+        }
+        for (int i = tid; i < (16 - group) * chunks; i += AM_THREADS)      // the rows no query head fills
+            *reinterpret_cast<uint4*>(sQ + (group + i / chunks) * ld + (i % chunks) * 8) = make_uint4(0u, 0u, 0u, 0u);
+        if (!am_mbar_wait(qbar, 0u)) failed = true;
+        if (!failed)
+            for (int i = tid; i < group * half_d; i += AM_THREADS) {
+                const int h = i / half_d, c = i % half_d;
+                const float* v = stg + h * d + c;
+                float a = v[0], b = v[half_d];
+                for (int s = 1; s < p.qkv_splits; ++s) { a += v[(size_t)s * group * d]; b += v[(size_t)s * group * d + half_d]; }
+                rope_rotate(a, b, cs_q);
+                sQ[h * ld + c] = __float2bfloat16_rn(a);
+                sQ[h * ld + c + half_d] = __float2bfloat16_rn(b);
+            }
+    } else {
+        am_wait<0>();                                       // this thread's part of Q has landed
+    }
     __syncthreads();                                        // and everyone else's
+    if (FUSED && t_new >= 0 && warp == (t_new & 3)) {       // everyone has read the queries' slices: the key's and the value's may land there
+        if (lane == 0) am_mbar_expect_tx(kvbar, (uint32_t)(2 * p.qkv_splits * d) * 4u);
+        __syncwarp();
+        for (int o = lane; o < 2 * p.qkv_splits; o += 32) {
+            const int s = o >> 1, is_v = o & 1;
+            am_bulk_copy(stg + (size_t)o * d, p.qkv_parts + (size_t)s * p.qkv_stride + ((size_t)row0 * heads_all + p.hq + (is_v ? p.hkv : 0) + kvh) * d,
+                         (uint32_t)d * 4u, kvbar);
+        }
+#pragma unroll
+        for (int j = 0; j < HD / 64; ++j) cs_k[j] = p.cos_sin[(size_t)row0 * (d >> 1) + lane + 32 * j];
+    }
 
     // Q as B fragments: lane (g, t) holds Q[row 8 nb + g][dims 16 ks + 2t, +1 and + 8 + 2t, +1].
     uint32_t bq[HD / 16][NB][2];
@@ -708,13 +783,45 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     const int cnt_lo = __reduce_min_sync(0xffffffffu, cnt_min);
     const float sc = p.cap > 0.f ? p.scale / p.cap : p.scale;
 
-    bool failed = false;
     KB_TL_MARK(attention, 3, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);          // the loop over the keys begins
-    for (int i = 0; warp + 4 * i < n_tiles; ++i) {
+    for (int i = 0; !failed && warp + 4 * i < n_tiles; ++i) {
         const int tile = warp + 4 * i, stage = i % AD_STAGES;
         if (!am_mbar_wait(bars + stage, (uint32_t)(i / AD_STAGES) & 1u)) { failed = true; break; }
         __syncwarp();                                       // zero rows written by other lanes are visible
         const uint32_t tk = my_pipe + (uint32_t)stage * stage_bytes;
+        if (FUSED && tile == t_new) {
+            // The row's own key and value: summed, the key rotated, rounded; to the cache's line, and over
+            // what TMA brought of that line into this tile (element c of key kk: box c / 64, row kk, the
+            // 16-byte piece (c % 64) / 8 exchanged by kk mod 8).
+            if (!am_mbar_wait(kvbar, 0u)) { failed = true; break; }
+            const int half_d = d >> 1, kk = (x.c_first - 1) & (AD_WK - 1);
+            unsigned char* tile_k = pipes_ptr + (size_t)(warp * AD_STAGES + stage) * stage_bytes;
+            unsigned char* tile_v = tile_k + nbox * 2048;
+            auto at = [&](unsigned char* base, int c) -> bf16* {
+                return reinterpret_cast<bf16*>(base + (c >> 6) * 2048 + kk * 128 + ((((c & 63) >> 3) ^ (kk & 7)) << 4)) + (c & 7);
+            };
+            const size_t dst_row = kv_row(line_new, kvh, p.hkv, p.page_size) * d;
+#pragma unroll
+            for (int j = 0; j < HD / 64; ++j) {
+                const int c = lane + 32 * j;
+                float a = stg[c], b = stg[c + half_d];
+                for (int s = 1; s < p.qkv_splits; ++s) { a += stg[(size_t)2 * s * d + c]; b += stg[(size_t)2 * s * d + c + half_d]; }
+                rope_rotate(a, b, cs_k[j]);
+                const bf16 ka = __float2bfloat16_rn(a), kb = __float2bfloat16_rn(b);
+                p.k_new[dst_row + c] = ka;
+                p.k_new[dst_row + c + half_d] = kb;
+                *at(tile_k, c) = ka;
+                *at(tile_k, c + half_d) = kb;
+            }
+            for (int c = lane; c < d; c += 32) {
+                float v = stg[d + c];
+                for (int s = 1; s < p.qkv_splits; ++s) v += stg[(size_t)(2 * s + 1) * d + c];
+                const bf16 vv = __float2bfloat16_rn(v);
+                p.v_new[dst_row + c] = vv;
+                *at(tile_v, c) = vv;
+            }
+            __syncwarp();                                   // the tile is whole before any lane reads it
+        }
         ad_tile<HD, NB, FULL>(bq, tk, tk + nbox * 2048u, d, k_begin + tile * AD_WK, cnt, fst, fst_hi, cnt_lo, klo, khi, sc, p.cap,
                               ot, m_run, l_run, lane);
         __syncwarp();                                       // every lane has read the stage
@@ -727,6 +834,10 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
         // A copy never completed. Give the others in flight the same bounded chance to land (they
         // write into this block's shared memory), raise the flag, and leave without writing.
         for (int s = 0; s < AD_STAGES; ++s) am_mbar_wait(bars + s, 0u), am_mbar_wait(bars + s, 1u);
+        if (FUSED) {
+            am_mbar_wait(qbar, 0u);
+            if (t_new >= 0 && warp == (t_new & 3)) am_mbar_wait(kvbar, 0u);
+        }
         if (lane == 0) atomicExch(&g_attention_error, 1);
     }
     failed = __syncthreads_or(failed);
@@ -1061,34 +1172,57 @@ static int launch_prompt(const AttMmaParams& p, int tiles, cudaStream_t s) {
 // max_rows: the most rows ((token, query head) pairs) any tile holds: up to 8 take one block of
 // eight "heads" in the MMAs' N, up to 16 two. The tensor maps cover the whole key and value tables
 // as [pages * kv heads * page size, head_dim] matrices.
-template <int HD>
-static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStream_t s) {
-    if (p.page_size % AD_WK != 0) return fail("attention_mma: decode mode needs pages of a multiple of %d positions, got %d", AD_WK, p.page_size);
-    const int ld = p.d + AM_PAD;
-    const int nbox = (p.d + 63) / 64;
+// Bytes of shared memory the decode kernel wants: Q, the four warps' pipelines (or the merge of their
+// states over them), the barriers, and for the kernel that takes the q|k|v product's slices the place
+// they land in (`stage_bytes`). `bars` gets the barriers' offset, `stage` the slices'.
+static size_t decode_smem(int d, size_t stage_bytes, size_t* bars_at, size_t* stage_at) {
+    const int ld = d + AM_PAD;
+    const int nbox = (d + 63) / 64;
     const size_t stage = (size_t)2 * nbox * 2048;
     const size_t pipes = (size_t)4 * AD_STAGES * stage;
-    const size_t merge = ((size_t)4 * 16 * (p.d + 4) + 2 * 4 * 16) * sizeof(float);
+    const size_t merge = ((size_t)4 * 16 * (d + 4) + 2 * 4 * 16) * sizeof(float);
     // Q, then up to 1023 bytes to reach the swizzle's period plus whatever the base itself is off by
     size_t bars = (size_t)16 * ld * sizeof(bf16) + 2048 + (pipes > merge ? pipes : merge);
     bars = (bars + 15) / 16 * 16;
-    const size_t smem = bars + 4 * AD_STAGES * sizeof(uint64_t);
-    if (smem > 220 * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
+    size_t at = bars + (4 * AD_STAGES + 2) * sizeof(uint64_t);
+    at = (at + 127) / 128 * 128;
+    if (bars_at) *bars_at = bars;
+    if (stage_at) *stage_at = at;
+    return stage_bytes ? at + stage_bytes : bars + (4 * AD_STAGES + 2) * sizeof(uint64_t);
+}
+static size_t fused_stage_bytes(int hq, int hkv, int d, int splits) {
+    const int group = hq / hkv;
+    return (size_t)splits * (group > 2 ? group : 2) * d * sizeof(float);    // the queries' slices, then the key's and the value's
+}
+
+// max_rows: the most rows ((token, query head) pairs) any tile holds: up to 8 take one block of
+// eight "heads" in the MMAs' N, up to 16 two. The tensor maps cover the whole key and value tables
+// as [pages * kv heads * page size, head_dim] matrices.
+template <int HD>
+static int launch_decode(const AttMmaParams& p, int tiles, int max_rows, cudaStream_t s) {
+    if (p.page_size % AD_WK != 0) return fail("attention_mma: decode mode needs pages of a multiple of %d positions, got %d", AD_WK, p.page_size);
+    const bool fused = p.qkv_parts != nullptr;
+    size_t bars, stage_at;
+    const size_t smem = decode_smem(p.d, fused ? fused_stage_bytes(p.hq, p.hkv, p.d, p.qkv_splits) : 0, &bars, &stage_at);
+    if (smem > (fused ? 227 : 220) * 1024) return fail("attention_mma: head_dim %d needs %zu bytes of shared memory", p.d, smem);
+    if (fused && p.d != HD) return fail("attention_mma: the kernel that takes the q|k|v product's slices is built for head sizes 64, 128 and 256, not %d", p.d);
     AttMmaParams q = p;
     q.decode_bar_offset = (int)bars;
+    q.stage_offset = (int)stage_at;
     const unsigned long long rows = (unsigned long long)p.n_pages * p.hkv * p.page_size;
     CUtensorMap map_k, map_v;
     if (int e = encode_map_bf16(&map_k, p.k_table, rows, p.d, p.d, AD_WK)) return e;
     if (int e = encode_map_bf16(&map_v, p.v_table, rows, p.d, p.d, AD_WK)) return e;
     dim3 grid(tiles, p.hkv, p.slots);
-#define KB_DECODE(NB, FULL)                                                                                                    \
+#define KB_DECODE(NB, FULL, FUSED)                                                                                             \
     do {                                                                                                                       \
         if (smem > 48 * 1024)                                                                                                  \
-            cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
-        launch_dependent_if(p.rows <= DEPENDENT_ROWS, attention_decode_kernel<HD, NB, FULL>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v KB_TL_SLOT(attention, 4, q.slots, q.window));     \
+            cudaFuncSetAttribute(attention_decode_kernel<HD, NB, FULL, FUSED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem); \
+        launch_dependent_if(p.rows <= DEPENDENT_ROWS, attention_decode_kernel<HD, NB, FULL, FUSED>, grid, dim3(AM_THREADS), (size_t)smem, s, q, map_k, map_v KB_TL_SLOT(attention, 4, q.slots, q.window));     \
     } while (0)
-    if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true); else KB_DECODE(1, false); }
-    else               { if (p.d == HD) KB_DECODE(2, true); else KB_DECODE(2, false); }
+    if (fused) { if (max_rows <= 8) KB_DECODE(1, true, true); else KB_DECODE(2, true, true); }
+    else if (max_rows <= 8) { if (p.d == HD) KB_DECODE(1, true, false); else KB_DECODE(1, false, false); }
+    else                    { if (p.d == HD) KB_DECODE(2, true, false); else KB_DECODE(2, false, false); }
 #undef KB_DECODE
     return check_launch("attention_decode");
 }
@@ -1133,6 +1267,32 @@ extern "C" int kb_attention_mma_combine(void* out, const int* row_count, const f
     return check_launch("attention_mma combine");
 }
 
+// The launches of a filled-in AttMmaParams: the kernel of the mode, then the merge of the key slots.
+static int attention_mma_run(const AttMmaParams& p, int tiles, int decode, float* scratch, void* stream) {
+    const int rows = p.rows, hq = p.hq, d = p.d, slots = p.slots;
+    cudaStream_t s = (cudaStream_t)stream;
+    int e;
+    if (d <= 64) e = decode ? launch_decode<64>(p, tiles, decode, s) : launch_prompt<64>(p, tiles, s);
+    else if (d <= 128) e = decode ? launch_decode<128>(p, tiles, decode, s) : launch_prompt<128>(p, tiles, s);
+    else e = decode ? launch_decode<256>(p, tiles, decode, s) : launch_prompt<256>(p, tiles, s);
+    if (e) return e;
+    if (slots > 1) {
+        if ((long long)rows * hq >= 4096) {                 // many pairs: a warp each
+            const unsigned blocks = (unsigned)(((long long)rows * hq + AC_WARPS - 1) / AC_WARPS);
+            if (int e2 = combine_smem(slots)) return e2;
+            launch_dependent_if(false, attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
+        } else if (slots > 8 && combine_bulk_smem(slots, d) <= 40 * 1024 && ((uintptr_t)scratch & 15) == 0) {
+            // few (a decode step): a block each, for the latency; many slots (a small batch): brought in by a
+            // bulk copy (28 slots: 2.9 us against 3.7), a few slots by the threads' loads (4 slots: 2.2 us against 2.9)
+            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_bulk_kernel, dim3(rows, hq), dim3(128), combine_bulk_smem(slots, d), s, p KB_TL_SLOT(attention, 5, p.slots, p.window));
+        } else {                                            // more slots than fit shared memory: the threads load them
+            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p KB_TL_SLOT(attention, 5, p.slots, p.window));
+        }
+        return check_launch("attention_mma combine");
+    }
+    return 0;
+}
+
 extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, const void* v_table,
                                 const int* block_table, const int* row_count, const int* tile_entry,
                                 const int* tile_row0, const int* tile_nq, int tiles, int rows, int hq, int hkv, int d,
@@ -1163,25 +1323,52 @@ extern "C" int kb_attention_mma(void* out, const void* q, const void* k_table, c
     p.decode_bar_offset = 0;
     p.direct = decode ? 0 : 1;
     p.relative = (decode && relative) ? 1 : 0;
-    cudaStream_t s = (cudaStream_t)stream;
-    int e;
-    if (d <= 64) e = decode ? launch_decode<64>(p, tiles, decode, s) : launch_prompt<64>(p, tiles, s);
-    else if (d <= 128) e = decode ? launch_decode<128>(p, tiles, decode, s) : launch_prompt<128>(p, tiles, s);
-    else e = decode ? launch_decode<256>(p, tiles, decode, s) : launch_prompt<256>(p, tiles, s);
-    if (e) return e;
-    if (slots > 1) {
-        if ((long long)rows * hq >= 4096) {                 // many pairs: a warp each
-            const unsigned blocks = (unsigned)(((long long)rows * hq + AC_WARPS - 1) / AC_WARPS);
-            if (int e2 = combine_smem(slots)) return e2;
-            launch_dependent_if(false, attention_mma_combine_warp_kernel, dim3(blocks), dim3(AC_WARPS * 32), (size_t)AC_WARPS * slots * sizeof(float), s, p);
-        } else if (slots > 8 && combine_bulk_smem(slots, d) <= 40 * 1024 && ((uintptr_t)scratch & 15) == 0) {
-            // few (a decode step): a block each, for the latency; many slots (a small batch): brought in by a
-            // bulk copy (28 slots: 2.9 us against 3.7), a few slots by the threads' loads (4 slots: 2.2 us against 2.9)
-            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_bulk_kernel, dim3(rows, hq), dim3(128), combine_bulk_smem(slots, d), s, p KB_TL_SLOT(attention, 5, p.slots, p.window));
-        } else {                                            // more slots than fit shared memory: the threads load them
-            launch_dependent_if(rows <= DEPENDENT_ROWS, attention_mma_combine_kernel, dim3(rows, hq), dim3(128), (size_t)slots * sizeof(float), s, p KB_TL_SLOT(attention, 5, p.slots, p.window));
-        }
-        return check_launch("attention_mma combine");
-    }
-    return 0;
+    p.qkv_parts = nullptr; p.qkv_stride = 0; p.qkv_splits = 0; p.stage_offset = 0; p.cos_sin = nullptr; p.lines = nullptr;
+    p.k_new = p.v_new = nullptr; p.table_lines = 0;
+    return attention_mma_run(p, tiles, decode, scratch, stream);
+}
+
+// Whether kb_attention_decode_fused takes these sizes (else: kb_rope_append, then kb_attention_mma).
+extern "C" int kb_attention_decode_fused_takes(int hq, int hkv, int d, int page_size, int splits) {
+    if (hq <= 0 || hkv <= 0 || hq % hkv != 0 || hq / hkv > 16 || splits < 1) return 0;
+    if (d != 64 && d != 128 && d != 256) return 0;
+    if (page_size <= 0 || page_size % AD_WK != 0) return 0;
+    return decode_smem(d, fused_stage_bytes(hq, hkv, d, splits), nullptr, nullptr) <= 227 * 1024 ? 1 : 0;
+}
+
+// A decode step in which every request brings one token, from the stacked q|k|v product's partial sums
+// (qkv_parts: f32 [splits][rows][(hq + 2 hkv) d], slices qkv_stride floats apart): rotation of the
+// whole head by cos_sin ([rows][d / 2]), the newest key and value to the tables at lines[row] when
+// write_kv is set, and attention over the cache as kb_attention_mma does it in decode mode with
+// `relative` set. Row r is request r (block_table's row r).
+extern "C" int kb_attention_decode_fused(void* out, const float* qkv_parts, int splits, long long qkv_stride, const void* cos_sin,
+                                         const int* lines, void* k_table, void* v_table, int write_kv, long long table_lines,
+                                         const int* block_table, const int* row_count, int rows, int hq, int hkv, int d,
+                                         int page_size, int table_width, int n_pages, int window, int split, int slots,
+                                         float scale, float cap, float* scratch, void* stream) {
+    KB_REQUIRE(rows >= 0 && hq > 0 && hkv > 0 && hq % hkv == 0, "attention_decode_fused: rows %d, heads %d over %d", rows, hq, hkv);
+    KB_REQUIRE(kb_attention_decode_fused_takes(hq, hkv, d, page_size, splits), "attention_decode_fused: heads %d over %d of size %d, pages of %d, %d slices: not taken (head sizes 64, 128, 256; at most 16 query heads a kv head; the slices must fit shared memory)", hq, hkv, d, page_size, splits);
+    KB_REQUIRE(qkv_parts != nullptr && cos_sin != nullptr && lines != nullptr, "attention_decode_fused: a null input");
+    KB_REQUIRE(((uintptr_t)qkv_parts & 15) == 0 && (qkv_stride * 4) % 16 == 0, "attention_decode_fused: the slices must start at multiples of 16 bytes");
+    KB_REQUIRE(table_width > 0 && n_pages > 0, "attention_decode_fused: table width %d, pages %d", table_width, n_pages);
+    KB_REQUIRE(window >= 0 && cap >= 0.f, "attention_decode_fused: window %d, cap %g", window, cap);
+    KB_REQUIRE((split == 0 && slots == 1) || (split > 0 && split % AM_KT == 0 && slots >= 1 && slots <= 8192),
+               "attention_decode_fused: split %d (a multiple of %d) with %d slots (at most 8192)", split, AM_KT, slots);
+    KB_REQUIRE(slots == 1 || scratch != nullptr, "attention_decode_fused: %d slots need scratch memory", slots);
+    KB_REQUIRE(hkv <= 65535, "attention_decode_fused: %d kv heads is too many for one launch", hkv);
+    if (rows == 0) return 0;
+    AttMmaParams p;
+    p.q = nullptr; p.k_table = (const bf16*)k_table; p.v_table = (const bf16*)v_table;
+    p.block_table = block_table; p.row_count = row_count; p.tile_entry = nullptr; p.tile_row0 = nullptr;
+    p.tile_nq = nullptr; p.out = (bf16*)out; p.partial = slots > 1 ? scratch : nullptr;
+    p.rows = rows; p.hq = hq; p.hkv = hkv; p.d = d; p.page_size = page_size; p.table_width = table_width;
+    p.n_pages = n_pages; p.window = window; p.split = split; p.slots = slots; p.scale = scale; p.cap = cap;
+    p.decode_bar_offset = 0;
+    p.direct = 0;
+    p.relative = 1;
+    p.qkv_parts = qkv_parts; p.qkv_stride = qkv_stride; p.qkv_splits = splits; p.stage_offset = 0;
+    p.cos_sin = (const float2*)cos_sin; p.lines = lines;
+    p.k_new = write_kv ? (bf16*)k_table : nullptr; p.v_new = write_kv ? (bf16*)v_table : nullptr;
+    p.table_lines = table_lines;
+    return attention_mma_run(p, rows, hq / hkv, scratch, stream);
 }

@@ -105,6 +105,15 @@ __device__ __forceinline__ size_t kv_row(long long line, int kvh, int hkv, int p
     return (size_t)(page * hkv + kvh) * page_size + off;
 }
 
+// (a, b) turned by the angle whose (cos, sin) is cs; the roundings are spelled out so that every
+// kernel that rotates gives the same bits.
+__device__ __forceinline__ void rope_rotate(float& a, float& b, const float2 cs) {
+    const float ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
+    const float rb = __fmaf_rn(b, cs.x, __fmul_rn(a, cs.y));
+    a = ra;
+    b = rb;
+}
+
 __device__ __forceinline__ float warp_sum(float v) {
 #pragma unroll
     for (int o = 16; o > 0; o >>= 1) v += __shfl_xor_sync(0xffffffffu, v, o);

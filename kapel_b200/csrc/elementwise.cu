@@ -49,15 +49,6 @@ __global__ void rope_table_kernel(float2* __restrict__ cos_sin, const int* __res
 // tables are [pages, Hkv, page_size, D]; a line is page * page_size + offset.
 // Pairing "half": (j, j + rotary/2) for j < rotary/2; components from `rotary` on pass through.
 // A row whose line is negative writes no key and no value (a padding row).
-// (a, b) turned by the angle whose (cos, sin) is cs; the roundings are spelled out so that every
-// kernel that rotates gives the same bits.
-__device__ __forceinline__ void rope_rotate(float& a, float& b, const float2 cs) {
-    const float ra = __fmaf_rn(a, cs.x, -__fmul_rn(b, cs.y));
-    const float rb = __fmaf_rn(b, cs.x, __fmul_rn(a, cs.y));
-    a = ra;
-    b = rb;
-}
-
 template <typename TI, typename T>
 __global__ void rope_append_kernel(const Src<TI> qkv, const float2* __restrict__ cos_sin,
                                    const int* __restrict__ lines, T* __restrict__ q_out, T* __restrict__ k_table,
@@ -155,7 +146,7 @@ __global__ void __launch_bounds__(256) rope_append_bulk_kernel(const float* __re
     // the angle and the cache line come by ordinary loads while the copies are on their way (in the
     // first layer the table of angles is the work of the kernel just before: not ahead of the wait)
     const float2 cs = rotate ? cos_sin[(size_t)r * half_r + i] : make_float2(1.f, 0.f);
-    const int line = h >= hq ? lines[r] : 0;
+    const int line = (h >= hq && write_kv) ? lines[r] : 0;  // a layer that writes no line is given no lines
     bool ok = false;
     {
         const long long start = clock64();

@@ -543,6 +543,66 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
     return "mma"
 
 
+# KAPEL_B200_DECODE_FUSED=0: the rotation and the cache's newest line stay a kernel of their own
+# ahead of the decode attention (the yardstick of the kernel that takes both over). The kernel that
+# takes them over is used from DECODE_FUSED_ROWS requests on: measured at Gemma 2 2B sizes with 6,144
+# tokens of history it gives +1 % at 4 requests, +4 % at 8, +5 to 6 % at 16 and 32, +2 % at 64, and
+# -1 to -2 % at 1 and 2 (its blocks wait 1.6 us longer for nine slices of queries than for finished
+# queries, which few keys a block do not make up for).
+DECODE_FUSED = _os.environ.get("KAPEL_B200_DECODE_FUSED", "1") != "0"
+DECODE_FUSED_ROWS = int(_os.environ.get("KAPEL_B200_DECODE_FUSED_ROWS", "4"))
+
+
+def attention_decode_fused_takes(qkv, hq: int, hkv: int, d: int, rotary: int, page_size: int, dtype: torch.dtype) -> bool:
+    """Whether `paged_attention_decode_fused` takes this stacked product: float32 split sums on the
+    bfloat16 path, the whole head rotated, sizes the kernel is built for."""
+    if not DECODE_FUSED or not isinstance(qkv, SplitSum) or dtype != torch.bfloat16 or rotary != d:
+        return False
+    if qkv.shape[0] < DECODE_FUSED_ROWS:
+        return False
+    return bool(library().kb_attention_decode_fused_takes(int(hq), int(hkv), int(d), int(page_size), qkv.splits))
+
+
+def paged_attention_decode_fused(qkv: "SplitSum", cos_sin, lines, k_table, v_table, block_table, row_count, hq: int, hkv: int,
+                                 d: int, write_kv: bool, page_size: int, window: Optional[int], scale: float,
+                                 softcap: Optional[float], split: int, slots: int) -> torch.Tensor:
+    """A decode step in which every request brings one token (row r is request r), straight from
+    the stacked q|k|v product's partial sums: the attention kernel adds up the slices of its row's
+    query heads, rotates them, and where a block's keys end with the row's own position it does the
+    same for the key and the value, writes them to the cache at `lines[row]` (with `write_kv`) and
+    uses them. The result is `rope_append` followed by `paged_attention_mma(decode, relative)`, bit
+    for bit, one kernel and one wait between kernels fewer."""
+    parts = qkv.partials
+    _need(parts, "attention qkv slices", torch.float32)
+    splits, rows, width = parts.shape
+    if width != (hq + 2 * hkv) * d:
+        raise KernelError(f"attention: qkv slices {tuple(parts.shape)}, expected a width of {(hq + 2 * hkv) * d}")
+    _need(cos_sin, "attention cos_sin", torch.float32, (rows, d // 2, 2))
+    _need(lines, "attention lines", torch.int32, (rows,))
+    _need(k_table, "attention k table", torch.bfloat16)
+    _need(v_table, "attention v table", torch.bfloat16)
+    if k_table.dim() != 4 or k_table.shape[1] != hkv or k_table.shape[2] != page_size or k_table.shape[3] != d or v_table.shape != k_table.shape:
+        raise KernelError(f"attention: tables {tuple(k_table.shape)} are not [pages, {hkv}, {page_size}, {d}]")
+    _need(block_table, "attention block table", torch.int32)
+    if block_table.dim() != 2 or block_table.shape[0] < rows:
+        raise KernelError(f"attention: a block table of {tuple(block_table.shape)} for {rows} requests")
+    _need(row_count, "attention row_count", torch.int32, (rows,))
+    out = _fresh((rows, hq, d), torch.bfloat16, parts.device)
+    lib = library()
+    need = lib.kb_attention_mma_scratch_floats(rows, hq, d, int(slots))
+    scratch = _fresh((need,), torch.float32, parts.device) if need else None
+    n_pages = k_table.shape[0]
+    _check(
+        lib.kb_attention_decode_fused(
+            _ptr(out), _ptr(parts), int(splits), ctypes.c_longlong(rows * width), _ptr(cos_sin), _ptr(lines), _ptr(k_table),
+            _ptr(v_table), int(bool(write_kv)), ctypes.c_longlong(n_pages * page_size), _ptr(block_table), _ptr(row_count), rows,
+            hq, hkv, d, int(page_size), int(block_table.shape[1]), int(n_pages), int(window or 0), int(split), int(slots),
+            _f(scale), _f(softcap or 0.0), _ptr(scratch), _stream(),
+        )
+    )
+    return out
+
+
 def paged_attention_mma(q, k_table, v_table, block_table, row_count, tiles, page_size: int, window: Optional[int],
                         scale: float, softcap: Optional[float], decode: int, split: int, slots: int,
                         relative: bool = False, pairs: Optional[int] = None) -> torch.Tensor:

@@ -49,12 +49,23 @@ class Attention(Part):
         qkv = linear(self.ctx, h, self.w_qkv, keep_split=True)
         k_table, v_table = cache.tables()
         group = batch.groups[cache.group]
+        heads_per_kv = s.num_heads // s.num_kv_heads
+        if K.attention_decode_fused_takes(qkv, s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim,
+                                          self.ctx.page_size, self.ctx.dtype):
+            decode, tiles, split, slots, relative = batch.attention_tiles(
+                heads_per_kv, s.num_kv_heads, s.window, s.head_dim,
+                K.attention_prompt_kernel(s.num_heads, s.num_kv_heads, s.head_dim, self.ctx.page_size, s.softcap))
+            if decode and relative:         # every request brings one token: rotation, the cache's new line and attention in one kernel
+                y = K.paged_attention_decode_fused(
+                    qkv, self.position.tables(batch), group.lines, k_table, v_table, group.block_table, batch.row_count,
+                    s.num_heads, s.num_kv_heads, s.head_dim, cache.owns, self.ctx.page_size, s.window, s.scale, s.softcap,
+                    split, slots)
+                return linear(self.ctx, y.view(y.shape[0], s.num_heads * s.head_dim), self.w_o, keep_split=True)
         q = K.rope_append(
             qkv, self.position.tables(batch), group.lines, k_table, v_table,
             s.num_heads, s.num_kv_heads, s.head_dim, self.position.rotary_dim, write_kv=cache.owns,
             out_dtype=self.ctx.dtype,
         )
-        heads_per_kv = s.num_heads // s.num_kv_heads
         if K.attention_mma_takes(q.dtype, s.head_dim, heads_per_kv):
             decode, tiles, split, slots, relative = batch.attention_tiles(
                 heads_per_kv, s.num_kv_heads, s.window, s.head_dim,

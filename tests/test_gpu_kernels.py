@@ -96,6 +96,11 @@ def test_rope_append_over_split_sums(hq, hkv, d, rotary, rows, splits):
     kd2, vd2 = dev(kt), dev(vt)
     q2 = K().rope_append(whole, cs, dev(lines), kd2, vd2, hq, hkv, d, rotary, out_dtype=torch.bfloat16).cpu().double()
     assert torch.equal(q, q2) and torch.equal(kd.cpu(), kd2.cpu()) and torch.equal(vd.cpu(), vd2.cpu())
+    # a layer that reads another layer's cache: the same queries, no line written (and none given)
+    kd3, vd3 = dev(kt), dev(vt)
+    q3 = K().rope_append(K().SplitSum(dev(parts)), cs, None, kd3, vd3, hq, hkv, d, rotary, write_kv=False, out_dtype=torch.bfloat16).cpu().double()
+    K().check_async_errors()
+    assert torch.equal(q, q3) and (kd3.cpu() == 7.0).all() and (vd3.cpu() == 7.0).all()
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
@@ -586,6 +591,49 @@ def test_paged_attention_decode_slots_counted_from_the_windows_start(hq, hkv, d,
     want = paged_reference(q, kt, vt, bt, re, rc, 16, window, scale, cap)
     assert (got[0] == 0).all()
     assert rel_err(got.numpy(), want.numpy()) < 1.5e-2
+
+
+@pytest.mark.parametrize("hq,hkv,d", [(8, 4, 256), (8, 4, 128), (4, 2, 64), (16, 1, 64), (6, 1, 128), (2, 2, 256)])
+@pytest.mark.parametrize("window,cap", [(None, None), (300, 50.0), (128, 50.0)])
+@pytest.mark.parametrize("split,splits", [(64, 9), (256, 5), (128, 1)])
+def test_decode_attention_from_the_qkv_products_slices(hq, hkv, d, window, cap, split, splits):
+    """The decode kernel that takes the stacked q|k|v product's partial sums (one token a request)
+    gives, bit for bit, what the rotation kernel followed by the decode attention gives: the same
+    output and the same key and value tables (the newest line written, nothing else touched). A
+    padding row (count 0, line -1) writes nothing and gives zeros. A layer that reads another
+    layer's cache writes no line."""
+    from kapel_b200.engine.batch import cut_tiles
+    import kapel_b200.kernels as KK
+
+    lengths = [1, 37, 300, 700, 64, 65, 129, 428]
+    rows, page, group = len(lengths), 16, hq // hkv
+    _, kt, vt, bt, re, rc = make_paged_case("bfloat16", hq, hkv, d, lengths, [1] * rows, seed=hq * 100 + d + 7)
+    rc[0] = 0                                               # a padding row
+    lines = torch.tensor([-1] + [int(bt[r, (n - 1) // page]) * page + (n - 1) % page for r, n in enumerate(lengths)][1:], dtype=torch.int32)
+    parts = rnd(splits, rows * (hq + 2 * hkv) * d, seed=d + splits).reshape(splits, rows, (hq + 2 * hkv) * d)
+    positions = torch.tensor([max(n - 1, 0) for n in lengths], dtype=torch.int32)
+    cs = K().rope_table(dev(positions), d, 10000.0)
+    scale = 1.0 / math.sqrt(d * 1.5)
+    assert K().attention_decode_fused_takes(KK.SplitSum(dev(parts)), hq, hkv, d, d, page, torch.bfloat16)
+    q_len = np.ones(rows, np.int32)
+    tiles = tuple(dev(torch.from_numpy(a)) for a in cut_tiles(np.arange(rows, dtype=np.int32), q_len, 1))
+    longest = min(max(lengths), window) if window else max(lengths)
+    slots = max(1, -(-longest // split))
+    for write_kv in (False, True):
+        kt_a, vt_a, kt_b, vt_b = dev(kt.clone()), dev(vt.clone()), dev(kt.clone()), dev(vt.clone())
+        q = K().rope_append(KK.SplitSum(dev(parts)), cs, dev(lines), kt_a, vt_a, hq, hkv, d, d, write_kv=write_kv, out_dtype=torch.bfloat16)
+        want = K().paged_attention_mma(q, kt_a, vt_a, dev(bt), dev(rc), tiles, page, window, scale, cap, group, split, slots, True)
+        got = K().paged_attention_decode_fused(KK.SplitSum(dev(parts)), cs, dev(lines), kt_b, vt_b, dev(bt), dev(rc), hq, hkv, d,
+                                               write_kv, page, window, scale, cap, split, slots)
+        torch.cuda.synchronize()
+        K().check_async_errors()
+        assert torch.equal(kt_a, kt_b) and torch.equal(vt_a, vt_b), "the cache differs"
+        assert (kt_a.cpu() != kt).any() == write_kv
+        assert (got[0] == 0).all()
+        assert torch.equal(got, want), f"write_kv {write_kv}: {(got != want).sum().item()} values differ"
+    # and against the plain rule, with the newest key in the cache
+    want = paged_reference(q.cpu(), kt_a.cpu(), vt_a.cpu(), bt, re, rc, page, window, scale, cap)
+    assert rel_err(got.cpu().double().numpy(), want.numpy()) < 1.5e-2
 
 
 @pytest.mark.parametrize("decode", [False, True])

@@ -104,3 +104,42 @@ def test_decoding_twice_gives_the_same_bits(case):
 
     first, second = run(), run()
     assert torch.equal(first, second)
+
+
+def test_requests_decoding_together_rotate_and_append_inside_the_attention(case, monkeypatch):
+    """Five requests of different lengths decode twelve tokens together. From four requests on, the
+    decode attention takes the q|k|v product's partial sums itself (rotation, the cache's newest
+    line, attention: one kernel). Its logits are, bit for bit, those of the rotation kernel followed
+    by the attention, and both agree with the plain implementation at every step."""
+    import torch
+
+    import kapel_b200.kernels as KK
+    from helpers import rel_err
+    from kapel_b200.engine import Engine, StepEntry
+
+    name, raw, folder, reqs, plain = case
+    a, b = reqs["a"], reqs["b"]
+    # prefixes of a and b: the plain logits at their places are the whole requests'
+    seqs = {"a": (a, "a"), "b": (b, "b"), "c": (a[:77], "a"), "d": (b[:49], "b"), "e": (a[:34], "a")}
+    steps = 12
+    assert len(seqs) >= KK.DECODE_FUSED_ROWS
+
+    def run(fused):
+        monkeypatch.setattr(KK, "DECODE_FUSED", fused)
+        engine = Engine.from_dir(folder, dtype="bfloat16", max_tokens=1024, max_sequences=8)
+        engine.step([StepEntry(r, s[: len(s) - steps], []) for r, (s, _) in seqs.items()])
+        out = []
+        for i in range(steps):
+            logits = engine.step([StepEntry(r, [s[len(s) - steps + i]], [0]) for r, (s, _) in seqs.items()])
+            out.append(logits.float().cpu().clone())
+        engine.check()
+        return torch.stack(out)                             # [steps, requests, vocab]
+
+    got, ref = run(True), run(False)
+    assert torch.equal(got, ref), f"{(got != ref).sum().item()} logits differ between the two ways"
+    worst = 0.0
+    for i in range(steps):
+        for j, (s, src) in enumerate(seqs.values()):
+            worst = max(worst, rel_err(got[i, j].numpy(), plain["bfloat16"][src][len(s) - steps + i]))
+    print(f"{name}: worst {worst:.2e}")
+    assert worst <= 4e-3
