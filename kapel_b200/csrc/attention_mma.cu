@@ -687,10 +687,13 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
     float2 cs_q = make_float2(1.f, 0.f);                    // FUSED: this thread's pairs all have component tid mod d/2 (128 is a multiple of d/2)
     float2 cs_k[HD / 64];                                   // FUSED: the angles of the key's pairs lane, lane + 32, .. for the warp that owns the newest tile
     if (FUSED) {
-        if (warp == 0) {
-            if (lane == 0) am_mbar_expect_tx(qbar, (uint32_t)(p.qkv_splits * group * d) * 4u);
-            __syncwarp();
-            for (int s = lane; s < p.qkv_splits; s += 32)   // a copy a lane: a request keeps its thread for a while
+        // A copy a thread, and the copies dealt out to the four warps in turn: a request keeps its thread,
+        // and with it its warp, for a while. (The barrier cannot complete before thread 0 has arrived
+        // with the bytes to expect, whichever copy lands first.)
+        if (tid == 0) am_mbar_expect_tx(qbar, (uint32_t)(p.qkv_splits * group * d) * 4u);
+        {
+            const int s = lane * 4 + warp;
+            if (s < p.qkv_splits)
                 am_bulk_copy(stg + (size_t)s * group * d, p.qkv_parts + (size_t)s * p.qkv_stride + ((size_t)row0 * heads_all + kvh * group) * d,
                              (uint32_t)(group * d) * 4u, qbar);
         }
@@ -720,29 +723,41 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
             *reinterpret_cast<uint4*>(sQ + (group + i / chunks) * ld + (i % chunks) * 8) = make_uint4(0u, 0u, 0u, 0u);
         if (!am_mbar_wait(qbar, 0u)) failed = true;
         if (!failed)
-            for (int i = tid; i < group * half_d; i += AM_THREADS) {
-                const int h = i / half_d, c = i % half_d;
-                const float* v = stg + h * d + c;
-                float a = v[0], b = v[half_d];
-                for (int s = 1; s < p.qkv_splits; ++s) { a += v[(size_t)s * group * d]; b += v[(size_t)s * group * d + half_d]; }
-                rope_rotate(a, b, cs_q);
-                sQ[h * ld + c] = __float2bfloat16_rn(a);
-                sQ[h * ld + c + half_d] = __float2bfloat16_rn(b);
+            for (int i = tid; i < group * half_d; i += 2 * AM_THREADS) {    // two pairs at a time: four sums side by side
+                const int c = i % half_d, h0 = i / half_d;
+                const bool two = i + AM_THREADS < group * half_d;
+                const int h1 = two ? (i + AM_THREADS) / half_d : h0;
+                const float* v0 = stg + h0 * d + c;
+                const float* v1 = stg + h1 * d + c;
+                float a0 = v0[0], b0 = v0[half_d], a1 = v1[0], b1 = v1[half_d];
+                for (int s = 1; s < p.qkv_splits; ++s) {
+                    const size_t o = (size_t)s * group * d;
+                    a0 += v0[o]; b0 += v0[o + half_d]; a1 += v1[o]; b1 += v1[o + half_d];
+                }
+                rope_rotate(a0, b0, cs_q);
+                sQ[h0 * ld + c] = __float2bfloat16_rn(a0);
+                sQ[h0 * ld + c + half_d] = __float2bfloat16_rn(b0);
+                if (two) {
+                    rope_rotate(a1, b1, cs_q);
+                    sQ[h1 * ld + c] = __float2bfloat16_rn(a1);
+                    sQ[h1 * ld + c + half_d] = __float2bfloat16_rn(b1);
+                }
             }
     } else {
         am_wait<0>();                                       // this thread's part of Q has landed
     }
     __syncthreads();                                        // and everyone else's
-    if (FUSED && t_new >= 0 && warp == (t_new & 3)) {       // everyone has read the queries' slices: the key's and the value's may land there
-        if (lane == 0) am_mbar_expect_tx(kvbar, (uint32_t)(2 * p.qkv_splits * d) * 4u);
-        __syncwarp();
-        for (int o = lane; o < 2 * p.qkv_splits; o += 32) {
+    if (FUSED && t_new >= 0) {                              // everyone has read the queries' slices: the key's and the value's may land there
+        if (tid == 0) am_mbar_expect_tx(kvbar, (uint32_t)(2 * p.qkv_splits * d) * 4u);
+        for (int o = lane * 4 + warp; o < 2 * p.qkv_splits; o += 128) {      // dealt out to the four warps as above
             const int s = o >> 1, is_v = o & 1;
             am_bulk_copy(stg + (size_t)o * d, p.qkv_parts + (size_t)s * p.qkv_stride + ((size_t)row0 * heads_all + p.hq + (is_v ? p.hkv : 0) + kvh) * d,
                          (uint32_t)d * 4u, kvbar);
         }
+        if (warp == (t_new & 3)) {                          // the warp that owns the newest tile will rotate the key
 #pragma unroll
-        for (int j = 0; j < HD / 64; ++j) cs_k[j] = p.cos_sin[(size_t)row0 * (d >> 1) + lane + 32 * j];
+            for (int j = 0; j < HD / 64; ++j) cs_k[j] = p.cos_sin[(size_t)row0 * (d >> 1) + lane + 32 * j];
+        }
     }
 
     // Q as B fragments: lane (g, t) holds Q[row 8 nb + g][dims 16 ks + 2t, +1 and + 8 + 2t, +1].
@@ -801,24 +816,36 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
                 return reinterpret_cast<bf16*>(base + (c >> 6) * 2048 + kk * 128 + ((((c & 63) >> 3) ^ (kk & 7)) << 4)) + (c & 7);
             };
             const size_t dst_row = kv_row(line_new, kvh, p.hkv, p.page_size) * d;
+            // One walk over the slices with every sum of this lane side by side (a walk a sum, each add
+            // waiting for its load, took 2 to 2.8 us here, at the end of the block's longest warp).
+            float ka[HD / 64], kb[HD / 64], vv[HD / 32];
+#pragma unroll
+            for (int j = 0; j < HD / 64; ++j) { ka[j] = stg[lane + 32 * j]; kb[j] = stg[lane + 32 * j + half_d]; }
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) vv[j] = stg[d + lane + 32 * j];
+            for (int s = 1; s < p.qkv_splits; ++s) {
+                const float* ks = stg + (size_t)2 * s * d + lane;
+#pragma unroll
+                for (int j = 0; j < HD / 64; ++j) { ka[j] += ks[32 * j]; kb[j] += ks[32 * j + half_d]; }
+#pragma unroll
+                for (int j = 0; j < HD / 32; ++j) vv[j] += ks[d + 32 * j];
+            }
 #pragma unroll
             for (int j = 0; j < HD / 64; ++j) {
                 const int c = lane + 32 * j;
-                float a = stg[c], b = stg[c + half_d];
-                for (int s = 1; s < p.qkv_splits; ++s) { a += stg[(size_t)2 * s * d + c]; b += stg[(size_t)2 * s * d + c + half_d]; }
-                rope_rotate(a, b, cs_k[j]);
-                const bf16 ka = __float2bfloat16_rn(a), kb = __float2bfloat16_rn(b);
-                p.k_new[dst_row + c] = ka;
-                p.k_new[dst_row + c + half_d] = kb;
-                *at(tile_k, c) = ka;
-                *at(tile_k, c + half_d) = kb;
+                rope_rotate(ka[j], kb[j], cs_k[j]);
+                const bf16 xa = __float2bfloat16_rn(ka[j]), xb = __float2bfloat16_rn(kb[j]);
+                p.k_new[dst_row + c] = xa;
+                p.k_new[dst_row + c + half_d] = xb;
+                *at(tile_k, c) = xa;
+                *at(tile_k, c + half_d) = xb;
             }
-            for (int c = lane; c < d; c += 32) {
-                float v = stg[d + c];
-                for (int s = 1; s < p.qkv_splits; ++s) v += stg[(size_t)(2 * s + 1) * d + c];
-                const bf16 vv = __float2bfloat16_rn(v);
-                p.v_new[dst_row + c] = vv;
-                *at(tile_v, c) = vv;
+#pragma unroll
+            for (int j = 0; j < HD / 32; ++j) {
+                const int c = lane + 32 * j;
+                const bf16 xv = __float2bfloat16_rn(vv[j]);
+                p.v_new[dst_row + c] = xv;
+                *at(tile_v, c) = xv;
             }
             __syncwarp();                                   // the tile is whole before any lane reads it
         }

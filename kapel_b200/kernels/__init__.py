@@ -544,13 +544,12 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
 
 
 # KAPEL_B200_DECODE_FUSED=0: the rotation and the cache's newest line stay a kernel of their own
-# ahead of the decode attention (the yardstick of the kernel that takes both over). The kernel that
-# takes them over is used from DECODE_FUSED_ROWS requests on: measured at Gemma 2 2B sizes with 6,144
-# tokens of history it gives +1 % at 4 requests, +4 % at 8, +5 to 6 % at 16 and 32, +2 % at 64, and
-# -1 to -2 % at 1 and 2 (its blocks wait 1.6 us longer for nine slices of queries than for finished
-# queries, which few keys a block do not make up for).
+# ahead of the decode attention (the yardstick of the kernel that takes both over). Measured at
+# Gemma 2 2B sizes with 6,144 tokens of history, both ways in one call: +1.3 % at one request, +1.5 % at
+# 2, +3.4 to 4.6 % at 8, +5 to 6 % at 16 and 32, +2 % at 64. DECODE_FUSED_ROWS is the number of
+# requests from which it is used.
 DECODE_FUSED = _os.environ.get("KAPEL_B200_DECODE_FUSED", "1") != "0"
-DECODE_FUSED_ROWS = int(_os.environ.get("KAPEL_B200_DECODE_FUSED_ROWS", "4"))
+DECODE_FUSED_ROWS = int(_os.environ.get("KAPEL_B200_DECODE_FUSED_ROWS", "1"))
 
 
 def attention_decode_fused_takes(qkv, hq: int, hkv: int, d: int, rotary: int, page_size: int, dtype: torch.dtype) -> bool:

@@ -107,9 +107,9 @@ def test_decoding_twice_gives_the_same_bits(case):
 
 
 def test_requests_decoding_together_rotate_and_append_inside_the_attention(case, monkeypatch):
-    """Five requests of different lengths decode twelve tokens together. From four requests on, the
-    decode attention takes the q|k|v product's partial sums itself (rotation, the cache's newest
-    line, attention: one kernel). Its logits are, bit for bit, those of the rotation kernel followed
+    """Five requests of different lengths decode twelve tokens together. When every request brings
+    one token, the decode attention takes the q|k|v product's partial sums itself (rotation, the
+    cache's newest line, attention: one kernel). Its logits are, bit for bit, those of the rotation kernel followed
     by the attention, and both agree with the plain implementation at every step."""
     import torch
 
