@@ -206,8 +206,39 @@ def main(argv=None) -> int:
                                                    Hq // Hkv, split, slots, True), args.iters)
         report(f"{name} split={split}x{slots}", us, B * seen * Hkv * D * 2 * 2)
 
+    def decode_fused_case(window):
+        """The same step from the q|k|v product's partial sums: the attention kernel adds up the slices,
+        rotates and writes the cache's newest line itself. Beside it, the rotation kernel followed by
+        the attention kernel over the same input."""
+        name = f"attention decode from q|k|v slices window={window}"
+        if not want(name):
+            return
+        splits = 9
+        parts = K.SplitSum(torch.randn(splits, B, (Hq + 2 * Hkv) * D, device=dev) * 0.3)
+        if not K.attention_decode_fused_takes(parts, Hq, Hkv, D, D, page, bf):
+            return
+        rc = torch.full((B,), ctx + 1, dtype=torch.int32, device=dev)
+        cs = K.rope_table(torch.full((B,), ctx, dtype=torch.int32, device=dev), D, 10000.0)
+        lines = (bt[:, ctx // page].to(torch.int64) * page + ctx % page).to(torch.int32)
+        split, slots = decode_split(B * Hkv, ctx + 1, sm_count(dev), window, True)
+        seen = min(ctx + 1, window) if window else ctx + 1
+        tiles = tuple(torch.from_numpy(a).to(dev) for a in cut_tiles(np.arange(B, dtype=np.int32), np.ones(B, np.int32), 1))
+        us = _time(lambda i: K.paged_attention_decode_fused(parts, cs, lines, tables[i % 2][0], tables[i % 2][1], bt, rc, Hq, Hkv, D,
+                                                            True, page, window, scale, cap, split, slots), args.iters)
+        nbytes = B * seen * Hkv * D * 2 * 2 + splits * B * (Hq + 2 * Hkv) * D * 4
+        report(f"{name} split={split}x{slots}", us, nbytes)
+
+        def two(i):
+            q = K.rope_append(parts, cs, lines, tables[i % 2][0], tables[i % 2][1], Hq, Hkv, D, D, out_dtype=bf)
+            return K.paged_attention_mma(q, tables[i % 2][0], tables[i % 2][1], bt, rc, tiles, page, window, scale, cap,
+                                         Hq // Hkv, split, slots, True)
+
+        report(f"rotation, then attention decode window={window} split={split}x{slots}", _time(two, args.iters), nbytes)
+
     decode_case(None)
     decode_case(args.window)
+    decode_fused_case(None)
+    decode_fused_case(args.window)
 
     def prompt_case(window):
         name = f"attention prompt window={window}"
