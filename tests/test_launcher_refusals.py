@@ -79,3 +79,28 @@ def test_tcgen05_attention_says_what_it_takes(lib):
     assert lib.kb_attention_tc_rows(256, 1) == 256 and lib.kb_attention_tc_rows(128, 1) == 256
     assert lib.kb_attention_tc_rows(64, 1) == 128 and lib.kb_attention_tc_rows(256, 0) == 128
     assert lib.kb_attention_tc_rows(256, 2) == 256 and lib.kb_attention_tc_rows(128, 2) == 128
+
+
+def test_decode_attention_from_slices_says_what_it_takes(lib):
+    takes = lib.kb_attention_decode_fused_takes
+    takes.argtypes = [i32, i32, i32, i32, i32]
+    assert takes(8, 4, 256, 16, 9) == 1 and takes(32, 16, 128, 16, 5) == 1 and takes(16, 1, 64, 16, 30) == 1
+    assert takes(8, 4, 96, 16, 9) == 0                       # head sizes 64, 128 and 256 only
+    assert takes(34, 2, 128, 16, 4) == 0                     # at most 16 query heads a kv head
+    assert takes(8, 3, 128, 16, 4) == 0                      # heads must divide into kv heads
+    assert takes(8, 4, 256, 24, 9) == 0                      # pages of a multiple of 16 positions
+    assert takes(8, 4, 256, 16, 12) == 1 and takes(8, 4, 256, 16, 13) == 0     # thirteen slices of two heads of 256 do not fit beside the pipelines
+    assert takes(8, 4, 256, 16, 0) == 0
+    fused = lib.kb_attention_decode_fused
+    fused.argtypes = [vp, vp, i32, i64, vp, vp, vp, vp, i32, i64, vp, vp] + [i32] * 10 + [f32, f32, vp, vp]
+
+    def call(parts=A, splits=9, stride=8 * 4096, d=256, split=1024, slots=4, scratch=A, hq=8, hkv=4):
+        return fused(A, parts, splits, stride, A, A, A, A, 1, 1 << 20, A, A, 8, hq, hkv, d, 16, 64, 4096, 0, split, slots,
+                     0.1, 50.0, scratch, None)
+
+    refused(lib, call(d=96), "attention_decode_fused", "not taken")
+    refused(lib, call(parts=A + 4), "multiples of 16 bytes")
+    refused(lib, call(stride=8 * 4096 + 1), "multiples of 16 bytes")
+    refused(lib, call(split=100), "split 100")
+    refused(lib, call(scratch=None), "4 slots need scratch memory")
+    refused(lib, call(hq=9), "heads 9 over 4")
