@@ -668,28 +668,23 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
             if (lane == 0) am_mbar_expect_tx(bars + stage, 0u);         // nothing to wait for: the phase completes
         }
     };
-    fetch_pages(0);
-    // The kernel before this one wrote the newest key of every row and nothing older: a first tile
-    // that ends below the first row's last position is asked for ahead of the wait.
-    bool early[AD_STAGES];
-#pragma unroll
-    for (int s = 0; s < AD_STAGES; ++s) {
-        early[s] = warp + 4 * s < n_tiles && k_begin + (warp + 4 * s) * AD_WK + AD_WK < x.c_first;
-        if (early[s]) load_tile(s, s);
-    }
-    dependent_wait();
-    KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
-    dependent_trigger();
     const int chunks = d / 8;
     float* stg = reinterpret_cast<float*>(am_smem + p.stage_offset);       // FUSED: [slice][query heads of the kv head][d], then [slice][key, value][d]
     const int heads_all = p.hq + 2 * p.hkv;
     bool failed = false;
     float2 cs_q = make_float2(1.f, 0.f);                    // FUSED: this thread's pairs all have component tid mod d/2 (128 is a multiple of d/2)
     float2 cs_k[HD / 64];                                   // FUSED: the angles of the key's pairs lane, lane + 32, .. for the warp that owns the newest tile
+    bool early[AD_STAGES];
     if (FUSED) {
-        // A copy a thread, and the copies dealt out to the four warps in turn: a request keeps its thread,
-        // and with it its warp, for a while. (The barrier cannot complete before thread 0 has arrived
-        // with the bytes to expect, whichever copy lands first.)
+        // This kernel's blocks fill a multiprocessor's shared memory: they start when the product's
+        // blocks have left, so the wait is short, and it comes first. The queries' slices are then asked
+        // for ahead of the 192 KB of keys and values, not behind them (behind them they landed 3.3 us
+        // after the wait). A copy a thread, the copies dealt out to the four warps in turn: a request
+        // keeps its thread, and with it its warp, for a while. (The barrier cannot complete before
+        // thread 0 has arrived with the bytes to expect, whichever copy lands first.)
+        dependent_wait();
+        KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+        dependent_trigger();
         if (tid == 0) am_mbar_expect_tx(qbar, (uint32_t)(p.qkv_splits * group * d) * 4u);
         {
             const int s = lane * 4 + warp;
@@ -698,7 +693,24 @@ attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMa
                              (uint32_t)(group * d) * 4u, qbar);
         }
         cs_q = p.cos_sin[(size_t)row0 * (d >> 1) + tid % (d >> 1)];        // on its way while the slices are
+        fetch_pages(0);
+#pragma unroll
+        for (int s = 0; s < AD_STAGES; ++s) {
+            early[s] = warp + 4 * s < n_tiles;
+            if (early[s]) load_tile(s, s);
+        }
     } else {
+        fetch_pages(0);
+        // The kernel before this one wrote the newest key of every row and nothing older: a first tile
+        // that ends below the first row's last position is asked for ahead of the wait.
+#pragma unroll
+        for (int s = 0; s < AD_STAGES; ++s) {
+            early[s] = warp + 4 * s < n_tiles && k_begin + (warp + 4 * s) * AD_WK + AD_WK < x.c_first;
+            if (early[s]) load_tile(s, s);
+        }
+        dependent_wait();
+        KB_TL_MARK(attention, 2, threadIdx.x == 0 && blockIdx.x == 0 && blockIdx.y == 0 && blockIdx.z == 0);
+        dependent_trigger();
         for (int i = tid; i < 16 * chunks; i += AM_THREADS) {
             const int r = i / chunks, ch = i % chunks;
             const bool valid = r < rows_valid;
