@@ -582,8 +582,8 @@ constexpr int AD_STAGES = 3;
 // owns the slot's last tile asks and waits, at the end of its walk), writes them to the cache's line
 // for the steps to come, and puts them into its own copy of that tile, which TMA fetched before the
 // line was written. The sums, the rotation and the roundings are rope_append's, bit for bit.
-// (The queries' slices by the threads' own loads, all in flight at once, landed no sooner, 3.3 us
-// after the wait either way, and their registers slowed the walk.)
+// (Asked for behind the block's first 192 KB of keys and values, the queries' slices landed 3.3 us
+// after the wait, by bulk copies and by the threads' own loads alike; hence the wait first.)
 template <int HD, int NB, bool FULL, bool FUSED>
 __global__ void __launch_bounds__(AM_THREADS)
 attention_decode_kernel(const AttMmaParams p, const __grid_constant__ CUtensorMap map_k,
